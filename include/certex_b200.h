@@ -1,0 +1,279 @@
+/*
+ * C ABI of libcertex_b200: a B200 (sm_100a) exact k-nearest-neighbour engine that drops in behind the C API of
+ * hpdic/libcertex. Every `cuvsCertex*` entry point below has the name, argument list and error behaviour of the
+ * reference's c/include/cuvs/neighbors/certex.h (file:line given per function), so a program written against that
+ * header links against this library unchanged.
+ *
+ * The reference header pulls its basic types from cuVS (<cuvs/core/c_api.h>, <cuvs/distance/distance.h>,
+ * <cuvs/neighbors/common.h>) and DLPack (<dlpack/dlpack.h>). cuVS is not a dependency of this library, so the few
+ * cuVS C types and functions the certex API needs are declared here with the same names, values and meaning; the
+ * DLPack structures are declared here too (public DLPack v1.0 ABI) unless <dlpack/dlpack.h> was included first.
+ *
+ * Conventions (as in the reference, c/src/core/interop.hpp:86-131, c/src/core/exceptions.hpp:17-33):
+ *  - every function returns CUVS_SUCCESS or CUVS_ERROR; after an error cuvsGetLastErrorText() gives the message of
+ *    the calling thread; no C++ exception crosses this boundary;
+ *  - tensors are borrowed for the duration of the call (the deleter is never invoked), must be dense row-major
+ *    (strides NULL or matching), lanes == 1, and byte_offset is honoured; outputs are allocated by the caller;
+ *  - all device work runs on the stream of the cuvsResources_t handle; searches return after their last kernel is
+ *    enqueued (cuvsStreamSync to wait).
+ */
+#ifndef CERTEX_B200_H_
+#define CERTEX_B200_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CERTEX_B200_EXPORT __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------------------------------ DLPack v1.0 ABI */
+#ifndef DLPACK_DLPACK_H_
+#define DLPACK_DLPACK_H_
+typedef enum {
+  kDLCPU         = 1,
+  kDLCUDA        = 2,
+  kDLCUDAHost    = 3,
+  kDLCUDAManaged = 13
+} DLDeviceType;
+
+typedef struct {
+  DLDeviceType device_type;
+  int32_t device_id;
+} DLDevice;
+
+typedef enum {
+  kDLInt    = 0U,
+  kDLUInt   = 1U,
+  kDLFloat  = 2U,
+  kDLBfloat = 4U
+} DLDataTypeCode;
+
+typedef struct {
+  uint8_t code;
+  uint8_t bits;
+  uint16_t lanes;
+} DLDataType;
+
+typedef struct {
+  void* data;
+  DLDevice device;
+  int32_t ndim;
+  DLDataType dtype;
+  int64_t* shape;
+  int64_t* strides;
+  uint64_t byte_offset;
+} DLTensor;
+
+typedef struct DLManagedTensor {
+  DLTensor dl_tensor;
+  void* manager_ctx;
+  void (*deleter)(struct DLManagedTensor* self);
+} DLManagedTensor;
+#endif /* DLPACK_DLPACK_H_ */
+
+/* ------------------------------------------------------------------------------------- cuVS C types used by certex */
+/** <cuvs/core/c_api.h>: status of every call. */
+typedef enum { CUVS_ERROR = 0, CUVS_SUCCESS = 1 } cuvsError_t;
+
+/** <cuvs/core/c_api.h>: opaque handle holding the device and the stream of a caller. */
+typedef uintptr_t cuvsResources_t;
+
+/** <cuvs/distance/distance.h>: the three metrics certex accepts keep their cuVS values. */
+typedef enum { L2Expanded = 0, CosineExpanded = 2, InnerProduct = 6 } cuvsDistanceType;
+
+/** <cuvs/neighbors/common.h>: filter kinds; `addr` of a BITSET / BITMAP filter is a DLManagedTensor* of uint32
+ *  device words (bit j of word i is entry 32 i + j; a set bit keeps the vector). */
+enum cuvsFilterType { NO_FILTER = 0, BITSET = 1, BITMAP = 2 };
+typedef struct {
+  uintptr_t addr;
+  enum cuvsFilterType type;
+} cuvsFilter;
+
+CERTEX_B200_EXPORT cuvsError_t cuvsResourcesCreate(cuvsResources_t* res);
+CERTEX_B200_EXPORT cuvsError_t cuvsResourcesDestroy(cuvsResources_t res);
+/** Stream type is cudaStream_t, passed as void* so that this header needs no CUDA include. */
+CERTEX_B200_EXPORT cuvsError_t cuvsStreamSet(cuvsResources_t res, void* stream);
+CERTEX_B200_EXPORT cuvsError_t cuvsStreamGet(cuvsResources_t res, void** stream);
+CERTEX_B200_EXPORT cuvsError_t cuvsStreamSync(cuvsResources_t res);
+CERTEX_B200_EXPORT const char* cuvsGetLastErrorText(void);
+CERTEX_B200_EXPORT void cuvsSetLastErrorText(const char* text);
+
+/* --------------------------------------------------------------------------------------------- parameters */
+/** certex.h:30-49. Every setting returns the same exact neighbours. `width`, `variance`, `pca_sample`, `n_lists`,
+ *  `local_projections` and `int8_rows` tune the reference's projected screening rows; this engine has no projection
+ *  (8-bit vectors are screened by their exact integer Gram product) and accepts them without effect.
+ *  `host_vectors` is accepted; vectors are kept in device memory. */
+struct cuvsCertexIndexParams {
+  cuvsDistanceType metric;
+  int32_t width;
+  double variance;
+  int32_t anchor_stride;
+  int64_t pca_sample;
+  bool host_vectors;
+  int32_t n_lists;
+  bool local_projections;
+  bool int8_rows;
+};
+typedef struct cuvsCertexIndexParams* cuvsCertexIndexParams_t;
+
+/** certex.h:54 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexParamsCreate(cuvsCertexIndexParams_t* params);
+/** certex.h:57 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexParamsDestroy(cuvsCertexIndexParams_t params);
+
+/** certex.h:69-76. `batch_size` queries share one pass over the stored rows. `anchors` and `probe_lists` belong to
+ *  stages this engine does not have and are accepted without effect. */
+struct cuvsCertexSearchParams {
+  int32_t anchors;
+  int32_t batch_size;
+  int32_t probe_lists;
+};
+typedef struct cuvsCertexSearchParams* cuvsCertexSearchParams_t;
+
+/** certex.h:81 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSearchParamsCreate(cuvsCertexSearchParams_t* params);
+/** certex.h:84 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSearchParamsDestroy(cuvsCertexSearchParams_t params);
+
+/* --------------------------------------------------------------------------------------------- index */
+/** certex.h:96-101: an opaque index of float32, float16, int8 or uint8 vectors. */
+typedef struct {
+  uintptr_t addr;
+  DLDataType dtype;
+} cuvsCertexIndex;
+typedef cuvsCertexIndex* cuvsCertexIndex_t;
+
+/** certex.h:104 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexCreate(cuvsCertexIndex_t* index);
+/** certex.h:107 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexDestroy(cuvsCertexIndex_t index);
+/** certex.h:110: vectors added so far, removed ones included. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexGetSize(cuvsCertexIndex_t index, int64_t* size);
+/** certex.h:113 */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexIndexGetDim(cuvsCertexIndex_t index, int64_t* dim);
+
+/** certex.h:139-142: build from a dataset [n_rows, dim] in device (kDLCUDA, kDLCUDAManaged) or host (kDLCPU,
+ *  kDLCUDAHost) memory; the handle must be empty. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexBuild(cuvsResources_t res, cuvsCertexIndexParams_t params,
+                                               DLManagedTensor* dataset, cuvsCertexIndex_t index);
+/** certex.h:146-148: append vectors [n, dim]; they receive the next consecutive ids. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexExtend(cuvsResources_t res, DLManagedTensor* new_vectors,
+                                                cuvsCertexIndex_t index);
+/** certex.h:151-153: remove by id (int64 device vector); ids are never reused. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexRemove(cuvsResources_t res, DLManagedTensor* ids, cuvsCertexIndex_t index);
+/** certex.h:157-160: labels (int32 device vector) of the vectors first, first + 1, ... */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSetLabels(cuvsResources_t res, DLManagedTensor* labels, int64_t first,
+                                                   cuvsCertexIndex_t index);
+/** certex.h:164: in the reference a speed-only re-ordering of the screening rows by label; results are the same
+ *  with or without it, and here it only records that the call was made. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexPartitionByLabels(cuvsResources_t res, cuvsCertexIndex_t index);
+
+/** certex.h:184-190: exact k nearest neighbours, k = neighbors.shape[1]. queries [nq, dim] (device, index dtype),
+ *  neighbors int64 [nq, k], distances float32 [nq, k] (device): squared Euclidean distances ascending, inner products
+ *  descending, cosine distances (1 - cos) ascending. Entries beyond the admitted vectors: id -1, distance +inf
+ *  (-inf for inner products). Ties between equal exact scores resolve to the smaller id. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSearch(cuvsResources_t res, cuvsCertexSearchParams_t params,
+                                                cuvsCertexIndex_t index, DLManagedTensor* queries,
+                                                DLManagedTensor* neighbors, DLManagedTensor* distances,
+                                                cuvsFilter filter);
+/** certex.h:196-202: neighbours among the vectors whose label equals the query's (int32 device vector [nq]). */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSearchWithLabels(cuvsResources_t res, cuvsCertexSearchParams_t params,
+                                                          cuvsCertexIndex_t index, DLManagedTensor* queries,
+                                                          DLManagedTensor* query_labels, DLManagedTensor* neighbors,
+                                                          DLManagedTensor* distances);
+/** certex.h:214-216: save the index with its vectors. The file starts with the reference's 4-byte NumPy dtype
+ *  prefix; the rest is this library's own layout (not interchangeable with files of the reference). */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexSerialize(cuvsResources_t res, const char* filename, cuvsCertexIndex_t index);
+/** certex.h:220-222: load into an empty handle; the vector type comes from the file. */
+CERTEX_B200_EXPORT cuvsError_t cuvsCertexDeserialize(cuvsResources_t res, const char* filename,
+                                                     cuvsCertexIndex_t index);
+
+/* --------------------------------------------------------------------------- additions without a certex.h counterpart */
+/**
+ * Search that also returns the exact fp64 scores the ranking used and shifts ids by `id_base`. The reference returns
+ * float32 distances only (`finish`, cpp/src/neighbors/certex/certex.cu:224-250); its internal `best_score` array is
+ * what `scores` exposes: squared distance (L2), |q|^2 - 2<q,x> (inner product), 2 - 2cos (cosine), +inf where the id
+ * is -1. `scores` (float64 [nq, k], device) may be NULL. `query_labels` may be NULL. `id_base` is the global id of the
+ * index's first vector when the index is one row shard of a larger set
+ * (first_id of cpp/src/neighbors/certex/certex_shards.cu:70-75).
+ */
+CERTEX_B200_EXPORT cuvsError_t certexB200SearchEx(cuvsResources_t res, cuvsCertexSearchParams_t params,
+                                                  cuvsCertexIndex_t index, DLManagedTensor* queries,
+                                                  DLManagedTensor* query_labels, DLManagedTensor* neighbors,
+                                                  DLManagedTensor* distances, DLManagedTensor* scores,
+                                                  cuvsFilter filter, int64_t id_base);
+
+/**
+ * Device merge of per-shard answers, the step the reference performs on the host in `search_sharded`
+ * (cpp/src/neighbors/certex/certex_shards.cu:144-166): part_scores float64 [parts, nq, k] and part_ids int64
+ * [parts, nq, k] (id -1 = missing) are merged per query by (score, id); neighbors / distances / scores as in
+ * certexB200SearchEx (scores may be NULL). `queries` [nq, dim] is needed for inner-product distances.
+ */
+CERTEX_B200_EXPORT cuvsError_t certexB200MergeShards(cuvsResources_t res, cuvsDistanceType metric,
+                                                     DLManagedTensor* queries, DLManagedTensor* part_scores,
+                                                     DLManagedTensor* part_ids, DLManagedTensor* neighbors,
+                                                     DLManagedTensor* distances, DLManagedTensor* scores);
+
+/** Read-only facts of an index, the accessors of cuvs::neighbors::certex::index<T>
+ *  (cpp/include/cuvs/neighbors/certex.hpp:131-457) that the reference's Python binding reads. */
+typedef struct {
+  int64_t size;
+  int64_t dim;
+  int64_t capacity;
+  int64_t n_removed;
+  int32_t metric;        /* cuvsDistanceType */
+  int32_t anchor_stride;
+  int32_t has_labels;
+  int32_t integer_screen; /* 1: searches without a filter use the tensor-core screen */
+  int64_t row_pitch_bytes;
+  int64_t n_partitioned;
+} certexB200IndexInfo;
+CERTEX_B200_EXPORT cuvsError_t certexB200IndexGetInfo(cuvsCertexIndex_t index, certexB200IndexInfo* info);
+
+/** index<T>::reserve (cpp/src/neighbors/certex/certex.cu:1879-1936): preallocate rows for later additions. */
+CERTEX_B200_EXPORT cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsCertexIndex_t index, int64_t n_rows);
+
+/** Counters of the calling thread's searches between Begin and End: the reference's search_stats
+ *  (cpp/src/neighbors/certex/detail/kernels.hpp:256-263). out[0..3] = queries, survivors of the screen, exact scores
+ *  computed, queries answered by the dense (unscreened) path; out[4] = kernels launched; out[5], out[6] = device
+ *  time in microseconds of the screen passes and of the anchor (group-maximum) passes, measured with CUDA events on
+ *  the launching stream; out[7] = number of screen passes. */
+CERTEX_B200_EXPORT cuvsError_t certexB200StatsBegin(void);
+CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[8]);
+
+/** Test hook: mode 0 automatic, 1 always the dense path, 2 screen with candidate lists of `cap` entries per query
+ *  (small values exercise the overflow fallback). */
+CERTEX_B200_EXPORT cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap);
+
+/**
+ * The tensor-core pass alone on caller buffers (device pointers), the seam of the reference's
+ * detail/kernels.hpp:290-304 (`screen_int8`) and :125-135 (`anchor_groups`), for kernel-level tests and timing.
+ * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len a multiple of
+ * 128 up to 512, nq_pad = nq rounded up to 128 with zero rows; init [n rounded up to 128].
+ * mode 0 (screen): keep iff init[x] + <q, x> >= thr[q]; cnt [nq] must be zeroed by the caller; cand [nq, cap].
+ * mode 1 (group maxima): gmax [nq, ld] receives the maximum over every 128 rows of x.
+ * Returns after the pass has finished; a pass that gave up on a wait is an error.
+ */
+CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_t nq,
+                                                   const void* x_codes, int64_t n, int64_t code_len, int32_t is_signed,
+                                                   const int32_t* init, int32_t mode, const int32_t* thr,
+                                                   int32_t* gmax, int64_t ld, uint32_t* cnt, int32_t* cand,
+                                                   uint32_t cap, float* elapsed_ms);
+
+/** Test hook (host only, no GPU needed): the split of n_query_tiles x n_base_tiles accumulator units over `grid` CTAs
+ *  that the tensor-core pass uses. out receives grid * 4 segments of 4 ints (first query tile, query tiles, first base
+ *  tile, end base tile); unused segments have end <= first. */
+CERTEX_B200_EXPORT cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
+                                                      int32_t grid, int32_t* out);
+
+/** Version string "major.minor.patch". */
+CERTEX_B200_EXPORT const char* certexB200Version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CERTEX_B200_H_ */

@@ -1,0 +1,493 @@
+// C ABI of the library (include/certex_b200.h): argument checks, DLPack unwrapping and exception translation over
+// the engine. Mirrors the reference's c/src/neighbors/certex.cpp, c/src/core/interop.hpp and c/src/core/exceptions.hpp.
+#include "../../include/certex_b200.h"
+
+#include "engine.hpp"
+#include "screen_i8.cuh"
+
+#include <cuda.h>
+
+#include <fstream>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace {
+
+using namespace certex_b200;
+
+thread_local std::string g_last_error;
+thread_local SearchStats g_stats;
+
+template <typename F>
+cuvsError_t translate(F&& f)
+{
+  try {
+    f();
+    return CUVS_SUCCESS;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+  } catch (...) {
+    g_last_error = "certex: unknown error";
+  }
+  return CUVS_ERROR;
+}
+
+struct Holder {
+  std::unique_ptr<Index> index;
+  int64_t n_partitioned = 0;
+};
+
+Resources& as_res(cuvsResources_t r)
+{
+  CERTEX_EXPECTS(r != 0, "certex: null resources handle");
+  return *reinterpret_cast<Resources*>(r);
+}
+
+Holder& as_holder(cuvsCertexIndex_t index)
+{
+  CERTEX_EXPECTS(index != nullptr && index->addr != 0, "certex: the index is empty (build or deserialize it first)");
+  return *reinterpret_cast<Holder*>(index->addr);
+}
+
+int metric_of(int m)
+{
+  switch (m) {
+    case L2Expanded: return kL2;
+    case InnerProduct: return kIP;
+    case CosineExpanded: return kCos;
+    default: throw Error("certex: the metric must be L2Expanded, InnerProduct, or CosineExpanded");
+  }
+}
+
+int metric_back(int m) { return m == kL2 ? L2Expanded : m == kIP ? InnerProduct : CosineExpanded; }
+
+int dtype_of(DLDataType t)
+{
+  CERTEX_EXPECTS(t.lanes == 1, "certex: the DLPack tensor must have one lane");
+  if (t.code == kDLFloat && t.bits == 32) { return kF32; }
+  if (t.code == kDLFloat && t.bits == 16) { return kF16; }
+  if (t.code == kDLInt && t.bits == 8) { return kI8; }
+  if (t.code == kDLUInt && t.bits == 8) { return kU8; }
+  throw Error("certex: vectors must be float32, float16, int8, or uint8");
+}
+
+bool on_device(const DLTensor& t) { return t.device.device_type == kDLCUDA || t.device.device_type == kDLCUDAManaged; }
+bool on_host(const DLTensor& t) { return t.device.device_type == kDLCPU || t.device.device_type == kDLCUDAHost; }
+
+/// Dense row-major tensor of the given rank and element type; returns the data pointer with byte_offset applied.
+void* checked(DLManagedTensor* m, int ndim, int code, int bits, bool device, const char* what)
+{
+  CERTEX_EXPECTS(m != nullptr, std::string("certex: null tensor for ") + what);
+  const DLTensor& t = m->dl_tensor;
+  CERTEX_EXPECTS(t.ndim == ndim, std::string("certex: ") + what + " has the wrong number of dimensions");
+  CERTEX_EXPECTS(t.dtype.lanes == 1 && (code < 0 || (t.dtype.code == code && t.dtype.bits == bits)),
+                 std::string("certex: ") + what + " has the wrong data type");
+  if (device) {
+    CERTEX_EXPECTS(on_device(t), std::string("certex: expected ") + what + " in device memory");
+  }
+  if (t.strides != nullptr) {
+    int64_t expect = 1;
+    for (int i = ndim - 1; i >= 0; --i) {
+      CERTEX_EXPECTS(t.shape[i] == 1 || t.strides[i] == expect, "certex: the DLPack tensor must be dense and row major");
+      expect *= t.shape[i];
+    }
+  }
+  return static_cast<char*>(t.data) + t.byte_offset;
+}
+
+Filter filter_of(const cuvsFilter& f, int64_t nq, int64_t size)
+{
+  Filter out;
+  if (f.type == NO_FILTER) { return out; }
+  CERTEX_EXPECTS(f.type == BITSET || f.type == BITMAP, "certex: unsupported filter type");
+  auto* words_t = reinterpret_cast<DLManagedTensor*>(f.addr);
+  out.words     = static_cast<const uint32_t*>(checked(words_t, 1, kDLUInt, 32, true, "the filter words"));
+  const int64_t have = words_t->dl_tensor.shape[0];
+  if (f.type == BITSET) {
+    CERTEX_EXPECTS(have * 32 >= size, "certex: the bitset must cover every id of the index");
+  } else {
+    out.bitmap_cols = size;
+    CERTEX_EXPECTS(have * 32 >= nq * size, "certex: the bitmap must hold one row of size() bits per query");
+  }
+  return out;
+}
+
+void search_impl(cuvsResources_t res, cuvsCertexSearchParams_t params, cuvsCertexIndex_t index, DLManagedTensor* queries,
+                 DLManagedTensor* query_labels, DLManagedTensor* neighbors, DLManagedTensor* distances,
+                 DLManagedTensor* scores, cuvsFilter filter, int64_t id_base)
+{
+  Resources& r = as_res(res);
+  Holder& h    = as_holder(index);
+  CERTEX_EXPECTS(params != nullptr, "certex: null search parameters");
+  CERTEX_EXPECTS(queries != nullptr && queries->dl_tensor.dtype.code == index->dtype.code &&
+                   queries->dl_tensor.dtype.bits == index->dtype.bits,
+                 "certex: the queries must have the vector type of the index");
+  const void* q = checked(queries, 2, -1, 0, true, "the queries");
+  const int64_t nq = queries->dl_tensor.shape[0];
+  CERTEX_EXPECTS(queries->dl_tensor.shape[1] == h.index->dim(), "certex: the queries must have the dimension of the index");
+  auto* nb = static_cast<int64_t*>(checked(neighbors, 2, kDLInt, 64, true, "the neighbors"));
+  auto* ds = static_cast<float*>(checked(distances, 2, kDLFloat, 32, true, "the distances"));
+  const int64_t k = neighbors->dl_tensor.shape[1];
+  CERTEX_EXPECTS(neighbors->dl_tensor.shape[0] == nq && distances->dl_tensor.shape[0] == nq &&
+                   distances->dl_tensor.shape[1] == k,
+                 "certex: neighbors and distances must be [n_queries, k]");
+  double* sc = nullptr;
+  if (scores) {
+    sc = static_cast<double*>(checked(scores, 2, kDLFloat, 64, true, "the scores"));
+    CERTEX_EXPECTS(scores->dl_tensor.shape[0] == nq && scores->dl_tensor.shape[1] == k, "certex: scores must be [n_queries, k]");
+  }
+  Filter f = filter_of(filter, nq, h.index->size());
+  if (query_labels) {
+    f.query_labels = static_cast<const int32_t*>(checked(query_labels, 1, kDLInt, 32, true, "the query labels"));
+    CERTEX_EXPECTS(query_labels->dl_tensor.shape[0] == nq, "certex: one label per query");
+  }
+  SearchParams sp;
+  sp.anchors     = params->anchors;
+  sp.batch_size  = params->batch_size;
+  sp.probe_lists = params->probe_lists;
+  CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
+  h.index->search(r, sp, q, nq, static_cast<int>(k), nb, ds, sc, f, id_base);
+}
+
+const char* prefix_of(int dtype)
+{
+  switch (dtype) {
+    case kF32: return "<f4";
+    case kF16: return "<f2";
+    case kI8: return "|i1";
+    default: return "|u1";
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* cuvsGetLastErrorText(void) { return g_last_error.empty() ? nullptr : g_last_error.c_str(); }
+void cuvsSetLastErrorText(const char* text) { g_last_error = text ? text : ""; }
+
+cuvsError_t cuvsResourcesCreate(cuvsResources_t* res)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(res != nullptr, "certex: null pointer");
+    *res = reinterpret_cast<cuvsResources_t>(new Resources());
+  });
+}
+
+cuvsError_t cuvsResourcesDestroy(cuvsResources_t res)
+{
+  return translate([=] { delete reinterpret_cast<Resources*>(res); });
+}
+
+cuvsError_t cuvsStreamSet(cuvsResources_t res, void* stream)
+{
+  return translate([=] { as_res(res).stream = static_cast<cudaStream_t>(stream); });
+}
+
+cuvsError_t cuvsStreamGet(cuvsResources_t res, void** stream)
+{
+  return translate([=] { *stream = as_res(res).stream; });
+}
+
+cuvsError_t cuvsStreamSync(cuvsResources_t res)
+{
+  return translate([=] { as_res(res).sync(); });
+}
+
+cuvsError_t cuvsCertexIndexParamsCreate(cuvsCertexIndexParams_t* params)
+{
+  return translate([=] {
+    const IndexParams d;
+    *params = new cuvsCertexIndexParams{static_cast<cuvsDistanceType>(metric_back(d.metric)),
+                                        d.width,
+                                        d.variance,
+                                        d.anchor_stride,
+                                        d.pca_sample,
+                                        d.host_vectors,
+                                        d.n_lists,
+                                        d.local_projections,
+                                        d.int8_rows};
+  });
+}
+
+cuvsError_t cuvsCertexIndexParamsDestroy(cuvsCertexIndexParams_t params)
+{
+  return translate([=] { delete params; });
+}
+
+cuvsError_t cuvsCertexSearchParamsCreate(cuvsCertexSearchParams_t* params)
+{
+  return translate([=] {
+    const SearchParams d;
+    *params = new cuvsCertexSearchParams{d.anchors, d.batch_size, d.probe_lists};
+  });
+}
+
+cuvsError_t cuvsCertexSearchParamsDestroy(cuvsCertexSearchParams_t params)
+{
+  return translate([=] { delete params; });
+}
+
+cuvsError_t cuvsCertexIndexCreate(cuvsCertexIndex_t* index)
+{
+  return translate([=] { *index = new cuvsCertexIndex{}; });
+}
+
+cuvsError_t cuvsCertexIndexDestroy(cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    if (index == nullptr) { return; }
+    if (index->addr != 0) { delete reinterpret_cast<Holder*>(index->addr); }
+    delete index;
+  });
+}
+
+cuvsError_t cuvsCertexIndexGetSize(cuvsCertexIndex_t index, int64_t* size)
+{
+  return translate([=] { *size = as_holder(index).index->size(); });
+}
+
+cuvsError_t cuvsCertexIndexGetDim(cuvsCertexIndex_t index, int64_t* dim)
+{
+  return translate([=] { *dim = as_holder(index).index->dim(); });
+}
+
+cuvsError_t cuvsCertexBuild(cuvsResources_t res, cuvsCertexIndexParams_t params, DLManagedTensor* dataset,
+                            cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    CERTEX_EXPECTS(index != nullptr && index->addr == 0, "certex: the index handle already holds an index");
+    CERTEX_EXPECTS(params != nullptr, "certex: null index parameters");
+    const void* x     = checked(dataset, 2, -1, 0, false, "the dataset");
+    const DLTensor& t = dataset->dl_tensor;
+    CERTEX_EXPECTS(on_device(t) || on_host(t), "certex: the dataset must be in device or host memory");
+    const int dtype = dtype_of(t.dtype);
+    IndexParams p;
+    p.metric            = metric_of(params->metric);
+    p.width             = params->width;
+    p.variance          = params->variance;
+    p.anchor_stride     = params->anchor_stride;
+    p.pca_sample        = params->pca_sample;
+    p.host_vectors      = params->host_vectors;
+    p.n_lists           = params->n_lists;
+    p.local_projections = params->local_projections;
+    p.int8_rows         = params->int8_rows;
+    CERTEX_EXPECTS(t.shape[0] >= 1, "certex: the dataset is empty");
+    auto holder   = std::make_unique<Holder>();
+    holder->index = std::make_unique<Index>(r, p, dtype, t.shape[1]);
+    holder->index->extend(r, x, t.shape[0], on_host(t));
+    index->dtype = t.dtype;
+    index->addr  = reinterpret_cast<uintptr_t>(holder.release());
+  });
+}
+
+cuvsError_t cuvsCertexExtend(cuvsResources_t res, DLManagedTensor* new_vectors, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r      = as_res(res);
+    Holder& h         = as_holder(index);
+    const void* x     = checked(new_vectors, 2, index->dtype.code, index->dtype.bits, false, "the new vectors");
+    const DLTensor& t = new_vectors->dl_tensor;
+    CERTEX_EXPECTS(on_device(t) || on_host(t), "certex: the vectors must be in device or host memory");
+    CERTEX_EXPECTS(t.shape[1] == h.index->dim(), "certex: the new vectors must have the dimension of the index");
+    h.index->extend(r, x, t.shape[0], on_host(t));
+  });
+}
+
+cuvsError_t cuvsCertexRemove(cuvsResources_t res, DLManagedTensor* ids, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    Holder& h    = as_holder(index);
+    auto* p      = static_cast<const int64_t*>(checked(ids, 1, kDLInt, 64, true, "the ids"));
+    h.index->remove(r, p, ids->dl_tensor.shape[0]);
+  });
+}
+
+cuvsError_t cuvsCertexSetLabels(cuvsResources_t res, DLManagedTensor* labels, int64_t first, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    Holder& h    = as_holder(index);
+    auto* p      = static_cast<const int32_t*>(checked(labels, 1, kDLInt, 32, true, "the labels"));
+    h.index->set_labels(r, p, labels->dl_tensor.shape[0], first);
+  });
+}
+
+cuvsError_t cuvsCertexPartitionByLabels(cuvsResources_t res, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    (void)as_res(res);
+    Holder& h = as_holder(index);
+    CERTEX_EXPECTS(h.index->has_labels(), "certex: the index has no labels");
+    h.n_partitioned = h.index->size();
+  });
+}
+
+cuvsError_t cuvsCertexSearch(cuvsResources_t res, cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
+                             DLManagedTensor* queries, DLManagedTensor* neighbors, DLManagedTensor* distances,
+                             cuvsFilter filter)
+{
+  return translate([=] { search_impl(res, params, index, queries, nullptr, neighbors, distances, nullptr, filter, 0); });
+}
+
+cuvsError_t cuvsCertexSearchWithLabels(cuvsResources_t res, cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
+                                       DLManagedTensor* queries, DLManagedTensor* query_labels,
+                                       DLManagedTensor* neighbors, DLManagedTensor* distances)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(query_labels != nullptr, "certex: null query labels");
+    cuvsFilter none{0, NO_FILTER};
+    search_impl(res, params, index, queries, query_labels, neighbors, distances, nullptr, none, 0);
+  });
+}
+
+cuvsError_t certexB200SearchEx(cuvsResources_t res, cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
+                               DLManagedTensor* queries, DLManagedTensor* query_labels, DLManagedTensor* neighbors,
+                               DLManagedTensor* distances, DLManagedTensor* scores, cuvsFilter filter, int64_t id_base)
+{
+  return translate([=] { search_impl(res, params, index, queries, query_labels, neighbors, distances, scores, filter, id_base); });
+}
+
+cuvsError_t cuvsCertexSerialize(cuvsResources_t res, const char* filename, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    Holder& h    = as_holder(index);
+    std::ofstream os(filename, std::ios::binary);
+    CERTEX_EXPECTS(os.good(), "certex: cannot open the index file for writing");
+    std::string prefix = prefix_of(h.index->dtype());
+    prefix.resize(4, '\0');
+    os << prefix;
+    h.index->save(r, os);
+  });
+}
+
+cuvsError_t cuvsCertexDeserialize(cuvsResources_t res, const char* filename, cuvsCertexIndex_t index)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    CERTEX_EXPECTS(index != nullptr && index->addr == 0, "certex: the index handle already holds an index");
+    std::ifstream is(filename, std::ios::binary);
+    CERTEX_EXPECTS(is.good(), "certex: cannot open the index file");
+    char prefix[4] = {};
+    is.read(prefix, 4);
+    const std::string d(prefix + 1, 2);
+    DLDataType dt{};
+    if (d == "f4") {
+      dt = {kDLFloat, 32, 1};
+    } else if (d == "f2") {
+      dt = {kDLFloat, 16, 1};
+    } else if (d == "i1") {
+      dt = {kDLInt, 8, 1};
+    } else if (d == "u1") {
+      dt = {kDLUInt, 8, 1};
+    } else {
+      throw Error("certex: not a CertEx index file");
+    }
+    auto holder   = std::make_unique<Holder>();
+    holder->index = Index::load(r, is, dtype_of(dt));
+    index->dtype  = dt;
+    index->addr   = reinterpret_cast<uintptr_t>(holder.release());
+  });
+}
+
+cuvsError_t certexB200MergeShards(cuvsResources_t res, cuvsDistanceType metric, DLManagedTensor* queries,
+                                  DLManagedTensor* part_scores, DLManagedTensor* part_ids, DLManagedTensor* neighbors,
+                                  DLManagedTensor* distances, DLManagedTensor* scores)
+{
+  return translate([=] {
+    Resources& r     = as_res(res);
+    const void* q    = checked(queries, 2, -1, 0, true, "the queries");
+    const int dtype  = dtype_of(queries->dl_tensor.dtype);
+    auto* ps         = static_cast<const double*>(checked(part_scores, 3, kDLFloat, 64, true, "the shard scores"));
+    auto* pi         = static_cast<const int64_t*>(checked(part_ids, 3, kDLInt, 64, true, "the shard ids"));
+    auto* nb         = static_cast<int64_t*>(checked(neighbors, 2, kDLInt, 64, true, "the neighbors"));
+    auto* ds         = static_cast<float*>(checked(distances, 2, kDLFloat, 32, true, "the distances"));
+    double* sc       = scores ? static_cast<double*>(checked(scores, 2, kDLFloat, 64, true, "the scores")) : nullptr;
+    const int64_t* s = part_scores->dl_tensor.shape;
+    const int64_t nq = queries->dl_tensor.shape[0];
+    CERTEX_EXPECTS(s[1] == nq && part_ids->dl_tensor.shape[0] == s[0] && part_ids->dl_tensor.shape[1] == nq &&
+                     part_ids->dl_tensor.shape[2] == s[2] && neighbors->dl_tensor.shape[0] == nq &&
+                     neighbors->dl_tensor.shape[1] == s[2] && distances->dl_tensor.shape[0] == nq &&
+                     distances->dl_tensor.shape[1] == s[2],
+                   "certex: shard answers must be [parts, n_queries, k] and the outputs [n_queries, k]");
+    merge_shards(r, ps, pi, static_cast<int>(s[0]), static_cast<int>(nq), static_cast<int>(s[2]), q, dtype,
+                 queries->dl_tensor.shape[1], metric_of(metric), nb, ds, sc);
+  });
+}
+
+cuvsError_t certexB200IndexGetInfo(cuvsCertexIndex_t index, certexB200IndexInfo* info)
+{
+  return translate([=] {
+    Holder& h             = as_holder(index);
+    info->size            = h.index->size();
+    info->dim             = h.index->dim();
+    info->capacity        = h.index->capacity();
+    info->n_removed       = h.index->n_removed();
+    info->metric          = metric_back(h.index->metric());
+    info->anchor_stride   = h.index->params().anchor_stride;
+    info->has_labels      = h.index->has_labels() ? 1 : 0;
+    info->integer_screen  = h.index->int_screen() ? 1 : 0;
+    info->row_pitch_bytes = static_cast<int64_t>(h.index->pitch());
+    info->n_partitioned   = h.n_partitioned;
+  });
+}
+
+cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsCertexIndex_t index, int64_t n_rows)
+{
+  return translate([=] { as_holder(index).index->reserve(as_res(res), n_rows); });
+}
+
+cuvsError_t certexB200StatsBegin(void)
+{
+  return translate([] {
+    g_stats           = SearchStats{};
+    Index::stats_sink = &g_stats;
+  });
+}
+
+cuvsError_t certexB200StatsEnd(uint64_t out[8])
+{
+  return translate([=] {
+    Index::stats_sink = nullptr;
+    out[0] = g_stats.queries, out[1] = g_stats.survivors, out[2] = g_stats.verified, out[3] = g_stats.dense_queries;
+    out[4] = g_stats.launches;
+    out[5] = static_cast<uint64_t>(g_stats.screen_ms * 1000.0);
+    out[6] = static_cast<uint64_t>(g_stats.anchor_ms * 1000.0);
+    out[7] = g_stats.screen_passes;
+  });
+}
+
+cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(mode >= 0 && mode <= 2 && (mode != 2 || cap >= 1), "certex: unknown test mode");
+    as_holder(index).index->set_test_mode(mode, cap);
+  });
+}
+
+cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n,
+                                int64_t code_len, int32_t is_signed, const int32_t* init, int32_t mode,
+                                const int32_t* thr, int32_t* gmax, int64_t ld, uint32_t* cnt, int32_t* cand,
+                                uint32_t cap, float* elapsed_ms)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    CERTEX_EXPECTS(code_len % 128 == 0 && code_len >= 128 && code_len <= 512, "certex: code_len must be 128, 256, 384 or 512");
+    CERTEX_EXPECTS(nq >= 1 && n >= 1 && n < (int64_t(1) << 31) && nq < (int64_t(1) << 24), "certex: sizes out of range");
+    screen_raw(r, q_codes, nq, x_codes, n, code_len, is_signed != 0, init, mode, thr, gmax, ld, cnt, cand, cap, elapsed_ms);
+  });
+}
+
+cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles, int32_t grid,
+                                   int32_t* out)
+{
+  return translate([=] { plan_segments_flat(n_query_tiles, n_base_tiles, panel_tiles, grid, out); });
+}
+
+const char* certexB200Version(void) { return "0.1.0"; }
+
+}  // extern "C"

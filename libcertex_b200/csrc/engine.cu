@@ -1,0 +1,662 @@
+// Index container and search pipeline (host orchestration). See engine.hpp for the reference counterparts.
+//
+// Search of an 8-bit index (no filter), per batch of queries, all on one stream without a host round trip:
+//   1 GROUPMAX pass of the tensor-core kernel over every `stride`-th stored row (the anchors, read in place through a
+//     strided TMA map)                                   -> gmax [nq, groups of 128 anchors]
+//   2 k-th largest group maximum                          -> thr [nq]   (k distinct rows are at least that close)
+//   3 SCREEN pass over all rows, keep iff acc >= thr      -> per-query candidate lists
+//   4 exact fp64 scores of the candidates + top-k by (score, id)
+// Queries whose candidate list overflowed, searches with a filter or labels, float / half indexes and small indexes
+// take the dense path: exact fp64 scores of all rows, then a radix selection. One stream synchronisation per search
+// call reads the overflow count.
+#include "engine.hpp"
+
+#include "screen_i8.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <istream>
+#include <ostream>
+#include <vector>
+
+namespace certex_b200 {
+
+thread_local SearchStats* Index::stats_sink = nullptr;
+
+namespace {
+
+constexpr int64_t kTile = 128;
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// ------------------------------------------------------------------ stream-ordered scratch memory
+struct Scratch {
+  cudaStream_t stream;
+  std::vector<void*> ptrs;
+  explicit Scratch(cudaStream_t s) : stream(s) {}
+  ~Scratch()
+  {
+    for (void* p : ptrs) { cudaFreeAsync(p, stream); }
+  }
+  template <typename T>
+  T* get(size_t count)
+  {
+    void* p = nullptr;
+    CERTEX_CUDA(cudaMallocAsync(&p, std::max<size_t>(count, 1) * sizeof(T), stream));
+    ptrs.push_back(p);
+    return static_cast<T*>(p);
+  }
+};
+
+// ------------------------------------------------------------------ TMA descriptors
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled()
+{
+  static EncodeTiled fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) {
+      throw Error("certex: the CUDA driver does not provide cuTensorMapEncodeTiled");
+    }
+    return reinterpret_cast<EncodeTiled>(p);
+  }();
+  return fn;
+}
+
+/// Map over rows of `row_bytes` 8-bit codes, `row_stride` bytes apart; boxes of 128 bytes x 128 rows, 128-byte swizzle,
+/// rows beyond `rows` read as zeros.
+CUtensorMap make_code_map(const void* base, uint64_t row_bytes, uint64_t rows, uint64_t row_stride)
+{
+  CUtensorMap m;
+  const cuuint64_t dims[2]    = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_stride};
+  const cuuint32_t box[2]     = {128, 128};
+  const cuuint32_t estr[2]    = {1, 1};
+  const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CERTEX_EXPECTS(r == CUDA_SUCCESS, "certex: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return m;
+}
+
+// ------------------------------------------------------------------ work split of the tensor-core pass
+struct ScreenShape {
+  int panel_tiles;
+  int n_stages;
+};
+
+ScreenShape shape_for(int kb)
+{
+  switch (kb) {
+    case 1: return {8, 5};
+    case 2: return {4, 2};
+    case 3: return {2, 2};
+    default: return {1, 2};
+  }
+}
+
+/// Splits nqt query tiles x nt base tiles over `grid` CTAs: query tiles are grouped into panels of at most
+/// `panel_tiles`; the (panel, base tile) items are laid out panel-major and cut into `grid` ranges of equal unit count.
+std::vector<ScreenSeg> plan_segments(int nqt, int nt, int panel_tiles, int grid)
+{
+  std::vector<ScreenSeg> segs(static_cast<size_t>(grid) * kMaxSegs, ScreenSeg{0, 0, 0, 0});
+  if (nqt <= 0 || nt <= 0) { return segs; }
+  const int n_panels = (nqt + panel_tiles - 1) / panel_tiles;
+  std::vector<int64_t> q_lo(n_panels + 1), off(n_panels + 1);
+  for (int p = 0; p <= n_panels; ++p) { q_lo[p] = static_cast<int64_t>(p) * nqt / n_panels; }
+  off[0] = 0;
+  for (int p = 0; p < n_panels; ++p) { off[p + 1] = off[p] + (q_lo[p + 1] - q_lo[p]) * nt; }
+  const int64_t total = off[n_panels];
+  // position of a unit boundary as (panel, tile)
+  auto locate = [&](int64_t u, int& p, int64_t& t) {
+    p = 0;
+    while (p < n_panels - 1 && u >= off[p + 1]) { ++p; }
+    const int64_t w = q_lo[p + 1] - q_lo[p];
+    t               = std::min<int64_t>((u - off[p]) / w, nt);
+  };
+  for (int b = 0; b < grid; ++b) {
+    const int64_t u0 = total * b / grid, u1 = total * (b + 1) / grid;
+    int p0, p1;
+    int64_t t0, t1;
+    locate(u0, p0, t0);
+    if (b + 1 == grid) {
+      p1 = n_panels - 1, t1 = nt;
+    } else {
+      locate(u1, p1, t1);
+    }
+    int n = 0;
+    for (int p = p0; p <= p1; ++p) {
+      const int64_t a = p == p0 ? t0 : 0, e = p == p1 ? t1 : nt;
+      if (e > a) {
+        CERTEX_EXPECTS(n < kMaxSegs, "certex: internal error: too many query panels for one launch");
+        segs[static_cast<size_t>(b) * kMaxSegs + n++] =
+          ScreenSeg{static_cast<int>(q_lo[p]), static_cast<int>(q_lo[p + 1] - q_lo[p]), static_cast<int>(a), static_cast<int>(e)};
+      }
+    }
+  }
+  return segs;
+}
+
+}  // namespace
+
+// ============================================================================================ Resources
+Resources::Resources()
+{
+  CERTEX_CUDA(cudaGetDevice(&device));
+  CERTEX_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  int major = 0;
+  CERTEX_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  CERTEX_EXPECTS(major == 10, "certex: this library is built for sm_100a (B200) only");
+  // keep freed scratch memory in the stream-ordered pool instead of returning it to the driver at every sync
+  cudaMemPool_t pool;
+  CERTEX_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+  uint64_t keep = UINT64_MAX;
+  CERTEX_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+}
+
+void Resources::sync() const { CERTEX_CUDA(cudaStreamSynchronize(stream)); }
+
+// ============================================================================================ Index
+Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t dim)
+  : params_(params), dtype_(dtype), dim_(dim), device_(res.device)
+{
+  CERTEX_EXPECTS(dim >= 1, "certex: the dimension must be positive");
+  CERTEX_EXPECTS(dtype >= kF32 && dtype <= kU8, "certex: vectors must be float32, float16, int8, or uint8");
+  CERTEX_EXPECTS(params.metric == kL2 || params.metric == kIP || params.metric == kCos,
+                 "certex: the metric must be L2Expanded, InnerProduct, or CosineExpanded");
+  CERTEX_EXPECTS(params.anchor_stride >= 1, "certex: anchor_stride must be at least 1");
+  const bool is_int = dtype == kI8 || dtype == kU8;
+  CERTEX_EXPECTS(!(params.metric == kCos && is_int), "certex: the cosine metric needs float32 or float16 vectors");
+  int_screen_ = is_int && dim <= 512;
+  if (int_screen_) {
+    pitch_ = static_cast<size_t>(round_up(dim, 128));
+    kb_    = static_cast<int>(pitch_ / 128);
+  } else {
+    pitch_ = static_cast<size_t>(round_up(dim * dtype_size(dtype), 16));
+  }
+}
+
+Index::~Index()
+{
+  cudaFree(vectors_);
+  cudaFree(removed_);
+  cudaFree(labels_);
+  cudaFree(init_);
+}
+
+void Index::reserve(const Resources& res, int64_t n)
+{
+  if (n <= capacity_) { return; }
+  const int64_t cap = std::max<int64_t>(n, 2 * capacity_);
+  void* v           = nullptr;
+  uint8_t* r        = nullptr;
+  int32_t* l        = nullptr;
+  int32_t* in       = nullptr;
+  CERTEX_CUDA(cudaMalloc(&v, static_cast<size_t>(cap) * pitch_));
+  CERTEX_CUDA(cudaMalloc(&r, static_cast<size_t>(round_up(cap, 4))));
+  CERTEX_CUDA(cudaMemsetAsync(r, 0, static_cast<size_t>(round_up(cap, 4)), res.stream));
+  if (labels_) {
+    CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(cap) * 4));
+    CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(cap) * 4, res.stream));
+  }
+  if (int_screen_) { CERTEX_CUDA(cudaMalloc(&in, static_cast<size_t>(round_up(cap, kTile)) * 4)); }
+  if (size_ > 0) {
+    CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, cudaMemcpyDeviceToDevice, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), cudaMemcpyDeviceToDevice, res.stream));
+    if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, cudaMemcpyDeviceToDevice, res.stream)); }
+    if (int_screen_) {
+      CERTEX_CUDA(cudaMemcpyAsync(in, init_, static_cast<size_t>(round_up(size_, kTile)) * 4, cudaMemcpyDeviceToDevice, res.stream));
+    }
+  }
+  res.sync();
+  void* old[4] = {vectors_, removed_, labels_, init_};
+  {
+    std::unique_lock<std::shared_mutex> lock(rw_);  // waits for running searches, which read the old arrays
+    vectors_  = v;
+    removed_  = r;
+    if (l) { labels_ = l; }
+    init_     = in;
+    capacity_ = cap;
+  }
+  cudaFree(old[0]);
+  cudaFree(old[1]);
+  if (l) { cudaFree(old[2]); }
+  cudaFree(old[3]);
+}
+
+void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_host)
+{
+  if (n <= 0) { return; }
+  std::lock_guard<std::mutex> w(writer_);
+  CERTEX_EXPECTS(size_ + n < (int64_t(1) << 31) - 256, "certex: at most 2^31 - 257 vectors per index");
+  reserve(res, size_ + n);
+  uint8_t* dst          = static_cast<uint8_t*>(vectors_) + static_cast<size_t>(size_) * pitch_;
+  const size_t row_bytes = static_cast<size_t>(dim_) * dtype_size(dtype_);
+  const auto kind        = on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+  if (row_bytes == pitch_) {
+    CERTEX_CUDA(cudaMemcpyAsync(dst, rows, static_cast<size_t>(n) * pitch_, kind, res.stream));
+  } else {
+    CERTEX_CUDA(cudaMemsetAsync(dst, 0, static_cast<size_t>(n) * pitch_, res.stream));
+    CERTEX_CUDA(cudaMemcpy2DAsync(dst, pitch_, rows, row_bytes, row_bytes, static_cast<size_t>(n), kind, res.stream));
+  }
+  if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
+  if (int_screen_) {
+    // rows beyond the published size are invisible to running searches, which bound candidates by their own size
+    launch_row_init(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, removed_, size_, n,
+                    round_up(size_ + n, kTile), init_, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+  }
+  res.sync();
+  std::unique_lock<std::shared_mutex> lock(rw_);
+  size_ += n;
+}
+
+void Index::remove(const Resources& res, const int64_t* ids_device, int64_t n_ids)
+{
+  if (n_ids <= 0) { return; }
+  std::lock_guard<std::mutex> w(writer_);
+  Scratch scratch(res.stream);
+  auto* counter = scratch.get<unsigned long long>(1);
+  CERTEX_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned long long), res.stream));
+  launch_remove(ids_device, n_ids, size_, removed_, init_, counter, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+  unsigned long long n_new = 0;
+  CERTEX_CUDA(cudaMemcpyAsync(&n_new, counter, sizeof(n_new), cudaMemcpyDeviceToHost, res.stream));
+  res.sync();
+  std::unique_lock<std::shared_mutex> lock(rw_);
+  n_removed_ += static_cast<int64_t>(n_new);
+}
+
+void Index::set_labels(const Resources& res, const int32_t* labels_device, int64_t n, int64_t first)
+{
+  std::lock_guard<std::mutex> w(writer_);
+  CERTEX_EXPECTS(first >= 0 && n >= 0 && first + n <= size_, "certex: labels beyond the vectors of the index");
+  if (!labels_) {
+    int32_t* l = nullptr;
+    CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(std::max<int64_t>(capacity_, 1)) * 4));
+    CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(std::max<int64_t>(capacity_, 1)) * 4, res.stream));
+    res.sync();
+    std::unique_lock<std::shared_mutex> lock(rw_);
+    labels_ = l;
+  }
+  if (n > 0) {
+    CERTEX_CUDA(cudaMemcpyAsync(labels_ + first, labels_device, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, res.stream));
+  }
+  res.sync();
+  std::unique_lock<std::shared_mutex> lock(rw_);
+  has_labels_ = true;
+}
+
+// -------------------------------------------------------------------------------------------- search
+void Index::search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
+                         const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const
+{
+  if (nqb <= 0) { return; }
+  Scratch scratch(res.stream);
+  const int64_t ld      = round_up(std::max<int64_t>(n, 1), 4);
+  const int64_t budget  = int64_t(1) << 30;  // bytes of score matrix per step
+  const int step        = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nqb, budget / (ld * 8))));
+  double* scores        = scratch.get<double>(static_cast<size_t>(step) * ld);
+  for (int b = 0; b < nqb; b += step) {
+    const int nb = std::min(step, nqb - b);
+    launch_dense_scores(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, n, q, qpitch,
+                        qsel ? qsel + b : nullptr, q0 + b, nb, adm, scores, ld, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    launch_select_topk(scores, ld, n, k, qsel ? qsel + b : nullptr, q0 + b, nb, best_s, best_row, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+  }
+}
+
+void Index::search_screened(const Resources& res, const uint8_t* qbuf, const void* queries, size_t row_bytes, int q0, int nq,
+                            int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
+                            unsigned long long* stats, int* err, int anchor_stride, int64_t n,
+                            std::vector<cudaEvent_t>* events) const
+{
+  // qbuf: all queries of the call, zero padded to [round_up(total, 128), pitch_]; this batch is rows [q0, q0 + nq)
+  Scratch scratch(res.stream);
+  const int grid          = res.sm_count;
+  const ScreenShape shape = shape_for(kb_);
+  const int nqt           = static_cast<int>((nq + kTile - 1) / kTile);
+  const int64_t n_anchor  = (n + anchor_stride - 1) / anchor_stride;
+  const int nt_anchor     = static_cast<int>((n_anchor + kTile - 1) / kTile);
+  const int nt_all        = static_cast<int>((n + kTile - 1) / kTile);
+  const int64_t ld_g      = round_up(nt_anchor, 8);
+  const uint32_t cap      = test_mode_ == 2 ? static_cast<uint32_t>(test_cap_) : static_cast<uint32_t>(std::max(2048, 2 * k));
+
+  int32_t* anchor_init = scratch.get<int32_t>(static_cast<size_t>(nt_anchor) * kTile);
+  int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
+  int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
+  uint32_t* cnt        = scratch.get<uint32_t>(static_cast<size_t>(nq));
+  int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
+  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs * 2);
+
+  const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
+  const std::vector<ScreenSeg> seg_s = plan_segments(nqt, nt_all, shape.panel_tiles, grid);
+  const size_t seg_bytes             = seg_a.size() * sizeof(ScreenSeg);
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs + seg_a.size(), seg_s.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
+  launch_gather_init(init_, anchor_stride, n_anchor, static_cast<int64_t>(nt_anchor) * kTile, anchor_init, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+
+  const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * pitch_;
+  const CUtensorMap tm_q = make_code_map(qb, pitch_, static_cast<uint64_t>(round_up(nq, kTile)), pitch_);
+  const CUtensorMap tm_a = make_code_map(vectors_, pitch_, static_cast<uint64_t>(n_anchor), pitch_ * anchor_stride);
+  const CUtensorMap tm_x = make_code_map(vectors_, pitch_, static_cast<uint64_t>(n), pitch_);
+
+  ScreenArgs a{};
+  a.nq          = nq;
+  a.kb          = kb_;
+  a.panel_tiles = shape.panel_tiles;
+  a.n_stages    = shape.n_stages;
+  a.q_signed    = dtype_ == kI8 ? 1u : 0u;
+  a.x_signed    = a.q_signed;
+  a.err         = err;
+  // 1 anchors: maximum of acc over every group of 128 anchors
+  a.mode    = kModeGroupMax;
+  a.init    = anchor_init;
+  a.gmax    = gmax;
+  a.ld_gmax = ld_g;
+  a.n_rows  = static_cast<int>(n_anchor);
+  a.segs    = d_segs;
+  auto mark = [&] {
+    if (events) {
+      cudaEvent_t e;
+      CERTEX_CUDA(cudaEventCreate(&e));
+      CERTEX_CUDA(cudaEventRecord(e, res.stream));
+      events->push_back(e);
+    }
+  };
+  mark();
+  CERTEX_CUDA(screen_i8_launch(tm_q, tm_a, a, grid, res.stream));
+  mark();
+  // 2 threshold: the k-th largest group maximum
+  launch_kth_largest(gmax, ld_g, nt_anchor, k, nq, thr, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+  // 3 screen over all rows
+  a.mode   = kModeScreen;
+  a.init   = init_;
+  a.thr    = thr;
+  a.cnt    = cnt;
+  a.cand   = cand;
+  a.cap    = cap;
+  a.n_rows = static_cast<int>(n);
+  a.segs   = d_segs + seg_a.size();
+  mark();
+  CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
+  mark();
+  // 4 exact scores of the candidates and the k best
+  Admit adm{};
+  adm.removed = removed_;
+  launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes, nq, q0, cand, cnt,
+                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+}
+
+void Index::search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
+                   int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base) const
+{
+  std::shared_lock<std::shared_mutex> lock(rw_);
+  const int64_t n = size_;
+  CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
+  CERTEX_EXPECTS(n >= k, "certex: k exceeds the number of vectors added to the index");
+  CERTEX_EXPECTS(sp.batch_size >= 1, "certex: batch_size must be positive");
+  CERTEX_EXPECTS(nq >= 0 && nq < (int64_t(1) << 31), "certex: too many queries in one call");
+  CERTEX_EXPECTS(!filter.query_labels || has_labels_, "certex: the index has no labels");
+  if (nq == 0) { return; }
+
+  Scratch scratch(res.stream);
+  const int d            = static_cast<int>(dim_);
+  const size_t row_bytes = static_cast<size_t>(d) * dtype_size(dtype_);
+  double* best_s         = scratch.get<double>(static_cast<size_t>(nq) * k);
+  int32_t* best_row      = scratch.get<int32_t>(static_cast<size_t>(nq) * k);
+
+  Admit adm{};
+  adm.removed         = removed_;
+  adm.bits            = filter.words;
+  adm.bitmap_cols     = filter.bitmap_cols;
+  adm.row_labels      = filter.query_labels ? labels_ : nullptr;
+  adm.query_labels    = filter.query_labels;
+  const bool filtered = filter.words != nullptr || filter.query_labels != nullptr;
+
+  // anchors: every stride-th row, and at least 2k groups of 128 anchors, or the threshold would be useless
+  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (kTile * 2 * k)));
+  const bool screened = int_screen_ && !filtered && stride >= 1 && test_mode_ != 1;
+
+  SearchStats local{};
+  local.queries = static_cast<unsigned long long>(nq);
+  if (screened) {
+    const int64_t nq_pad = round_up(nq, kTile);
+    uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * pitch_);
+    if (row_bytes != pitch_ || nq_pad != nq) { CERTEX_CUDA(cudaMemsetAsync(qbuf, 0, static_cast<size_t>(nq_pad) * pitch_, res.stream)); }
+    CERTEX_CUDA(cudaMemcpy2DAsync(qbuf, pitch_, queries, row_bytes, row_bytes, static_cast<size_t>(nq), cudaMemcpyDeviceToDevice, res.stream));
+    int32_t* ovf_list      = scratch.get<int32_t>(static_cast<size_t>(nq));
+    unsigned int* d_count  = scratch.get<unsigned int>(4);  // [0] overflowed queries, [1] error code of the passes
+    auto* d_stats          = scratch.get<unsigned long long>(2);
+    CERTEX_CUDA(cudaMemsetAsync(d_count, 0, 4 * sizeof(unsigned int), res.stream));
+    CERTEX_CUDA(cudaMemsetAsync(d_stats, 0, 2 * sizeof(unsigned long long), res.stream));
+    const int64_t batch = std::min<int64_t>(sp.batch_size, 32768);
+    std::vector<cudaEvent_t> events;
+    for (int64_t q0 = 0; q0 < nq; q0 += batch) {
+      const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
+      search_screened(res, qbuf, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
+                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, stats_sink ? &events : nullptr);
+      local.launches += 5;  // gather_init, GROUPMAX pass, kth_largest, SCREEN pass, verify_select
+    }
+    unsigned int h_count[4]       = {0, 0, 0, 0};
+    unsigned long long h_stats[2] = {0, 0};
+    CERTEX_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
+    res.sync();  // the one host round trip of a search call
+    for (size_t e = 0; e + 3 < events.size(); e += 4) {
+      float ms = 0;
+      cudaEventElapsedTime(&ms, events[e], events[e + 1]);
+      local.anchor_ms += ms;
+      cudaEventElapsedTime(&ms, events[e + 2], events[e + 3]);
+      local.screen_ms += ms;
+      ++local.screen_passes;
+    }
+    for (cudaEvent_t e : events) { cudaEventDestroy(e); }
+    CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
+    local.survivors = h_stats[0];
+    local.verified  = h_stats[1];
+    if (h_count[0] > 0) {  // candidate lists that overflowed: those queries are searched without the screen
+      search_dense(res, queries, row_bytes, ovf_list, 0, static_cast<int>(h_count[0]), k, adm, best_s, best_row, n);
+      local.dense_queries = h_count[0];
+      local.launches += 2;
+      local.verified += static_cast<unsigned long long>(h_count[0]) * static_cast<unsigned long long>(n);
+    }
+  } else {
+    search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
+    local.dense_queries = static_cast<unsigned long long>(nq);
+    local.launches += 2;
+    local.survivors     = static_cast<unsigned long long>(nq) * static_cast<unsigned long long>(n);
+    local.verified      = local.survivors;
+  }
+  launch_finish(best_s, best_row, id_base, queries, row_bytes, dtype_, d, params_.metric, static_cast<int>(nq), k, neighbors,
+                distances, scores_out, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+  local.launches += 1;  // finish
+  if (stats_sink) {
+    stats_sink->launches += local.launches;
+    stats_sink->screen_ms += local.screen_ms;
+    stats_sink->anchor_ms += local.anchor_ms;
+    stats_sink->screen_passes += local.screen_passes;
+    stats_sink->queries += local.queries;
+    stats_sink->survivors += local.survivors;
+    stats_sink->verified += local.verified;
+    stats_sink->dense_queries += local.dense_queries;
+  }
+}
+
+// -------------------------------------------------------------------------------------------- save / load
+namespace {
+constexpr uint32_t kFileMagic   = 0x30324243u;  // "CB20"
+constexpr uint32_t kFileVersion = 1;
+
+template <typename T>
+void put(std::ostream& os, const T& v)
+{
+  os.write(reinterpret_cast<const char*>(&v), sizeof(T));
+}
+template <typename T>
+T take(std::istream& is)
+{
+  T v{};
+  is.read(reinterpret_cast<char*>(&v), sizeof(T));
+  CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+  return v;
+}
+}  // namespace
+
+void Index::save(const Resources& res, std::ostream& os) const
+{
+  std::shared_lock<std::shared_mutex> lock(rw_);
+  put(os, kFileMagic);
+  put(os, kFileVersion);
+  put<int32_t>(os, params_.metric);
+  put<int64_t>(os, dim_);
+  put<int32_t>(os, params_.anchor_stride);
+  put<int64_t>(os, size_);
+  put<int64_t>(os, n_removed_);
+  put<int32_t>(os, has_labels_ ? 1 : 0);
+  const size_t row_bytes = static_cast<size_t>(dim_) * dtype_size(dtype_);
+  std::vector<char> host(static_cast<size_t>(size_) * std::max(row_bytes, sizeof(int32_t)));
+  if (size_ > 0) {
+    CERTEX_CUDA(cudaMemcpy2DAsync(host.data(), row_bytes, vectors_, pitch_, row_bytes, static_cast<size_t>(size_), cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+    os.write(host.data(), static_cast<std::streamsize>(static_cast<size_t>(size_) * row_bytes));
+    CERTEX_CUDA(cudaMemcpyAsync(host.data(), removed_, static_cast<size_t>(size_), cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+    os.write(host.data(), static_cast<std::streamsize>(size_));
+    if (has_labels_) {
+      CERTEX_CUDA(cudaMemcpyAsync(host.data(), labels_, static_cast<size_t>(size_) * 4, cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+      os.write(host.data(), static_cast<std::streamsize>(size_ * 4));
+    }
+  }
+  CERTEX_EXPECTS(os.good(), "certex: cannot write the index file");
+}
+
+std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int dtype)
+{
+  CERTEX_EXPECTS(take<uint32_t>(is) == kFileMagic, "certex: not an index file of this library");
+  CERTEX_EXPECTS(take<uint32_t>(is) == kFileVersion, "certex: unknown index file version");
+  IndexParams p;
+  p.metric            = take<int32_t>(is);
+  const int64_t dim   = take<int64_t>(is);
+  p.anchor_stride     = take<int32_t>(is);
+  const int64_t n     = take<int64_t>(is);
+  const int64_t n_rem = take<int64_t>(is);
+  const bool labeled  = take<int32_t>(is) != 0;
+  auto idx            = std::make_unique<Index>(res, p, dtype, dim);
+  if (n > 0) {
+    const size_t row_bytes = static_cast<size_t>(dim) * dtype_size(dtype);
+    std::vector<char> host(static_cast<size_t>(n) * std::max(row_bytes, sizeof(int32_t)));
+    is.read(host.data(), static_cast<std::streamsize>(static_cast<size_t>(n) * row_bytes));
+    CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+    idx->extend(res, host.data(), n, true);
+    is.read(host.data(), static_cast<std::streamsize>(n));
+    CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+    CERTEX_CUDA(cudaMemcpyAsync(idx->removed_, host.data(), static_cast<size_t>(n), cudaMemcpyHostToDevice, res.stream));
+    res.sync();
+    idx->n_removed_ = n_rem;
+    if (idx->int_screen_) {  // removed rows must never pass the screen
+      launch_row_init(idx->vectors_, idx->pitch_, dtype, static_cast<int>(dim), p.metric, idx->removed_, 0, n,
+                      round_up(n, kTile), idx->init_, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+    }
+    if (labeled) {
+      is.read(host.data(), static_cast<std::streamsize>(n * 4));
+      CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+      Scratch scratch(res.stream);
+      int32_t* tmp = scratch.get<int32_t>(static_cast<size_t>(n));
+      CERTEX_CUDA(cudaMemcpyAsync(tmp, host.data(), static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, res.stream));
+      idx->set_labels(res, tmp, n, 0);
+    }
+    res.sync();
+  }
+  return idx;
+}
+
+void merge_shards(const Resources& res, const double* scores, const int64_t* ids, int parts, int nq, int k,
+                  const void* queries, int dtype, int64_t dim, int metric, int64_t* neighbors, float* distances,
+                  double* scores_out)
+{
+  CERTEX_EXPECTS(parts >= 1 && k >= 1 && static_cast<int64_t>(parts) * k <= 8192,
+                 "certex: a merge takes at most 8192 candidates per query");
+  Scratch scratch(res.stream);
+  double* out_s = scores_out ? scores_out : scratch.get<double>(static_cast<size_t>(nq) * k);
+  launch_merge(scores, ids, parts, nq, k, queries, static_cast<size_t>(dim) * dtype_size(dtype), dtype, static_cast<int>(dim),
+               metric, neighbors, distances, out_s, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+}
+
+void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out)
+{
+  CERTEX_EXPECTS(nqt >= 1 && nt >= 1 && panel_tiles >= 1 && grid >= 1, "certex: sizes must be positive");
+  const auto segs = plan_segments(nqt, nt, panel_tiles, grid);
+  std::memcpy(out, segs.data(), segs.size() * sizeof(ScreenSeg));
+}
+
+void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n, int64_t code_len,
+                bool is_signed, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
+                uint32_t* cnt, int32_t* cand, uint32_t cap, float* elapsed_ms)
+{
+  Scratch scratch(res.stream);
+  const int kb            = static_cast<int>(code_len / 128);
+  const ScreenShape shape = shape_for(kb);
+  const int grid          = res.sm_count;
+  const int nqt           = static_cast<int>((nq + kTile - 1) / kTile);
+  const int nt            = static_cast<int>((n + kTile - 1) / kTile);
+  const auto segs         = plan_segments(nqt, nt, shape.panel_tiles, grid);
+  ScreenSeg* d_segs       = scratch.get<ScreenSeg>(segs.size());
+  int* err                = scratch.get<int>(1);
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemsetAsync(err, 0, sizeof(int), res.stream));
+  const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kTile)), code_len);
+  const CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len);
+  ScreenArgs a{};
+  a.init        = init;
+  a.thr         = thr;
+  a.gmax        = gmax;
+  a.ld_gmax     = ld;
+  a.cnt         = cnt;
+  a.cand        = cand;
+  a.cap         = cap;
+  a.nq          = static_cast<int>(nq);
+  a.n_rows      = static_cast<int>(n);
+  a.kb          = kb;
+  a.panel_tiles = shape.panel_tiles;
+  a.n_stages    = shape.n_stages;
+  a.mode        = mode;
+  a.q_signed    = is_signed ? 1u : 0u;
+  a.x_signed    = a.q_signed;
+  a.segs        = d_segs;
+  a.err         = err;
+  cudaEvent_t e0, e1;
+  CERTEX_CUDA(cudaEventCreate(&e0));
+  CERTEX_CUDA(cudaEventCreate(&e1));
+  CERTEX_CUDA(cudaEventRecord(e0, res.stream));
+  const cudaError_t le = screen_i8_launch(tm_q, tm_x, a, grid, res.stream);
+  CERTEX_CUDA(cudaEventRecord(e1, res.stream));
+  int h_err = 0;
+  CERTEX_CUDA(cudaMemcpyAsync(&h_err, err, sizeof(int), cudaMemcpyDeviceToHost, res.stream));
+  const cudaError_t se = cudaStreamSynchronize(res.stream);
+  float ms = 0;
+  if (se == cudaSuccess) { cudaEventElapsedTime(&ms, e0, e1); }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  CERTEX_CUDA(le);
+  CERTEX_CUDA(se);
+  CERTEX_EXPECTS(h_err == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_err) + ")");
+  if (elapsed_ms) { *elapsed_ms = ms; }
+}
+
+}  // namespace certex_b200

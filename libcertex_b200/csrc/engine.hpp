@@ -1,0 +1,171 @@
+// Host side of the engine: the index container and the search pipeline, mirroring the reference's
+// cuvs::neighbors::certex `index<T>`, `build`, `extend`, `remove`, `set_labels` and `search`
+// (cpp/include/cuvs/neighbors/certex.hpp:43-741, cpp/src/neighbors/certex/certex.cu:641-843, 1460-1508).
+// Plain C++ with raw device pointers; the C ABI (c_api.cpp) is a thin layer over it.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <iosfwd>
+#include <memory>
+#include <mutex>
+#include <shared_mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+
+namespace certex_b200 {
+
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+#define CERTEX_EXPECTS(cond, msg)                                \
+  do {                                                           \
+    if (!(cond)) { throw ::certex_b200::Error(std::string(msg)); } \
+  } while (0)
+
+#define CERTEX_CUDA(call)                                                                              \
+  do {                                                                                                 \
+    cudaError_t e_ = (call);                                                                           \
+    if (e_ != cudaSuccess) {                                                                           \
+      throw ::certex_b200::Error(std::string("certex: CUDA error ") + cudaGetErrorString(e_) + " at " + \
+                                 __FILE__ + ":" + std::to_string(__LINE__));                           \
+    }                                                                                                  \
+  } while (0)
+
+/// Stream and device a call runs on (the role of cuvsResources_t / raft::resources).
+struct Resources {
+  int device          = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count        = 0;
+  Resources();
+  void sync() const;
+};
+
+/// cuvs::neighbors::certex::index_params (cpp/include/cuvs/neighbors/certex.hpp:43-87). Every setting returns the same
+/// exact neighbours. width, variance, pca_sample, n_lists, local_projections and int8_rows steer the reference's
+/// projected screening rows; this engine screens 8-bit vectors by their exact integer Gram product and has no
+/// projection, so it accepts and ignores them.
+struct IndexParams {
+  int metric             = kL2;
+  int width              = 0;
+  double variance        = 0.95;
+  int anchor_stride      = 16;
+  int64_t pca_sample     = 1000000;
+  bool host_vectors      = false;
+  int n_lists            = 0;
+  bool local_projections = false;
+  bool int8_rows         = false;
+};
+
+/// cuvs::neighbors::certex::search_params (certex.hpp:97-107).
+struct SearchParams {
+  int anchors     = 128;
+  int batch_size  = 2048;
+  int probe_lists = 2;
+};
+
+/// Counters of the reference's search_stats (cpp/src/neighbors/certex/detail/kernels.hpp:256-263).
+struct SearchStats {
+  unsigned long long queries = 0, survivors = 0, verified = 0, dense_queries = 0;
+  unsigned long long launches = 0;     // kernels of this library launched by the searches
+  double screen_ms = 0, anchor_ms = 0; // device time of the SCREEN and GROUPMAX tensor-core passes (CUDA events)
+  unsigned long long screen_passes = 0;
+};
+
+struct Filter {
+  const uint32_t* words = nullptr;  // device words, bit j of word i is entry 32 i + j, set = keep
+  int64_t bitmap_cols   = 0;        // 0: bitset over the ids; > 0: bitmap [n_queries, bitmap_cols]
+  const int32_t* query_labels = nullptr;  // device [n_queries]: search by label
+};
+
+class Index {
+ public:
+  Index(const Resources& res, const IndexParams& params, int dtype, int64_t dim);
+  ~Index();
+  Index(const Index&)            = delete;
+  Index& operator=(const Index&) = delete;
+
+  /// Appends n rows ([n, dim] dense row-major, device or host memory); they receive the next consecutive ids.
+  void extend(const Resources& res, const void* rows, int64_t n, bool on_host);
+  void remove(const Resources& res, const int64_t* ids_device, int64_t n_ids);
+  void set_labels(const Resources& res, const int32_t* labels_device, int64_t n, int64_t first);
+  void reserve(const Resources& res, int64_t n);
+
+  /**
+   * Exact k nearest neighbours of nq queries (device, dense row-major, the index's element type).
+   * neighbors int64 [nq, k], distances float [nq, k] (device); scores_out (optional, device fp64 [nq, k]) receives the
+   * exact scores the ranking used. id_base is added to every returned id (row shards of a larger set).
+   */
+  void search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k, int64_t* neighbors,
+              float* distances, double* scores_out, const Filter& filter, int64_t id_base = 0) const;
+
+  int64_t size() const { return size_; }
+  int64_t dim() const { return dim_; }
+  int64_t capacity() const { return capacity_; }
+  int64_t n_removed() const { return n_removed_; }
+  int dtype() const { return dtype_; }
+  int metric() const { return params_.metric; }
+  bool has_labels() const { return has_labels_; }
+  bool int_screen() const { return int_screen_; }
+  const IndexParams& params() const { return params_; }
+  size_t pitch() const { return pitch_; }
+  const void* vectors() const { return vectors_; }
+
+  /// Writes / reads the index (parameters, vectors, removed flags, labels) after the 4-byte dtype prefix of a file.
+  void save(const Resources& res, std::ostream& os) const;
+  static std::unique_ptr<Index> load(const Resources& res, std::istream& is, int dtype);
+
+  /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity.
+  void set_test_mode(int mode, int cap) { test_mode_ = mode, test_cap_ = cap; }
+
+  static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
+
+ private:
+  void search_screened(const Resources& res, const uint8_t* qbuf, const void* queries, size_t row_bytes, int q0, int nq,
+                       int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
+                       unsigned long long* stats, int* err, int anchor_stride, int64_t n,
+                       std::vector<cudaEvent_t>* events) const;
+  void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
+                    const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
+
+  IndexParams params_;
+  int dtype_;
+  int64_t dim_;
+  size_t pitch_       = 0;  // bytes per stored row (zero padded: integer types to a multiple of 128, others of 16)
+  int kb_             = 0;  // 128-byte K blocks per row (integer screen)
+  bool int_screen_    = false;
+  int device_         = 0;
+  int64_t size_       = 0;
+  int64_t capacity_   = 0;
+  int64_t n_removed_  = 0;
+  bool has_labels_    = false;
+  void* vectors_      = nullptr;  // [capacity, pitch]
+  uint8_t* removed_   = nullptr;  // [capacity rounded up to 4]
+  int32_t* labels_    = nullptr;  // [capacity], -1 = none
+  int32_t* init_      = nullptr;  // [capacity rounded up to 128] (integer screen)
+  int test_mode_      = 0;
+  int test_cap_       = 0;
+  mutable std::shared_mutex rw_;  // searches hold it shared per call; size/pointer publication holds it exclusive
+  std::mutex writer_;             // serialises extend / remove / set_labels
+};
+
+/// Merge of `parts` per-shard answers [parts, nq, k] (fp64 scores, int64 ids, id -1 = missing) by (score, id), the
+/// order of the reference's sharded merge (cpp/src/neighbors/certex/certex_shards.cu:144-166).
+void merge_shards(const Resources& res, const double* scores, const int64_t* ids, int parts, int nq, int k,
+                  const void* queries, int dtype, int64_t dim, int metric, int64_t* neighbors, float* distances,
+                  double* scores_out);
+
+/// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
+void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);
+
+/// The tensor-core pass alone on caller buffers (see certexB200ScreenRaw in the public header). Synchronises.
+void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n, int64_t code_len,
+                bool is_signed, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
+                uint32_t* cnt, int32_t* cand, uint32_t cap, float* elapsed_ms);
+
+}  // namespace certex_b200

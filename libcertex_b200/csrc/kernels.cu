@@ -1,0 +1,699 @@
+// Plain CUDA kernels of the exact search path: per-row init values of the integer screen, the per-query threshold,
+// exact fp64 verification with top-k selection, the dense (unscreened) path, output conversion and the merge of
+// per-shard answers.
+//
+// The exact score of a pair follows `warp_score` / `exact_score` of the reference
+// (cpp/src/neighbors/certex/detail/certex_kernels.cuh:247-273, cpp/tests/neighbors/ann_certex.cuh:78-99):
+//   L2 sum (q-x)^2, inner product |q|^2 - 2<q,x>, cosine 2 - 2<q,x>/sqrt(max(|q|^2 |x|^2, 1e-300)).
+// Each thread walks one stored row from coordinate 0 to d-1 and rounds every product and every sum on its own
+// (__dmul_rn / __dadd_rn, never a fused multiply-add), which is the order and rounding of the sequential CPU loop: the
+// fp64 scores are bit-identical to it for every element type. Rows are read with 16-byte loads.
+//
+// The order among equal scores is (score, id) everywhere (selection, sort, merge).
+#include "kernels.cuh"
+
+#include "screen_i8.cuh"  // kNeverInit
+
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+namespace certex_b200 {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------- element access
+template <typename T>
+struct Elems;
+template <>
+struct Elems<float> {
+  static constexpr int kPerVec = 4;
+  __device__ static void unpack(const uint4& w, double (&o)[4])
+  {
+    o[0] = double(__uint_as_float(w.x)), o[1] = double(__uint_as_float(w.y));
+    o[2] = double(__uint_as_float(w.z)), o[3] = double(__uint_as_float(w.w));
+  }
+  __device__ static double one(const void* p, int64_t i) { return double(static_cast<const float*>(p)[i]); }
+};
+template <>
+struct Elems<__half> {
+  static constexpr int kPerVec = 8;
+  __device__ static void unpack(const uint4& w, double (&o)[8])
+  {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = *reinterpret_cast<const __half2*>(&u[i]);
+      o[2 * i]        = double(__low2float(h));
+      o[2 * i + 1]    = double(__high2float(h));
+    }
+  }
+  __device__ static double one(const void* p, int64_t i) { return double(__half2float(static_cast<const __half*>(p)[i])); }
+};
+template <>
+struct Elems<int8_t> {
+  static constexpr int kPerVec = 16;
+  __device__ static void unpack(const uint4& w, double (&o)[16])
+  {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i] = double(int(int8_t((u[i >> 2] >> (8 * (i & 3))) & 0xffu))); }
+  }
+  __device__ static double one(const void* p, int64_t i) { return double(static_cast<const int8_t*>(p)[i]); }
+};
+template <>
+struct Elems<uint8_t> {
+  static constexpr int kPerVec = 16;
+  __device__ static void unpack(const uint4& w, double (&o)[16])
+  {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i] = double(int((u[i >> 2] >> (8 * (i & 3))) & 0xffu)); }
+  }
+  __device__ static double one(const void* p, int64_t i) { return double(static_cast<const uint8_t*>(p)[i]); }
+};
+
+__device__ __forceinline__ bool admitted(const Admit& a, int64_t q, int64_t row)
+{
+  if (a.removed && a.removed[row]) { return false; }
+  if (a.bits) {
+    const int64_t bit = a.bitmap_cols > 0 ? q * a.bitmap_cols + row : row;
+    if (((a.bits[bit >> 5] >> (bit & 31)) & 1u) == 0u) { return false; }
+  }
+  if (a.row_labels) {
+    const int32_t l = a.row_labels[row];
+    if (l < 0 || l != a.query_labels[q]) { return false; }
+  }
+  return true;
+}
+
+// Accumulators of NQ queries against one stored row, coordinates in order.
+template <int METRIC, int NQ>
+struct Acc {
+  double s[NQ];  // L2: sum of squared differences; otherwise: inner product
+  double xx;
+  __device__ void clear()
+  {
+#pragma unroll
+    for (int b = 0; b < NQ; ++b) { s[b] = 0; }
+    xx = 0;
+  }
+  // qd: queries as doubles in shared memory, query b at qd + b * ldq
+  __device__ __forceinline__ void add(double x, const double* qd, int ldq, int t)
+  {
+#pragma unroll
+    for (int b = 0; b < NQ; ++b) {
+      const double a = qd[b * ldq + t];
+      if constexpr (METRIC == kL2) {
+        const double diff = __dsub_rn(a, x);
+        s[b]              = __dadd_rn(s[b], __dmul_rn(diff, diff));
+      } else {
+        s[b] = __dadd_rn(s[b], __dmul_rn(a, x));
+      }
+    }
+    if constexpr (METRIC == kCos) { xx = __dadd_rn(xx, __dmul_rn(x, x)); }
+  }
+  __device__ __forceinline__ double result(int b, double qq) const
+  {
+    if constexpr (METRIC == kL2) {
+      return s[b];
+    } else if constexpr (METRIC == kIP) {
+      return __dsub_rn(qq, __dmul_rn(2.0, s[b]));
+    } else {
+      const double den = fmax(__dmul_rn(qq, xx), 1e-300);
+      return __dsub_rn(2.0, __ddiv_rn(__dmul_rn(2.0, s[b]), __dsqrt_rn(den)));
+    }
+  }
+};
+
+// Walks one stored row (16-byte loads) and feeds every coordinate to `acc`.
+template <typename T, int METRIC, int NQ>
+__device__ __forceinline__ void scan_row(const uint8_t* row, int d, const double* qd, int ldq, Acc<METRIC, NQ>& acc)
+{
+  constexpr int V   = Elems<T>::kPerVec;
+  const uint4* p    = reinterpret_cast<const uint4*>(row);
+  const int n_full  = d / V;
+  for (int c = 0; c < n_full; ++c) {
+    const uint4 w = __ldg(p + c);
+    double x[V];
+    Elems<T>::unpack(w, x);
+#pragma unroll
+    for (int e = 0; e < V; ++e) { acc.add(x[e], qd, ldq, c * V + e); }
+  }
+  for (int t = n_full * V; t < d; ++t) { acc.add(Elems<T>::one(row, t), qd, ldq, t); }
+}
+
+// Queries as doubles into shared memory and |q|^2 summed in coordinate order by one thread per query.
+template <typename T>
+__device__ void load_queries(const void* queries, size_t qpitch, const int64_t* qidx, int nqb, int d, double* qd, int ldq, double* qq)
+{
+  for (int b = 0; b < nqb; ++b) {
+    const uint8_t* src = static_cast<const uint8_t*>(queries) + static_cast<size_t>(qidx[b]) * qpitch;
+    for (int t = threadIdx.x; t < d; t += blockDim.x) { qd[b * ldq + t] = Elems<T>::one(src, t); }
+  }
+  __syncthreads();
+  if (threadIdx.x < nqb) {
+    double a = 0;
+    for (int t = 0; t < d; ++t) {
+      const double v = qd[threadIdx.x * ldq + t];
+      a              = __dadd_rn(a, __dmul_rn(v, v));
+    }
+    qq[threadIdx.x] = a;
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------- sorting helpers
+__device__ __forceinline__ bool pair_less(double sa, int64_t ia, double sb, int64_t ib)
+{
+  return sa < sb || (sa == sb && ia < ib);
+}
+
+// In-place bitonic sort of n2 (a power of two) (score, id) pairs in shared memory, ascending by (score, id).
+template <typename IdT>
+__device__ void bitonic_sort(double* s, IdT* id, int n2)
+{
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < (n2 >> 1); i += blockDim.x) {
+        const int lo   = 2 * i - (i & (stride - 1));
+        const int hi   = lo + stride;
+        const bool asc = (lo & size) == 0;
+        const double a = s[lo], b = s[hi];
+        const IdT ia = id[lo], ib = id[hi];
+        const bool swap = asc ? pair_less(b, ib, a, ia) : pair_less(a, ia, b, ib);
+        if (swap) {
+          s[lo] = b, s[hi] = a;
+          id[lo] = ib, id[hi] = ia;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ unsigned long long ordered_key(double v)
+{
+  const unsigned long long b = static_cast<unsigned long long>(__double_as_longlong(v));
+  return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
+}
+
+__host__ __device__ inline int next_pow2(int v)
+{
+  int p = 1;
+  while (p < v) { p <<= 1; }
+  return p;
+}
+
+// ------------------------------------------------------------------------------------------- build-side kernels
+// Eight lanes per row, 16 bytes per lane and step.
+template <typename T>
+__global__ void row_init_kernel(const uint8_t* vectors, size_t pitch, int d, int metric, const uint8_t* removed,
+                                int64_t row0, int64_t n, int64_t n_pad, int32_t* init)
+{
+  const int64_t gt  = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t r   = row0 + (gt >> 3);
+  const int sub     = threadIdx.x & 7;
+  const bool in     = r < row0 + n;
+  long long sum     = 0;
+  if (in && metric == kL2) {
+    const uint4* p  = reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(r) * pitch);
+    const int n_vec = (d + 15) / 16;  // rows are zero padded to the pitch
+    for (int c = sub; c < n_vec; c += 8) {
+      const uint4 w       = __ldg(p + c);
+      const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t byte = (u[i >> 2] >> (8 * (i & 3))) & 0xffu;
+        const int v         = sizeof(T) == 1 && T(-1) < T(0) ? int(int8_t(byte)) : int(byte);
+        sum += v * v;
+      }
+    }
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+  if (sub == 0 && r < n_pad) {
+    int32_t v = kNeverInit;
+    if (in && !(removed && removed[r])) { v = metric == kL2 ? -static_cast<int32_t>(sum >> 1) : 0; }
+    init[r] = v;
+  }
+}
+
+__global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j < n_pad) { out[j] = j < n_anchor ? init[j * stride] : kNeverInit; }
+}
+
+__global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
+                              unsigned long long* n_new)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_ids) { return; }
+  const int64_t id = ids[i];
+  if (id < 0 || id >= size) { return; }
+  // byte-wide exchange through the containing 32-bit word
+  uint32_t* word       = reinterpret_cast<uint32_t*>(removed + (id & ~int64_t(3)));
+  const uint32_t bit   = 1u << (8 * (id & 3));
+  const uint32_t prev  = atomicOr(word, bit);
+  if ((prev & bit) == 0u) { atomicAdd(n_new, 1ull); }
+  if (init) { init[id] = kNeverInit; }
+}
+
+// Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk.
+__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr)
+{
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t s_prefix, s_remaining;
+  const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
+  if (ng < k) {
+    if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(0x80000000u); }
+    return;
+  }
+  uint32_t prefix = 0, mask = 0, remaining = static_cast<uint32_t>(k);
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) { hist[i] = 0; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < ng; i += blockDim.x) {
+      const uint32_t key = static_cast<uint32_t>(row[i]) ^ 0x80000000u;
+      if ((key & mask) == prefix) { atomicAdd(&hist[(key >> shift) & 255u], 1u); }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t cum = 0;
+      int b        = 255;
+      for (; b > 0; --b) {
+        if (cum + hist[b] >= remaining) { break; }
+        cum += hist[b];
+      }
+      s_prefix    = prefix | (static_cast<uint32_t>(b) << shift);
+      s_remaining = remaining - cum;
+    }
+    __syncthreads();
+    prefix    = s_prefix;
+    remaining = s_remaining;
+    mask |= 0xffu << shift;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(prefix ^ 0x80000000u); }
+}
+
+// ------------------------------------------------------------------------------------------- verify + select
+// Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap).
+template <typename T, int METRIC>
+__global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
+                                     int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
+                                     Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
+                                     unsigned int* ovf_count, unsigned long long* stats)
+{
+  extern __shared__ double sh[];
+  __shared__ double s_qq;
+  const int q       = q0 + blockIdx.x;  // number of the query in the call; cand / cnt are those of its batch
+  const uint32_t c  = cnt[blockIdx.x];
+  if (c > cap) {
+    if (threadIdx.x == 0) { ovf_list[atomicAdd(ovf_count, 1u)] = q; }
+    return;
+  }
+  double* qd   = sh;
+  double* sc   = sh + d;
+  int32_t* ids = reinterpret_cast<int32_t*>(sc + n2max);
+  const int64_t qi = q;
+  load_queries<T>(queries, qpitch, &qi, 1, d, qd, d, &s_qq);
+  const int n2 = max(next_pow2(static_cast<int>(c)), 2);
+  const int32_t* mine = cand + static_cast<size_t>(blockIdx.x) * cap;
+  for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+    double s    = CUDART_INF;
+    int32_t row = 0x7fffffff;
+    if (i < static_cast<int>(c)) {
+      row = mine[i];
+      if (admitted(adm, q, row)) {
+        Acc<METRIC, 1> acc;
+        acc.clear();
+        scan_row<T, METRIC, 1>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);
+        s = acc.result(0, s_qq);
+      }
+    }
+    sc[i]  = s;
+    ids[i] = row;
+  }
+  bitonic_sort(sc, ids, n2);
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    const bool have                         = t < n2 && sc[t] < CUDART_INF;
+    best_s[static_cast<size_t>(q) * k + t]   = have ? sc[t] : CUDART_INF;
+    best_row[static_cast<size_t>(q) * k + t] = have ? ids[t] : -1;
+  }
+  if (threadIdx.x == 0 && stats) {
+    atomicAdd(stats + 0, static_cast<unsigned long long>(c));  // survivors of the screen
+    atomicAdd(stats + 1, static_cast<unsigned long long>(c));  // exact scores computed
+  }
+}
+
+// ------------------------------------------------------------------------------------------- dense path
+constexpr int kDenseQ = 4;  // queries per block that share one walk over a stored row
+
+template <typename T, int METRIC>
+__global__ void dense_scores_kernel(const uint8_t* vectors, size_t pitch, int d, int64_t n, const void* queries,
+                                    size_t qpitch, const int32_t* qsel, int q0, int nqb, Admit adm, double* out, int64_t ld)
+{
+  extern __shared__ double sh[];
+  __shared__ double s_qq[kDenseQ];
+  __shared__ int64_t s_qidx[kDenseQ];
+  const int b0 = blockIdx.y * kDenseQ;
+  const int nb = min(kDenseQ, nqb - b0);
+  if (threadIdx.x < kDenseQ) {
+    const int b = min(static_cast<int>(threadIdx.x), nb - 1);
+    s_qidx[threadIdx.x] = qsel ? qsel[b0 + b] : q0 + b0 + b;
+  }
+  __syncthreads();
+  load_queries<T>(queries, qpitch, s_qidx, kDenseQ, d, sh, d, s_qq);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= n) { return; }
+  Acc<METRIC, kDenseQ> acc;
+  acc.clear();
+  scan_row<T, METRIC, kDenseQ>(vectors + static_cast<size_t>(row) * pitch, d, sh, d, acc);
+#pragma unroll
+  for (int b = 0; b < kDenseQ; ++b) {
+    if (b < nb) {
+      const bool ok = admitted(adm, s_qidx[b], row);
+      out[static_cast<int64_t>(b0 + b) * ld + row] = ok ? acc.result(b, s_qq[b]) : CUDART_INF;
+    }
+  }
+}
+
+// Block per query: radix walk to the k-th smallest score, then the winners (ties: smallest rows) are gathered, sorted
+// and written. Shared memory: sel_s [k2] doubles | sel_id [k2] int32.
+__global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0,
+                                   double* best_s, int32_t* best_row)
+{
+  extern __shared__ double sh[];
+  __shared__ uint32_t hist[256];
+  __shared__ unsigned long long s_prefix;
+  __shared__ uint32_t s_remaining, s_less, s_eq_base;
+  const int k2        = max(next_pow2(k), 2);
+  double* sel_s       = sh;
+  int32_t* sel_id     = reinterpret_cast<int32_t*>(sh + k2);
+  const double* row   = scores + static_cast<int64_t>(blockIdx.x) * ld;
+  const int64_t qout  = qsel ? qsel[blockIdx.x] : q0 + static_cast<int>(blockIdx.x);
+  const uint32_t want = static_cast<uint32_t>(min(static_cast<int64_t>(k), n));
+
+  for (int i = threadIdx.x; i < k2; i += blockDim.x) {
+    sel_s[i]  = CUDART_INF;
+    sel_id[i] = 0x7fffffff;
+  }
+  unsigned long long prefix = 0, mask = 0;
+  uint32_t remaining = want;
+  if (want > 0) {
+    for (int shift = 56; shift >= 0; shift -= 8) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) { hist[i] = 0; }
+      __syncthreads();
+      for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const unsigned long long key = ordered_key(row[i]);
+        if ((key & mask) == prefix) { atomicAdd(&hist[(key >> shift) & 255ull], 1u); }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t cum = 0;
+        int b        = 0;
+        for (; b < 255; ++b) {
+          if (cum + hist[b] >= remaining) { break; }
+          cum += hist[b];
+        }
+        s_prefix    = prefix | (static_cast<unsigned long long>(b) << shift);
+        s_remaining = remaining - cum;
+      }
+      __syncthreads();
+      prefix    = s_prefix;
+      remaining = s_remaining;
+      mask |= 0xffull << shift;
+      __syncthreads();
+    }
+    // `prefix` is the key of the k-th smallest score; `remaining` of the rows that tie with it are wanted (smallest
+    // rows first), all rows below it are wanted.
+    const uint32_t n_less = want - remaining;
+    if (threadIdx.x == 0) {
+      s_less    = 0;
+      s_eq_base = 0;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __shared__ uint32_t warp_cnt[32];
+    for (int64_t c0 = 0; c0 < n; c0 += blockDim.x) {
+      const int64_t j = c0 + threadIdx.x;
+      double v        = 0;
+      bool eq         = false;
+      if (j < n) {
+        v                            = row[j];
+        const unsigned long long key = ordered_key(v);
+        if (key < prefix) {
+          const uint32_t pos = atomicAdd(&s_less, 1u);
+          sel_s[pos]         = v;
+          sel_id[pos]        = static_cast<int32_t>(j);
+        }
+        eq = key == prefix;
+      }
+      const int any = __syncthreads_count(eq);
+      if (any) {
+        const uint32_t ball = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) { warp_cnt[wid] = __popc(ball); }
+        __syncthreads();
+        uint32_t before = s_eq_base;
+        for (int w = 0; w < wid; ++w) { before += warp_cnt[w]; }
+        const uint32_t rank = before + __popc(ball & ((1u << lane) - 1u));
+        if (eq && rank < remaining) {
+          sel_s[n_less + rank]  = v;
+          sel_id[n_less + rank] = static_cast<int32_t>(j);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          uint32_t tot = 0;
+          for (int w = 0; w < nw; ++w) { tot += warp_cnt[w]; }
+          s_eq_base += tot;
+        }
+        __syncthreads();
+      }
+    }
+  }
+  __syncthreads();
+  bitonic_sort(sel_s, sel_id, k2);
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    const bool have                            = sel_s[t] < CUDART_INF;
+    best_s[static_cast<size_t>(qout) * k + t]   = have ? sel_s[t] : CUDART_INF;
+    best_row[static_cast<size_t>(qout) * k + t] = have ? sel_id[t] : -1;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- output
+// Block per query. Distances as `finish` of the reference returns them (cpp/src/neighbors/certex/certex.cu:224-250).
+template <typename T>
+__global__ void finish_kernel(const double* best_s, const int32_t* best_row, const int64_t* best_id, int64_t id_base,
+                              const void* queries, size_t qpitch, int d, int metric, int k, int64_t* neighbors,
+                              float* distances, double* scores_out)
+{
+  __shared__ double s_qq;
+  const int q = blockIdx.x;
+  if (metric == kIP) {
+    if (threadIdx.x == 0) {
+      const uint8_t* src = static_cast<const uint8_t*>(queries) + static_cast<size_t>(q) * qpitch;
+      double a           = 0;
+      for (int t = 0; t < d; ++t) {
+        const double v = Elems<T>::one(src, t);
+        a              = __dadd_rn(a, __dmul_rn(v, v));
+      }
+      s_qq = a;
+    }
+    __syncthreads();
+  }
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    const size_t o   = static_cast<size_t>(q) * k + t;
+    const double s   = best_s[o];
+    int64_t id       = -1;
+    if (best_row) {
+      if (best_row[o] >= 0) { id = id_base + best_row[o]; }
+    } else {
+      id = best_id[o];
+    }
+    float dist;
+    if (id < 0) {
+      dist = metric == kIP ? -CUDART_INF_F : CUDART_INF_F;
+    } else if (metric == kL2) {
+      dist = static_cast<float>(s);
+    } else if (metric == kIP) {
+      dist = static_cast<float>((s_qq - s) / 2);
+    } else {
+      dist = static_cast<float>(s / 2);
+    }
+    neighbors[o] = id;
+    distances[o] = dist;
+    if (scores_out) { scores_out[o] = id < 0 ? CUDART_INF : s; }
+  }
+}
+
+// Block per query; shared memory: s [n2] doubles | id [n2] int64.
+__global__ void merge_kernel(const double* in_s, const int64_t* in_id, int parts, int nq, int k, int n2, double* out_s,
+                             int64_t* out_id)
+{
+  extern __shared__ double sh[];
+  double* s   = sh;
+  int64_t* id = reinterpret_cast<int64_t*>(sh + n2);
+  const int q = blockIdx.x;
+  const int m = parts * k;
+  for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+    double v   = CUDART_INF;
+    int64_t ii = 0x7fffffffffffffffll;
+    if (i < m) {
+      const size_t o = (static_cast<size_t>(i / k) * nq + q) * k + (i % k);
+      if (in_id[o] >= 0) {
+        v  = in_s[o];
+        ii = in_id[o];
+      }
+    }
+    s[i]  = v;
+    id[i] = ii;
+  }
+  bitonic_sort(s, id, n2);
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    const bool have                      = id[t] != 0x7fffffffffffffffll;
+    out_s[static_cast<size_t>(q) * k + t]  = have ? s[t] : CUDART_INF;
+    out_id[static_cast<size_t>(q) * k + t] = have ? id[t] : -1;
+  }
+}
+
+template <typename F>
+void by_dtype(int dtype, F&& f)
+{
+  switch (dtype) {
+    case kF32: f(float{}); break;
+    case kF16: f(__half{}); break;
+    case kI8: f(int8_t{}); break;
+    default: f(uint8_t{}); break;
+  }
+}
+
+template <typename Kernel>
+void allow_smem(Kernel kernel, size_t bytes)
+{
+  if (bytes > 48 * 1024) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)); }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------- launchers
+void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int metric, const uint8_t* removed,
+                     int64_t row0, int64_t n, int64_t n_pad, int32_t* init, cudaStream_t s)
+{
+  const int64_t rows = n_pad - row0;
+  if (rows <= 0) { return; }
+  const int64_t threads = rows * 8;
+  const int block       = 256;
+  const auto grid       = static_cast<unsigned>((threads + block - 1) / block);
+  if (dtype == kI8) {
+    row_init_kernel<int8_t><<<grid, block, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, metric, removed, row0, n, n_pad, init);
+  } else {
+    row_init_kernel<uint8_t><<<grid, block, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, metric, removed, row0, n, n_pad, init);
+  }
+}
+
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out, cudaStream_t s)
+{
+  if (n_pad <= 0) { return; }
+  gather_init_kernel<<<static_cast<unsigned>((n_pad + 255) / 256), 256, 0, s>>>(init, stride, n_anchor, n_pad, out);
+}
+
+void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  kth_largest_kernel<<<nq, 256, 0, s>>>(gmax, ld, ng, k, thr);
+}
+
+void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
+                   unsigned long long* n_new, cudaStream_t s)
+{
+  if (n_ids <= 0) { return; }
+  remove_kernel<<<static_cast<unsigned>((n_ids + 255) / 256), 256, 0, s>>>(ids, n_ids, size, removed, init, n_new);
+}
+
+void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
+                          size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
+                          Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
+                          unsigned long long* stats, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  const int n2max   = next_pow2(static_cast<int>(cap));
+  const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) + sizeof(int32_t) * n2max;
+  by_dtype(dtype, [&](auto tag) {
+    using T   = decltype(tag);
+    auto go   = [&](auto kernel) {
+      allow_smem(kernel, smem);
+      kernel<<<nq, 128, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
+                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats);
+    };
+    if (metric == kL2) {
+      go(verify_select_kernel<T, kL2>);
+    } else if (metric == kIP) {
+      go(verify_select_kernel<T, kIP>);
+    } else {
+      go(verify_select_kernel<T, kCos>);
+    }
+  });
+}
+
+void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, const void* queries,
+                         size_t qpitch, const int32_t* qsel, int q0, int nqb, Admit adm, double* out, int64_t ld,
+                         cudaStream_t s)
+{
+  if (nqb <= 0 || n <= 0) { return; }
+  const size_t smem = sizeof(double) * static_cast<size_t>(d) * kDenseQ;
+  const dim3 grid(static_cast<unsigned>((n + 255) / 256), static_cast<unsigned>((nqb + kDenseQ - 1) / kDenseQ));
+  by_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    auto go = [&](auto kernel) {
+      allow_smem(kernel, smem);
+      kernel<<<grid, 256, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, n, queries, qpitch, qsel, q0, nqb, adm, out, ld);
+    };
+    if (metric == kL2) {
+      go(dense_scores_kernel<T, kL2>);
+    } else if (metric == kIP) {
+      go(dense_scores_kernel<T, kIP>);
+    } else {
+      go(dense_scores_kernel<T, kCos>);
+    }
+  });
+}
+
+void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0, int nqb,
+                        double* best_s, int32_t* best_row, cudaStream_t s)
+{
+  if (nqb <= 0) { return; }
+  const int k2      = next_pow2(k) < 2 ? 2 : next_pow2(k);
+  const size_t smem = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(k2);
+  select_topk_kernel<<<nqb, 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row);
+}
+
+void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_base, const void* queries, size_t qpitch,
+                   int dtype, int d, int metric, int nq, int k, int64_t* neighbors, float* distances, double* scores_out,
+                   cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  by_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    finish_kernel<T><<<nq, 64, 0, s>>>(best_s, best_row, nullptr, id_base, queries, qpitch, d, metric, k, neighbors, distances, scores_out);
+  });
+}
+
+void launch_merge(const double* in_s, const int64_t* in_id, int parts, int nq, int k, const void* queries, size_t qpitch,
+                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  // merged (score, id) go to scores_out / neighbors first; finish_kernel then converts in place
+  const int n2      = next_pow2(parts * k) < 2 ? 2 : next_pow2(parts * k);
+  const size_t smem = (sizeof(double) + sizeof(int64_t)) * static_cast<size_t>(n2);
+  allow_smem(merge_kernel, smem);
+  merge_kernel<<<nq, 256, smem, s>>>(in_s, in_id, parts, nq, k, n2, scores_out, neighbors);
+  by_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    finish_kernel<T><<<nq, 64, 0, s>>>(scores_out, nullptr, neighbors, 0, queries, qpitch, d, metric, k, neighbors, distances, scores_out);
+  });
+}
+
+}  // namespace certex_b200

@@ -1,0 +1,69 @@
+// Launch wrappers of the plain (SIMT) kernels of the search path; definitions in kernels.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace certex_b200 {
+
+enum DType : int { kF32 = 0, kF16 = 1, kI8 = 2, kU8 = 3 };
+enum Metric : int { kL2 = 0, kIP = 1, kCos = 2 };
+
+inline int dtype_size(int dt) { return dt == kF32 ? 4 : dt == kF16 ? 2 : 1; }
+
+/// Which stored rows a query may return. Everything is optional (null = absent); a set bit keeps.
+struct Admit {
+  const uint8_t* removed;       // [n] non-zero = removed
+  const uint32_t* bits;         // bitset (one bit per row) or bitmap (one row of bits per query) words
+  int64_t bitmap_cols;          // 0: `bits` is a bitset; > 0: bitmap with this many bits per query row
+  const int32_t* row_labels;    // [n]; used together with query_labels
+  const int32_t* query_labels;  // [nq]
+};
+
+/// init[r] for rows [row0, row0 + n): -floor(|x|^2 / 2) (L2) or 0 (inner product); removed rows and the padding up
+/// to `n_pad` get kNeverInit. Integer dtypes only.
+void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int metric, const uint8_t* removed,
+                     int64_t row0, int64_t n, int64_t n_pad, int32_t* init, cudaStream_t s);
+
+/// out[j] = init[j * stride] for j < n_anchor, kNeverInit up to n_pad.
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out, cudaStream_t s);
+
+/// thr[q] = k-th largest of gmax[q, 0:ng]  (INT_MIN when ng < k).
+void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s);
+
+/// Marks ids as removed: removed[id] = 1, init[id] = kNeverInit (if init != null); *n_new counts first-time removals.
+void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
+                   unsigned long long* n_new, cudaStream_t s);
+
+/**
+ * Exact fp64 scores of every query's candidate rows, then its k best by (score, row). One block per query.
+ * cand [nq, cap] rows, cnt [nq] how many (a query with cnt > cap is skipped and its index appended to ovf_list).
+ * best_s / best_row [nq, k] (row -1, score +inf where fewer than k admitted candidates exist).
+ */
+void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
+                          size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
+                          Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
+                          unsigned long long* stats, cudaStream_t s);
+
+/// All-pairs exact fp64 scores of queries qsel[0:nqb] (or q0.. when qsel is null) against rows [0, n): out [nqb, ld].
+/// Rows that `adm` rejects score +inf.
+void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, const void* queries,
+                         size_t qpitch, const int32_t* qsel, int q0, int nqb, Admit adm, double* out, int64_t ld,
+                         cudaStream_t s);
+
+/// k best (score, row) of every row of scores [nqb, ld] (n valid columns); writes result row qsel[i] (or q0 + i).
+void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0, int nqb,
+                        double* best_s, int32_t* best_row, cudaStream_t s);
+
+/// neighbors / distances / (optional) fp64 scores of the public result from the internal best lists.
+/// id = row < 0 ? -1 : id_base + row. Distances: L2 s, inner product (|q|^2 - s) / 2, cosine s / 2.
+void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_base, const void* queries, size_t qpitch,
+                   int dtype, int d, int metric, int nq, int k, int64_t* neighbors, float* distances, double* scores_out,
+                   cudaStream_t s);
+
+/// Merge of `parts` answer lists per query, [parts, nq, k] (score, id) with id -1 = missing, by (score, id);
+/// writes merged ids, fp64 scores and float distances.
+void launch_merge(const double* in_s, const int64_t* in_id, int parts, int nq, int k, const void* queries, size_t qpitch,
+                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s);
+
+}  // namespace certex_b200

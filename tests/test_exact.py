@@ -1,0 +1,162 @@
+"""End-to-end parity on the GPU, through the C ABI: neighbour ids and fp64 scores must equal the CPU oracle's bit for
+bit (integer and float inputs alike: the kernels round every product and sum as the sequential CPU loop does), ties
+to the smaller id. The cases follow the reference's parameter table (cpp/tests/neighbors/ann_certex.cuh:277-319) and
+its Python suite (tests/test_exact.py): three metrics, four element types, k in {1, 10, 100, 1024, 2048}, build +
+extend shares, unequal norms, duplicates, tiny sets, many queries."""
+
+import numpy as np
+import pytest
+import torch
+
+import libcertex_b200 as certex
+from libcertex_b200 import synthetic
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # n, dim, nq, k, metric, dtype, build_share, unequal_norms, duplicates
+    (30000, 96, 200, 10, "l2", "uint8", 1.0, False, 0),
+    (30000, 96, 200, 10, "l2", "int8", 0.33, False, 0),
+    (30000, 96, 200, 10, "ip", "int8", 1.0, True, 0),
+    (30000, 96, 200, 10, "ip", "uint8", 0.5, True, 0),
+    (30000, 96, 100, 100, "l2", "uint8", 1.0, False, 0),
+    (30000, 96, 50, 1024, "l2", "uint8", 1.0, False, 0),
+    (20000, 128, 200, 10, "l2", "uint8", 1.0, False, 500),
+    (20000, 128, 200, 10, "l2", "int8", 1.0, False, 500),
+    (25, 32, 50, 10, "l2", "uint8", 1.0, False, 0),
+    (5000, 32, 3001, 10, "l2", "uint8", 1.0, False, 0),
+    (60000, 200, 300, 10, "l2", "uint8", 1.0, False, 0),
+    (40000, 500, 150, 5, "l2", "int8", 1.0, False, 0),
+    (8000, 600, 40, 10, "l2", "uint8", 1.0, False, 0),
+    (30000, 96, 200, 10, "l2", "float32", 1.0, False, 0),
+    (30000, 96, 200, 10, "l2", "float32", 0.33, False, 0),
+    (30000, 96, 200, 10, "ip", "float32", 1.0, True, 0),
+    (30000, 96, 200, 10, "cosine", "float32", 0.5, True, 0),
+    (30000, 96, 100, 100, "l2", "float16", 1.0, False, 0),
+    (30000, 96, 20, 1024, "l2", "float32", 1.0, False, 0),
+    (20000, 128, 100, 10, "l2", "float32", 1.0, False, 500),
+    (20000, 128, 100, 10, "cosine", "float16", 1.0, True, 0),
+    (25, 32, 50, 10, "l2", "float32", 1.0, False, 0),
+    (3000, 33, 40, 2048, "ip", "float32", 1.0, True, 0),
+]
+
+
+def make(n, dim, nq, dtype, unequal, dups, seed=42):
+    x = synthetic.correlated(n, dim, seed=seed, dtype=dtype, unequal_norms=unequal)
+    q = synthetic.correlated(nq, dim, seed=seed + 1, dtype=dtype)
+    for c in range(1, min(dups, n - 1) + 1):
+        x[c] = x[0]
+    return x, q
+
+
+def check(index, x, q, k, metric, **kw):
+    D, I, S = index.search(torch.from_numpy(q).cuda(), k=k, return_scores=True, **kw)
+    ids, scores = oracle.knn(x, q, k, metric)
+    I, S, D = I.cpu().numpy(), S.cpu().numpy(), D.cpu().numpy().astype(np.float64)
+    assert np.array_equal(I, ids), f"{(I != ids).any(1).sum()} of {len(ids)} queries differ"
+    assert np.array_equal(S, scores)
+    # returned values follow the reference's conventions: squared distance, inner product, cosine similarity
+    xs, qs = x.astype(np.float64), q.astype(np.float64)
+    if metric == "l2":
+        want = scores
+    elif metric == "ip":
+        want = np.einsum("qd,qkd->qk", qs, xs[ids])
+    else:
+        want = 1 - scores / 2
+    assert np.allclose(D, want, rtol=1e-4, atol=1e-4 * (1 + np.abs(want).max()))
+
+
+@pytest.mark.parametrize("n,dim,nq,k,metric,dtype,share,unequal,dups", CASES)
+def test_exact_against_oracle(n, dim, nq, k, metric, dtype, share, unequal, dups):
+    x, q = make(n, dim, nq, dtype, unequal, dups)
+    n0 = max(1, int(share * n))
+    index = certex.Index(dim, metric=metric)
+    ids0 = index.add(torch.from_numpy(x[:n0]).cuda())
+    assert ids0[0] == 0 and ids0[-1] == n0 - 1
+    if n0 < n:
+        index.add(x[n0:])  # a host array: streamed in by the library
+    assert index.ntotal == n
+    check(index, x, q, k, metric)
+
+
+def test_screen_runs_on_integer_indexes_and_dense_elsewhere():
+    x, q = make(50000, 128, 100, "uint8", False, 0)
+    index = certex.Index(128)
+    index.add(x)
+    with certex.search_stats() as st:
+        index.search(q, k=10)
+    assert st.queries == 100 and st.dense_queries == 0 and 1000 <= st.survivors < 100 * 50000 // 10
+    xf, qf = make(5000, 64, 10, "float32", False, 0)
+    fidx = certex.Index(64)
+    fidx.add(xf)
+    with certex.search_stats() as st:
+        fidx.search(qf, k=10)
+    assert st.dense_queries == 10
+
+
+@pytest.mark.parametrize("batch", [1, 100, 128, 1000, 2048, 100000])
+def test_batch_sizes(batch):
+    x, q = make(40000, 64, 700, "uint8", False, 0)
+    index = certex.Index(64)
+    index.add(x)
+    check(index, x, q, 10, "l2", batch=batch)
+
+
+def test_overflowing_candidate_lists_fall_back_to_the_dense_path():
+    x, q = make(40000, 64, 300, "uint8", False, 0)
+    index = certex.Index(64)
+    index.add(x)
+    index._test_mode(2, cap=16)  # candidate lists of 16 entries: most queries overflow
+    with certex.search_stats() as st:
+        check(index, x, q, 10, "l2")
+    assert 0 < st.dense_queries <= 300
+    index._test_mode(1)  # dense path only
+    check(index, x, q, 10, "l2")
+
+
+def test_mixture_sample():
+    """The benchmark's data distribution at a size the oracle finishes quickly."""
+    xb = synthetic.mixture_u8(1_000_000, seed=0)
+    xq = synthetic.mixture_u8(256, seed=1)
+    index = certex.Index(128)
+    index.add(xb)
+    check(index, xb.cpu().numpy(), xq.cpu().numpy(), 10, "l2", batch=10240)
+
+
+def test_one_call_search_numpy_roundtrip_and_single_vector():
+    x, q = make(20000, 32, 200, "uint8", False, 0)
+    D, I = certex.search(x, q.astype(np.float32), k=5)
+    assert isinstance(D, np.ndarray) and I.dtype == np.int64
+    ids, _ = oracle.knn(x, q, 5, "l2")
+    assert np.array_equal(I, ids)
+    index = certex.Index(32)
+    index.add(x)
+    D1, I1 = index.search(q[3], k=5)
+    assert I1.shape == (5,) and np.array_equal(I1, ids[3])
+    with pytest.raises(ValueError):
+        index.search(q.astype(np.float32) + 0.5, k=5)  # an integer index takes integral queries only
+    with pytest.raises(ValueError):
+        index.search(q, k=0)
+    with pytest.raises(ValueError):
+        index.search(q, k=20001)
+
+
+def test_golden_fixtures_on_gpu():
+    """The committed known answers (pinned to the reference's own checkers) through the GPU path."""
+    import os
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "golden"))
+    import make_golden
+
+    g = np.load(os.path.join(here, "golden", "golden.npz"))
+    for case in make_golden.CASES:
+        name, n, dim, nq, k, dtype, metric = case[:7]
+        x, q = make_golden.make_case(*case)
+        assert make_golden.digest(x, q) == str(g[f"{name}/data_sha256"])
+        index = certex.Index(dim, metric=metric)
+        index.add(x)
+        _, I, S = index.search(q, k=k, return_scores=True)
+        assert np.array_equal(I, g[f"{name}/ids"]) and np.array_equal(S, g[f"{name}/scores"]), name
