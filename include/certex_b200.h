@@ -251,10 +251,12 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t inde
 /**
  * The tensor-core pass alone on caller buffers (device pointers), the seam of the reference's
  * detail/kernels.hpp:290-304 (`screen_int8`) and :125-135 (`anchor_groups`), for kernel-level tests and timing.
- * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len a multiple of
- * 128 up to 512, nq_pad = nq rounded up to 128 with zero rows; init [n rounded up to 128].
+ * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len 128 or 256,
+ * nq_pad = nq rounded up to 128 with zero rows; init [n rounded up to 64] in row order (the per-row term added to the
+ * product: -floor(|x|^2 / 2) for L2, -2^30 for rows that must never pass).
  * mode 0 (screen): keep iff init[x] + <q, x> >= thr[q]; cnt [nq] must be zeroed by the caller; cand [nq, cap].
- * mode 1 (group maxima): gmax [nq, ld] receives the maximum over every 128 rows of x.
+ * mode 1 (group maxima): gmax [nq, ld] receives the maximum over every 64 rows of x, 4 * ceil(n / 256) groups.
+ * mode 2 (rate probe): the same loads and MMAs with no epilogue and no output.
  * Returns after the pass has finished; a pass that gave up on a wait is an error.
  */
 CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_t nq,

@@ -476,7 +476,7 @@ cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_
 {
   return translate([=] {
     Resources& r = as_res(res);
-    CERTEX_EXPECTS(code_len % 128 == 0 && code_len >= 128 && code_len <= 512, "certex: code_len must be 128, 256, 384 or 512");
+    CERTEX_EXPECTS(code_len == 128 || code_len == 256, "certex: code_len must be 128 or 256");
     CERTEX_EXPECTS(nq >= 1 && n >= 1 && n < (int64_t(1) << 31) && nq < (int64_t(1) << 24), "certex: sizes out of range");
     screen_raw(r, q_codes, nq, x_codes, n, code_len, is_signed != 0, init, mode, thr, gmax, ld, cnt, cand, cap, elapsed_ms);
   });

@@ -16,6 +16,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <istream>
 #include <ostream>
@@ -27,7 +28,8 @@ thread_local SearchStats* Index::stats_sink = nullptr;
 
 namespace {
 
-constexpr int64_t kTile = 128;
+constexpr int64_t kTile = kBaseTile;  // stored rows per base tile of the tensor-core pass
+constexpr int64_t kQTile = kQueryTile;
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
@@ -69,14 +71,14 @@ EncodeTiled encode_tiled()
   return fn;
 }
 
-/// Map over rows of `row_bytes` 8-bit codes, `row_stride` bytes apart; boxes of 128 bytes x 128 rows, 128-byte swizzle,
+/// Map over rows of `row_bytes` 8-bit codes, `row_stride` bytes apart; boxes of 128 bytes x box_rows, 128-byte swizzle,
 /// rows beyond `rows` read as zeros.
-CUtensorMap make_code_map(const void* base, uint64_t row_bytes, uint64_t rows, uint64_t row_stride)
+CUtensorMap make_code_map(const void* base, uint64_t row_bytes, uint64_t rows, uint64_t row_stride, uint32_t box_rows)
 {
   CUtensorMap m;
   const cuuint64_t dims[2]    = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_stride};
-  const cuuint32_t box[2]     = {128, 128};
+  const cuuint32_t box[2]     = {128, box_rows};
   const cuuint32_t estr[2]    = {1, 1};
   const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -93,12 +95,8 @@ struct ScreenShape {
 
 ScreenShape shape_for(int kb)
 {
-  switch (kb) {
-    case 1: return {8, 5};
-    case 2: return {4, 2};
-    case 3: return {2, 2};
-    default: return {1, 2};
-  }
+  // shared memory: panel_tiles * kb * 16 KB + n_stages * (kb * 32 KB + 1 KB) + 9 KB must stay below 227 KB
+  return kb == 1 ? ScreenShape{7, 3} : ScreenShape{2, 2};
 }
 
 /// Splits nqt query tiles x nt base tiles over `grid` CTAs: query tiles are grouped into panels of at most
@@ -173,7 +171,7 @@ Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t
   CERTEX_EXPECTS(params.anchor_stride >= 1, "certex: anchor_stride must be at least 1");
   const bool is_int = dtype == kI8 || dtype == kU8;
   CERTEX_EXPECTS(!(params.metric == kCos && is_int), "certex: the cosine metric needs float32 or float16 vectors");
-  int_screen_ = is_int && dim <= 512;
+  int_screen_ = is_int && dim <= 256;
   if (int_screen_) {
     pitch_ = static_cast<size_t>(round_up(dim, 128));
     kb_    = static_cast<int>(pitch_ / 128);
@@ -187,7 +185,11 @@ Index::~Index()
   cudaFree(vectors_);
   cudaFree(removed_);
   cudaFree(labels_);
+  cudaFree(codes_);
+  cudaFree(perm_);
+  cudaFree(inv_);
   cudaFree(init_);
+  cudaFree(cmax_);
 }
 
 void Index::reserve(const Resources& res, int64_t n)
@@ -197,7 +199,9 @@ void Index::reserve(const Resources& res, int64_t n)
   void* v           = nullptr;
   uint8_t* r        = nullptr;
   int32_t* l        = nullptr;
-  int32_t* in       = nullptr;
+  void* co          = nullptr;
+  int32_t *pe = nullptr, *iv = nullptr, *in = nullptr, *cm = nullptr;
+  const int64_t pad_old = round_up(size_, kTile), pad_new = round_up(cap, kTile);
   CERTEX_CUDA(cudaMalloc(&v, static_cast<size_t>(cap) * pitch_));
   CERTEX_CUDA(cudaMalloc(&r, static_cast<size_t>(round_up(cap, 4))));
   CERTEX_CUDA(cudaMemsetAsync(r, 0, static_cast<size_t>(round_up(cap, 4)), res.stream));
@@ -205,29 +209,42 @@ void Index::reserve(const Resources& res, int64_t n)
     CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(cap) * 4));
     CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(cap) * 4, res.stream));
   }
-  if (int_screen_) { CERTEX_CUDA(cudaMalloc(&in, static_cast<size_t>(round_up(cap, kTile)) * 4)); }
+  if (int_screen_) {
+    CERTEX_CUDA(cudaMalloc(&co, static_cast<size_t>(cap) * pitch_));
+    CERTEX_CUDA(cudaMalloc(&pe, static_cast<size_t>(cap) * 4));
+    CERTEX_CUDA(cudaMalloc(&iv, static_cast<size_t>(cap) * 4));
+    CERTEX_CUDA(cudaMalloc(&in, static_cast<size_t>(pad_new) * 4));
+    CERTEX_CUDA(cudaMalloc(&cm, static_cast<size_t>(pad_new / kChainRows) * 4));
+    launch_fill_i32(in, pad_new, kNeverInit, res.stream);
+    launch_fill_i32(cm, pad_new / kChainRows, kNeverInit, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+  }
   if (size_ > 0) {
-    CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, cudaMemcpyDeviceToDevice, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), cudaMemcpyDeviceToDevice, res.stream));
-    if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, cudaMemcpyDeviceToDevice, res.stream)); }
+    const auto d2d = cudaMemcpyDeviceToDevice;
+    CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, d2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), d2d, res.stream));
+    if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, d2d, res.stream)); }
     if (int_screen_) {
-      CERTEX_CUDA(cudaMemcpyAsync(in, init_, static_cast<size_t>(round_up(size_, kTile)) * 4, cudaMemcpyDeviceToDevice, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(co, codes_, static_cast<size_t>(size_) * pitch_, d2d, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(pe, perm_, static_cast<size_t>(size_) * 4, d2d, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(iv, inv_, static_cast<size_t>(size_) * 4, d2d, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(in, init_, static_cast<size_t>(pad_old) * 4, d2d, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(cm, cmax_, static_cast<size_t>(pad_old / kChainRows) * 4, d2d, res.stream));
     }
   }
   res.sync();
-  void* old[4] = {vectors_, removed_, labels_, init_};
+  void* old[8] = {vectors_, removed_, labels_, codes_, perm_, inv_, init_, cmax_};
   {
     std::unique_lock<std::shared_mutex> lock(rw_);  // waits for running searches, which read the old arrays
-    vectors_  = v;
-    removed_  = r;
+    vectors_ = v;
+    removed_ = r;
     if (l) { labels_ = l; }
-    init_     = in;
+    codes_ = co, perm_ = pe, inv_ = iv, init_ = in, cmax_ = cm;
     capacity_ = cap;
   }
-  cudaFree(old[0]);
-  cudaFree(old[1]);
-  if (l) { cudaFree(old[2]); }
-  cudaFree(old[3]);
+  for (int i = 0; i < 8; ++i) {
+    if (i != 2 || l) { cudaFree(old[i]); }
+  }
 }
 
 void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_host)
@@ -247,9 +264,23 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
   }
   if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
   if (int_screen_) {
-    // rows beyond the published size are invisible to running searches, which bound candidates by their own size
-    launch_row_init(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, removed_, size_, n,
-                    round_up(size_ + n, kTile), init_, res.stream);
+    // The batch goes into sorted rows [size, size + n), ordered by squared norm. Rows beyond the published size are
+    // invisible to running searches, which bound tiles and candidates by their own size.
+    Scratch scratch(res.stream);
+    int32_t* e        = scratch.get<int32_t>(static_cast<size_t>(n));
+    uint32_t* keys_in = scratch.get<uint32_t>(static_cast<size_t>(n));
+    uint32_t* keys_out = scratch.get<uint32_t>(static_cast<size_t>(n));
+    int32_t* ids_in   = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* ids_out  = scratch.get<int32_t>(static_cast<size_t>(n));
+    const size_t tb   = sort_batch_temp_bytes(n);
+    void* temp        = scratch.get<uint8_t>(tb);
+    launch_row_init(dst, pitch_, dtype_, static_cast<int>(dim_), kL2, nullptr, 0, n, n, e, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    launch_sort_batch(e, n, static_cast<int32_t>(size_), size_, vectors_, pitch_, params_.metric, keys_in, keys_out, ids_in,
+                      ids_out, temp, tb, codes_, perm_, inv_, init_, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    const int64_t c0 = size_ / kChainRows, c1 = (size_ + n + kChainRows - 1) / kChainRows;
+    launch_chain_max(init_, c0, c1 - c0, cmax_, res.stream);
     CERTEX_CUDA(cudaGetLastError());
   }
   res.sync();
@@ -264,7 +295,7 @@ void Index::remove(const Resources& res, const int64_t* ids_device, int64_t n_id
   Scratch scratch(res.stream);
   auto* counter = scratch.get<unsigned long long>(1);
   CERTEX_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned long long), res.stream));
-  launch_remove(ids_device, n_ids, size_, removed_, init_, counter, res.stream);
+  launch_remove(ids_device, n_ids, size_, removed_, init_, inv_, cmax_, counter, res.stream);
   CERTEX_CUDA(cudaGetLastError());
   unsigned long long n_new = 0;
   CERTEX_CUDA(cudaMemcpyAsync(&n_new, counter, sizeof(n_new), cudaMemcpyDeviceToHost, res.stream));
@@ -322,18 +353,22 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   Scratch scratch(res.stream);
   const int grid          = res.sm_count;
   const ScreenShape shape = shape_for(kb_);
-  const int nqt           = static_cast<int>((nq + kTile - 1) / kTile);
+  const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
   const int64_t n_anchor  = (n + anchor_stride - 1) / anchor_stride;
   const int nt_anchor     = static_cast<int>((n_anchor + kTile - 1) / kTile);
   const int nt_all        = static_cast<int>((n + kTile - 1) / kTile);
-  const int64_t ld_g      = round_up(nt_anchor, 8);
+  const int n_groups      = nt_anchor * (kBaseTile / kGroupRows);
+  const int64_t ld_g      = round_up(n_groups, 8);
   const uint32_t cap      = test_mode_ == 2 ? static_cast<uint32_t>(test_cap_) : static_cast<uint32_t>(std::max(2048, 2 * k));
+  const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
 
   int32_t* anchor_init = scratch.get<int32_t>(static_cast<size_t>(nt_anchor) * kTile);
   int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
   int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
   uint32_t* cnt        = scratch.get<uint32_t>(static_cast<size_t>(nq));
   int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
+  uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
+  auto* rec_count      = scratch.get<unsigned long long>(1);
   ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs * 2);
 
   const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
@@ -342,13 +377,14 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemcpyAsync(d_segs + seg_a.size(), seg_s.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
-  launch_gather_init(init_, anchor_stride, n_anchor, static_cast<int64_t>(nt_anchor) * kTile, anchor_init, res.stream);
+  CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
+  launch_gather_init(init_, anchor_stride, n_anchor, static_cast<int64_t>(nt_anchor) * kTile, anchor_init, res.stream);  // e of the anchors
   CERTEX_CUDA(cudaGetLastError());
 
   const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * pitch_;
-  const CUtensorMap tm_q = make_code_map(qb, pitch_, static_cast<uint64_t>(round_up(nq, kTile)), pitch_);
-  const CUtensorMap tm_a = make_code_map(vectors_, pitch_, static_cast<uint64_t>(n_anchor), pitch_ * anchor_stride);
-  const CUtensorMap tm_x = make_code_map(vectors_, pitch_, static_cast<uint64_t>(n), pitch_);
+  const CUtensorMap tm_q = make_code_map(qb, pitch_, static_cast<uint64_t>(round_up(nq, kQTile)), pitch_, kQueryTile);
+  const CUtensorMap tm_a = make_code_map(codes_, pitch_, static_cast<uint64_t>(n_anchor), pitch_ * anchor_stride, kBaseTile);
+  const CUtensorMap tm_x = make_code_map(codes_, pitch_, static_cast<uint64_t>(n), pitch_, kBaseTile);
 
   ScreenArgs a{};
   a.nq          = nq;
@@ -358,13 +394,6 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   a.q_signed    = dtype_ == kI8 ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.err         = err;
-  // 1 anchors: maximum of acc over every group of 128 anchors
-  a.mode    = kModeGroupMax;
-  a.init    = anchor_init;
-  a.gmax    = gmax;
-  a.ld_gmax = ld_g;
-  a.n_rows  = static_cast<int>(n_anchor);
-  a.segs    = d_segs;
   auto mark = [&] {
     if (events) {
       cudaEvent_t e;
@@ -373,29 +402,37 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
       events->push_back(e);
     }
   };
+  // 1 anchors: maximum of acc over every group of 64 anchors
+  a.mode    = kModeGroupMax;
+  a.init    = anchor_init;
+  a.gmax    = gmax;
+  a.ld_gmax = ld_g;
+  a.segs    = d_segs;
   mark();
   CERTEX_CUDA(screen_i8_launch(tm_q, tm_a, a, grid, res.stream));
   mark();
   // 2 threshold: the k-th largest group maximum
-  launch_kth_largest(gmax, ld_g, nt_anchor, k, nq, thr, res.stream);
+  launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
   CERTEX_CUDA(cudaGetLastError());
-  // 3 screen over all rows
-  a.mode   = kModeScreen;
-  a.init   = init_;
-  a.thr    = thr;
-  a.cnt    = cnt;
-  a.cand   = cand;
-  a.cap    = cap;
-  a.n_rows = static_cast<int>(n);
-  a.segs   = d_segs + seg_a.size();
+  // 3 screen over all rows: survivor records, then per-query candidate lists
+  a.mode      = kModeScreen;
+  a.init      = init_;
+  a.cmax      = cmax_;
+  a.thr       = thr;
+  a.rec       = rec;
+  a.rec_count = rec_count;
+  a.rec_cap   = rec_cap;
+  a.segs      = d_segs + seg_a.size();
   mark();
   CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
   mark();
+  launch_expand_records(rec, rec_count, rec_cap, n, perm_, cnt, cand, cap, res.sm_count, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
   // 4 exact scores of the candidates and the k best
   Admit adm{};
   adm.removed = removed_;
   launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes, nq, q0, cand, cnt,
-                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, res.stream);
+                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, res.stream);
   CERTEX_CUDA(cudaGetLastError());
 }
 
@@ -425,14 +462,14 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   adm.query_labels    = filter.query_labels;
   const bool filtered = filter.words != nullptr || filter.query_labels != nullptr;
 
-  // anchors: every stride-th row, and at least 2k groups of 128 anchors, or the threshold would be useless
-  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (kTile * 2 * k)));
+  // anchors: every stride-th row, and at least 2k groups of 64 anchors, or the threshold would be useless
+  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (int64_t(kGroupRows) * 2 * k)));
   const bool screened = int_screen_ && !filtered && stride >= 1 && test_mode_ != 1;
 
   SearchStats local{};
   local.queries = static_cast<unsigned long long>(nq);
   if (screened) {
-    const int64_t nq_pad = round_up(nq, kTile);
+    const int64_t nq_pad = round_up(nq, kQTile);
     uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * pitch_);
     if (row_bytes != pitch_ || nq_pad != nq) { CERTEX_CUDA(cudaMemsetAsync(qbuf, 0, static_cast<size_t>(nq_pad) * pitch_, res.stream)); }
     CERTEX_CUDA(cudaMemcpy2DAsync(qbuf, pitch_, queries, row_bytes, row_bytes, static_cast<size_t>(nq), cudaMemcpyDeviceToDevice, res.stream));
@@ -447,7 +484,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
       const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
       search_screened(res, qbuf, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
                       d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, stats_sink ? &events : nullptr);
-      local.launches += 5;  // gather_init, GROUPMAX pass, kth_largest, SCREEN pass, verify_select
+      local.launches += 6;  // gather_init, GROUPMAX pass, kth_largest, SCREEN pass, expand_records, verify_select
     }
     unsigned int h_count[4]       = {0, 0, 0, 0};
     unsigned long long h_stats[2] = {0, 0};
@@ -567,10 +604,20 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
     CERTEX_CUDA(cudaMemcpyAsync(idx->removed_, host.data(), static_cast<size_t>(n), cudaMemcpyHostToDevice, res.stream));
     res.sync();
     idx->n_removed_ = n_rem;
-    if (idx->int_screen_) {  // removed rows must never pass the screen
-      launch_row_init(idx->vectors_, idx->pitch_, dtype, static_cast<int>(dim), p.metric, idx->removed_, 0, n,
-                      round_up(n, kTile), idx->init_, res.stream);
+    if (idx->int_screen_ && n_rem > 0) {  // removed rows must never pass the screen
+      Scratch scratch(res.stream);
+      int64_t* ids     = scratch.get<int64_t>(static_cast<size_t>(n));
+      auto* counter    = scratch.get<unsigned long long>(1);
+      std::vector<int64_t> gone;
+      for (int64_t i = 0; i < n; ++i) {
+        if (host[static_cast<size_t>(i)]) { gone.push_back(i); }
+      }
+      CERTEX_CUDA(cudaMemcpyAsync(ids, gone.data(), gone.size() * 8, cudaMemcpyHostToDevice, res.stream));
+      CERTEX_CUDA(cudaMemsetAsync(idx->removed_, 0, static_cast<size_t>(n), res.stream));
+      CERTEX_CUDA(cudaMemsetAsync(counter, 0, 8, res.stream));
+      launch_remove(ids, static_cast<int64_t>(gone.size()), n, idx->removed_, idx->init_, idx->inv_, idx->cmax_, counter, res.stream);
       CERTEX_CUDA(cudaGetLastError());
+      res.sync();
     }
     if (labeled) {
       is.read(host.data(), static_cast<std::streamsize>(n * 4));
@@ -613,25 +660,38 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   const int kb            = static_cast<int>(code_len / 128);
   const ScreenShape shape = shape_for(kb);
   const int grid          = res.sm_count;
-  const int nqt           = static_cast<int>((nq + kTile - 1) / kTile);
+  const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
   const int nt            = static_cast<int>((n + kTile - 1) / kTile);
   const auto segs         = plan_segments(nqt, nt, shape.panel_tiles, grid);
   ScreenSeg* d_segs       = scratch.get<ScreenSeg>(segs.size());
   int* err                = scratch.get<int>(1);
   CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(err, 0, sizeof(int), res.stream));
-  const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kTile)), code_len);
-  const CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len);
+  const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kQTile)), code_len, kQueryTile);
+  const CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len, kBaseTile);
+  // init arrives for n rounded up to 64 rows; the pass reads whole base tiles, and chain maxima
+  const int64_t n_in  = round_up(n, kGroupRows);
+  const int64_t n_pad = static_cast<int64_t>(nt) * kTile;
+  int32_t* init_pad   = scratch.get<int32_t>(static_cast<size_t>(n_pad));
+  int32_t* cmax       = scratch.get<int32_t>(static_cast<size_t>(n_pad / kChainRows));
+  launch_fill_i32(init_pad, n_pad, kNeverInit, res.stream);
+  CERTEX_CUDA(cudaMemcpyAsync(init_pad, init, static_cast<size_t>(n_in) * 4, cudaMemcpyDeviceToDevice, res.stream));
+  launch_chain_max(init_pad, 0, n_pad / kChainRows, cmax, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+  const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
+  uint64_t* rec   = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
+  auto* rec_count = scratch.get<unsigned long long>(1);
+  CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
   ScreenArgs a{};
-  a.init        = init;
+  a.init        = init_pad;
+  a.cmax        = cmax;
   a.thr         = thr;
   a.gmax        = gmax;
   a.ld_gmax     = ld;
-  a.cnt         = cnt;
-  a.cand        = cand;
-  a.cap         = cap;
+  a.rec         = rec;
+  a.rec_count   = rec_count;
+  a.rec_cap     = rec_cap;
   a.nq          = static_cast<int>(nq);
-  a.n_rows      = static_cast<int>(n);
   a.kb          = kb;
   a.panel_tiles = shape.panel_tiles;
   a.n_stages    = shape.n_stages;
@@ -646,16 +706,22 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   CERTEX_CUDA(cudaEventRecord(e0, res.stream));
   const cudaError_t le = screen_i8_launch(tm_q, tm_x, a, grid, res.stream);
   CERTEX_CUDA(cudaEventRecord(e1, res.stream));
-  int h_err = 0;
+  if (mode == kModeScreen && le == cudaSuccess) {
+    launch_expand_records(rec, rec_count, rec_cap, n, nullptr, cnt, cand, cap, res.sm_count, res.stream);
+  }
+  int h_err                  = 0;
+  unsigned long long h_count = 0;
   CERTEX_CUDA(cudaMemcpyAsync(&h_err, err, sizeof(int), cudaMemcpyDeviceToHost, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(&h_count, rec_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
   const cudaError_t se = cudaStreamSynchronize(res.stream);
-  float ms = 0;
+  float ms             = 0;
   if (se == cudaSuccess) { cudaEventElapsedTime(&ms, e0, e1); }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   CERTEX_CUDA(le);
   CERTEX_CUDA(se);
   CERTEX_EXPECTS(h_err == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_err) + ")");
+  CERTEX_EXPECTS(h_count <= rec_cap, "certex: the survivor record buffer overflowed");
   if (elapsed_ms) { *elapsed_ms = ms; }
 }
 

@@ -147,7 +147,12 @@ class Index {
   void* vectors_      = nullptr;  // [capacity, pitch]
   uint8_t* removed_   = nullptr;  // [capacity rounded up to 4]
   int32_t* labels_    = nullptr;  // [capacity], -1 = none
-  int32_t* init_      = nullptr;  // [capacity rounded up to 128] (integer screen)
+  // integer screen: a copy of the rows sorted by squared norm (each appended batch on its own), and per sorted row
+  void* codes_        = nullptr;  // [capacity, pitch] rows in sorted order
+  int32_t* perm_      = nullptr;  // [capacity] sorted row -> id
+  int32_t* inv_       = nullptr;  // [capacity] id -> sorted row
+  int32_t* init_      = nullptr;  // [capacity rounded up to 256] e of the sorted row (kNeverInit: removed / padding)
+  int32_t* cmax_      = nullptr;  // [capacity rounded up to 256, / 16] maximum of e over each chain of 16 sorted rows
   int test_mode_      = 0;
   int test_cap_       = 0;
   mutable std::shared_mutex rw_;  // searches hold it shared per call; size/pointer publication holds it exclusive

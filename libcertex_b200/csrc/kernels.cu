@@ -14,6 +14,7 @@
 
 #include "screen_i8.cuh"  // kNeverInit
 
+#include <cub/cub.cuh>
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -243,11 +244,14 @@ __global__ void row_init_kernel(const uint8_t* vectors, size_t pitch, int d, int
 __global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (j < n_pad) { out[j] = j < n_anchor ? init[j * stride] : kNeverInit; }
+  if (j < n_pad) {
+    const int64_t r = j * stride;
+    out[j] = j < n_anchor ? init[r] : kNeverInit;
+  }
 }
 
 __global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
-                              unsigned long long* n_new)
+                              const int32_t* inv, unsigned long long* n_new)
 {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_ids) { return; }
@@ -258,7 +262,93 @@ __global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, u
   const uint32_t bit   = 1u << (8 * (id & 3));
   const uint32_t prev  = atomicOr(word, bit);
   if ((prev & bit) == 0u) { atomicAdd(n_new, 1ull); }
-  if (init) { init[id] = kNeverInit; }
+  if (init) { init[inv ? inv[id] : id] = kNeverInit; }
+}
+
+// cmax[c] = max of e over rows [16c, 16c + 16) for chains c0 .. c0 + n - 1 (e padded with kNeverInit).
+__global__ void chain_max_kernel(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) { return; }
+  const int4* e = reinterpret_cast<const int4*>(init + (c0 + i) * 16);
+  int m         = kNeverInit;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int4 t = e[k];
+    m            = max(max(max(m, t.x), max(t.y, t.z)), t.w);
+  }
+  cmax[c0 + i] = m;
+}
+
+// The chains that hold removed ids get their maximum recomputed (after remove_kernel has marked the rows).
+__global__ void chain_max_of_ids_kernel(const int64_t* ids, int64_t n_ids, int64_t size, const int32_t* inv,
+                                        const int32_t* init, int32_t* cmax)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_ids) { return; }
+  const int64_t id = ids[i];
+  if (id < 0 || id >= size) { return; }
+  const int64_t c = (inv ? inv[id] : id) / 16;
+  int m           = kNeverInit;
+  for (int k = 0; k < 16; ++k) { m = max(m, init[c * 16 + k]); }
+  cmax[c] = m;
+}
+
+// keys[j] = -e[j] (half the squared norm, ascending sort key), vals[j] = id0 + j.
+__global__ void sort_keys_kernel(const int32_t* e, int64_t n, int32_t id0, uint32_t* keys, int32_t* vals)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j < n) {
+    keys[j] = static_cast<uint32_t>(-e[j]);
+    vals[j] = id0 + static_cast<int32_t>(j);
+  }
+}
+
+// Sorted batch -> index arrays: perm[row0 + j] = id, inv[id] = row0 + j, init[row0 + j] = -key, and the code row.
+__global__ void place_sorted_kernel(const uint32_t* keys, const int32_t* ids, int64_t n, int64_t row0, const uint8_t* vectors,
+                                    size_t pitch, uint8_t* codes, int32_t* perm, int32_t* inv, int32_t* init, int metric)
+{
+  const int64_t gt   = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int chunks   = static_cast<int>(pitch / 16);
+  const int64_t j    = gt / chunks;
+  const int c        = static_cast<int>(gt % chunks);
+  if (j >= n) { return; }
+  const int32_t id = ids[j];
+  reinterpret_cast<uint4*>(codes + static_cast<size_t>(row0 + j) * pitch)[c] =
+    __ldg(reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(id) * pitch) + c);
+  if (c == 0) {
+    perm[row0 + j] = id;
+    inv[id]        = static_cast<int32_t>(row0 + j);
+    init[row0 + j] = metric == kL2 ? -static_cast<int32_t>(keys[j]) : 0;
+  }
+}
+
+__global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t v)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j < n) { p[j] = v; }
+}
+
+// Survivor records -> per-query candidate lists. One thread per record; the appends of a query go through cnt[q].
+__global__ void expand_records_kernel(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,
+                                      int64_t n_rows, const int32_t* perm, uint32_t* cnt, int32_t* cand, uint32_t cap)
+{
+  const unsigned long long n = min(*rec_count, rec_cap);
+  for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
+    const uint64_t r     = rec[i];
+    const uint32_t q     = static_cast<uint32_t>(r >> 48);
+    const int64_t row0   = static_cast<int64_t>((r >> 16) & 0xffffffffull) * 16;
+    uint32_t mask        = static_cast<uint32_t>(r & 0xffffu);
+    while (mask) {
+      const int b = __ffs(mask) - 1;
+      mask &= mask - 1;
+      if (row0 + b < n_rows) {
+        const uint32_t pos = atomicAdd(cnt + q, 1u);
+        if (pos < cap) { cand[static_cast<size_t>(q) * cap + pos] = perm ? perm[row0 + b] : static_cast<int32_t>(row0 + b); }
+      }
+    }
+  }
 }
 
 // Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk.
@@ -305,13 +395,15 @@ template <typename T, int METRIC>
 __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
                                      Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
-                                     unsigned int* ovf_count, unsigned long long* stats)
+                                     unsigned int* ovf_count, unsigned long long* stats,
+                                     const unsigned long long* rec_count, unsigned long long rec_cap)
 {
   extern __shared__ double sh[];
   __shared__ double s_qq;
   const int q       = q0 + blockIdx.x;  // number of the query in the call; cand / cnt are those of its batch
   const uint32_t c  = cnt[blockIdx.x];
-  if (c > cap) {
+  // a candidate list that overflowed, or a survivor record buffer that did (then no list of the batch is complete)
+  if (c > cap || (rec_count && *rec_count > rec_cap)) {
     if (threadIdx.x == 0) { ovf_list[atomicAdd(ovf_count, 1u)] = q; }
     return;
   }
@@ -600,23 +692,65 @@ void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, i
   gather_init_kernel<<<static_cast<unsigned>((n_pad + 255) / 256), 256, 0, s>>>(init, stride, n_anchor, n_pad, out);
 }
 
+void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,
+                           int64_t n_rows, const int32_t* perm, uint32_t* cnt, int32_t* cand, uint32_t cap, int sm_count,
+                           cudaStream_t s)
+{
+  expand_records_kernel<<<sm_count * 8, 256, 0, s>>>(rec, rec_count, rec_cap, n_rows, perm, cnt, cand, cap);
+}
+
+void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  chain_max_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(init, c0, n, cmax);
+}
+
+void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  fill_i32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p, n, v);
+}
+
+size_t sort_batch_temp_bytes(int64_t n)
+{
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
+                                  static_cast<const int32_t*>(nullptr), static_cast<int32_t*>(nullptr), n);
+  return bytes;
+}
+
+void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* vectors, size_t pitch, int metric,
+                       uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out, void* temp, size_t temp_bytes,
+                       void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  sort_keys_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e, n, id0, keys_in, ids_in);
+  cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys_in, keys_out, ids_in, ids_out, n, 0, 32, s);
+  const int64_t threads = n * static_cast<int64_t>(pitch / 16);
+  place_sorted_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(
+    keys_out, ids_out, n, row0, static_cast<const uint8_t*>(vectors), pitch, static_cast<uint8_t*>(codes), perm, inv, init, metric);
+}
+
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s)
 {
   if (nq <= 0) { return; }
   kth_largest_kernel<<<nq, 256, 0, s>>>(gmax, ld, ng, k, thr);
 }
 
-void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
-                   unsigned long long* n_new, cudaStream_t s)
+void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
+                   int32_t* cmax, unsigned long long* n_new, cudaStream_t s)
 {
   if (n_ids <= 0) { return; }
-  remove_kernel<<<static_cast<unsigned>((n_ids + 255) / 256), 256, 0, s>>>(ids, n_ids, size, removed, init, n_new);
+  const auto grid = static_cast<unsigned>((n_ids + 255) / 256);
+  remove_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, removed, init, inv, n_new);
+  if (init && cmax) { chain_max_of_ids_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, inv, init, cmax); }
 }
 
 void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
-                          unsigned long long* stats, cudaStream_t s)
+                          unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
+                          cudaStream_t s)
 {
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
@@ -626,7 +760,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
     auto go   = [&](auto kernel) {
       allow_smem(kernel, smem);
       kernel<<<nq, 128, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
-                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats);
+                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap);
     };
     if (metric == kL2) {
       go(verify_select_kernel<T, kL2>);

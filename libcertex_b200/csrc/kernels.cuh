@@ -20,30 +20,53 @@ struct Admit {
   const int32_t* query_labels;  // [nq]
 };
 
-/// init[r] for rows [row0, row0 + n): -floor(|x|^2 / 2) (L2) or 0 (inner product); removed rows and the padding up
-/// to `n_pad` get kNeverInit. Integer dtypes only.
+/// e[r] for rows [row0, row0 + n) of `vectors`: -floor(|x|^2 / 2) (L2) or 0 (inner product); removed rows and the
+/// padding up to `n_pad` get kNeverInit. Integer dtypes only.
 void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int metric, const uint8_t* removed,
                      int64_t row0, int64_t n, int64_t n_pad, int32_t* init, cudaStream_t s);
 
 /// out[j] = init[j * stride] for j < n_anchor, kNeverInit up to n_pad.
 void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out, cudaStream_t s);
 
+/// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1.
+void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, cudaStream_t s);
+
+void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s);
+
+/// Sorts one appended batch by squared norm and writes it into the index arrays of the integer screen: e [n] are the
+/// per-row terms of ids id0 .. id0 + n - 1 (see launch_row_init), the batch occupies sorted rows row0 .. row0 + n - 1;
+/// perm [row] = id, inv [id] = row, init [row] = e of that id, codes [row] = vectors [id]. keys / ids are scratch of n
+/// elements each, temp of sort_batch_temp_bytes(n).
+size_t sort_batch_temp_bytes(int64_t n);
+void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* vectors, size_t pitch, int metric,
+                       uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out, void* temp, size_t temp_bytes,
+                       void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s);
+
+/// Survivor records of the screen (see make_record) -> cnt [nq] / cand [nq, cap]; rows >= n_rows are dropped, rows are
+/// translated to ids through perm (when not null).
+void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,
+                           int64_t n_rows, const int32_t* perm, uint32_t* cnt, int32_t* cand, uint32_t cap, int sm_count,
+                           cudaStream_t s);
+
 /// thr[q] = k-th largest of gmax[q, 0:ng]  (INT_MIN when ng < k).
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s);
 
-/// Marks ids as removed: removed[id] = 1, init[id] = kNeverInit (if init != null); *n_new counts first-time removals.
-void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
-                   unsigned long long* n_new, cudaStream_t s);
+/// Marks ids as removed: removed[id] = 1, and for the integer screen init[inv[id]] = kNeverInit with the chain maxima
+/// of the touched chains recomputed; *n_new counts first-time removals.
+void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
+                   int32_t* cmax, unsigned long long* n_new, cudaStream_t s);
 
 /**
  * Exact fp64 scores of every query's candidate rows, then its k best by (score, row). One block per query.
- * cand [nq, cap] rows, cnt [nq] how many (a query with cnt > cap is skipped and its index appended to ovf_list).
+ * cand [nq, cap] rows, cnt [nq] how many (a query with cnt > cap is skipped and its index appended to ovf_list;
+ * so is every query when *rec_count > rec_cap, i.e. when the screen's survivor records did not all fit).
  * best_s / best_row [nq, k] (row -1, score +inf where fewer than k admitted candidates exist).
  */
 void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
-                          unsigned long long* stats, cudaStream_t s);
+                          unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
+                          cudaStream_t s);
 
 /// All-pairs exact fp64 scores of queries qsel[0:nqb] (or q0.. when qsel is null) against rows [0, n): out [nqb, ld].
 /// Rows that `adm` rejects score +inf.

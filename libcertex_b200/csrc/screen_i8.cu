@@ -7,19 +7,26 @@
 // an mma.sync kernel) and, in its second mode, the anchor pass `anchor_groups`
 // (cpp/src/neighbors/certex/detail/kernels.hpp:125-135).
 //
-// One accumulator unit is 128 queries (TMEM lanes) x 128 stored rows (TMEM columns), K = 128 bytes per K block.
-//   acc[q][x] = init[x] + <q, x>        init[x] = -floor(|x|^2 / 2) for L2, 0 for inner product, -2^30 for removed rows
-// The per-row term is not added in the epilogue: the epilogue threads write init[] into the accumulator columns with
-// tcgen05.st before the MMA of that unit starts, and every MMA accumulates onto it. The epilogue is then one running
-// maximum per thread (3-input integer max) and one compare per 64 columns:
-//   SCREEN    keep (q, x) iff acc >= thr[q]; survivors are appended to the per-query candidate list
-//   GROUPMAX  gmax[q][tile] = max over the 128 columns (the k-th largest group maximum of a query is its threshold:
-//             k distinct stored rows are at least that close)
+// One accumulator unit is 128 queries (TMEM lanes) x 256 stored rows (TMEM columns), K = 128 bytes per K block; one
+// tcgen05.mma instruction covers the whole 128 x 256 unit for 32 bytes of K (N = 256 is what keeps the tensor pipe fed:
+// with N = 128 the operand reads from shared memory cap the rate at about 60 % of peak).
+//   value[q][x] = <q, x> + e[x]
+//   e[x] = -floor(|x|^2 / 2) for L2, 0 for inner product, -2^30 for removed rows and padding
+// SCREEN keeps (q, x) iff value >= thr[q]. The stored rows are kept sorted by |x|^2 (per appended batch), so e is
+// almost constant over 16 adjacent rows and the epilogue never touches e per element: a thread (one query row, 64
+// columns of the unit) takes the maximum of the raw products over each chain of 16 columns (3-input integer max, half
+// an instruction per element) and tests  max + cmax[chain] >= thr  with cmax = max of e over the chain. That test
+// never rejects a pair that should be kept. Only a chain that passes it (rare) is looked at element by element with
+// the exact e[x]; its survivors form one record (query, chain, 16-bit mask) in the warp's staging buffer in shared
+// memory, and a full buffer goes to global memory with one atomic add for the whole batch.
+// GROUPMAX writes gmax[q][group] = max over 64 rows of value (exact, e is staged in shared memory with the tile); the
+// k-th largest group maximum of a query is its threshold: k distinct stored rows are at least that close.
 //
-// CTA = 10 warps: warp 0 lane 0 issues TMA loads (queries panel once per segment, base tiles through a ring of
-// stages), warp 1 lane 0 issues tcgen05.mma, warps 2..9 are two epilogue groups of four warps (one per TMEM lane
-// quarter) that take alternate units. TMEM holds four accumulator slots of 128 columns, so the MMA runs up to three
-// units ahead of the epilogue. No cluster launch, no multicast: each CTA loads its own tiles from its GPU's memory.
+// CTA = 18 warps: warp 0 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
+// warp 1 lane 0 issues tcgen05.mma, warps 2..17 are the epilogue: four warps per TMEM lane quarter, each owning one
+// 64-column piece of every unit. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
+// epilogue reads the other; a slot goes back to the MMA warp as soon as its columns are in registers. No cluster
+// launch, no multicast: each CTA loads its own tiles from its GPU's memory.
 #include "screen_i8.cuh"
 
 #include "ptx.cuh"
@@ -30,57 +37,18 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kTileRows  = 128;
-constexpr int kTileBytes = 128 * 128;  // one K block of one tile: 128 rows x 128 bytes
-constexpr int kSlots     = 4;          // TMEM accumulator slots (4 x 128 columns = all 512)
-constexpr int kThreads   = 320;
-
-// Walks the CTA's units in issue order: for every base tile of a segment, the query tiles of the segment's panel.
-struct Walker {
-  const ScreenSeg* segs;
-  int nseg;
-  int s;     // segment
-  int tile;  // base tile (absolute)
-  int j;     // query tile inside the panel
-  int ts;    // base tiles started before this one (ring position)
-  bool valid;
-
-  __device__ void init(const ScreenSeg* sg, int n)
-  {
-    segs  = sg;
-    nseg  = n;
-    s     = 0;
-    j     = 0;
-    ts    = 0;
-    valid = n > 0;
-    tile  = valid ? sg[0].t0 : 0;
-  }
-  __device__ void step()
-  {
-    if (!valid) { return; }
-    if (++j == segs[s].n_qtiles) {
-      j = 0;
-      ++ts;
-      if (++tile == segs[s].t1) {
-        if (++s == nseg) {
-          valid = false;
-        } else {
-          tile = segs[s].t0;
-        }
-      }
-    }
-  }
-  __device__ void advance(int n)
-  {
-    for (int i = 0; i < n; ++i) { step(); }
-  }
-};
+constexpr int kQTileBytes = kQueryTile * 128;  // one K block of a query tile: 128 rows x 128 bytes
+constexpr int kBTileBytes = kBaseTile * 128;   // one K block of a base tile: 256 rows x 128 bytes
+constexpr int kSlots      = 2;                 // TMEM accumulator slots (2 x 256 columns = all 512)
+constexpr int kEpiWarps   = 16;
+constexpr int kThreads    = 32 * (2 + kEpiWarps);
+constexpr int kRecBuf     = 64;                // staged survivor records per epilogue warp
 
 struct SharedCtl {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
-  uint64_t tmem_full[kSlots];
-  uint64_t tmem_ready[kSlots];
+  uint64_t full[kMaxStages];    // TMA landed a base tile (GROUPMAX: and its e values) in the stage
+  uint64_t empty[kMaxStages];   // the stage may be overwritten (GROUPMAX: also every epilogue warp is done with e)
+  uint64_t tmem_full[kSlots];   // the MMAs of a unit are complete
+  uint64_t tmem_empty[kSlots];  // the unit's accumulator is in registers (all 16 epilogue warps)
   uint64_t panel_full;
   uint64_t panel_empty;
   uint64_t drain;
@@ -89,31 +57,56 @@ struct SharedCtl {
   ScreenSeg segs[kMaxSegs];
 };
 
-__device__ __forceinline__ int max3(int a, int b, int c) { return __vimax3_s32(a, b, c); }
+// Position in the CTA's unit sequence: for every base tile of a segment, the query tiles of the segment's panel.
+struct Cursor {
+  int s, t, j, ts, nqt, t1, q_tile0;
+  bool valid;
+};
 
-template <int N>
-__device__ __forceinline__ int max_of(const int32_t (&v)[N])
+__device__ __forceinline__ void cursor_seg(Cursor& c, const ScreenSeg* segs, int nseg)
 {
-  int m = max3(v[0], v[1], v[2]);
-#pragma unroll
-  for (int i = 3; i + 1 < N; i += 2) { m = max3(m, v[i], v[i + 1]); }
-  if constexpr ((N - 3) % 2 == 1) { m = max(m, v[N - 1]); }
-  return m;
-}
-
-template <int N>
-__device__ __forceinline__ void emit_survivors(
-  const int32_t (&v)[N], int thr, int q, int row0, int n_rows, uint32_t* cnt, int32_t* cand, uint32_t cap)
-{
-#pragma unroll
-  for (int i = 0; i < N; ++i) {
-    if (v[i] >= thr && row0 + i < n_rows) {
-      const uint32_t pos = atomicAdd(cnt + q, 1u);
-      if (pos < cap) { cand[static_cast<size_t>(q) * cap + pos] = row0 + i; }
-    }
+  c.valid = c.s < nseg;
+  if (c.valid) {
+    const ScreenSeg sg = segs[c.s];
+    c.t                = sg.t0;
+    c.t1               = sg.t1;
+    c.nqt              = sg.n_qtiles;
+    c.q_tile0          = sg.q_tile0;
   }
 }
 
+__device__ __forceinline__ int max3(int a, int b, int c) { return __vimax3_s32(a, b, c); }
+__device__ __forceinline__ int addmax(int a, int b, int c) { return __viaddmax_s32(a, b, c); }  // max(a + b, c)
+
+// Maximum of 16 adjacent accumulator columns (two chains).
+__device__ __forceinline__ int max16(const int32_t* v)
+{
+  int m = max3(v[0], v[1], v[2]);
+  int n = max3(v[3], v[4], v[5]);
+  m     = max3(m, v[6], v[7]);
+  n     = max3(n, v[8], v[9]);
+  m     = max3(m, v[10], v[11]);
+  n     = max3(n, v[12], v[13]);
+  return max3(m, n, max(v[14], v[15]));
+}
+
+// Maximum of v[i] + e[i] over 32 columns, e in shared memory (two chains).
+__device__ __forceinline__ int max32_plus(const int32_t (&v)[32], const int32_t* e)
+{
+  const int4* e4 = reinterpret_cast<const int4*>(e);
+  int m = kNeverInit * 2 + 1, n = m;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int4 t = e4[i];
+    m = addmax(v[4 * i], t.x, m);
+    n = addmax(v[4 * i + 1], t.y, n);
+    m = addmax(v[4 * i + 2], t.z, m);
+    n = addmax(v[4 * i + 3], t.w, n);
+  }
+  return max(m, n);
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_x,
                                                                 const ScreenArgs p)
@@ -130,25 +123,27 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   const uint32_t base      = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base        = smem_raw + (base - smem_u32(smem_raw));
   const int kb             = p.kb;
+  const int ns             = p.n_stages;
   const uint32_t panel_off = 0;
-  const uint32_t stage_off = panel_off + static_cast<uint32_t>(p.panel_tiles) * kb * kTileBytes;
-  const uint32_t init_off  = stage_off + static_cast<uint32_t>(p.n_stages) * kb * kTileBytes;
-  const uint32_t ctl_off   = init_off + static_cast<uint32_t>(p.n_stages) * kTileRows * 4;
+  const uint32_t stage_off = panel_off + static_cast<uint32_t>(p.panel_tiles) * kb * kQTileBytes;
+  const uint32_t init_off  = stage_off + static_cast<uint32_t>(ns) * kb * kBTileBytes;
+  const uint32_t rec_off   = init_off + static_cast<uint32_t>(ns) * kBaseTile * 4;
+  const uint32_t ctl_off   = rec_off + kEpiWarps * kRecBuf * 8;
   SharedCtl* ctl           = reinterpret_cast<SharedCtl*>(gen_base + ctl_off);
   const int32_t* init_smem = reinterpret_cast<const int32_t*>(gen_base + init_off);
   volatile int* abort_flag = &ctl->abort_flag;
-  const int ns             = p.n_stages;
+  constexpr bool kStageE   = MODE == kModeGroupMax;  // e values travel with the tile and are read by the epilogue
 
   const ScreenSeg* segs = ctl->segs;
   if (threadIdx.x < kMaxSegs) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
   if (threadIdx.x == 0) {
     for (int i = 0; i < ns; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
-      mbar_init(smem_u32(&ctl->empty[i]), 1);
+      mbar_init(smem_u32(&ctl->empty[i]), kStageE ? 1 + kEpiWarps : 1);
     }
     for (int i = 0; i < kSlots; ++i) {
       mbar_init(smem_u32(&ctl->tmem_full[i]), 1);
-      mbar_init(smem_u32(&ctl->tmem_ready[i]), 4);  // one arrival per warp of an epilogue group
+      mbar_init(smem_u32(&ctl->tmem_empty[i]), kEpiWarps);
     }
     mbar_init(smem_u32(&ctl->panel_full), 1);
     mbar_init(smem_u32(&ctl->panel_empty), 1);
@@ -176,10 +171,10 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         const ScreenSeg sg = segs[s];
         if (s > 0 && !mbar_wait(smem_u32(&ctl->panel_empty), (s - 1) & 1, abort_flag, p.err, 1)) { break; }
         const uint32_t pbar = smem_u32(&ctl->panel_full);
-        mbar_arrive_expect_tx(pbar, static_cast<uint32_t>(sg.n_qtiles) * kb * kTileBytes);
+        mbar_arrive_expect_tx(pbar, static_cast<uint32_t>(sg.n_qtiles) * kb * kQTileBytes);
         for (int j = 0; j < sg.n_qtiles; ++j) {
           for (int b = 0; b < kb; ++b) {
-            tma_load_2d(base + panel_off + (j * kb + b) * kTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kTileRows, pbar);
+            tma_load_2d(base + panel_off + (j * kb + b) * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, pbar);
           }
         }
         for (int t = sg.t0; t < sg.t1; ++t, ++ts) {
@@ -189,18 +184,20 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             break;
           }
           const uint32_t fbar = smem_u32(&ctl->full[st]);
-          mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(kb) * kTileBytes + kTileRows * 4);
+          mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(kb) * kBTileBytes + (kStageE ? kBaseTile * 4 : 0));
           for (int b = 0; b < kb; ++b) {
-            tma_load_2d(base + stage_off + (st * kb + b) * kTileBytes, &tm_x, b * 128, t * kTileRows, fbar);
+            tma_load_2d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
           }
-          bulk_load_1d(base + init_off + st * kTileRows * 4, p.init + static_cast<size_t>(t) * kTileRows, kTileRows * 4, fbar);
+          if (kStageE) {
+            bulk_load_1d(base + init_off + st * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4, fbar);
+          }
         }
       }
       if (*abort_flag) {
         // let the copies that are still in flight land before the CTA leaves (bounded)
         for (int back = 1; back <= ns && back <= ts; ++back) {
-          const int u         = ts - back;
-          const long long t0  = clock64();
+          const int u        = ts - back;
+          const long long t0 = clock64();
           while (!mbar_try_wait(smem_u32(&ctl->full[u % ns]), (u / ns) & 1) && clock64() - t0 < (1ll << 24)) {}
         }
       }
@@ -208,35 +205,41 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   } else if (warp == 1) {
     // ================================================================ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(2u, p.q_signed, p.x_signed, 128u, 128u);
-      Walker w;
-      w.init(segs, nseg);
-      int gu = 0, cur_seg = -1;
-      while (w.valid) {
-        if (w.s != cur_seg) {
-          cur_seg = w.s;
-          if (!mbar_wait(smem_u32(&ctl->panel_full), cur_seg & 1, abort_flag, p.err, 3)) { break; }
-        }
-        const int st = w.ts % ns, slot = gu & (kSlots - 1);
-        if (w.j == 0 && !mbar_wait(smem_u32(&ctl->full[st]), (w.ts / ns) & 1, abort_flag, p.err, 4)) { break; }
-        if (!mbar_wait(smem_u32(&ctl->tmem_ready[slot]), (gu / kSlots) & 1, abort_flag, p.err, 5)) { break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem + static_cast<uint32_t>(slot * kTileRows);
-        for (int b = 0; b < kb; ++b) {
-          const uint32_t a_addr = base + panel_off + (w.j * kb + b) * kTileBytes;
-          const uint32_t b_addr = base + stage_off + (st * kb + b) * kTileBytes;
+      const uint32_t idesc = instr_desc(2u, p.q_signed, p.x_signed, kQueryTile, kBaseTile);
+      // descriptors differ only in their 14-bit start-address field: (byte offset >> 4) is added to the low word
+      const uint64_t a_desc0 = smem_desc_sw128(base + panel_off);
+      const uint64_t b_desc0 = smem_desc_sw128(base + stage_off);
+      int gu = 0, ts = 0;
+      bool ok = true;
+      for (int s = 0; s < nseg && ok; ++s) {
+        const ScreenSeg sg = segs[s];
+        ok                 = mbar_wait(smem_u32(&ctl->panel_full), s & 1, abort_flag, p.err, 3);
+        for (int t = sg.t0; t < sg.t1 && ok; ++t, ++ts) {
+          const int st = ts % ns;
+          ok           = mbar_wait(smem_u32(&ctl->full[st]), (ts / ns) & 1, abort_flag, p.err, 4);
+          if (!ok) { break; }
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(st * kb) * (kBTileBytes >> 4);
+          for (int j = 0; j < sg.n_qtiles; ++j, ++gu) {
+            const int slot = gu & (kSlots - 1);
+            if (MODE != kModeRate && gu >= kSlots) {
+              ok = mbar_wait(smem_u32(&ctl->tmem_empty[slot]), ((gu >> 1) - 1) & 1, abort_flag, p.err, 5);
+              if (!ok) { break; }
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + static_cast<uint32_t>(slot * kBaseTile);
+            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(j * kb) * (kQTileBytes >> 4);
+            for (int b = 0; b < kb; ++b) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            mma_i8(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, 1u);
+              for (int k = 0; k < 4; ++k) {
+                mma_i8(d_tmem, a_desc + static_cast<uint64_t>(b * (kQTileBytes >> 4) + k * 2),
+                       b_desc + static_cast<uint64_t>(b * (kBTileBytes >> 4) + k * 2), idesc, (b | k) != 0 ? 1u : 0u);
+              }
+            }
+            tc_commit(smem_u32(&ctl->tmem_full[slot]));
           }
+          if (ok) { tc_commit(smem_u32(&ctl->empty[st])); }
         }
-        tc_commit(smem_u32(&ctl->tmem_full[slot]));
-        const bool last_q    = w.j == segs[w.s].n_qtiles - 1;
-        const bool last_tile = last_q && w.tile == segs[w.s].t1 - 1;
-        if (last_q) { tc_commit(smem_u32(&ctl->empty[st])); }
-        if (last_tile) { tc_commit(smem_u32(&ctl->panel_empty)); }
-        w.step();
-        ++gu;
+        if (ok) { tc_commit(smem_u32(&ctl->panel_empty)); }
       }
       // every MMA issued above has completed before TMEM is released
       tc_commit(smem_u32(&ctl->drain));
@@ -245,79 +248,117 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         while (!mbar_try_wait(smem_u32(&ctl->drain), 0) && clock64() - t0 < kWaitLimitCycles) {}
       }
     }
-  } else {
-    // ================================================================ epilogue (two groups of four warps)
-    const int ew = warp - 2, group = ew >> 2;
+  } else if (MODE != kModeRate) {
+    // ================================================================ epilogue (16 warps, one 64-column piece each)
+    const int ew             = warp - 2;
+    const int piece          = ew >> 2;   // which 64 columns of a unit
     const int quarter        = warp & 3;  // the TMEM lane quarter this warp may access
     const int row            = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    uint64_t* rec_buf        = reinterpret_cast<uint64_t*>(gen_base + rec_off) + ew * kRecBuf;
+    int n_rec                = 0;  // staged records of this warp (warp-uniform)
 
-    // Writes init[] of the unit's base tile into the unit's accumulator slot and hands the slot to the MMA warp.
-    auto init_slot = [&](const Walker& w, int gu) -> bool {
-      const int st = w.ts % ns, slot = gu & (kSlots - 1);
-      if (!mbar_wait(smem_u32(&ctl->full[st]), (w.ts / ns) & 1, abort_flag, p.err, 6)) { return false; }
-      const int4* src      = reinterpret_cast<const int4*>(init_smem + st * kTileRows);
-      const uint32_t taddr = tmem + lane_base + static_cast<uint32_t>(slot * kTileRows);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        int32_t v[64];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int4 t = src[h * 16 + i];
-          v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
-        }
-        tmem_st64(taddr + h * 64, v);
-      }
-      tmem_wait_st();
-      tc_fence_before();
+    Cursor cur;
+    cur.s = 0, cur.j = 0, cur.ts = 0;
+    cursor_seg(cur, segs, nseg);
+    int gu  = 0;
+    bool ok = true;
+
+    // Staged records -> global memory: one atomic add reserves the range, the lanes copy.
+    auto flush = [&]() {
       __syncwarp();
-      if (lane == 0) { mbar_arrive(smem_u32(&ctl->tmem_ready[slot])); }
-      return true;
+      unsigned long long at = 0;
+      if (lane == 0) { at = atomicAdd(p.rec_count, static_cast<unsigned long long>(n_rec)); }
+      at = __shfl_sync(0xffffffffu, at, 0);
+      for (int i = lane; i < n_rec; i += 32) {
+        if (at + i < p.rec_cap) { p.rec[at + i] = rec_buf[i]; }
+      }
+      __syncwarp();
+      n_rec = 0;
+    };
+    // A chain of 16 columns that may hold survivors of some rows of the warp (`hit`): exact test per element.
+    auto records = [&](const int32_t* v, bool hit, int thr, int q, int64_t row0) {
+      const uint32_t ball = __ballot_sync(0xffffffffu, hit);
+      if (ball == 0u) { return; }
+      uint32_t mask = 0;
+      if (hit) {
+        const int4* e4 = reinterpret_cast<const int4*>(p.init + row0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int4 t = __ldg(e4 + i);
+          mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
+          mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
+          mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
+          mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
+        }
+      }
+      const uint32_t keep = __ballot_sync(0xffffffffu, mask != 0u);
+      if (keep == 0u) { return; }
+      const int n_new = __popc(keep);
+      if (n_rec + n_new > kRecBuf) { flush(); }
+      if (mask != 0u) {
+        rec_buf[n_rec + __popc(keep & ((1u << lane) - 1u))] =
+          make_record(static_cast<uint32_t>(q), static_cast<uint32_t>(row0 / kChainRows), mask);
+      }
+      n_rec += n_new;
     };
 
-    Walker cur, nxt;
-    cur.init(segs, nseg);
-    cur.advance(group);
-    nxt     = cur;
-    int gu  = group, gun = group;
-    bool ok = true;
-    for (int i = 0; i < 2 && nxt.valid && ok; ++i) {  // the group's first two units have no predecessor in their slots
-      ok = init_slot(nxt, gun);
-      nxt.advance(2);
-      gun += 2;
-    }
     while (ok && cur.valid) {
       const int slot = gu & (kSlots - 1);
-      const int q    = (segs[cur.s].q_tile0 + cur.j) * kTileRows + row;
+      const int q    = (cur.q_tile0 + cur.j) * kQueryTile + row;
       int thr        = 0x7fffffff;
-      if (p.mode == kModeScreen && q < p.nq) { thr = __ldg(p.thr + q); }
-      if (!mbar_wait(smem_u32(&ctl->tmem_full[slot]), (gu / kSlots) & 1, abort_flag, p.err, 7)) { break; }
+      int4 ce        = make_int4(0, 0, 0, 0);
+      if (MODE == kModeScreen) {
+        if (q < p.nq) { thr = __ldg(p.thr + q); }
+        // the four chain maxima of e for this warp's piece (one address per warp)
+        ce = __ldg(reinterpret_cast<const int4*>(p.cmax + static_cast<size_t>(cur.t) * (kBaseTile / kChainRows)) + piece);
+      }
+      if (!mbar_wait(smem_u32(&ctl->tmem_full[slot]), (gu >> 1) & 1, abort_flag, p.err, 7)) { break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + lane_base + static_cast<uint32_t>(slot * kTileRows);
-      int32_t a[64], b[64];
-      tmem_ld64(taddr, a);
+      const uint32_t taddr = tmem + lane_base + static_cast<uint32_t>(slot * kBaseTile + piece * kGroupRows);
+      int32_t a[32], b[32];
+      tmem_ld32(taddr, a);
+      tmem_ld32(taddr + 32, b);
       tmem_wait_ld(a);
-      tmem_ld64(taddr + 64, b);
-      const int ma = max_of(a);
-      if (p.mode == kModeScreen) {
-        if (ma >= thr) { emit_survivors(a, thr, q, cur.tile * kTileRows, p.n_rows, p.cnt, p.cand, p.cap); }
-        tmem_wait_ld(b);
-        const int mb = max_of(b);
-        if (mb >= thr) { emit_survivors(b, thr, q, cur.tile * kTileRows + 64, p.n_rows, p.cnt, p.cand, p.cap); }
+      reg_fence32(b);
+      // the piece is in registers: the slot goes back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(smem_u32(&ctl->tmem_empty[slot])); }
+
+      if (MODE == kModeScreen) {
+        const int m0 = max16(a), m1 = max16(a + 16), m2 = max16(b), m3 = max16(b + 16);
+        const bool h0 = m0 + ce.x >= thr, h1 = m1 + ce.y >= thr, h2 = m2 + ce.z >= thr, h3 = m3 + ce.w >= thr;
+        if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
+          const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
+          records(a, h0, thr, q, row0);
+          records(a + 16, h1, thr, q, row0 + 16);
+          records(b, h2, thr, q, row0 + 32);
+          records(b + 16, h3, thr, q, row0 + 48);
+        }
       } else {
-        tmem_wait_ld(b);
-        const int mb = max_of(b);
-        if (q < p.nq) { p.gmax[static_cast<size_t>(q) * p.ld_gmax + cur.tile] = max(ma, mb); }
+        // exact group maximum: e of the tile was staged with it
+        if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
+        const int32_t* e = init_smem + (cur.ts % ns) * kBaseTile + piece * kGroupRows;
+        const int m      = max(max32_plus(a, e), max32_plus(b, e + 32));
+        if (q < p.nq) { p.gmax[static_cast<size_t>(q) * p.ld_gmax + cur.t * (kBaseTile / kGroupRows) + piece] = m; }
       }
-      // the slot has been read: prepare it for the unit that uses it next
-      if (nxt.valid) {
-        ok = init_slot(nxt, gun);
-        nxt.advance(2);
-        gun += 2;
+      // next unit; a finished tile's e values are released (GROUPMAX)
+      ++gu;
+      if (++cur.j == cur.nqt) {
+        cur.j = 0;
+        if (kStageE) {
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(smem_u32(&ctl->empty[cur.ts % ns])); }
+        }
+        ++cur.ts;
+        if (++cur.t == cur.t1) {
+          ++cur.s;
+          cursor_seg(cur, segs, nseg);
+        }
       }
-      cur.advance(2);
-      gu += 2;
     }
+    if (MODE == kModeScreen && n_rec > 0) { flush(); }
   }
 
   // ---- teardown: all roles meet here, also when a wait gave up
@@ -331,17 +372,20 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
 
 size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages)
 {
-  return 1024 + static_cast<size_t>(panel_tiles + n_stages) * kb * kTileBytes + static_cast<size_t>(n_stages) * kTileRows * 4 +
-         sizeof(SharedCtl) + 64;
+  return 1024 + static_cast<size_t>(panel_tiles) * kb * kQTileBytes + static_cast<size_t>(n_stages) * kb * kBTileBytes +
+         static_cast<size_t>(n_stages) * kBaseTile * 4 + kEpiWarps * kRecBuf * 8 + sizeof(SharedCtl) + 64;
 }
 
 cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args, int grid, cudaStream_t stream)
 {
   const size_t smem = screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
   // opt-in to large dynamic shared memory (cheap; set on every launch so that every device of the process has it)
-  cudaError_t e = cudaFuncSetAttribute(screen_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  auto kernel = args.mode == kModeScreen     ? screen_i8_kernel<kModeScreen>
+                : args.mode == kModeGroupMax ? screen_i8_kernel<kModeGroupMax>
+                                             : screen_i8_kernel<kModeRate>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) { return e; }
-  screen_i8_kernel<<<grid, kThreads, smem, stream>>>(tm_q, tm_x, args);
+  kernel<<<grid, kThreads, smem, stream>>>(tm_q, tm_x, args);
   return cudaGetLastError();
 }
 

@@ -10,12 +10,20 @@ namespace certex_b200 {
 constexpr int kMaxSegs   = 4;  // segments (query panel, base-tile range) one CTA may be given
 constexpr int kMaxStages = 8;  // upper bound of the base-tile ring
 
-enum : int { kModeScreen = 0, kModeGroupMax = 1 };
+constexpr int kQueryTile = 128;  // queries per accumulator unit (TMEM lanes)
+constexpr int kBaseTile  = 256;  // stored rows per accumulator unit (TMEM columns, N of one MMA instruction)
+constexpr int kGroupRows = 64;   // rows per group maximum (one epilogue warp's piece of a unit)
+
+// kModeRate issues the loads and MMAs of every unit back to back with no epilogue (tensor-pipe rate probe).
+enum : int { kModeScreen = 0, kModeGroupMax = 1, kModeRate = 2 };
 
 /// Init value of a column that must never pass a threshold (removed rows, padding beyond the last row).
 constexpr int32_t kNeverInit = -(1 << 30);
 
-/// One contiguous piece of work of a CTA: query tiles [q_tile0, q_tile0 + n_qtiles) against base tiles [t0, t1).
+constexpr int kChainRows = 16;  // rows per chain: the unit of the conservative threshold test and of a survivor record
+
+/// One contiguous piece of work of a CTA: query tiles [q_tile0, q_tile0 + n_qtiles) against base tiles [t0, t1)
+/// (query tiles of 128 queries, base tiles of 256 rows).
 struct ScreenSeg {
   int q_tile0;
   int n_qtiles;
@@ -23,24 +31,31 @@ struct ScreenSeg {
   int t1;
 };
 
+/// A survivor record: bits 63..48 query (inside the batch), bits 47..16 chunk = row / 16, bits 15..0 one bit per row
+/// of the chunk that reached the query's threshold.
+__host__ __device__ inline uint64_t make_record(uint32_t q, uint32_t chunk, uint32_t mask16)
+{
+  return (static_cast<uint64_t>(q) << 48) | (static_cast<uint64_t>(chunk) << 16) | mask16;
+}
+
 struct ScreenArgs {
-  const int32_t* init;    // [n_tiles * 128] initial accumulator of every column (16-byte aligned)
-  const int32_t* thr;     // SCREEN: [nq] keep iff acc >= thr[q]
-  int32_t* gmax;          // GROUPMAX: [nq, ld_gmax] maximum of every 128-column group
+  const int32_t* init;            // [n_tiles * 256] per-row term e[x] added to <q, x> (kNeverInit: removed / padding)
+  const int32_t* cmax;            // SCREEN: [n_tiles * 16] maximum of e over every chain of 16 rows
+  const int32_t* thr;             // SCREEN: [nq] keep iff <q, x> + e[x] >= thr[q]
+  int32_t* gmax;                  // GROUPMAX: [nq, ld_gmax] maximum of <q, x> + e[x] over every group of 64 rows
   int64_t ld_gmax;
-  uint32_t* cnt;          // SCREEN: [nq] candidates found (may exceed cap: overflow)
-  int32_t* cand;          // SCREEN: [nq, cap] candidate rows
-  uint32_t cap;
+  uint64_t* rec;                  // SCREEN: survivor records
+  unsigned long long* rec_count;  // SCREEN: records appended (may exceed rec_cap: overflow, the excess is not written)
+  unsigned long long rec_cap;
   int nq;
-  int n_rows;             // rows >= n_rows are padding
-  int kb;                 // K blocks of 128 bytes per row
-  int panel_tiles;        // query tiles resident in shared memory
-  int n_stages;           // base-tile ring depth
+  int kb;                         // K blocks of 128 bytes per row
+  int panel_tiles;                // query tiles resident in shared memory
+  int n_stages;                   // base-tile ring depth
   int mode;
-  uint32_t q_signed;      // 0 = uint8 codes, 1 = int8 codes
+  uint32_t q_signed;              // 0 = uint8 codes, 1 = int8 codes
   uint32_t x_signed;
-  const ScreenSeg* segs;  // [grid, kMaxSegs]; unused entries have t1 <= t0
-  int* err;               // set to a non-zero code when a bounded wait gave up
+  const ScreenSeg* segs;          // [grid, kMaxSegs]; unused entries have t1 <= t0
+  int* err;                       // set to a non-zero code when a bounded wait gave up
 };
 
 size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages);

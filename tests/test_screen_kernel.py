@@ -21,10 +21,11 @@ SHAPES = [
     (129, 5000, 128, 1),
     (1000, 20011, 256, 0),
     (17, 333, 128, 0),
-    (64, 7777, 512, 1),
+    (64, 7777, 256, 1),
     (2100, 3000, 128, 0),
-    (130, 40000, 384, 0),
+    (130, 40000, 256, 0),
     (1, 128, 128, 0),
+    (513, 255, 128, 0),
 ]
 
 
@@ -32,13 +33,13 @@ def _run(mode, q, x, init, thr=None, cap=64, signed=0):
     L = _lib.lib()
     res = _lib.resources()
     nq, n, cl = q.shape[0], x.shape[0], x.shape[1]
-    nq_pad, n_pad = -(-nq // 128) * 128, -(-n // 128) * 128
+    nq_pad, n_pad = -(-nq // 128) * 128, -(-n // 256) * 256
     dq = torch.zeros((nq_pad, cl), dtype=torch.uint8, device="cuda")
     dq[:nq] = torch.from_numpy(q.view(np.uint8)).cuda()
     dx = torch.from_numpy(x.view(np.uint8)).cuda()
     dinit = torch.full((n_pad,), NEVER, dtype=torch.int32, device="cuda")
     dinit[:n] = torch.from_numpy(init).cuda()
-    ld = -(-(n_pad // 128) // 8) * 8
+    ld = -(-(n_pad // 64) // 8) * 8
     gmax = torch.full((nq, ld), -7, dtype=torch.int32, device="cuda")
     cnt = torch.zeros((nq,), dtype=torch.int32, device="cuda")
     cand = torch.full((nq, cap), -1, dtype=torch.int32, device="cuda")
@@ -69,12 +70,12 @@ def _data(nq, n, cl, signed, seed):
 def test_group_maxima_match_int32_gram(nq, n, cl, signed):
     q, x, init = _data(nq, n, cl, signed, seed=nq + n)
     acc = oracle.int_gram(q, x, init)
-    n_pad = -(-n // 128) * 128
+    n_pad = -(-n // 256) * 256
     full = np.full((nq, n_pad), NEVER, dtype=np.int64)
     full[:, :n] = acc
-    want = full.reshape(nq, n_pad // 128, 128).max(2)
+    want = full.reshape(nq, n_pad // 64, 64).max(2)
     gmax, _, _, _ = _run(1, q, x, init, signed=signed)
-    assert np.array_equal(gmax[:, : n_pad // 128], want)
+    assert np.array_equal(gmax[:, : n_pad // 64], want)
 
 
 @pytest.mark.parametrize("nq,n,cl,signed", SHAPES)
