@@ -351,15 +351,25 @@ __global__ void expand_records_kernel(const uint64_t* rec, const unsigned long l
   }
 }
 
-// Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk.
-__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr)
+// Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk. The row is copied to
+// shared memory first when it fits (vals != global row).
+__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr, int in_smem)
 {
+  extern __shared__ int32_t row_smem[];
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_remaining;
   const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
   if (ng < k) {
     if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(0x80000000u); }
     return;
+  }
+  if (in_smem) {
+    const int n4 = ng >> 2;  // rows start 16-byte aligned (ld is a multiple of 8)
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      reinterpret_cast<int4*>(row_smem)[i] = __ldg(reinterpret_cast<const int4*>(row) + i);
+    }
+    for (int i = (n4 << 2) + threadIdx.x; i < ng; i += blockDim.x) { row_smem[i] = row[i]; }
+    row = row_smem;
   }
   uint32_t prefix = 0, mask = 0, remaining = static_cast<uint32_t>(k);
   for (int shift = 24; shift >= 0; shift -= 8) {
@@ -370,21 +380,38 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
       if ((key & mask) == prefix) { atomicAdd(&hist[(key >> shift) & 255u], 1u); }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t cum = 0;
-      int b        = 255;
-      for (; b > 0; --b) {
-        if (cum + hist[b] >= remaining) { break; }
-        cum += hist[b];
+    if (threadIdx.x < 32) {
+      // bucket b (from the top) where the running count reaches `remaining`: warp scan over 8 buckets per lane
+      const int lane = threadIdx.x;
+      uint32_t c[8], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        c[i] = hist[255 - (lane * 8 + i)];
+        sum += c[i];
       }
-      s_prefix    = prefix | (static_cast<uint32_t>(b) << shift);
-      s_remaining = remaining - cum;
+      uint32_t incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) { incl += v; }
+      }
+      const uint32_t before = incl - sum;
+      const bool mine       = before < remaining && incl >= remaining;
+      if (mine) {
+        uint32_t cum = before;
+        int i        = 0;
+        for (; i < 7; ++i) {
+          if (cum + c[i] >= remaining) { break; }
+          cum += c[i];
+        }
+        s_prefix    = prefix | (static_cast<uint32_t>(255 - (lane * 8 + i)) << shift);
+        s_remaining = remaining - cum;
+      }
     }
     __syncthreads();
     prefix    = s_prefix;
     remaining = s_remaining;
     mask |= 0xffu << shift;
-    __syncthreads();
   }
   if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(prefix ^ 0x80000000u); }
 }
@@ -734,7 +761,10 @@ void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, c
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s)
 {
   if (nq <= 0) { return; }
-  kth_largest_kernel<<<nq, 256, 0, s>>>(gmax, ld, ng, k, thr);
+  const size_t bytes = static_cast<size_t>(ng) * 4;
+  const int in_smem  = bytes <= 160 * 1024;
+  if (in_smem) { allow_smem(kth_largest_kernel, bytes); }
+  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem);
 }
 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,

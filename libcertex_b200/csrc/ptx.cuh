@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA (cp.async.bulk[.tensor], never
-// with cluster multicast), tensor memory (tcgen05.alloc/ld/st) and the fifth-generation tensor-core MMA
+// with cluster multicast), tensor memory (tcgen05.alloc/ld) and the fifth-generation tensor-core MMA
 // (tcgen05.mma / tcgen05.commit). Every wait in here is bounded; see `mbar_wait`.
 #pragma once
 
@@ -149,20 +149,6 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_
     : "memory");
 }
 
-/// Same for fp16/bf16 operands with fp32 accumulate.
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc)
-{
-  asm volatile(
-    "{\n\t"
-    ".reg .pred p;\n\t"
-    "setp.ne.b32 p, %4, 0;\n\t"
-    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-    "}\n"
-    :
-    : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
-    : "memory");
-}
-
 /**
  * Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the 128-byte swizzle
  * (what a TMA box of 128 bytes x rows with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are 1024 bytes apart
@@ -188,86 +174,6 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t c_fmt, uint32_t a_fmt
   return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-// 32 lanes x 32-bit, 64 consecutive columns per thread: thread i of the warp reads lane (base lane + i).
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, int32_t (&v)[64])
-{
-  asm volatile(
-    "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-    "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-    "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]),
-      "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]),
-      "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]),
-      "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]),
-      "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
-    : "r"(taddr)
-    : "memory");
-}
-
-/// tcgen05.wait::ld that also names the 64 destination registers of the load as read-write operands, so that the
-/// compiler cannot move a use of them above the wait.
-__device__ __forceinline__ void tmem_wait_ld(int32_t (&v)[64])
-{
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]), "+r"(v[32]), "+r"(v[33]), "+r"(v[34]), "+r"(v[35]), "+r"(v[36]), "+r"(v[37]), "+r"(v[38]), "+r"(v[39]), "+r"(v[40]), "+r"(v[41]), "+r"(v[42]), "+r"(v[43]), "+r"(v[44]), "+r"(v[45]), "+r"(v[46]), "+r"(v[47]), "+r"(v[48]), "+r"(v[49]), "+r"(v[50]), "+r"(v[51]), "+r"(v[52]), "+r"(v[53]), "+r"(v[54]), "+r"(v[55]), "+r"(v[56]), "+r"(v[57]), "+r"(v[58]), "+r"(v[59]), "+r"(v[60]), "+r"(v[61]), "+r"(v[62]), "+r"(v[63])
-               :
-               : "memory");
-}
-
-/// Compiler-only fence on 64 registers (no instruction): placed after a wait, it keeps uses of `v` below the wait.
-__device__ __forceinline__ void reg_fence(int32_t (&v)[64])
-{
-  asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]), "+r"(v[32]), "+r"(v[33]), "+r"(v[34]), "+r"(v[35]), "+r"(v[36]), "+r"(v[37]), "+r"(v[38]), "+r"(v[39]), "+r"(v[40]), "+r"(v[41]), "+r"(v[42]), "+r"(v[43]), "+r"(v[44]), "+r"(v[45]), "+r"(v[46]), "+r"(v[47]), "+r"(v[48]), "+r"(v[49]), "+r"(v[50]), "+r"(v[51]), "+r"(v[52]), "+r"(v[53]), "+r"(v[54]), "+r"(v[55]), "+r"(v[56]), "+r"(v[57]), "+r"(v[58]), "+r"(v[59]), "+r"(v[60]), "+r"(v[61]), "+r"(v[62]), "+r"(v[63]) : : "memory");
-}
-
-__device__ __forceinline__ void tmem_st64(uint32_t taddr, const int32_t (&v)[64])
-{
-  asm volatile(
-    "tcgen05.st.sync.aligned.32x32b.x64.b32 [%64], "
-    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-    "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-    "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63};"
-    :
-    : "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
-      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
-      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
-      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]), "r"(v[32]), "r"(v[33]), "r"(v[34]), "r"(v[35]), "r"(v[36]),
-      "r"(v[37]), "r"(v[38]), "r"(v[39]), "r"(v[40]), "r"(v[41]), "r"(v[42]), "r"(v[43]), "r"(v[44]), "r"(v[45]),
-      "r"(v[46]), "r"(v[47]), "r"(v[48]), "r"(v[49]), "r"(v[50]), "r"(v[51]), "r"(v[52]), "r"(v[53]), "r"(v[54]),
-      "r"(v[55]), "r"(v[56]), "r"(v[57]), "r"(v[58]), "r"(v[59]), "r"(v[60]), "r"(v[61]), "r"(v[62]), "r"(v[63]),
-      "r"(taddr)
-    : "memory");
-}
-
-/**
- * Writes 16 TMEM lanes x 128 columns from 32 values per thread (shape 16x256b, 16 repeats along the columns). In this
- * shape thread t of the warp supplies, for column group i (columns 8i .. 8i+7), the two columns 8i + 2(t%4) and
- * 8i + 2(t%4) + 1 of lane t/4 and again of lane t/4 + 8. Here every lane receives the same row of values, so a
- * thread passes each of its 32 values e[2i], e[2i+1] twice.
- */
-__device__ __forceinline__ void tmem_st_rows16(uint32_t taddr, const int32_t (&e)[32])
-{
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x16.b32 [%64], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63};"
-               :
-               : "r"(e[0]), "r"(e[1]), "r"(e[0]), "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]), "r"(e[6]), "r"(e[7]), "r"(e[8]), "r"(e[9]), "r"(e[8]), "r"(e[9]), "r"(e[10]), "r"(e[11]), "r"(e[10]), "r"(e[11]), "r"(e[12]), "r"(e[13]), "r"(e[12]), "r"(e[13]), "r"(e[14]), "r"(e[15]), "r"(e[14]), "r"(e[15]), "r"(e[16]), "r"(e[17]), "r"(e[16]), "r"(e[17]), "r"(e[18]), "r"(e[19]), "r"(e[18]), "r"(e[19]), "r"(e[20]), "r"(e[21]), "r"(e[20]), "r"(e[21]), "r"(e[22]), "r"(e[23]), "r"(e[22]), "r"(e[23]), "r"(e[24]), "r"(e[25]), "r"(e[24]), "r"(e[25]), "r"(e[26]), "r"(e[27]), "r"(e[26]), "r"(e[27]), "r"(e[28]), "r"(e[29]), "r"(e[28]), "r"(e[29]), "r"(e[30]), "r"(e[31]), "r"(e[30]), "r"(e[31]), "r"(taddr)
-               : "memory");
-}
-
-/// Same for 64 columns (8 repeats): 16 values per thread.
-__device__ __forceinline__ void tmem_st_rows16_x8(uint32_t taddr, const int32_t (&e)[16])
-{
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x8.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
-               :
-               : "r"(e[0]), "r"(e[1]), "r"(e[0]), "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]), "r"(e[6]), "r"(e[7]), "r"(e[8]), "r"(e[9]), "r"(e[8]), "r"(e[9]), "r"(e[10]), "r"(e[11]), "r"(e[10]), "r"(e[11]), "r"(e[12]), "r"(e[13]), "r"(e[12]), "r"(e[13]), "r"(e[14]), "r"(e[15]), "r"(e[14]), "r"(e[15]), "r"(taddr)
-               : "memory");
-}
-
 // 32 lanes x 32-bit, 32 consecutive columns per thread.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32])
 {
@@ -277,22 +183,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32])
                : "memory");
 }
 
-/// tcgen05.wait::ld naming the 32 destination registers of a load (see tmem_wait_ld for 64).
+/// tcgen05.wait::ld that also names the 32 destination registers of a load as read-write operands, so that the
+/// compiler cannot move a use of them above the wait.
 __device__ __forceinline__ void tmem_wait_ld(int32_t (&v)[32])
 {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]) : : "memory");
 }
 
-/// 16 lanes x 32 columns from 8 values per thread (shape 16x256b, 4 repeats; see tmem_st_rows16).
-__device__ __forceinline__ void tmem_st_rows16_x4(uint32_t taddr, const int32_t (&e)[8])
-{
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-               :
-               : "r"(e[0]), "r"(e[1]), "r"(e[0]), "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]), "r"(e[6]), "r"(e[7]), "r"(taddr)
-               : "memory");
-}
-
-/// Compiler-only fence on 32 registers (see reg_fence).
+/// Compiler-only fence on 32 registers (no instruction): placed after a wait, it keeps uses of `v` below the wait.
 __device__ __forceinline__ void reg_fence32(int32_t (&v)[32])
 {
   asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]) : : "memory");

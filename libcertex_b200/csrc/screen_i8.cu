@@ -22,9 +22,9 @@
 // GROUPMAX writes gmax[q][group] = max over 64 rows of value (exact, e is staged in shared memory with the tile); the
 // k-th largest group maximum of a query is its threshold: k distinct stored rows are at least that close.
 //
-// CTA = 18 warps: warp 0 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
-// warp 1 lane 0 issues tcgen05.mma, warps 2..17 are the epilogue: four warps per TMEM lane quarter, each owning one
-// 64-column piece of every unit. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
+// CTA = 18 warps: warps 0..15 are the epilogue (four warps per TMEM lane quarter, each owning one 64-column piece of
+// every unit), warp 16 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
+// warp 17 lane 0 issues tcgen05.mma. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
 // epilogue reads the other; a slot goes back to the MMA warp as soon as its columns are in registers. No cluster
 // launch, no multicast: each CTA loads its own tiles from its GPU's memory.
 #include "screen_i8.cuh"
@@ -42,6 +42,9 @@ constexpr int kBTileBytes = kBaseTile * 128;   // one K block of a base tile: 25
 constexpr int kSlots      = 2;                 // TMEM accumulator slots (2 x 256 columns = all 512)
 constexpr int kEpiWarps   = 16;
 constexpr int kThreads    = 32 * (2 + kEpiWarps);
+// The two single-thread roles sit in the last two warps; warps 0..15 are the epilogue (TMEM lane quarter = warp % 4).
+constexpr int kTmaWarp    = kEpiWarps;
+constexpr int kMmaWarp    = kEpiWarps + 1;
 constexpr int kRecBuf     = 64;                // staged survivor records per epilogue warp
 
 struct SharedCtl {
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   SharedCtl* ctl           = reinterpret_cast<SharedCtl*>(gen_base + ctl_off);
   const int32_t* init_smem = reinterpret_cast<const int32_t*>(gen_base + init_off);
   volatile int* abort_flag = &ctl->abort_flag;
-  constexpr bool kStageE   = MODE == kModeGroupMax;  // e values travel with the tile and are read by the epilogue
+  constexpr bool kStageE   = MODE != kModeRate;  // e values travel with the tile and are read by the epilogue
 
   const ScreenSeg* segs = ctl->segs;
   if (threadIdx.x < kMaxSegs) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_x);
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&ctl->tmem_base), 512);
     tmem_relinquish();
   }
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 
-  if (warp == 0) {
+  if (warp == kTmaWarp) {
     // ================================================================ TMA producer
     if (lane == 0) {
       int ts       = 0;
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ================================================================ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(2u, p.q_signed, p.x_signed, kQueryTile, kBaseTile);
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     }
   } else if (MODE != kModeRate) {
     // ================================================================ epilogue (16 warps, one 64-column piece each)
-    const int ew             = warp - 2;
+    const int ew             = warp;
     const int piece          = ew >> 2;   // which 64 columns of a unit
     const int quarter        = warp & 3;  // the TMEM lane quarter this warp may access
     const int row            = quarter * 32 + lane;
@@ -277,15 +280,15 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       n_rec = 0;
     };
     // A chain of 16 columns that may hold survivors of some rows of the warp (`hit`): exact test per element.
-    auto records = [&](const int32_t* v, bool hit, int thr, int q, int64_t row0) {
+    auto records = [&](const int32_t* v, bool hit, int thr, int q, int64_t row0, const int32_t* e) {
       const uint32_t ball = __ballot_sync(0xffffffffu, hit);
       if (ball == 0u) { return; }
       uint32_t mask = 0;
       if (hit) {
-        const int4* e4 = reinterpret_cast<const int4*>(p.init + row0);
+        const int4* e4 = reinterpret_cast<const int4*>(e);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int4 t = __ldg(e4 + i);
+          const int4 t = e4[i];
           mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
           mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
           mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
@@ -330,11 +333,14 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         const int m0 = max16(a), m1 = max16(a + 16), m2 = max16(b), m3 = max16(b + 16);
         const bool h0 = m0 + ce.x >= thr, h1 = m1 + ce.y >= thr, h2 = m2 + ce.z >= thr, h3 = m3 + ce.w >= thr;
         if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
+          // the exact e of the tile was staged with it
+          if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
+          const int32_t* e   = init_smem + (cur.ts % ns) * kBaseTile + piece * kGroupRows;
           const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
-          records(a, h0, thr, q, row0);
-          records(a + 16, h1, thr, q, row0 + 16);
-          records(b, h2, thr, q, row0 + 32);
-          records(b + 16, h3, thr, q, row0 + 48);
+          records(a, h0, thr, q, row0, e);
+          records(a + 16, h1, thr, q, row0 + 16, e + 16);
+          records(b, h2, thr, q, row0 + 32, e + 32);
+          records(b + 16, h3, thr, q, row0 + 48, e + 48);
         }
       } else {
         // exact group maximum: e of the tile was staged with it
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) { tmem_dealloc(tmem, 512); }
+  if (warp == kMmaWarp) { tmem_dealloc(tmem, 512); }
 }
 
 }  // namespace

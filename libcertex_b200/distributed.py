@@ -21,11 +21,12 @@ def shard_bounds(n, world, rank):
 def gather_lists(scores, ids, group=None):
     """All-gather of per-rank answer lists: ([world, nq, k] scores, [world, nq, k] ids) on every rank."""
     world = dist.get_world_size(group)
-    all_s = torch.empty((world,) + tuple(scores.shape), dtype=scores.dtype, device=scores.device)
-    all_i = torch.empty((world,) + tuple(ids.shape), dtype=ids.dtype, device=ids.device)
+    nq, k = scores.shape
+    all_s = torch.empty((world * nq, k), dtype=scores.dtype, device=scores.device)  # rank-major concatenation
+    all_i = torch.empty((world * nq, k), dtype=ids.dtype, device=ids.device)
     dist.all_gather_into_tensor(all_s, scores.contiguous(), group=group)
     dist.all_gather_into_tensor(all_i, ids.contiguous(), group=group)
-    return all_s, all_i
+    return all_s.view(world, nq, k), all_i.view(world, nq, k)
 
 
 class DistributedIndex:

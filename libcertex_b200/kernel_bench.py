@@ -32,9 +32,11 @@ def main():
     q[:nq] = torch.randint(0, 256, (nq, cl), generator=g, device="cuda", dtype=torch.uint8)
     x = torch.randint(0, 256, (n, cl), generator=g, device="cuda", dtype=torch.uint8)
     init = torch.full((n_pad,), -(1 << 30), dtype=torch.int32, device="cuda")
-    init[:n] = -((x.long() ** 2).sum(1) >> 1).int()
+    for i in range(0, n, 1 << 20):  # chunked: the int64 squares of a large x would not fit
+        init[i : i + (1 << 20)][: min(1 << 20, n - i)] = -((x[i : i + (1 << 20)].long() ** 2).sum(1) >> 1).int()
     ld = -(-(n_pad // 64) // 8) * 8
-    gmax = torch.zeros((nq, ld), dtype=torch.int32, device="cuda")
+    need_gmax = args.mode == "groupmax" or args.survivors > 0
+    gmax = torch.zeros((nq if need_gmax else 1, ld), dtype=torch.int32, device="cuda")
     cap = 4096
     cnt = torch.zeros((nq,), dtype=torch.int32, device="cuda")
     cand = torch.zeros((nq, cap), dtype=torch.int32, device="cuda")

@@ -1,0 +1,168 @@
+"""Updates and filtered search on the GPU against the CPU oracle with a keep predicate: removals (including every
+query's true nearest neighbour), additions after removals, labels at several selectivities, labels after extend and
+remove, bitset and bitmap filters, save / load, a reader concurrent with a writer. The scenarios follow the reference's
+cpp/tests/neighbors/ann_certex/test_updates.cu:92-591 and tests/test_exact.py."""
+
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+import libcertex_b200 as certex
+from libcertex_b200 import synthetic
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def data(n, dim, nq, dtype, seed=5):
+    return synthetic.correlated(n, dim, seed=seed, dtype=dtype), synthetic.correlated(nq, dim, seed=seed + 1, dtype=dtype)
+
+
+def same(index, x, q, k, metric="l2", keep_row=None, keep_pair=None, row_labels=None, query_labels=None, **kw):
+    _, I, S = index.search(q, k=k, return_scores=True, **kw)
+    ids, scores = oracle.knn(x, q, k, metric, keep_row=keep_row, keep_pair=keep_pair, row_labels=row_labels,
+                             query_labels=query_labels)
+    assert np.array_equal(I, ids), f"{(I != ids).any(1).sum()} of {len(ids)} queries differ"
+    assert np.array_equal(S, scores)
+
+
+@pytest.mark.parametrize("dtype", ["uint8", "float32"])
+def test_remove_then_add(dtype):
+    x, q = data(30000, 48, 300, dtype)
+    index = certex.Index(48, capacity=12000)
+    index.add(x[:20000])
+    same(index, x[:20000], q, 10)
+    # remove every query's nearest neighbour and a random 5 %
+    nn, _ = oracle.knn(x[:20000], q, 1, "l2")
+    rng = np.random.default_rng(0)
+    gone = np.unique(np.concatenate([nn[:, 0], rng.choice(20000, 1000, replace=False)]))
+    index.remove(gone)
+    index.remove(gone[:10])  # removing twice changes nothing
+    keep = np.ones(20000, dtype=np.uint8)
+    keep[gone] = 0
+    assert index.ntotal == 20000 - len(gone)
+    same(index, x[:20000], q, 10, keep_row=keep)
+    # ids continue after the removed ones and are never reused
+    new_ids = index.add(x[20000:])
+    assert new_ids[0] == 20000 and new_ids[-1] == 29999
+    keep = np.concatenate([keep, np.ones(10000, dtype=np.uint8)])
+    same(index, x, q, 10, keep_row=keep)
+
+
+@pytest.mark.parametrize("n_labels", [5, 50, 500, 5000])
+def test_search_by_label(n_labels):
+    x, q = data(20000, 32, 200, "uint8")
+    rng = np.random.default_rng(1)
+    lab = rng.integers(0, n_labels, 20000).astype(np.int32)
+    ql = rng.integers(0, n_labels, 200).astype(np.int32)
+    index = certex.Index(32)
+    index.add(x, labels=lab)
+    same(index, x, q, 10, row_labels=lab, query_labels=ql, labels=ql)
+    with pytest.raises(ValueError):
+        index.add(x[:5])  # a labeled index needs labels with every addition
+
+
+def test_labels_after_extend_and_remove():
+    x, q = data(24000, 40, 150, "float32")
+    rng = np.random.default_rng(2)
+    lab = rng.integers(0, 16, 24000).astype(np.int32)
+    ql = rng.integers(0, 17, 150).astype(np.int32)  # label 16 has no vectors: all -1
+    index = certex.Index(40)
+    index.add(x[:16000], labels=lab[:16000])
+    index.add(x[16000:], labels=lab[16000:])
+    gone = rng.choice(24000, 2000, replace=False)
+    index.remove(gone)
+    masked = lab.copy()
+    masked[gone] = -1  # the oracle treats -1 as "matches nothing"
+    D, I, S = index.search(q, k=10, labels=ql, return_scores=True)
+    ids, scores = oracle.knn(x, q, 10, "l2", row_labels=masked, query_labels=ql)
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    assert (I[ql == 16] == -1).all() and np.isinf(D[ql == 16]).all()
+
+
+@pytest.mark.parametrize("dtype", ["uint8", "float16"])
+def test_bitset_and_bitmap(dtype):
+    x, q = data(15000, 64, 120, dtype)
+    rng = np.random.default_rng(3)
+    index = certex.Index(64)
+    index.add(x)
+    mask = rng.random(15000) < 0.3
+    same(index, x, q, 10, keep_row=mask.astype(np.uint8), filter=mask)
+    per_query = rng.random((120, 15000)) < 0.05
+    per_query[7] = False  # a query with no admitted vector
+    per_query[8, :3] = True
+    per_query[8, 3:] = False  # fewer than k admitted
+    D, I, S = index.search(q, k=10, filter=per_query, return_scores=True)
+    ids, scores = oracle.knn(x, q, 10, "l2", keep_pair=per_query.astype(np.uint8))
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    assert (I[7] == -1).all() and (I[8, 3:] == -1).all() and (I[8, :3] >= 0).all()
+
+
+@pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("float32", "cosine")])
+def test_save_load(tmp_path, dtype, metric):
+    x, q = data(12000, 32, 100, dtype)
+    index = certex.Index(32, metric=metric)
+    rng = np.random.default_rng(4)
+    lab = rng.integers(0, 4, 12000).astype(np.int32)
+    index.add(x, labels=lab)
+    gone = rng.choice(12000, 500, replace=False)
+    index.remove(gone)
+    D0, I0 = index.search(q, k=10)
+    path = tmp_path / "index.bin"
+    index.save(path)
+    loaded = certex.Index.load(path)
+    assert loaded.ntotal == index.ntotal and loaded.metric == metric
+    D1, I1 = loaded.search(q, k=10)
+    assert np.array_equal(I0, I1) and np.array_equal(D0, D1)
+    ql = rng.integers(0, 4, 100).astype(np.int32)
+    _, Ia = index.search(q, k=5, labels=ql)
+    _, Ib = loaded.search(q, k=5, labels=ql)
+    assert np.array_equal(Ia, Ib)
+
+
+def test_search_concurrent_with_extend():
+    """A search sees one consistent snapshot: its result equals the exact answer over one of the published prefixes
+    (the reference's cpp/tests/neighbors/ann_certex/test_updates.cu:504-591)."""
+    x, q = data(40000, 32, 64, "uint8")
+    index = certex.Index(32)
+    index.add(x[:10000])
+    prefixes = [10000, 20000, 30000, 40000]
+    answers = [oracle.knn(x[:p], q, 10, "l2")[0] for p in prefixes]
+    results, errors = [], []
+
+    def reader():
+        try:
+            for _ in range(30):
+                _, I = index.search(q, k=10)
+                results.append(I)
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    def writer():
+        try:
+            for p0, p1 in zip(prefixes[:-1], prefixes[1:]):
+                index.add(x[p0:p1])
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=reader) for _ in range(3)] + [threading.Thread(target=writer)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for I in results:
+        assert any(np.array_equal(I, a) for a in answers)
+    _, I = index.search(q, k=10)
+    assert np.array_equal(I, answers[-1])
+
+
+def test_removed_rows_exceeding_k_leave_missing_entries():
+    x, q = data(64, 16, 20, "uint8")
+    index = certex.Index(16)
+    index.add(x)
+    index.remove(np.arange(60))
+    D, I = index.search(q, k=10)
+    assert (I[:, 4:] == -1).all() and (I[:, :4] >= 60).all() and np.isinf(D[:, 4:]).all()
