@@ -99,6 +99,23 @@ ScreenShape shape_for(int kb)
   return kb == 1 ? ScreenShape{7, 3} : ScreenShape{2, 2};
 }
 
+/// 3-D map (bytes of a row, column of a tile, tile) with free byte strides between columns and between tiles; box
+/// 128 bytes x 256 columns x 1 tile. The anchors of the threshold stage use it: anchor a = sorted row a * stride, and
+/// column c of tile t is anchor c * n_tiles + t (column stride n_tiles * stride rows, tile stride `stride` rows).
+CUtensorMap make_tile_map(const void* base, uint64_t row_bytes, uint64_t column_stride, uint64_t tile_stride, uint64_t n_tiles)
+{
+  CUtensorMap m;
+  const cuuint64_t dims[3]    = {row_bytes, static_cast<cuuint64_t>(kBaseTile), n_tiles};
+  const cuuint64_t strides[2] = {column_stride, tile_stride};
+  const cuuint32_t box[3]     = {128, static_cast<cuuint32_t>(kBaseTile), 1};
+  const cuuint32_t estr[3]    = {1, 1, 1};
+  const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CERTEX_EXPECTS(r == CUDA_SUCCESS, "certex: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return m;
+}
+
 /// Splits nqt query tiles x nt base tiles over `grid` CTAs: query tiles are grouped into panels of at most
 /// `panel_tiles`; the (panel, base tile) items are laid out panel-major and cut into `grid` ranges of equal unit count.
 std::vector<ScreenSeg> plan_segments(int nqt, int nt, int panel_tiles, int grid)
@@ -354,8 +371,8 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   const int grid          = res.sm_count;
   const ScreenShape shape = shape_for(kb_);
   const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
-  const int64_t n_anchor  = (n + anchor_stride - 1) / anchor_stride;
-  const int nt_anchor     = static_cast<int>((n_anchor + kTile - 1) / kTile);
+  // anchors: sorted rows 0, stride, 2 stride, ...; only whole tiles of 256 anchors take part
+  const int nt_anchor     = static_cast<int>(n / (static_cast<int64_t>(anchor_stride) * kTile));
   const int nt_all        = static_cast<int>((n + kTile - 1) / kTile);
   const int n_groups      = nt_anchor * (kBaseTile / kGroupRows);
   const int64_t ld_g      = round_up(n_groups, 8);
@@ -378,12 +395,13 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   CERTEX_CUDA(cudaMemcpyAsync(d_segs + seg_a.size(), seg_s.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
-  launch_gather_init(init_, anchor_stride, n_anchor, static_cast<int64_t>(nt_anchor) * kTile, anchor_init, res.stream);  // e of the anchors
+  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream);  // e of the anchors
   CERTEX_CUDA(cudaGetLastError());
 
   const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * pitch_;
   const CUtensorMap tm_q = make_code_map(qb, pitch_, static_cast<uint64_t>(round_up(nq, kQTile)), pitch_, kQueryTile);
-  const CUtensorMap tm_a = make_code_map(codes_, pitch_, static_cast<uint64_t>(n_anchor), pitch_ * anchor_stride, kBaseTile);
+  const CUtensorMap tm_a = make_tile_map(codes_, pitch_, static_cast<uint64_t>(nt_anchor) * anchor_stride * pitch_,
+                                         static_cast<uint64_t>(anchor_stride) * pitch_, static_cast<uint64_t>(nt_anchor));
   const CUtensorMap tm_x = make_code_map(codes_, pitch_, static_cast<uint64_t>(n), pitch_, kBaseTile);
 
   ScreenArgs a{};
@@ -462,8 +480,9 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   adm.query_labels    = filter.query_labels;
   const bool filtered = filter.words != nullptr || filter.query_labels != nullptr;
 
-  // anchors: every stride-th row, and at least 2k groups of 64 anchors, or the threshold would be useless
-  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (int64_t(kGroupRows) * 2 * k)));
+  // anchors: every stride-th row in whole tiles of 256, and at least 2k groups of 64 anchors, or the threshold would be
+  // useless
+  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (kTile * ((2 * k + 3) / 4))));
   const bool screened = int_screen_ && !filtered && stride >= 1 && test_mode_ != 1;
 
   SearchStats local{};
@@ -668,7 +687,14 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(err, 0, sizeof(int), res.stream));
   const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kQTile)), code_len, kQueryTile);
-  const CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len, kBaseTile);
+  CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len, kBaseTile);
+  if (mode == kModeGroupMax) {
+    // group maxima over consecutive rows: the pass reads whole tiles through the 3-D map, so the rows are padded
+    uint8_t* x_pad = scratch.get<uint8_t>(static_cast<size_t>(nt) * kTile * code_len);
+    CERTEX_CUDA(cudaMemsetAsync(x_pad, 0, static_cast<size_t>(nt) * kTile * code_len, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(x_pad, x_codes, static_cast<size_t>(n) * code_len, cudaMemcpyDeviceToDevice, res.stream));
+    tm_x = make_tile_map(x_pad, code_len, code_len, static_cast<uint64_t>(kTile) * code_len, static_cast<uint64_t>(nt));
+  }
   // init arrives for n rounded up to 64 rows; the pass reads whole base tiles, and chain maxima
   const int64_t n_in  = round_up(n, kGroupRows);
   const int64_t n_pad = static_cast<int64_t>(nt) * kTile;

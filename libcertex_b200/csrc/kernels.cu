@@ -241,12 +241,13 @@ __global__ void row_init_kernel(const uint8_t* vectors, size_t pitch, int d, int
   }
 }
 
-__global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out)
+// e of the anchors in tile order: out[t * 256 + c] = init[(c * n_tiles + t) * stride].
+__global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (j < n_pad) {
-    const int64_t r = j * stride;
-    out[j] = j < n_anchor ? init[r] : kNeverInit;
+  if (j < n_tiles * kBaseTile) {
+    const int64_t t = j / kBaseTile, c = j % kBaseTile;
+    out[j]          = init[(c * n_tiles + t) * stride];
   }
 }
 
@@ -713,10 +714,10 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
   }
 }
 
-void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out, cudaStream_t s)
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s)
 {
-  if (n_pad <= 0) { return; }
-  gather_init_kernel<<<static_cast<unsigned>((n_pad + 255) / 256), 256, 0, s>>>(init, stride, n_anchor, n_pad, out);
+  if (n_tiles <= 0) { return; }
+  gather_init_kernel<<<static_cast<unsigned>(n_tiles), kBaseTile, 0, s>>>(init, stride, n_tiles, out);
 }
 
 void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,

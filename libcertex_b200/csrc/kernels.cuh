@@ -25,8 +25,8 @@ struct Admit {
 void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int metric, const uint8_t* removed,
                      int64_t row0, int64_t n, int64_t n_pad, int32_t* init, cudaStream_t s);
 
-/// out[j] = init[j * stride] for j < n_anchor, kNeverInit up to n_pad.
-void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_anchor, int64_t n_pad, int32_t* out, cudaStream_t s);
+/// e of the anchors of the threshold stage in tile order: out[t * 256 + c] = init[(c * n_tiles + t) * stride].
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s);
 
 /// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1.
 void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, cudaStream_t s);

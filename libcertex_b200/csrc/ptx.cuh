@@ -98,6 +98,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
     : "memory");
 }
 
+/// 3-D tiled load (same shared-memory layout as the 2-D load of the box's two inner dimensions).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, int32_t x, int32_t y, int32_t z, uint32_t bar)
+{
+  asm volatile(
+    "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+    :
+    : "r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+    : "memory");
+}
+
 /// 1-D bulk copy global -> shared; both addresses 16-byte aligned, `bytes` a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
 {

@@ -19,8 +19,10 @@
 // never rejects a pair that should be kept. Only a chain that passes it (rare) is looked at element by element with
 // the exact e[x]; its survivors form one record (query, chain, 16-bit mask) in the warp's staging buffer in shared
 // memory, and a full buffer goes to global memory with one atomic add for the whole batch.
-// GROUPMAX writes gmax[q][group] = max over 64 rows of value (exact, e is staged in shared memory with the tile); the
-// k-th largest group maximum of a query is its threshold: k distinct stored rows are at least that close.
+// GROUPMAX writes gmax[q][group] = max over 64 anchors of value (exact, e is staged in shared memory with the tile);
+// the k-th largest group maximum of a query is its threshold: k distinct stored rows are at least that close. The
+// anchors of one tile are spread over the whole sorted set (column c of tile t is anchor c * n_tiles + t), so that the
+// anchors of one cluster of similar rows do not share a group.
 //
 // CTA = 18 warps: warps 0..15 are the epilogue (four warps per TMEM lane quarter, each owning one 64-column piece of
 // every unit), warp 16 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
@@ -189,7 +191,13 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           const uint32_t fbar = smem_u32(&ctl->full[st]);
           mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(kb) * kBTileBytes + (kStageE ? kBaseTile * 4 : 0));
           for (int b = 0; b < kb; ++b) {
-            tma_load_2d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
+            if (MODE == kModeGroupMax) {
+              // anchors: column c of tile t is anchor c * n_tiles + t, so every group of 64 columns samples the whole
+              // (norm-sorted) set; the map is 3-D (bytes, column, tile)
+              tma_load_3d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, t, fbar);
+            } else {
+              tma_load_2d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
+            }
           }
           if (kStageE) {
             bulk_load_1d(base + init_off + st * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4, fbar);
