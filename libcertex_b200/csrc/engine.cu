@@ -351,12 +351,15 @@ void Index::search_dense(const Resources& res, const void* q, size_t qpitch, con
   const int64_t budget  = int64_t(1) << 30;  // bytes of score matrix per step
   const int step        = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nqb, budget / (ld * 8))));
   double* scores        = scratch.get<double>(static_cast<size_t>(step) * ld);
+  const int parts       = select_topk_parts(n, k);
+  double* part_s        = scratch.get<double>(static_cast<size_t>(step) * parts * k);
+  int32_t* part_row     = scratch.get<int32_t>(static_cast<size_t>(step) * parts * k);
   for (int b = 0; b < nqb; b += step) {
     const int nb = std::min(step, nqb - b);
     launch_dense_scores(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, n, q, qpitch,
                         qsel ? qsel + b : nullptr, q0 + b, nb, adm, scores, ld, res.stream);
     CERTEX_CUDA(cudaGetLastError());
-    launch_select_topk(scores, ld, n, k, qsel ? qsel + b : nullptr, q0 + b, nb, best_s, best_row, res.stream);
+    launch_select_topk(scores, ld, n, k, qsel ? qsel + b : nullptr, q0 + b, nb, best_s, best_row, part_s, part_row, res.stream);
     CERTEX_CUDA(cudaGetLastError());
   }
 }

@@ -18,6 +18,8 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <algorithm>
+
 namespace certex_b200 {
 
 namespace {
@@ -503,8 +505,8 @@ __global__ void dense_scores_kernel(const uint8_t* vectors, size_t pitch, int d,
 
 // Block per query: radix walk to the k-th smallest score, then the winners (ties: smallest rows) are gathered, sorted
 // and written. Shared memory: sel_s [k2] doubles | sel_id [k2] int32.
-__global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0,
-                                   double* best_s, int32_t* best_row)
+__global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n_all, int k, const int32_t* qsel, int q0,
+                                   double* best_s, int32_t* best_row, int64_t chunk, double* part_s, int32_t* part_row)
 {
   extern __shared__ double sh[];
   __shared__ uint32_t hist[256];
@@ -513,7 +515,10 @@ __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, 
   const int k2        = max(next_pow2(k), 2);
   double* sel_s       = sh;
   int32_t* sel_id     = reinterpret_cast<int32_t*>(sh + k2);
-  const double* row   = scores + static_cast<int64_t>(blockIdx.x) * ld;
+  // blockIdx.y selects a chunk of columns [col0, col0 + n); with several chunks the winners go to part_* and are merged
+  const int64_t col0  = static_cast<int64_t>(blockIdx.y) * chunk;
+  const int64_t n     = min(chunk, n_all - col0);
+  const double* row   = scores + static_cast<int64_t>(blockIdx.x) * ld + col0;
   const int64_t qout  = qsel ? qsel[blockIdx.x] : q0 + static_cast<int>(blockIdx.x);
   const uint32_t want = static_cast<uint32_t>(min(static_cast<int64_t>(k), n));
 
@@ -568,7 +573,7 @@ __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, 
         if (key < prefix) {
           const uint32_t pos = atomicAdd(&s_less, 1u);
           sel_s[pos]         = v;
-          sel_id[pos]        = static_cast<int32_t>(j);
+          sel_id[pos]        = static_cast<int32_t>(col0 + j);
         }
         eq = key == prefix;
       }
@@ -582,7 +587,7 @@ __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, 
         const uint32_t rank = before + __popc(ball & ((1u << lane) - 1u));
         if (eq && rank < remaining) {
           sel_s[n_less + rank]  = v;
-          sel_id[n_less + rank] = static_cast<int32_t>(j);
+          sel_id[n_less + rank] = static_cast<int32_t>(col0 + j);
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -597,9 +602,37 @@ __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n, 
   __syncthreads();
   bitonic_sort(sel_s, sel_id, k2);
   for (int t = threadIdx.x; t < k; t += blockDim.x) {
-    const bool have                            = sel_s[t] < CUDART_INF;
-    best_s[static_cast<size_t>(qout) * k + t]   = have ? sel_s[t] : CUDART_INF;
-    best_row[static_cast<size_t>(qout) * k + t] = have ? sel_id[t] : -1;
+    const bool have = sel_s[t] < CUDART_INF;
+    if (part_s) {
+      const size_t o = (static_cast<size_t>(blockIdx.x) * gridDim.y + blockIdx.y) * k + t;
+      part_s[o]      = have ? sel_s[t] : CUDART_INF;
+      part_row[o]    = have ? sel_id[t] : 0x7fffffff;
+    } else {
+      best_s[static_cast<size_t>(qout) * k + t]   = have ? sel_s[t] : CUDART_INF;
+      best_row[static_cast<size_t>(qout) * k + t] = have ? sel_id[t] : -1;
+    }
+  }
+}
+
+// Block per query: the k best of `parts` partial lists of k (score, row) pairs each, by (score, row).
+// Shared memory: s [n2] doubles | row [n2] int32.
+__global__ void merge_partials_kernel(const double* part_s, const int32_t* part_row, int parts, int k, int n2,
+                                      const int32_t* qsel, int q0, double* best_s, int32_t* best_row)
+{
+  extern __shared__ double sh[];
+  double* s    = sh;
+  int32_t* row = reinterpret_cast<int32_t*>(sh + n2);
+  const int m  = parts * k;
+  for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+    s[i]   = i < m ? part_s[static_cast<size_t>(blockIdx.x) * m + i] : CUDART_INF;
+    row[i] = i < m ? part_row[static_cast<size_t>(blockIdx.x) * m + i] : 0x7fffffff;
+  }
+  bitonic_sort(s, row, n2);
+  const int64_t qout = qsel ? qsel[blockIdx.x] : q0 + static_cast<int>(blockIdx.x);
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    const bool have                            = s[t] < CUDART_INF;
+    best_s[static_cast<size_t>(qout) * k + t]   = have ? s[t] : CUDART_INF;
+    best_row[static_cast<size_t>(qout) * k + t] = have ? row[t] : -1;
   }
 }
 
@@ -826,13 +859,31 @@ void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, in
   });
 }
 
+int select_topk_parts(int64_t n, int k)
+{
+  // long rows are cut into chunks that separate blocks select from; at most 8192 partial winners per query
+  if (n <= (1 << 18)) { return 1; }
+  const int64_t by_size = (n + (1 << 17) - 1) >> 17;
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({by_size, 64, 8192 / k})));
+}
+
 void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0, int nqb,
-                        double* best_s, int32_t* best_row, cudaStream_t s)
+                        double* best_s, int32_t* best_row, double* part_s, int32_t* part_row, cudaStream_t s)
 {
   if (nqb <= 0) { return; }
   const int k2      = next_pow2(k) < 2 ? 2 : next_pow2(k);
   const size_t smem = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(k2);
-  select_topk_kernel<<<nqb, 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row);
+  const int parts   = select_topk_parts(n, k);
+  if (parts == 1) {
+    select_topk_kernel<<<nqb, 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, n, nullptr, nullptr);
+    return;
+  }
+  const int64_t chunk = (n + parts - 1) / parts;
+  select_topk_kernel<<<dim3(nqb, parts), 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, chunk, part_s, part_row);
+  const int n2       = next_pow2(parts * k);
+  const size_t smem2 = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(n2);
+  allow_smem(merge_partials_kernel, smem2);
+  merge_partials_kernel<<<nqb, 256, smem2, s>>>(part_s, part_row, parts, k, n2, qsel, q0, best_s, best_row);
 }
 
 void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_base, const void* queries, size_t qpitch,

@@ -75,8 +75,11 @@ void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, in
                          cudaStream_t s);
 
 /// k best (score, row) of every row of scores [nqb, ld] (n valid columns); writes result row qsel[i] (or q0 + i).
+/// Long rows are selected from in select_topk_parts(n, k) chunks by separate blocks and merged; part_s / part_row are
+/// scratch of nqb * parts * k elements (unused when parts == 1).
+int select_topk_parts(int64_t n, int k);
 void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0, int nqb,
-                        double* best_s, int32_t* best_row, cudaStream_t s);
+                        double* best_s, int32_t* best_row, double* part_s, int32_t* part_row, cudaStream_t s);
 
 /// neighbors / distances / (optional) fp64 scores of the public result from the internal best lists.
 /// id = row < 0 ? -1 : id_base + row. Distances: L2 s, inner product (|q|^2 - s) / 2, cosine s / 2.

@@ -115,6 +115,27 @@ def test_overflowing_candidate_lists_fall_back_to_the_dense_path():
     check(index, x, q, 10, "l2")
 
 
+def test_dense_path_on_long_rows():
+    """Rows longer than 2^18 are selected from in chunks by separate blocks and merged; ties across chunks go to the
+    smaller id."""
+    x = synthetic.correlated(700_000, 16, seed=9, dtype="float32")
+    q = synthetic.correlated(24, 16, seed=10, dtype="float32")
+    x[150_000] = x[7]
+    x[420_001] = x[7]
+    x[699_999] = x[7]
+    q[0] = x[7]
+    index = certex.Index(16)
+    index.add(x)
+    check(index, x, q, 10, "l2")
+    check(index, x, q, 300, "l2")
+    xi = synthetic.correlated(400_000, 32, seed=11, dtype="uint8")
+    qi = synthetic.correlated(16, 32, seed=12, dtype="uint8")
+    ii = certex.Index(32)
+    ii.add(xi)
+    ii._test_mode(1)  # the dense path on an integer index
+    check(ii, xi, qi, 10, "l2")
+
+
 def test_mixture_sample():
     """The benchmark's data distribution at a size the oracle finishes quickly."""
     xb = synthetic.mixture_u8(1_000_000, seed=0)
