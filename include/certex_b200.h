@@ -271,6 +271,31 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const vo
 CERTEX_B200_EXPORT cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
                                                       int32_t grid, int32_t* out);
 
+/**
+ * Exact search that allocates no device memory. It has no counterpart in the reference, whose searches take their
+ * temporaries from a memory pool. It exists for callers that cannot allocate on the GPU at search time: a process in
+ * which another allocator has already claimed the device's memory (an inference server that reserves the whole GPU at
+ * start-up), or a latency-bound loop that cannot accept the device-wide synchronisation an allocation or a free may
+ * cause. The caller passes plain device pointers to its own buffers: vectors [n_rows, dim] and queries
+ * [n_queries, dim] of `dtype` (dense, 16-byte aligned, dim * sizeof(element) a multiple of 16), neighbors int64
+ * [n_queries, k], distances float32 [n_queries, k]; results and conventions are those of cuvsCertexSearch on an index
+ * built from the same vectors (every stored vector is scored in fp64, no screening).
+ *
+ * The temporaries live in one array of CERTEX_B200_STATIC_SCRATCH_BYTES that is part of the library image: every GPU on
+ * which the library is used holds it from load to process exit. A call whose temporaries
+ * (n_queries * n_rows * 8 bytes for the scores plus the selection lists) exceed it fails with CUVS_ERROR and a message
+ * that names both sizes. The first call on a device looks up the array's address on that device (the device must be
+ * current, as for every call); make that first call outside any stream capture. All calls share the array and it keeps
+ * the previous call's contents: every value a call reads it has written itself, so no clearing is needed, but two
+ * calls that overlap on the GPU (different streams, or different host threads without ordering between their
+ * streams) race on it. Work is enqueued on the stream of `res`; the call returns without synchronising.
+ */
+#define CERTEX_B200_STATIC_SCRATCH_BYTES (16u << 20)
+CERTEX_B200_EXPORT cuvsError_t certexB200SearchStatic(cuvsResources_t res, cuvsDistanceType metric, DLDataType dtype,
+                                                      const void* vectors, int64_t n_rows, const void* queries,
+                                                      int64_t n_queries, int64_t dim, int32_t k, int64_t* neighbors,
+                                                      float* distances);
+
 /** Version string "major.minor.patch". */
 CERTEX_B200_EXPORT const char* certexB200Version(void);
 
