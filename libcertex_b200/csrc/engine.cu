@@ -188,12 +188,22 @@ Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t
   CERTEX_EXPECTS(params.anchor_stride >= 1, "certex: anchor_stride must be at least 1");
   const bool is_int = dtype == kI8 || dtype == kU8;
   CERTEX_EXPECTS(!(params.metric == kCos && is_int), "certex: the cosine metric needs float32 or float16 vectors");
-  int_screen_ = is_int && dim <= 256;
-  if (int_screen_) {
-    pitch_ = static_cast<size_t>(round_up(dim, 128));
-    kb_    = static_cast<int>(pitch_ / 128);
+  if (is_int && dim <= 256) {
+    screen_kind_ = 1;  // the stored row is its own code
+    pitch_       = static_cast<size_t>(round_up(dim, 128));
+    code_pitch_  = pitch_;
   } else {
     pitch_ = static_cast<size_t>(round_up(dim * dtype_size(dtype), 16));
+    if (!is_int && dim <= 128) {
+      screen_kind_ = 2;  // fp16 codes
+      code_pitch_  = static_cast<size_t>(round_up(dim * 2, 128));
+    }
+  }
+  kb_ = static_cast<int>(code_pitch_ / 128);
+  if (screen_kind_ == 2) {
+    CERTEX_CUDA(cudaMalloc(&maxima_, 4 * sizeof(unsigned int)));
+    CERTEX_CUDA(cudaMemsetAsync(maxima_, 0, 4 * sizeof(unsigned int), res.stream));
+    res.sync();
   }
 }
 
@@ -207,6 +217,7 @@ Index::~Index()
   cudaFree(inv_);
   cudaFree(init_);
   cudaFree(cmax_);
+  cudaFree(maxima_);
 }
 
 void Index::reserve(const Resources& res, int64_t n)
@@ -226,14 +237,15 @@ void Index::reserve(const Resources& res, int64_t n)
     CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(cap) * 4));
     CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(cap) * 4, res.stream));
   }
-  if (int_screen_) {
-    CERTEX_CUDA(cudaMalloc(&co, static_cast<size_t>(cap) * pitch_));
+  if (screen_kind_) {
+    const int32_t never = screen_kind_ == 2 ? static_cast<int32_t>(0xff800000u) : kNeverInit;  // -inf or -2^30
+    CERTEX_CUDA(cudaMalloc(&co, static_cast<size_t>(cap) * code_pitch_));
     CERTEX_CUDA(cudaMalloc(&pe, static_cast<size_t>(cap) * 4));
     CERTEX_CUDA(cudaMalloc(&iv, static_cast<size_t>(cap) * 4));
     CERTEX_CUDA(cudaMalloc(&in, static_cast<size_t>(pad_new) * 4));
     CERTEX_CUDA(cudaMalloc(&cm, static_cast<size_t>(pad_new / kChainRows) * 4));
-    launch_fill_i32(in, pad_new, kNeverInit, res.stream);
-    launch_fill_i32(cm, pad_new / kChainRows, kNeverInit, res.stream);
+    launch_fill_i32(in, pad_new, never, res.stream);
+    launch_fill_i32(cm, pad_new / kChainRows, never, res.stream);
     CERTEX_CUDA(cudaGetLastError());
   }
   if (size_ > 0) {
@@ -241,8 +253,8 @@ void Index::reserve(const Resources& res, int64_t n)
     CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, d2d, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), d2d, res.stream));
     if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, d2d, res.stream)); }
-    if (int_screen_) {
-      CERTEX_CUDA(cudaMemcpyAsync(co, codes_, static_cast<size_t>(size_) * pitch_, d2d, res.stream));
+    if (screen_kind_) {
+      CERTEX_CUDA(cudaMemcpyAsync(co, codes_, static_cast<size_t>(size_) * code_pitch_, d2d, res.stream));
       CERTEX_CUDA(cudaMemcpyAsync(pe, perm_, static_cast<size_t>(size_) * 4, d2d, res.stream));
       CERTEX_CUDA(cudaMemcpyAsync(iv, inv_, static_cast<size_t>(size_) * 4, d2d, res.stream));
       CERTEX_CUDA(cudaMemcpyAsync(in, init_, static_cast<size_t>(pad_old) * 4, d2d, res.stream));
@@ -280,25 +292,45 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
     CERTEX_CUDA(cudaMemcpy2DAsync(dst, pitch_, rows, row_bytes, row_bytes, static_cast<size_t>(n), kind, res.stream));
   }
   if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
-  if (int_screen_) {
+  if (screen_kind_) {
     // The batch goes into sorted rows [size, size + n), ordered by squared norm. Rows beyond the published size are
     // invisible to running searches, which bound tiles and candidates by their own size.
     Scratch scratch(res.stream);
-    int32_t* e        = scratch.get<int32_t>(static_cast<size_t>(n));
-    uint32_t* keys_in = scratch.get<uint32_t>(static_cast<size_t>(n));
+    const bool f16     = screen_kind_ == 2;
+    int32_t* e         = scratch.get<int32_t>(static_cast<size_t>(n));
+    uint32_t* keys_in  = scratch.get<uint32_t>(static_cast<size_t>(n));
     uint32_t* keys_out = scratch.get<uint32_t>(static_cast<size_t>(n));
-    int32_t* ids_in   = scratch.get<int32_t>(static_cast<size_t>(n));
-    int32_t* ids_out  = scratch.get<int32_t>(static_cast<size_t>(n));
-    const size_t tb   = sort_batch_temp_bytes(n);
-    void* temp        = scratch.get<uint8_t>(tb);
-    launch_row_init(dst, pitch_, dtype_, static_cast<int>(dim_), kL2, nullptr, 0, n, n, e, res.stream);
+    int32_t* ids_in    = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* ids_out   = scratch.get<int32_t>(static_cast<size_t>(n));
+    const size_t tb    = sort_batch_temp_bytes(n);
+    void* temp         = scratch.get<uint8_t>(tb);
+    const void* src    = vectors_;  // code rows by id: the stored rows themselves (8-bit), or fresh fp16 codes
+    int64_t src_id0    = 0;
+    if (f16) {
+      uint8_t* fresh = scratch.get<uint8_t>(static_cast<size_t>(n) * code_pitch_);
+      launch_encode_f16_rows(dst, pitch_, dtype_, static_cast<int>(dim_), params_.metric, n, fresh, code_pitch_,
+                             reinterpret_cast<float*>(e), maxima_, res.stream);
+      src     = fresh;
+      src_id0 = size_;
+    } else {
+      launch_row_init(dst, pitch_, dtype_, static_cast<int>(dim_), kL2, nullptr, 0, n, n, e, res.stream);
+    }
     CERTEX_CUDA(cudaGetLastError());
-    launch_sort_batch(e, n, static_cast<int32_t>(size_), size_, vectors_, pitch_, params_.metric, keys_in, keys_out, ids_in,
-                      ids_out, temp, tb, codes_, perm_, inv_, init_, res.stream);
+    launch_sort_batch(e, n, static_cast<int32_t>(size_), size_, src, src_id0, code_pitch_, params_.metric, f16, keys_in,
+                      keys_out, ids_in, ids_out, temp, tb, codes_, perm_, inv_, init_, res.stream);
     CERTEX_CUDA(cudaGetLastError());
     const int64_t c0 = size_ / kChainRows, c1 = (size_ + n + kChainRows - 1) / kChainRows;
-    launch_chain_max(init_, c0, c1 - c0, cmax_, res.stream);
+    launch_chain_max(init_, c0, c1 - c0, cmax_, f16, res.stream);
     CERTEX_CUDA(cudaGetLastError());
+    if (f16) {
+      unsigned int h[4] = {0, 0, 0, 0};
+      CERTEX_CUDA(cudaMemcpyAsync(h, maxima_, sizeof(h), cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+      std::memcpy(&n1max_, &h[0], 4);
+      std::memcpy(&n2max_, &h[1], 4);
+      std::memcpy(&emax_, &h[2], 4);
+      code_overflow_ = h[3] != 0;
+    }
   }
   res.sync();
   std::unique_lock<std::shared_mutex> lock(rw_);
@@ -312,7 +344,7 @@ void Index::remove(const Resources& res, const int64_t* ids_device, int64_t n_id
   Scratch scratch(res.stream);
   auto* counter = scratch.get<unsigned long long>(1);
   CERTEX_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned long long), res.stream));
-  launch_remove(ids_device, n_ids, size_, removed_, init_, inv_, cmax_, counter, res.stream);
+  launch_remove(ids_device, n_ids, size_, removed_, init_, inv_, cmax_, screen_kind_ == 2, counter, res.stream);
   CERTEX_CUDA(cudaGetLastError());
   unsigned long long n_new = 0;
   CERTEX_CUDA(cudaMemcpyAsync(&n_new, counter, sizeof(n_new), cudaMemcpyDeviceToHost, res.stream));
@@ -364,12 +396,13 @@ void Index::search_dense(const Resources& res, const void* q, size_t qpitch, con
   }
 }
 
-void Index::search_screened(const Resources& res, const uint8_t* qbuf, const void* queries, size_t row_bytes, int q0, int nq,
-                            int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
-                            unsigned long long* stats, int* err, int anchor_stride, int64_t n,
+void Index::search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries,
+                            size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
+                            unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
                             std::vector<cudaEvent_t>* events) const
 {
-  // qbuf: all queries of the call, zero padded to [round_up(total, 128), pitch_]; this batch is rows [q0, q0 + nq)
+  // qbuf: the code rows of all queries of the call, zero padded to [round_up(total, 128), code_pitch_]; this batch is
+  // rows [q0, q0 + nq). shift (fp16 codes only): the rounding allowance of every query.
   Scratch scratch(res.stream);
   const int grid          = res.sm_count;
   const ScreenShape shape = shape_for(kb_);
@@ -401,17 +434,19 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream);  // e of the anchors
   CERTEX_CUDA(cudaGetLastError());
 
-  const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * pitch_;
-  const CUtensorMap tm_q = make_code_map(qb, pitch_, static_cast<uint64_t>(round_up(nq, kQTile)), pitch_, kQueryTile);
-  const CUtensorMap tm_a = make_tile_map(codes_, pitch_, static_cast<uint64_t>(nt_anchor) * anchor_stride * pitch_,
-                                         static_cast<uint64_t>(anchor_stride) * pitch_, static_cast<uint64_t>(nt_anchor));
-  const CUtensorMap tm_x = make_code_map(codes_, pitch_, static_cast<uint64_t>(n), pitch_, kBaseTile);
+  const size_t cp        = code_pitch_;
+  const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * cp;
+  const CUtensorMap tm_q = make_code_map(qb, cp, static_cast<uint64_t>(round_up(nq, kQTile)), cp, kQueryTile);
+  const CUtensorMap tm_a = make_tile_map(codes_, cp, static_cast<uint64_t>(nt_anchor) * anchor_stride * cp,
+                                         static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor));
+  const CUtensorMap tm_x = make_code_map(codes_, cp, static_cast<uint64_t>(n), cp, kBaseTile);
 
   ScreenArgs a{};
   a.nq          = nq;
   a.kb          = kb_;
   a.panel_tiles = shape.panel_tiles;
   a.n_stages    = shape.n_stages;
+  a.f16         = screen_kind_ == 2 ? 1 : 0;
   a.q_signed    = dtype_ == kI8 ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.err         = err;
@@ -434,6 +469,7 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const voi
   mark();
   // 2 threshold: the k-th largest group maximum
   launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
+  if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, res.stream); }
   CERTEX_CUDA(cudaGetLastError());
   // 3 screen over all rows: survivor records, then per-query candidate lists
   a.mode      = kModeScreen;
@@ -486,15 +522,27 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   // anchors: every stride-th row in whole tiles of 256, and at least 2k groups of 64 anchors, or the threshold would be
   // useless
   const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (kTile * ((2 * k + 3) / 4))));
-  const bool screened = int_screen_ && !filtered && stride >= 1 && test_mode_ != 1;
+  const bool screened = screen_kind_ != 0 && !code_overflow_ && !filtered && stride >= 1 && test_mode_ != 1;
 
   SearchStats local{};
   local.queries = static_cast<unsigned long long>(nq);
   if (screened) {
     const int64_t nq_pad = round_up(nq, kQTile);
-    uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * pitch_);
-    if (row_bytes != pitch_ || nq_pad != nq) { CERTEX_CUDA(cudaMemsetAsync(qbuf, 0, static_cast<size_t>(nq_pad) * pitch_, res.stream)); }
-    CERTEX_CUDA(cudaMemcpy2DAsync(qbuf, pitch_, queries, row_bytes, row_bytes, static_cast<size_t>(nq), cudaMemcpyDeviceToDevice, res.stream));
+    uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * code_pitch_);
+    float* shift         = nullptr;
+    unsigned int* q_ovf  = scratch.get<unsigned int>(1);  // a query coordinate that does not fit fp16
+    CERTEX_CUDA(cudaMemsetAsync(q_ovf, 0, sizeof(unsigned int), res.stream));
+    if (screen_kind_ == 2) {
+      shift = scratch.get<float>(static_cast<size_t>(nq));
+      CERTEX_CUDA(cudaMemsetAsync(qbuf + static_cast<size_t>(nq) * code_pitch_, 0, static_cast<size_t>(nq_pad - nq) * code_pitch_, res.stream));
+      launch_encode_f16_queries(queries, row_bytes, dtype_, d, nq, qbuf, code_pitch_, n1max_, n2max_, emax_, shift, q_ovf, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+    } else {
+      if (row_bytes != code_pitch_ || nq_pad != nq) {
+        CERTEX_CUDA(cudaMemsetAsync(qbuf, 0, static_cast<size_t>(nq_pad) * code_pitch_, res.stream));
+      }
+      CERTEX_CUDA(cudaMemcpy2DAsync(qbuf, code_pitch_, queries, row_bytes, row_bytes, static_cast<size_t>(nq), cudaMemcpyDeviceToDevice, res.stream));
+    }
     int32_t* ovf_list      = scratch.get<int32_t>(static_cast<size_t>(nq));
     unsigned int* d_count  = scratch.get<unsigned int>(4);  // [0] overflowed queries, [1] error code of the passes
     auto* d_stats          = scratch.get<unsigned long long>(2);
@@ -504,14 +552,16 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     std::vector<cudaEvent_t> events;
     for (int64_t q0 = 0; q0 < nq; q0 += batch) {
       const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
-      search_screened(res, qbuf, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
+      search_screened(res, qbuf, shift, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
                       d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, stats_sink ? &events : nullptr);
-      local.launches += 6;  // gather_init, GROUPMAX pass, kth_largest, SCREEN pass, expand_records, verify_select
+      local.launches += screen_kind_ == 2 ? 7 : 6;  // gather_init, GROUPMAX, kth_largest (+ thresholds), SCREEN, expand, verify
     }
     unsigned int h_count[4]       = {0, 0, 0, 0};
     unsigned long long h_stats[2] = {0, 0};
     CERTEX_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
+    unsigned int h_q_ovf = 0;
     CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(&h_q_ovf, q_ovf, sizeof(h_q_ovf), cudaMemcpyDeviceToHost, res.stream));
     res.sync();  // the one host round trip of a search call
     for (size_t e = 0; e + 3 < events.size(); e += 4) {
       float ms = 0;
@@ -525,7 +575,11 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
     local.survivors = h_stats[0];
     local.verified  = h_stats[1];
-    if (h_count[0] > 0) {  // candidate lists that overflowed: those queries are searched without the screen
+    if (h_q_ovf) {  // a query coordinate beyond the fp16 range: no threshold of this call is trusted
+      search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
+      local.dense_queries = static_cast<unsigned long long>(nq);
+      local.launches += 2;
+    } else if (h_count[0] > 0) {  // candidate lists that overflowed: those queries are searched without the screen
       search_dense(res, queries, row_bytes, ovf_list, 0, static_cast<int>(h_count[0]), k, adm, best_s, best_row, n);
       local.dense_queries = h_count[0];
       local.launches += 2;
@@ -626,7 +680,7 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
     CERTEX_CUDA(cudaMemcpyAsync(idx->removed_, host.data(), static_cast<size_t>(n), cudaMemcpyHostToDevice, res.stream));
     res.sync();
     idx->n_removed_ = n_rem;
-    if (idx->int_screen_ && n_rem > 0) {  // removed rows must never pass the screen
+    if (idx->screen_kind_ && n_rem > 0) {  // removed rows must never pass the screen
       Scratch scratch(res.stream);
       int64_t* ids     = scratch.get<int64_t>(static_cast<size_t>(n));
       auto* counter    = scratch.get<unsigned long long>(1);
@@ -637,7 +691,8 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
       CERTEX_CUDA(cudaMemcpyAsync(ids, gone.data(), gone.size() * 8, cudaMemcpyHostToDevice, res.stream));
       CERTEX_CUDA(cudaMemsetAsync(idx->removed_, 0, static_cast<size_t>(n), res.stream));
       CERTEX_CUDA(cudaMemsetAsync(counter, 0, 8, res.stream));
-      launch_remove(ids, static_cast<int64_t>(gone.size()), n, idx->removed_, idx->init_, idx->inv_, idx->cmax_, counter, res.stream);
+      launch_remove(ids, static_cast<int64_t>(gone.size()), n, idx->removed_, idx->init_, idx->inv_, idx->cmax_,
+                    idx->screen_kind_ == 2, counter, res.stream);
       CERTEX_CUDA(cudaGetLastError());
       res.sync();
     }
@@ -705,7 +760,7 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   int32_t* cmax       = scratch.get<int32_t>(static_cast<size_t>(n_pad / kChainRows));
   launch_fill_i32(init_pad, n_pad, kNeverInit, res.stream);
   CERTEX_CUDA(cudaMemcpyAsync(init_pad, init, static_cast<size_t>(n_in) * 4, cudaMemcpyDeviceToDevice, res.stream));
-  launch_chain_max(init_pad, 0, n_pad / kChainRows, cmax, res.stream);
+  launch_chain_max(init_pad, 0, n_pad / kChainRows, cmax, false, res.stream);
   CERTEX_CUDA(cudaGetLastError());
   const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
   uint64_t* rec   = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));

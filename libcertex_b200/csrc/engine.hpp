@@ -111,7 +111,7 @@ class Index {
   int dtype() const { return dtype_; }
   int metric() const { return params_.metric; }
   bool has_labels() const { return has_labels_; }
-  bool int_screen() const { return int_screen_; }
+  bool int_screen() const { return screen_kind_ != 0 && !code_overflow_; }  // a tensor-core screen is available
   const IndexParams& params() const { return params_; }
   size_t pitch() const { return pitch_; }
   const void* vectors() const { return vectors_; }
@@ -126,9 +126,9 @@ class Index {
   static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
 
  private:
-  void search_screened(const Resources& res, const uint8_t* qbuf, const void* queries, size_t row_bytes, int q0, int nq,
-                       int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
-                       unsigned long long* stats, int* err, int anchor_stride, int64_t n,
+  void search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries, size_t row_bytes,
+                       int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
+                       unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
                        std::vector<cudaEvent_t>* events) const;
   void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
                     const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
@@ -137,8 +137,12 @@ class Index {
   int dtype_;
   int64_t dim_;
   size_t pitch_       = 0;  // bytes per stored row (zero padded: integer types to a multiple of 128, others of 16)
-  int kb_             = 0;  // 128-byte K blocks per row (integer screen)
-  bool int_screen_    = false;
+  size_t code_pitch_  = 0;  // bytes per code row of the screen: the vector itself (8-bit types) or its fp16 rounding
+  int kb_             = 0;  // 128-byte K blocks per code row
+  int screen_kind_    = 0;  // 0: no tensor-core screen (dense path only), 1: 8-bit codes, 2: fp16 codes of float data
+  bool code_overflow_ = false;      // a float coordinate did not fit fp16: the index answers by the dense path
+  float n1max_ = 0, n2max_ = 0, emax_ = 0;  // fp16 codes: largest |code|, |rounding residual|, |e| over all rows
+  unsigned int* maxima_ = nullptr;  // device copy of the three maxima (float bits) and the overflow flag
   int device_         = 0;
   int64_t size_       = 0;
   int64_t capacity_   = 0;
@@ -147,7 +151,7 @@ class Index {
   void* vectors_      = nullptr;  // [capacity, pitch]
   uint8_t* removed_   = nullptr;  // [capacity rounded up to 4]
   int32_t* labels_    = nullptr;  // [capacity], -1 = none
-  // integer screen: a copy of the rows sorted by squared norm (each appended batch on its own), and per sorted row
+  // screen: the code rows sorted by squared norm (each appended batch on its own), and per sorted row
   void* codes_        = nullptr;  // [capacity, pitch] rows in sorted order
   int32_t* perm_      = nullptr;  // [capacity] sorted row -> id
   int32_t* inv_       = nullptr;  // [capacity] id -> sorted row

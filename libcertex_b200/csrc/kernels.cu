@@ -254,7 +254,7 @@ __global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t 
 }
 
 __global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
-                              const int32_t* inv, unsigned long long* n_new)
+                              const int32_t* inv, unsigned long long* n_new, int32_t never)
 {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_ids) { return; }
@@ -265,7 +265,7 @@ __global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, u
   const uint32_t bit   = 1u << (8 * (id & 3));
   const uint32_t prev  = atomicOr(word, bit);
   if ((prev & bit) == 0u) { atomicAdd(n_new, 1ull); }
-  if (init) { init[inv ? inv[id] : id] = kNeverInit; }
+  if (init) { init[inv ? inv[id] : id] = never; }
 }
 
 // cmax[c] = max of e over rows [16c, 16c + 16) for chains c0 .. c0 + n - 1 (e padded with kNeverInit).
@@ -285,31 +285,40 @@ __global__ void chain_max_kernel(const int32_t* init, int64_t c0, int64_t n, int
 
 // The chains that hold removed ids get their maximum recomputed (after remove_kernel has marked the rows).
 __global__ void chain_max_of_ids_kernel(const int64_t* ids, int64_t n_ids, int64_t size, const int32_t* inv,
-                                        const int32_t* init, int32_t* cmax)
+                                        const int32_t* init, int32_t* cmax, int is_float)
 {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_ids) { return; }
   const int64_t id = ids[i];
   if (id < 0 || id >= size) { return; }
   const int64_t c = (inv ? inv[id] : id) / 16;
-  int m           = kNeverInit;
-  for (int k = 0; k < 16; ++k) { m = max(m, init[c * 16 + k]); }
-  cmax[c] = m;
+  if (is_float) {
+    float m = -CUDART_INF_F;
+    for (int k = 0; k < 16; ++k) { m = fmaxf(m, __int_as_float(init[c * 16 + k])); }
+    cmax[c] = __float_as_int(m);
+  } else {
+    int m = kNeverInit;
+    for (int k = 0; k < 16; ++k) { m = max(m, init[c * 16 + k]); }
+    cmax[c] = m;
+  }
 }
 
-// keys[j] = -e[j] (half the squared norm, ascending sort key), vals[j] = id0 + j.
-__global__ void sort_keys_kernel(const int32_t* e, int64_t n, int32_t id0, uint32_t* keys, int32_t* vals)
+// keys[j] = -e[j] (half the squared norm, ascending sort key; for floats the bits of the non-negative float),
+// vals[j] = id0 + j.
+__global__ void sort_keys_kernel(const int32_t* e, int64_t n, int32_t id0, uint32_t* keys, int32_t* vals, int is_float)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (j < n) {
-    keys[j] = static_cast<uint32_t>(-e[j]);
+    keys[j] = is_float ? __float_as_uint(-__int_as_float(e[j])) : static_cast<uint32_t>(-e[j]);
     vals[j] = id0 + static_cast<int32_t>(j);
   }
 }
 
 // Sorted batch -> index arrays: perm[row0 + j] = id, inv[id] = row0 + j, init[row0 + j] = -key, and the code row.
-__global__ void place_sorted_kernel(const uint32_t* keys, const int32_t* ids, int64_t n, int64_t row0, const uint8_t* vectors,
-                                    size_t pitch, uint8_t* codes, int32_t* perm, int32_t* inv, int32_t* init, int metric)
+// `src` holds the code row of id at src + (id - src_id0) * pitch.
+__global__ void place_sorted_kernel(const uint32_t* keys, const int32_t* ids, int64_t n, int64_t row0, const uint8_t* src,
+                                    int64_t src_id0, size_t pitch, uint8_t* codes, int32_t* perm, int32_t* inv, int32_t* init,
+                                    int metric, int is_float)
 {
   const int64_t gt   = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int chunks   = static_cast<int>(pitch / 16);
@@ -318,11 +327,11 @@ __global__ void place_sorted_kernel(const uint32_t* keys, const int32_t* ids, in
   if (j >= n) { return; }
   const int32_t id = ids[j];
   reinterpret_cast<uint4*>(codes + static_cast<size_t>(row0 + j) * pitch)[c] =
-    __ldg(reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(id) * pitch) + c);
+    __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(id - src_id0) * pitch) + c);
   if (c == 0) {
     perm[row0 + j] = id;
     inv[id]        = static_cast<int32_t>(row0 + j);
-    init[row0 + j] = metric == kL2 ? -static_cast<int32_t>(keys[j]) : 0;
+    init[row0 + j] = metric != kL2 ? 0 : is_float ? __float_as_int(-__uint_as_float(keys[j])) : -static_cast<int32_t>(keys[j]);
   }
 }
 
@@ -330,6 +339,136 @@ __global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t v)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (j < n) { p[j] = v; }
+}
+
+// ------------------------------------------------------------------------------------------- fp16 codes of float data
+// One warp per row: the row rounded to fp16 (for the cosine metric: the row scaled to unit length first), and what the
+// certified threshold test needs to know about the rounding:
+//   |h|           norm of the fp16 code                          (rounded up)
+//   |y - h|       norm of the rounding residual                  (rounded up)
+//   e = -|x|^2/2  per-row term of the L2 value <q, x> - |x|^2/2  (rounded up; 0 for inner product and cosine)
+// All sums are fp64. maxima[0..2] collect the largest |h|, |y - h| and |e| as float bits (non-negative floats order
+// like their bits); maxima[3] is raised when a coordinate does not fit fp16.
+template <typename T>
+__global__ void encode_f16_rows_kernel(const uint8_t* vectors, size_t pitch, int d, int metric, int64_t n, uint8_t* codes,
+                                       size_t code_pitch, float* e, unsigned int* maxima)
+{
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane    = threadIdx.x & 31;
+  if (row >= n) { return; }
+  const uint8_t* src = vectors + static_cast<size_t>(row) * pitch;
+  double xx          = 0;
+  for (int t = lane; t < d; t += 32) {
+    const double v = Elems<T>::one(src, t);
+    xx += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { xx += __shfl_xor_sync(0xffffffffu, xx, o); }
+  const double scale = metric == kCos ? (xx > 0 ? 1.0 / sqrt(xx) : 0.0) : 1.0;
+  __half* dst        = reinterpret_cast<__half*>(codes + static_cast<size_t>(row) * code_pitch);
+  const int d_pad    = static_cast<int>(code_pitch / 2);
+  double hh = 0, rr = 0;
+  bool bad = false;
+  for (int t = lane; t < d_pad; t += 32) {
+    __half h = __float2half_rn(0.f);
+    if (t < d) {
+      const double y  = Elems<T>::one(src, t) * scale;
+      h               = __double2half(y);
+      const double hf = static_cast<double>(__half2float(h));
+      bad |= isinf(hf) || isnan(hf);
+      hh += hf * hf;
+      rr += (y - hf) * (y - hf);
+    }
+    dst[t] = h;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    hh += __shfl_xor_sync(0xffffffffu, hh, o);
+    rr += __shfl_xor_sync(0xffffffffu, rr, o);
+  }
+  bad = __any_sync(0xffffffffu, bad);
+  if (lane == 0) {
+    // the unit-length scaling is itself rounded (fp64): a relative 2^-50 on every coordinate, far inside the slack
+    const float n1 = __double2float_ru(sqrt(hh) * (1.0 + 1e-9));
+    const float n2 = __double2float_ru(sqrt(rr) * (1.0 + 1e-9) + (metric == kCos ? 1e-12 : 0.0));
+    const float ev = metric == kL2 ? __double2float_ru(-0.5 * xx) : 0.f;
+    e[row]         = ev;
+    atomicMax(maxima + 0, __float_as_uint(n1));
+    atomicMax(maxima + 1, __float_as_uint(n2));
+    atomicMax(maxima + 2, __float_as_uint(fabsf(ev)));
+    if (bad) { atomicExch(maxima + 3, 1u); }
+  }
+}
+
+// One warp per query: the fp16 code of the query and shift[q] = 2 (E + slack), the amount by which the k-th largest
+// group maximum of the anchors is lowered to become the screen's threshold. With h = fp16(q), x~ = fp16 code of a row:
+//   <q, x> = <h, x~> + <q - h, x~> + <q, x - x~>,   |<q - h, x~>| <= |q - h| |x~|,   |<q, x - x~>| <= |q| |x - x~|
+//   |acc - <h, x~>| <= gamma |h| |x~|    (fp32 accumulation of exact fp16 products, gamma = (d + 16) 2^-20)
+// so |acc - <q, x>| <= E(q) = (|q - h| + gamma |h|) N1 + |q| N2 with N1, N2 the largest |x~|, |x - x~| of the index.
+// slack covers the fp32 additions of the epilogue, the rounding of e and of the exact fp64 scores: 2^-18 (|h| N1 + Emax).
+// The anchors give a value every one of k rows certainly reaches (their group maximum minus E + slack); a row is
+// kept unless its value certainly lies below that (its maximum plus E + slack): hence twice.
+template <typename T>
+__global__ void encode_f16_queries_kernel(const uint8_t* queries, size_t qpitch, int d, int64_t nq, uint8_t* codes,
+                                          size_t code_pitch, float n1max, float n2max, float emax, float* shift,
+                                          unsigned int* overflow)
+{
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane    = threadIdx.x & 31;
+  if (row >= nq) { return; }
+  const uint8_t* src = queries + static_cast<size_t>(row) * qpitch;
+  __half* dst        = reinterpret_cast<__half*>(codes + static_cast<size_t>(row) * code_pitch);
+  const int d_pad    = static_cast<int>(code_pitch / 2);
+  double qq = 0, hh = 0, rr = 0;
+  bool bad = false;
+  for (int t = lane; t < d_pad; t += 32) {
+    __half h = __float2half_rn(0.f);
+    if (t < d) {
+      const double y  = Elems<T>::one(src, t);
+      h               = __double2half(y);
+      const double hf = static_cast<double>(__half2float(h));
+      bad |= isinf(hf) || isnan(hf);
+      qq += y * y;
+      hh += hf * hf;
+      rr += (y - hf) * (y - hf);
+    }
+    dst[t] = h;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    qq += __shfl_xor_sync(0xffffffffu, qq, o);
+    hh += __shfl_xor_sync(0xffffffffu, hh, o);
+    rr += __shfl_xor_sync(0xffffffffu, rr, o);
+  }
+  bad = __any_sync(0xffffffffu, bad);
+  if (lane == 0) {
+    const double gamma = (d + 16) * 9.5367431640625e-07;  // 2^-20
+    const double nqh = sqrt(hh) * (1.0 + 1e-9), dq = sqrt(rr) * (1.0 + 1e-9), nqn = sqrt(qq) * (1.0 + 1e-9);
+    const double E     = (dq + gamma * nqh) * n1max + nqn * n2max;
+    const double slack = 3.814697265625e-06 * (nqh * n1max + emax);  // 2^-18
+    shift[row]         = __double2float_ru(2.0 * (E + slack) * (1.0 + 1e-6));
+    if (bad) { atomicExch(overflow, 1u); }
+  }
+}
+
+// thr[q]: the key of the k-th largest group maximum (see float_key in the screen kernel) -> float bits of the
+// screen's threshold, value - shift[q], rounded down.
+__global__ void finish_thr_f16_kernel(int32_t* thr, const float* shift, int nq)
+{
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= nq) { return; }
+  const int32_t key = thr[q];
+  const float v     = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
+  thr[q]            = __float_as_int(__fadd_rd(v, -shift[q]));
+}
+
+__global__ void chain_max_f32_kernel(const float* init, int64_t c0, int64_t n, float* cmax)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) { return; }
+  float m = -CUDART_INF_F;
+  for (int k = 0; k < 16; ++k) { m = fmaxf(m, init[(c0 + i) * 16 + k]); }
+  cmax[c0 + i] = m;
 }
 
 // Survivor records -> per-query candidate lists. One thread per record; the appends of a query go through cnt[q].
@@ -760,10 +899,50 @@ void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_co
   expand_records_kernel<<<sm_count * 8, 256, 0, s>>>(rec, rec_count, rec_cap, n_rows, perm, cnt, cand, cap);
 }
 
-void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, cudaStream_t s)
+void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, bool is_float, cudaStream_t s)
 {
   if (n <= 0) { return; }
-  chain_max_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(init, c0, n, cmax);
+  const auto grid = static_cast<unsigned>((n + 255) / 256);
+  if (is_float) {
+    chain_max_f32_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float*>(init), c0, n, reinterpret_cast<float*>(cmax));
+  } else {
+    chain_max_kernel<<<grid, 256, 0, s>>>(init, c0, n, cmax);
+  }
+}
+
+void launch_encode_f16_rows(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, void* codes,
+                            size_t code_pitch, float* e, unsigned int* maxima, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  const auto grid = static_cast<unsigned>((n * 32 + 255) / 256);
+  if (dtype == kF32) {
+    encode_f16_rows_kernel<float><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, metric, n,
+                                                       static_cast<uint8_t*>(codes), code_pitch, e, maxima);
+  } else {
+    encode_f16_rows_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, metric, n,
+                                                        static_cast<uint8_t*>(codes), code_pitch, e, maxima);
+  }
+}
+
+void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, int d, int64_t nq, void* codes,
+                               size_t code_pitch, float n1max, float n2max, float emax, float* shift,
+                               unsigned int* overflow, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  const auto grid = static_cast<unsigned>((nq * 32 + 255) / 256);
+  if (dtype == kF32) {
+    encode_f16_queries_kernel<float><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(queries), qpitch, d, nq,
+                                                          static_cast<uint8_t*>(codes), code_pitch, n1max, n2max, emax, shift, overflow);
+  } else {
+    encode_f16_queries_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(queries), qpitch, d, nq,
+                                                           static_cast<uint8_t*>(codes), code_pitch, n1max, n2max, emax, shift, overflow);
+  }
+}
+
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq);
 }
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s)
@@ -780,16 +959,17 @@ size_t sort_batch_temp_bytes(int64_t n)
   return bytes;
 }
 
-void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* vectors, size_t pitch, int metric,
-                       uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out, void* temp, size_t temp_bytes,
-                       void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s)
+void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* src, int64_t src_id0, size_t pitch,
+                       int metric, bool is_float, uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out,
+                       void* temp, size_t temp_bytes, void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s)
 {
   if (n <= 0) { return; }
-  sort_keys_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e, n, id0, keys_in, ids_in);
+  sort_keys_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e, n, id0, keys_in, ids_in, is_float ? 1 : 0);
   cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys_in, keys_out, ids_in, ids_out, n, 0, 32, s);
   const int64_t threads = n * static_cast<int64_t>(pitch / 16);
   place_sorted_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(
-    keys_out, ids_out, n, row0, static_cast<const uint8_t*>(vectors), pitch, static_cast<uint8_t*>(codes), perm, inv, init, metric);
+    keys_out, ids_out, n, row0, static_cast<const uint8_t*>(src), src_id0, pitch, static_cast<uint8_t*>(codes), perm, inv, init,
+    metric, is_float ? 1 : 0);
 }
 
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s)
@@ -802,12 +982,13 @@ void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, 
 }
 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
-                   int32_t* cmax, unsigned long long* n_new, cudaStream_t s)
+                   int32_t* cmax, bool is_float, unsigned long long* n_new, cudaStream_t s)
 {
   if (n_ids <= 0) { return; }
-  const auto grid = static_cast<unsigned>((n_ids + 255) / 256);
-  remove_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, removed, init, inv, n_new);
-  if (init && cmax) { chain_max_of_ids_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, inv, init, cmax); }
+  const auto grid     = static_cast<unsigned>((n_ids + 255) / 256);
+  const int32_t never = is_float ? static_cast<int32_t>(0xff800000u) : kNeverInit;  // -inf or -2^30
+  remove_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, removed, init, inv, n_new, never);
+  if (init && cmax) { chain_max_of_ids_kernel<<<grid, 256, 0, s>>>(ids, n_ids, size, inv, init, cmax, is_float ? 1 : 0); }
 }
 
 void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,

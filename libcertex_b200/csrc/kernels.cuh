@@ -28,19 +28,34 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
 /// e of the anchors of the threshold stage in tile order: out[t * 256 + c] = init[(c * n_tiles + t) * stride].
 void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s);
 
-/// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1.
-void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, cudaStream_t s);
+/// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1 (int32 values, or float bits).
+void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, bool is_float, cudaStream_t s);
+
+/// fp16 codes of n float32 / float16 rows (natural order, rows zero padded to code_pitch) with e [n] and the running
+/// maxima (|code|, |rounding residual|, |e| as float bits; [3]: a coordinate did not fit fp16). See kernels.cu.
+void launch_encode_f16_rows(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, void* codes,
+                            size_t code_pitch, float* e, unsigned int* maxima, cudaStream_t s);
+
+/// fp16 codes of the queries and shift [nq], the per-query allowance for rounding that separates the anchors' k-th
+/// group maximum from the screen's threshold; *overflow is raised when a query coordinate does not fit fp16.
+void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, int d, int64_t nq, void* codes,
+                               size_t code_pitch, float n1max, float n2max, float emax, float* shift,
+                               unsigned int* overflow, cudaStream_t s);
+
+/// thr [nq]: float keys of the k-th largest group maxima -> float bits of (value - shift), rounded down.
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, cudaStream_t s);
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s);
 
 /// Sorts one appended batch by squared norm and writes it into the index arrays of the integer screen: e [n] are the
 /// per-row terms of ids id0 .. id0 + n - 1 (see launch_row_init), the batch occupies sorted rows row0 .. row0 + n - 1;
-/// perm [row] = id, inv [id] = row, init [row] = e of that id, codes [row] = vectors [id]. keys / ids are scratch of n
+/// perm [row] = id, inv [id] = row, init [row] = e of that id, codes [row] = code row of that id (read from
+/// src + (id - src_id0) * pitch). e holds int32 values or, with is_float, float bits. keys / ids are scratch of n
 /// elements each, temp of sort_batch_temp_bytes(n).
 size_t sort_batch_temp_bytes(int64_t n);
-void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* vectors, size_t pitch, int metric,
-                       uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out, void* temp, size_t temp_bytes,
-                       void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s);
+void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, const void* src, int64_t src_id0, size_t pitch,
+                       int metric, bool is_float, uint32_t* keys_in, uint32_t* keys_out, int32_t* ids_in, int32_t* ids_out,
+                       void* temp, size_t temp_bytes, void* codes, int32_t* perm, int32_t* inv, int32_t* init, cudaStream_t s);
 
 /// Survivor records of the screen (see make_record) -> cnt [nq] / cand [nq, cap]; rows >= n_rows are dropped, rows are
 /// translated to ids through perm (when not null).
@@ -54,7 +69,7 @@ void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, 
 /// Marks ids as removed: removed[id] = 1, and for the integer screen init[inv[id]] = kNeverInit with the chain maxima
 /// of the touched chains recomputed; *n_new counts first-time removals.
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
-                   int32_t* cmax, unsigned long long* n_new, cudaStream_t s);
+                   int32_t* cmax, bool is_float, unsigned long long* n_new, cudaStream_t s);
 
 /**
  * Exact fp64 scores of every query's candidate rows, then its k best by (score, row). One block per query.

@@ -24,6 +24,13 @@
 // anchors of one tile are spread over the whole sorted set (column c of tile t is anchor c * n_tiles + t), so that the
 // anchors of one cluster of similar rows do not share a group.
 //
+// The same kernel screens float data (F16 = true): the operands are the vectors rounded to fp16, the MMA is
+// kind::f16 with fp32 accumulators, the per-row term e[x] = -|x|^2 / 2 and the thresholds are floats. What the fp16
+// rounding and the fp32 accumulation can add to or take from <q, x> is bounded per query (Cauchy-Schwarz on the
+// rounding residuals, see encode_f16 in kernels.cu) and sits inside thr[q], so the test keeps every pair that the
+// exact arithmetic would keep. It replaces the reference's fp16 pass `screen`
+// (cpp/src/neighbors/certex/detail/kernels.hpp:101-114; on B200 the mma.sync kernel of detail/screen_sm80.cu).
+//
 // CTA = 18 warps: warps 0..15 are the epilogue (four warps per TMEM lane quarter, each owning one 64-column piece of
 // every unit), warp 16 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
 // warp 17 lane 0 issues tcgen05.mma. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
@@ -32,6 +39,8 @@
 #include "screen_i8.cuh"
 
 #include "ptx.cuh"
+
+#include <math_constants.h>
 
 namespace certex_b200 {
 
@@ -111,7 +120,43 @@ __device__ __forceinline__ int max32_plus(const int32_t (&v)[32], const int32_t*
   return max(m, n);
 }
 
-template <int MODE>
+// float versions; accumulators arrive as the raw 32 bits of an fp32 value
+__device__ __forceinline__ float fmax3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
+
+__device__ __forceinline__ float max16f(const int32_t* v)
+{
+  float m = fmax3(__int_as_float(v[0]), __int_as_float(v[1]), __int_as_float(v[2]));
+  float n = fmax3(__int_as_float(v[3]), __int_as_float(v[4]), __int_as_float(v[5]));
+  m       = fmax3(m, __int_as_float(v[6]), __int_as_float(v[7]));
+  n       = fmax3(n, __int_as_float(v[8]), __int_as_float(v[9]));
+  m       = fmax3(m, __int_as_float(v[10]), __int_as_float(v[11]));
+  n       = fmax3(n, __int_as_float(v[12]), __int_as_float(v[13]));
+  return fmax3(m, n, fmaxf(__int_as_float(v[14]), __int_as_float(v[15])));
+}
+
+__device__ __forceinline__ float max32f_plus(const int32_t (&v)[32], const int32_t* e)
+{
+  const float4* e4 = reinterpret_cast<const float4*>(e);
+  float m = -CUDART_INF_F, n = m;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 t = e4[i];
+    m = fmaxf(m, __int_as_float(v[4 * i]) + t.x);
+    n = fmaxf(n, __int_as_float(v[4 * i + 1]) + t.y);
+    m = fmaxf(m, __int_as_float(v[4 * i + 2]) + t.z);
+    n = fmaxf(n, __int_as_float(v[4 * i + 3]) + t.w);
+  }
+  return fmaxf(m, n);
+}
+
+/// Monotone map of a float to an int32 (and back), so that integer selection kernels can rank floats.
+__device__ __forceinline__ int32_t float_key(float f)
+{
+  const int32_t i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+
+template <int MODE, bool F16>
 __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_x,
                                                                 const ScreenArgs p)
@@ -216,7 +261,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   } else if (warp == kMmaWarp) {
     // ================================================================ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(2u, p.q_signed, p.x_signed, kQueryTile, kBaseTile);
+      const uint32_t idesc = F16 ? instr_desc(1u, 0u, 0u, kQueryTile, kBaseTile)
+                                 : instr_desc(2u, p.q_signed, p.x_signed, kQueryTile, kBaseTile);
       // descriptors differ only in their 14-bit start-address field: (byte offset >> 4) is added to the low word
       const uint64_t a_desc0 = smem_desc_sw128(base + panel_off);
       const uint64_t b_desc0 = smem_desc_sw128(base + stage_off);
@@ -242,8 +288,13 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             for (int b = 0; b < kb; ++b) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                mma_i8(d_tmem, a_desc + static_cast<uint64_t>(b * (kQTileBytes >> 4) + k * 2),
-                       b_desc + static_cast<uint64_t>(b * (kBTileBytes >> 4) + k * 2), idesc, (b | k) != 0 ? 1u : 0u);
+                const uint64_t ad = a_desc + static_cast<uint64_t>(b * (kQTileBytes >> 4) + k * 2);
+                const uint64_t bd = b_desc + static_cast<uint64_t>(b * (kBTileBytes >> 4) + k * 2);
+                if (F16) {
+                  mma_f16(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
+                } else {
+                  mma_i8(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
+                }
               }
             }
             tc_commit(smem_u32(&ctl->tmem_full[slot]));
@@ -297,10 +348,18 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int4 t = e4[i];
-          mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
-          mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
-          mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
-          mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
+          if (F16) {
+            const float tf = __int_as_float(thr);
+            mask |= (__int_as_float(v[4 * i]) + __int_as_float(t.x) >= tf ? 1u : 0u) << (4 * i);
+            mask |= (__int_as_float(v[4 * i + 1]) + __int_as_float(t.y) >= tf ? 1u : 0u) << (4 * i + 1);
+            mask |= (__int_as_float(v[4 * i + 2]) + __int_as_float(t.z) >= tf ? 1u : 0u) << (4 * i + 2);
+            mask |= (__int_as_float(v[4 * i + 3]) + __int_as_float(t.w) >= tf ? 1u : 0u) << (4 * i + 3);
+          } else {
+            mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
+            mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
+            mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
+            mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
+          }
         }
       }
       const uint32_t keep = __ballot_sync(0xffffffffu, mask != 0u);
@@ -317,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     while (ok && cur.valid) {
       const int slot = gu & (kSlots - 1);
       const int q    = (cur.q_tile0 + cur.j) * kQueryTile + row;
-      int thr        = 0x7fffffff;
+      int thr        = F16 ? __float_as_int(CUDART_INF_F) : 0x7fffffff;  // float bits when F16
       int4 ce        = make_int4(0, 0, 0, 0);
       if (MODE == kModeScreen) {
         if (q < p.nq) { thr = __ldg(p.thr + q); }
@@ -338,8 +397,19 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       if (lane == 0) { mbar_arrive(smem_u32(&ctl->tmem_empty[slot])); }
 
       if (MODE == kModeScreen) {
-        const int m0 = max16(a), m1 = max16(a + 16), m2 = max16(b), m3 = max16(b + 16);
-        const bool h0 = m0 + ce.x >= thr, h1 = m1 + ce.y >= thr, h2 = m2 + ce.z >= thr, h3 = m3 + ce.w >= thr;
+        bool h0, h1, h2, h3;
+        if (F16) {
+          const float tf = __int_as_float(thr);
+          h0 = max16f(a) + __int_as_float(ce.x) >= tf;
+          h1 = max16f(a + 16) + __int_as_float(ce.y) >= tf;
+          h2 = max16f(b) + __int_as_float(ce.z) >= tf;
+          h3 = max16f(b + 16) + __int_as_float(ce.w) >= tf;
+        } else {
+          h0 = max16(a) + ce.x >= thr;
+          h1 = max16(a + 16) + ce.y >= thr;
+          h2 = max16(b) + ce.z >= thr;
+          h3 = max16(b + 16) + ce.w >= thr;
+        }
         if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
           // the exact e of the tile was staged with it
           if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
@@ -354,7 +424,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         // exact group maximum: e of the tile was staged with it
         if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
         const int32_t* e = init_smem + (cur.ts % ns) * kBaseTile + piece * kGroupRows;
-        const int m      = max(max32_plus(a, e), max32_plus(b, e + 32));
+        const int m = F16 ? float_key(fmaxf(max32f_plus(a, e), max32f_plus(b, e + 32)))
+                          : max(max32_plus(a, e), max32_plus(b, e + 32));
         if (q < p.nq) { p.gmax[static_cast<size_t>(q) * p.ld_gmax + cur.t * (kBaseTile / kGroupRows) + piece] = m; }
       }
       // next unit; a finished tile's e values are released (GROUPMAX)
@@ -394,9 +465,9 @@ cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, c
 {
   const size_t smem = screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
   // opt-in to large dynamic shared memory (cheap; set on every launch so that every device of the process has it)
-  auto kernel = args.mode == kModeScreen     ? screen_i8_kernel<kModeScreen>
-                : args.mode == kModeGroupMax ? screen_i8_kernel<kModeGroupMax>
-                                             : screen_i8_kernel<kModeRate>;
+  auto kernel = args.mode == kModeRate       ? screen_i8_kernel<kModeRate, false>
+                : args.mode == kModeScreen   ? (args.f16 ? screen_i8_kernel<kModeScreen, true> : screen_i8_kernel<kModeScreen, false>)
+                                             : (args.f16 ? screen_i8_kernel<kModeGroupMax, true> : screen_i8_kernel<kModeGroupMax, false>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) { return e; }
   kernel<<<grid, kThreads, smem, stream>>>(tm_q, tm_x, args);

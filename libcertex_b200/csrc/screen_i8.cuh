@@ -52,6 +52,7 @@ struct ScreenArgs {
   int panel_tiles;                // query tiles resident in shared memory
   int n_stages;                   // base-tile ring depth
   int mode;
+  int f16;                        // 1: fp16 codes, fp32 accumulators; init / cmax / thr hold float bits, gmax float keys
   uint32_t q_signed;              // 0 = uint8 codes, 1 = int8 codes
   uint32_t x_signed;
   const ScreenSeg* segs;          // [grid, kMaxSegs]; unused entries have t1 <= t0

@@ -80,19 +80,54 @@ def test_exact_against_oracle(n, dim, nq, k, metric, dtype, share, unequal, dups
     check(index, x, q, k, metric)
 
 
-def test_screen_runs_on_integer_indexes_and_dense_elsewhere():
+def test_which_searches_the_tensor_cores_screen():
     x, q = make(50000, 128, 100, "uint8", False, 0)
     index = certex.Index(128)
     index.add(x)
     with certex.search_stats() as st:
         index.search(q, k=10)
     assert st.queries == 100 and st.dense_queries == 0 and 1000 <= st.survivors < 100 * 50000 // 10
-    xf, qf = make(5000, 64, 10, "float32", False, 0)
-    fidx = certex.Index(64)
+    # float vectors of up to 128 dimensions: fp16 codes, certified threshold
+    xf, qf = make(50000, 96, 100, "float32", False, 0)
+    fidx = certex.Index(96)
     fidx.add(xf)
     with certex.search_stats() as st:
-        fidx.search(qf, k=10)
+        check(fidx, xf, qf, 10, "l2")
+    assert st.dense_queries == 0 and 1000 <= st.survivors < 100 * 50000 // 10
+    # wider float vectors, tiny sets and filtered searches: every vector is scored
+    xw, qw = make(5000, 200, 10, "float32", False, 0)
+    widx = certex.Index(200)
+    widx.add(xw)
+    with certex.search_stats() as st:
+        widx.search(qw, k=10)
     assert st.dense_queries == 10
+    with certex.search_stats() as st:
+        fidx.search(qf, k=10, filter=np.ones(50000, dtype=bool))
+    assert st.dense_queries == 100
+
+
+def test_fp16_screen_keeps_near_ties_and_large_values():
+    """Rows that differ from a query by less than the fp16 rounding of their coordinates, rows of very different
+    norms, and values near the fp16 range: the certified threshold must keep every true neighbour."""
+    rng = np.random.default_rng(0)
+    n, d = 40000, 64
+    x = rng.standard_normal((n, d)).astype(np.float32) * rng.choice([0.01, 1.0, 300.0], (n, 1)).astype(np.float32)
+    q = x[rng.choice(n, 150, replace=False)].copy()
+    for j in range(150):  # 30 near-copies of every query, apart by a few float32 ulps to a few fp16 ulps
+        rows = rng.choice(n, 30, replace=False)
+        x[rows] = q[j] * (1 + rng.standard_normal((30, d)).astype(np.float32) * rng.choice([1e-7, 1e-5, 1e-3], (30, 1)))
+    for metric in ("l2", "ip", "cosine"):
+        index = certex.Index(d, metric=metric)
+        index.add(x)
+        with certex.search_stats() as st:
+            check(index, x, q, 10, metric)
+            check(index, x, q, 40, metric)
+    big = rng.standard_normal((20000, 32)).astype(np.float32) * 3e4  # some coordinates beyond 65504: no fp16 code
+    bidx = certex.Index(32)
+    bidx.add(big)
+    with certex.search_stats() as st:
+        check(bidx, big, big[:20].copy(), 5, "l2")
+    assert st.dense_queries == 20
 
 
 @pytest.mark.parametrize("batch", [1, 100, 128, 1000, 2048, 100000])
