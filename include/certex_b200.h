@@ -251,7 +251,7 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t inde
 /**
  * The tensor-core pass alone on caller buffers (device pointers), the seam of the reference's
  * detail/kernels.hpp:290-304 (`screen_int8`) and :125-135 (`anchor_groups`), for kernel-level tests and timing.
- * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len 128 or 256,
+ * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len a multiple of 128 up to 4096,
  * nq_pad = nq rounded up to 128 with zero rows; init [n rounded up to 64] in row order (the per-row term added to the
  * product: -floor(|x|^2 / 2) for L2, -2^30 for rows that must never pass).
  * mode 0 (screen): keep iff init[x] + <q, x> >= thr[q]; cnt [nq] must be zeroed by the caller; cand [nq, cap].

@@ -35,7 +35,6 @@ cuvsError_t translate(F&& f)
 
 struct Holder {
   std::unique_ptr<Index> index;
-  int64_t n_partitioned = 0;
 };
 
 Resources& as_res(cuvsResources_t r)
@@ -319,10 +318,9 @@ cuvsError_t cuvsCertexSetLabels(cuvsResources_t res, DLManagedTensor* labels, in
 cuvsError_t cuvsCertexPartitionByLabels(cuvsResources_t res, cuvsCertexIndex_t index)
 {
   return translate([=] {
-    (void)as_res(res);
-    Holder& h = as_holder(index);
-    CERTEX_EXPECTS(h.index->has_labels(), "certex: the index has no labels");
-    h.n_partitioned = h.index->size();
+    Resources& r = as_res(res);
+    Holder& h    = as_holder(index);
+    h.index->partition_by_labels(r);
   });
 }
 
@@ -432,7 +430,7 @@ cuvsError_t certexB200IndexGetInfo(cuvsCertexIndex_t index, certexB200IndexInfo*
     info->has_labels      = h.index->has_labels() ? 1 : 0;
     info->integer_screen  = h.index->int_screen() ? 1 : 0;
     info->row_pitch_bytes = static_cast<int64_t>(h.index->pitch());
-    info->n_partitioned   = h.n_partitioned;
+    info->n_partitioned   = h.index->n_partitioned();
   });
 }
 
@@ -476,7 +474,7 @@ cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_
 {
   return translate([=] {
     Resources& r = as_res(res);
-    CERTEX_EXPECTS(code_len == 128 || code_len == 256, "certex: code_len must be 128 or 256");
+    CERTEX_EXPECTS(code_len >= 128 && code_len <= 4096 && code_len % 128 == 0, "certex: code_len must be a multiple of 128 up to 4096");
     CERTEX_EXPECTS(nq >= 1 && n >= 1 && n < (int64_t(1) << 31) && nq < (int64_t(1) << 24), "certex: sizes out of range");
     screen_raw(r, q_codes, nq, x_codes, n, code_len, is_signed != 0, init, mode, thr, gmax, ld, cnt, cand, cap, elapsed_ms);
   });

@@ -30,6 +30,7 @@ namespace {
 
 constexpr int64_t kTile = kBaseTile;  // stored rows per base tile of the tensor-core pass
 constexpr int64_t kQTile = kQueryTile;
+constexpr int64_t kMaxCodeBytes = 4096;  // longest code row the tensor-core pass takes (32 K blocks)
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
@@ -95,7 +96,8 @@ struct ScreenShape {
 
 ScreenShape shape_for(int kb)
 {
-  // shared memory: panel_tiles * kb * 16 KB + n_stages * (kb * 32 KB + 1 KB) + 9 KB must stay below 227 KB
+  // shared memory: panel_tiles * kb * 16 KB + n_stages * (kb * 32 KB + 1 KB) + 9 KB must stay below 227 KB; rows of
+  // more than two K blocks stream their K blocks instead (two query tiles per segment, stages fixed by the kernel)
   return kb == 1 ? ScreenShape{7, 3} : ScreenShape{2, 2};
 }
 
@@ -188,13 +190,13 @@ Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t
   CERTEX_EXPECTS(params.anchor_stride >= 1, "certex: anchor_stride must be at least 1");
   const bool is_int = dtype == kI8 || dtype == kU8;
   CERTEX_EXPECTS(!(params.metric == kCos && is_int), "certex: the cosine metric needs float32 or float16 vectors");
-  if (is_int && dim <= 256) {
+  if (is_int && dim <= kMaxCodeBytes) {
     screen_kind_ = 1;  // the stored row is its own code
     pitch_       = static_cast<size_t>(round_up(dim, 128));
     code_pitch_  = pitch_;
   } else {
     pitch_ = static_cast<size_t>(round_up(dim * dtype_size(dtype), 16));
-    if (!is_int && dim <= 128) {
+    if (!is_int && dim * 2 <= kMaxCodeBytes) {
       screen_kind_ = 2;  // fp16 codes
       code_pitch_  = static_cast<size_t>(round_up(dim * 2, 128));
     }
@@ -212,6 +214,7 @@ Index::~Index()
   cudaFree(vectors_);
   cudaFree(removed_);
   cudaFree(labels_);
+  cudaFree(part_ids_);
   cudaFree(codes_);
   cudaFree(perm_);
   cudaFree(inv_);
@@ -371,6 +374,53 @@ void Index::set_labels(const Resources& res, const int32_t* labels_device, int64
   res.sync();
   std::unique_lock<std::shared_mutex> lock(rw_);
   has_labels_ = true;
+  if (first < n_part_ && n > 0) { n_part_ = 0; }  // labels of partitioned rows changed: the partition is void
+}
+
+void Index::partition_by_labels(const Resources& res)
+{
+  std::lock_guard<std::mutex> w(writer_);
+  CERTEX_EXPECTS(has_labels_, "certex: the index has no labels");
+  const int64_t n = size_;
+  if (n == 0) { return; }
+  int32_t* ids = nullptr;
+  CERTEX_CUDA(cudaMalloc(&ids, static_cast<size_t>(n) * 4));
+  std::vector<int32_t> distinct, counts;
+  try {
+    Scratch scratch(res.stream);
+    int32_t* sorted   = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* iota     = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* d_dist   = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* d_counts = scratch.get<int32_t>(static_cast<size_t>(n));
+    int32_t* d_n      = scratch.get<int32_t>(1);
+    const size_t tb   = label_partition_temp_bytes(n);
+    void* temp        = scratch.get<uint8_t>(tb);
+    launch_label_partition(labels_, n, sorted, iota, ids, d_dist, d_counts, d_n, temp, tb, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    int32_t n_distinct = 0;
+    CERTEX_CUDA(cudaMemcpyAsync(&n_distinct, d_n, 4, cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+    distinct.resize(static_cast<size_t>(n_distinct));
+    counts.resize(static_cast<size_t>(n_distinct));
+    CERTEX_CUDA(cudaMemcpyAsync(distinct.data(), d_dist, distinct.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(counts.data(), d_counts, counts.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+  } catch (...) {
+    cudaFree(ids);
+    throw;
+  }
+  std::vector<int64_t> offsets(distinct.size() + 1, 0);
+  for (size_t i = 0; i < distinct.size(); ++i) { offsets[i + 1] = offsets[i] + counts[i]; }
+  int32_t* old = nullptr;
+  {
+    std::unique_lock<std::shared_mutex> lock(rw_);
+    old           = part_ids_;
+    part_ids_     = ids;
+    n_part_       = n;
+    part_labels_  = std::move(distinct);
+    part_offsets_ = std::move(offsets);
+  }
+  cudaFree(old);
 }
 
 // -------------------------------------------------------------------------------------------- search
@@ -447,6 +497,7 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   a.panel_tiles = shape.panel_tiles;
   a.n_stages    = shape.n_stages;
   a.f16         = screen_kind_ == 2 ? 1 : 0;
+  a.wide        = kb_ > 2 ? 1 : 0;
   a.q_signed    = dtype_ == kI8 ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.err         = err;
@@ -493,6 +544,104 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   CERTEX_CUDA(cudaGetLastError());
 }
 
+unsigned long long Index::search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k,
+                                           const Admit& adm, double* best_s, int32_t* best_row, int64_t n,
+                                           unsigned long long* launches) const
+{
+  // The one host decision of the path: which queries share a label. Their labels come to the host, the queries are
+  // ordered by label, and every label becomes a group (queries x that label's partition entries + the rows added
+  // since). Groups are scored, selected from and translated to ids in waves of bounded score memory, three launches
+  // per wave whatever the number of labels.
+  std::vector<int32_t> lab(static_cast<size_t>(nq));
+  CERTEX_CUDA(cudaMemcpyAsync(lab.data(), adm.query_labels, lab.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+  res.sync();
+  std::vector<int32_t> order(static_cast<size_t>(nq));
+  for (int i = 0; i < nq; ++i) { order[static_cast<size_t>(i)] = i; }
+  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return lab[a] < lab[b]; });
+
+  const int64_t n_tail  = n - n_part_;
+  const int64_t budget  = int64_t(1) << 28;  // doubles of score memory per wave
+  std::vector<LabelGroup> groups;
+  std::vector<int64_t> row_off;
+  std::vector<int32_t> row_n;
+  unsigned long long pairs = 0;
+  Scratch keep(res.stream);
+  int32_t* d_order = keep.get<int32_t>(static_cast<size_t>(nq));
+  CERTEX_CUDA(cudaMemcpyAsync(d_order, order.data(), order.size() * 4, cudaMemcpyHostToDevice, res.stream));
+
+  int wave_q0 = 0;           // first query (in label order) of the wave being collected
+  int64_t wave_scores = 0, wave_blocks = 0, wave_max_cols = 0;
+  auto flush = [&](int q_end) {
+    if (q_end == wave_q0) { return; }
+    Scratch scratch(res.stream);
+    const int nqw      = q_end - wave_q0;
+    double* scores     = scratch.get<double>(static_cast<size_t>(wave_scores));
+    LabelGroup* d_grp  = scratch.get<LabelGroup>(groups.size());
+    int64_t* d_off     = scratch.get<int64_t>(static_cast<size_t>(nqw));
+    int32_t* d_n       = scratch.get<int32_t>(static_cast<size_t>(nqw));
+    const int parts    = select_topk_parts(wave_max_cols, k);
+    double* part_s     = scratch.get<double>(static_cast<size_t>(nqw) * parts * k);
+    int32_t* part_row  = scratch.get<int32_t>(static_cast<size_t>(nqw) * parts * k);
+    CERTEX_CUDA(cudaMemcpyAsync(d_grp, groups.data(), groups.size() * sizeof(LabelGroup), cudaMemcpyHostToDevice, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_off, row_off.data(), row_off.size() * 8, cudaMemcpyHostToDevice, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_n, row_n.data(), row_n.size() * 4, cudaMemcpyHostToDevice, res.stream));
+    launch_dense_scores_grouped(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, q, qpitch, d_order, d_grp,
+                                static_cast<int>(groups.size()), wave_blocks, part_ids_, n_part_, n_tail, adm, scores, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    launch_select_topk_ragged(scores, d_off, d_n, wave_max_cols, k, d_order + wave_q0, nqw, best_s, best_row, part_s, part_row,
+                              res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    launch_group_columns_to_ids(best_row, k, d_order, d_grp, static_cast<int>(groups.size()), part_ids_, n_part_, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    *launches += 3;
+    groups.clear();
+    row_off.clear();
+    row_n.clear();
+    wave_q0 = q_end, wave_scores = 0, wave_blocks = 0, wave_max_cols = 0;
+  };
+
+  for (int i = 0; i < nq;) {
+    const int32_t l = lab[order[static_cast<size_t>(i)]];
+    int j           = i;
+    while (j < nq && lab[order[static_cast<size_t>(j)]] == l) { ++j; }
+    int64_t part_off = 0, n_in_part = 0;
+    const auto it = std::lower_bound(part_labels_.begin(), part_labels_.end(), l);
+    if (l >= 0 && it != part_labels_.end() && *it == l) {
+      const size_t at = static_cast<size_t>(it - part_labels_.begin());
+      part_off        = part_offsets_[at];
+      n_in_part       = part_offsets_[at + 1] - part_offsets_[at];
+    }
+    const int64_t n_cols = n_in_part + n_tail;
+    const int64_t ld     = round_up(n_cols, 4);
+    const int at_most    = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nq, budget / std::max<int64_t>(ld, 1))));
+    for (int a = i; a < j;) {  // the label's queries, in pieces that fit the score memory of a wave
+      const int nqg = std::min(j - a, at_most);
+      if (wave_scores > 0 && wave_scores + static_cast<int64_t>(nqg) * ld > budget) { flush(a); }
+      LabelGroup g{};
+      g.q_begin   = a;
+      g.nq        = nqg;
+      g.part_off  = part_off;
+      g.n_part    = static_cast<int32_t>(n_in_part);
+      g.ld        = static_cast<int32_t>(ld);
+      g.score_off = wave_scores;
+      g.blk_begin = wave_blocks;
+      groups.push_back(g);
+      for (int t = 0; t < nqg; ++t) {
+        row_off.push_back(wave_scores + static_cast<int64_t>(t) * ld);
+        row_n.push_back(static_cast<int32_t>(n_cols));
+      }
+      wave_scores += static_cast<int64_t>(nqg) * ld;
+      wave_blocks += grouped_blocks(nqg, n_cols);
+      wave_max_cols = std::max(wave_max_cols, n_cols);
+      pairs += static_cast<unsigned long long>(nqg) * static_cast<unsigned long long>(n_cols);
+      a += nqg;
+    }
+    i = j;
+  }
+  flush(nq);
+  return pairs;
+}
+
 void Index::search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
                    int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base) const
 {
@@ -526,7 +675,11 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
 
   SearchStats local{};
   local.queries = static_cast<unsigned long long>(nq);
-  if (screened) {
+  if (filter.query_labels && !filter.words && n_part_ > 0 && test_mode_ != 1) {
+    local.survivors = search_by_labels(res, queries, row_bytes, static_cast<int>(nq), k, adm, best_s, best_row, n, &local.launches);
+    local.verified      = local.survivors;
+    local.dense_queries = static_cast<unsigned long long>(nq);
+  } else if (screened) {
     const int64_t nq_pad = round_up(nq, kQTile);
     uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * code_pitch_);
     float* shift         = nullptr;
@@ -780,6 +933,7 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   a.panel_tiles = shape.panel_tiles;
   a.n_stages    = shape.n_stages;
   a.mode        = mode;
+  a.wide        = kb > 2 ? 1 : 0;
   a.q_signed    = is_signed ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.segs        = d_segs;

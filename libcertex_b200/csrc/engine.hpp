@@ -95,6 +95,9 @@ class Index {
   void remove(const Resources& res, const int64_t* ids_device, int64_t n_ids);
   void set_labels(const Resources& res, const int32_t* labels_device, int64_t n, int64_t first);
   void reserve(const Resources& res, int64_t n);
+  /// Groups the ids by label (the reference's partition_by_labels, cpp/src/neighbors/certex/certex.cu:1542-1606):
+  /// searches by label then score only the rows of the query's label, plus the rows added since.
+  void partition_by_labels(const Resources& res);
 
   /**
    * Exact k nearest neighbours of nq queries (device, dense row-major, the index's element type).
@@ -111,6 +114,7 @@ class Index {
   int dtype() const { return dtype_; }
   int metric() const { return params_.metric; }
   bool has_labels() const { return has_labels_; }
+  int64_t n_partitioned() const { return n_part_; }
   bool int_screen() const { return screen_kind_ != 0 && !code_overflow_; }  // a tensor-core screen is available
   const IndexParams& params() const { return params_; }
   size_t pitch() const { return pitch_; }
@@ -132,6 +136,9 @@ class Index {
                        std::vector<cudaEvent_t>* events) const;
   void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
                     const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
+  /// Search by label over the label partition; returns the (query, row) pairs scored and counts its launches.
+  unsigned long long search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k, const Admit& adm,
+                                      double* best_s, int32_t* best_row, int64_t n, unsigned long long* launches) const;
 
   IndexParams params_;
   int dtype_;
@@ -151,6 +158,12 @@ class Index {
   void* vectors_      = nullptr;  // [capacity, pitch]
   uint8_t* removed_   = nullptr;  // [capacity rounded up to 4]
   int32_t* labels_    = nullptr;  // [capacity], -1 = none
+  // label partition: ids 0 .. n_part_ - 1 in (label, id) order; label part_labels_[i] owns entries
+  // part_offsets_[i] .. part_offsets_[i + 1] - 1
+  int32_t* part_ids_  = nullptr;
+  int64_t n_part_     = 0;
+  std::vector<int32_t> part_labels_;
+  std::vector<int64_t> part_offsets_;
   // screen: the code rows sorted by squared norm (each appended batch on its own), and per sorted row
   void* codes_        = nullptr;  // [capacity, pitch] rows in sorted order
   int32_t* perm_      = nullptr;  // [capacity] sorted row -> id

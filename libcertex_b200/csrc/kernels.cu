@@ -642,10 +642,72 @@ __global__ void dense_scores_kernel(const uint8_t* vectors, size_t pitch, int d,
   }
 }
 
+// Dense scores of label groups in one launch. Group g pairs the queries order[q_begin .. q_begin + nq) (all of one
+// label) with the columns of that label: the n_part ids part_ids[part_off ..] of the label partition, then the rows
+// tail0 .. tail0 + n_tail - 1 added after the partition was made (`adm` keeps those of the query's label). Blocks
+// blk_begin[g] .. blk_begin[g + 1] - 1 belong to group g: quads of queries (slow) by chunks of 256 columns (fast).
+template <typename T, int METRIC>
+__global__ void dense_scores_grouped_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
+                                            const int32_t* order, const LabelGroup* groups, int n_groups,
+                                            const int32_t* part_ids, int64_t tail0, int64_t n_tail, Admit adm, double* out)
+{
+  extern __shared__ double sh[];
+  __shared__ double s_qq[kDenseQ];
+  __shared__ int64_t s_qidx[kDenseQ];
+  int lo = 0, hi = n_groups - 1;  // last group whose first block is <= blockIdx.x
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (groups[mid].blk_begin <= static_cast<int64_t>(blockIdx.x)) {
+      lo = mid;
+    } else {
+      hi = mid - 1;
+    }
+  }
+  const LabelGroup g    = groups[lo];
+  const int64_t n_cols  = g.n_part + n_tail;
+  const int64_t chunks  = (n_cols + blockDim.x - 1) / blockDim.x;
+  const int64_t local   = static_cast<int64_t>(blockIdx.x) - g.blk_begin;
+  const int b0          = static_cast<int>(local / chunks) * kDenseQ;
+  const int64_t col     = (local % chunks) * blockDim.x + threadIdx.x;
+  const int nb          = min(kDenseQ, g.nq - b0);
+  if (threadIdx.x < kDenseQ) {
+    const int b         = min(static_cast<int>(threadIdx.x), nb - 1);
+    s_qidx[threadIdx.x] = order[g.q_begin + b0 + b];
+  }
+  __syncthreads();
+  load_queries<T>(queries, qpitch, s_qidx, kDenseQ, d, sh, d, s_qq);
+  if (col >= n_cols) { return; }
+  const int64_t row = col < g.n_part ? part_ids[g.part_off + col] : tail0 + (col - g.n_part);
+  Acc<METRIC, kDenseQ> acc;
+  acc.clear();
+  scan_row<T, METRIC, kDenseQ>(vectors + static_cast<size_t>(row) * pitch, d, sh, d, acc);
+#pragma unroll
+  for (int b = 0; b < kDenseQ; ++b) {
+    if (b < nb) {
+      const bool ok = admitted(adm, s_qidx[b], row);
+      out[g.score_off + static_cast<int64_t>(b0 + b) * g.ld + col] = ok ? acc.result(b, s_qq[b]) : CUDART_INF;
+    }
+  }
+}
+
+// Columns of a label group's score row -> ids, for the k winners of every query of the group (see above).
+__global__ void group_columns_to_ids_kernel(int32_t* best_row, int k, const int32_t* order, const LabelGroup* groups,
+                                            const int32_t* part_ids, int64_t tail0)
+{
+  const LabelGroup g = groups[blockIdx.x];
+  for (int i = threadIdx.x; i < g.nq * k; i += blockDim.x) {
+    const size_t o    = static_cast<size_t>(order[g.q_begin + i / k]) * k + (i % k);
+    const int32_t col = best_row[o];
+    if (col >= 0) { best_row[o] = col < g.n_part ? part_ids[g.part_off + col] : static_cast<int32_t>(tail0 + (col - g.n_part)); }
+  }
+}
+
 // Block per query: radix walk to the k-th smallest score, then the winners (ties: smallest rows) are gathered, sorted
 // and written. Shared memory: sel_s [k2] doubles | sel_id [k2] int32.
+// With `row_off` the score rows are ragged: row blockIdx.x starts at scores + row_off[blockIdx.x] and has row_n[] columns.
 __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n_all, int k, const int32_t* qsel, int q0,
-                                   double* best_s, int32_t* best_row, int64_t chunk, double* part_s, int32_t* part_row)
+                                   double* best_s, int32_t* best_row, int64_t chunk, double* part_s, int32_t* part_row,
+                                   const int64_t* row_off, const int32_t* row_n)
 {
   extern __shared__ double sh[];
   __shared__ uint32_t hist[256];
@@ -656,8 +718,9 @@ __global__ void select_topk_kernel(const double* scores, int64_t ld, int64_t n_a
   int32_t* sel_id     = reinterpret_cast<int32_t*>(sh + k2);
   // blockIdx.y selects a chunk of columns [col0, col0 + n); with several chunks the winners go to part_* and are merged
   const int64_t col0  = static_cast<int64_t>(blockIdx.y) * chunk;
-  const int64_t n     = min(chunk, n_all - col0);
-  const double* row   = scores + static_cast<int64_t>(blockIdx.x) * ld + col0;
+  if (row_off) { n_all = row_n[blockIdx.x]; }
+  const int64_t n     = max(static_cast<int64_t>(0), min(chunk, n_all - col0));
+  const double* row   = scores + (row_off ? row_off[blockIdx.x] : static_cast<int64_t>(blockIdx.x) * ld) + col0;
   const int64_t qout  = qsel ? qsel[blockIdx.x] : q0 + static_cast<int>(blockIdx.x);
   const uint32_t want = static_cast<uint32_t>(min(static_cast<int64_t>(k), n));
 
@@ -1056,15 +1119,100 @@ void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, cons
   const size_t smem = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(k2);
   const int parts   = select_topk_parts(n, k);
   if (parts == 1) {
-    select_topk_kernel<<<nqb, 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, n, nullptr, nullptr);
+    select_topk_kernel<<<nqb, 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, n, nullptr, nullptr, nullptr, nullptr);
     return;
   }
   const int64_t chunk = (n + parts - 1) / parts;
-  select_topk_kernel<<<dim3(nqb, parts), 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, chunk, part_s, part_row);
+  select_topk_kernel<<<dim3(nqb, parts), 256, smem, s>>>(scores, ld, n, k, qsel, q0, best_s, best_row, chunk, part_s, part_row, nullptr, nullptr);
   const int n2       = next_pow2(parts * k);
   const size_t smem2 = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(n2);
   allow_smem(merge_partials_kernel, smem2);
   merge_partials_kernel<<<nqb, 256, smem2, s>>>(part_s, part_row, parts, k, n2, qsel, q0, best_s, best_row);
+}
+
+void launch_select_topk_ragged(const double* scores, const int64_t* row_off, const int32_t* row_n, int64_t n_max, int k,
+                               const int32_t* qsel, int nqb, double* best_s, int32_t* best_row, double* part_s,
+                               int32_t* part_row, cudaStream_t s)
+{
+  if (nqb <= 0) { return; }
+  const int k2      = next_pow2(k) < 2 ? 2 : next_pow2(k);
+  const size_t smem = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(k2);
+  const int parts   = select_topk_parts(n_max, k);
+  if (parts == 1) {
+    select_topk_kernel<<<nqb, 256, smem, s>>>(scores, 0, 0, k, qsel, 0, best_s, best_row, std::max<int64_t>(n_max, 1), nullptr,
+                                              nullptr, row_off, row_n);
+    return;
+  }
+  const int64_t chunk = (n_max + parts - 1) / parts;
+  select_topk_kernel<<<dim3(nqb, parts), 256, smem, s>>>(scores, 0, 0, k, qsel, 0, best_s, best_row, chunk, part_s, part_row,
+                                                         row_off, row_n);
+  const int n2       = next_pow2(parts * k);
+  const size_t smem2 = (sizeof(double) + sizeof(int32_t)) * static_cast<size_t>(n2);
+  allow_smem(merge_partials_kernel, smem2);
+  merge_partials_kernel<<<nqb, 256, smem2, s>>>(part_s, part_row, parts, k, n2, qsel, 0, best_s, best_row);
+}
+
+void launch_dense_scores_grouped(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
+                                 size_t qpitch, const int32_t* order, const LabelGroup* groups, int n_groups,
+                                 int64_t n_blocks, const int32_t* part_ids, int64_t tail0, int64_t n_tail, Admit adm,
+                                 double* out, cudaStream_t s)
+{
+  if (n_groups <= 0 || n_blocks <= 0) { return; }
+  const size_t smem = sizeof(double) * static_cast<size_t>(d) * kDenseQ;
+  by_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    auto go = [&](auto kernel) {
+      allow_smem(kernel, smem);
+      kernel<<<static_cast<unsigned>(n_blocks), 256, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch,
+                                                                 order, groups, n_groups, part_ids, tail0, n_tail, adm, out);
+    };
+    if (metric == kL2) {
+      go(dense_scores_grouped_kernel<T, kL2>);
+    } else if (metric == kIP) {
+      go(dense_scores_grouped_kernel<T, kIP>);
+    } else {
+      go(dense_scores_grouped_kernel<T, kCos>);
+    }
+  });
+}
+
+int64_t grouped_blocks(int nq, int64_t n_cols)
+{
+  return static_cast<int64_t>((nq + kDenseQ - 1) / kDenseQ) * ((n_cols + 255) / 256);
+}
+
+void launch_group_columns_to_ids(int32_t* best_row, int k, const int32_t* order, const LabelGroup* groups, int n_groups,
+                                 const int32_t* part_ids, int64_t tail0, cudaStream_t s)
+{
+  if (n_groups <= 0) { return; }
+  group_columns_to_ids_kernel<<<n_groups, 256, 0, s>>>(best_row, k, order, groups, part_ids, tail0);
+}
+
+// ids of all rows sorted by label (stable: ascending ids inside a label), the distinct labels and their counts
+__global__ void iota_kernel(int32_t* p, int64_t n)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) { p[i] = static_cast<int32_t>(i); }
+}
+
+size_t label_partition_temp_bytes(int64_t n)
+{
+  size_t a = 0, b = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, a, static_cast<const int32_t*>(nullptr), static_cast<int32_t*>(nullptr),
+                                  static_cast<const int32_t*>(nullptr), static_cast<int32_t*>(nullptr), n);
+  cub::DeviceRunLengthEncode::Encode(nullptr, b, static_cast<const int32_t*>(nullptr), static_cast<int32_t*>(nullptr),
+                                     static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), n);
+  return std::max(a, b);
+}
+
+void launch_label_partition(const int32_t* labels, int64_t n, int32_t* labels_sorted, int32_t* ids_in, int32_t* part_ids,
+                            int32_t* distinct, int32_t* counts, int32_t* n_distinct, void* temp, size_t temp_bytes,
+                            cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  iota_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(ids_in, n);
+  cub::DeviceRadixSort::SortPairs(temp, temp_bytes, labels, labels_sorted, ids_in, part_ids, n, 0, 32, s);
+  cub::DeviceRunLengthEncode::Encode(temp, temp_bytes, labels_sorted, distinct, counts, n_distinct, n, s);
 }
 
 void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_base, const void* queries, size_t qpitch,

@@ -96,6 +96,45 @@ int select_topk_parts(int64_t n, int k);
 void launch_select_topk(const double* scores, int64_t ld, int64_t n, int k, const int32_t* qsel, int q0, int nqb,
                         double* best_s, int32_t* best_row, double* part_s, int32_t* part_row, cudaStream_t s);
 
+/// One label's share of a search by labels: queries order[q_begin .. q_begin + nq) against the n_part partition entries
+/// part_ids[part_off ..] followed by the rows added after the partition. Its scores are nq rows of ld doubles from
+/// score_off; blk_begin is the first block of the group in the scoring launch.
+struct LabelGroup {
+  int32_t q_begin;
+  int32_t nq;
+  int64_t part_off;
+  int32_t n_part;
+  int32_t ld;
+  int64_t score_off;
+  int64_t blk_begin;
+};
+
+/// Blocks the scoring launch spends on a group of nq queries and n_cols columns.
+int64_t grouped_blocks(int nq, int64_t n_cols);
+
+/// Exact fp64 scores of every group (rows `adm` rejects score +inf); n_blocks = sum of grouped_blocks over the groups.
+void launch_dense_scores_grouped(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
+                                 size_t qpitch, const int32_t* order, const LabelGroup* groups, int n_groups,
+                                 int64_t n_blocks, const int32_t* part_ids, int64_t tail0, int64_t n_tail, Admit adm,
+                                 double* out, cudaStream_t s);
+
+/// launch_select_topk over ragged score rows: row i starts at scores + row_off[i], has row_n[i] <= n_max columns and
+/// answers query qsel[i]. part_s / part_row: nqb * select_topk_parts(n_max, k) * k elements.
+void launch_select_topk_ragged(const double* scores, const int64_t* row_off, const int32_t* row_n, int64_t n_max, int k,
+                               const int32_t* qsel, int nqb, double* best_s, int32_t* best_row, double* part_s,
+                               int32_t* part_row, cudaStream_t s);
+
+/// best_row of the queries of every group: column of the group's score row -> id.
+void launch_group_columns_to_ids(int32_t* best_row, int k, const int32_t* order, const LabelGroup* groups, int n_groups,
+                                 const int32_t* part_ids, int64_t tail0, cudaStream_t s);
+
+/// Label partition: part_ids = ids 0 .. n - 1 in (label, id) order, distinct / counts = the distinct labels ascending
+/// and how many rows carry each, *n_distinct their number. labels_sorted, ids_in: scratch of n; distinct, counts: n.
+size_t label_partition_temp_bytes(int64_t n);
+void launch_label_partition(const int32_t* labels, int64_t n, int32_t* labels_sorted, int32_t* ids_in, int32_t* part_ids,
+                            int32_t* distinct, int32_t* counts, int32_t* n_distinct, void* temp, size_t temp_bytes,
+                            cudaStream_t s);
+
 /// neighbors / distances / (optional) fp64 scores of the public result from the internal best lists.
 /// id = row < 0 ? -1 : id_base + row. Distances: L2 s, inner product (|q|^2 - s) / 2, cosine s / 2.
 void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_base, const void* queries, size_t qpitch,

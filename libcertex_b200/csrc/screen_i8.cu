@@ -31,6 +31,11 @@
 // exact arithmetic would keep. It replaces the reference's fp16 pass `screen`
 // (cpp/src/neighbors/certex/detail/kernels.hpp:101-114; on B200 the mma.sync kernel of detail/screen_sm80.cu).
 //
+// Rows longer than two K blocks (WIDE = true: fp16 codes of more than 128 dimensions, 8-bit vectors of more than 256)
+// do not fit shared memory as a resident query panel. There a stage of the ring holds one K block of up to two query
+// tiles and of one base tile (64 KB), the MMAs of both query tiles accumulate over the K blocks into the two TMEM slots,
+// and the e values of a tile travel through a small ring of their own.
+//
 // CTA = 18 warps: warps 0..15 are the epilogue (four warps per TMEM lane quarter, each owning one 64-column piece of
 // every unit), warp 16 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
 // warp 17 lane 0 issues tcgen05.mma. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
@@ -57,6 +62,10 @@ constexpr int kThreads    = 32 * (2 + kEpiWarps);
 constexpr int kTmaWarp    = kEpiWarps;
 constexpr int kMmaWarp    = kEpiWarps + 1;
 constexpr int kRecBuf     = 64;                // staged survivor records per epilogue warp
+constexpr int kWideStage  = 2 * kQTileBytes + kBTileBytes;  // WIDE: one K block of two query tiles and a base tile
+constexpr int kWideStages = 3;
+constexpr int kERing      = 4;                 // WIDE: tiles whose e values may be in flight
+constexpr int kSharedSegs = 64;                // segments of a CTA (a CTA is never given more)
 
 struct SharedCtl {
   uint64_t full[kMaxStages];    // TMA landed a base tile (GROUPMAX: and its e values) in the stage
@@ -66,18 +75,21 @@ struct SharedCtl {
   uint64_t panel_full;
   uint64_t panel_empty;
   uint64_t drain;
+  uint64_t e_full[kERing];      // WIDE: the e values of a tile have landed
+  uint64_t e_empty[kERing];     // WIDE: every epilogue warp is done with them
   uint32_t tmem_base;
   int abort_flag;
-  ScreenSeg segs[kMaxSegs];
+  ScreenSeg segs[kSharedSegs];
 };
 
 // Position in the CTA's unit sequence: for every base tile of a segment, the query tiles of the segment's panel.
 struct Cursor {
-  int s, t, j, ts, nqt, t1, q_tile0;
+  int s, t, j, ts, nqt, t1, q_tile0, col0;
   bool valid;
 };
 
-__device__ __forceinline__ void cursor_seg(Cursor& c, const ScreenSeg* segs, int nseg)
+template <bool COL0>
+__device__ __forceinline__ void cursor_seg(Cursor& c, const ScreenSeg* segs, const int* seg_col0, int nseg)
 {
   c.valid = c.s < nseg;
   if (c.valid) {
@@ -86,6 +98,7 @@ __device__ __forceinline__ void cursor_seg(Cursor& c, const ScreenSeg* segs, int
     c.t1               = sg.t1;
     c.nqt              = sg.n_qtiles;
     c.q_tile0          = sg.q_tile0;
+    if (COL0) { c.col0 = seg_col0 ? seg_col0[c.s] : 0; }
   }
 }
 
@@ -156,7 +169,7 @@ __device__ __forceinline__ int32_t float_key(float f)
   return i ^ ((i >> 31) & 0x7fffffff);
 }
 
-template <int MODE, bool F16>
+template <int MODE, bool F16, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_x,
                                                                 const ScreenArgs p)
@@ -164,28 +177,36 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const ScreenSeg* gsegs = p.segs + static_cast<size_t>(blockIdx.x) * kMaxSegs;
+  // the CTA's segments: a slice of one list (seg_begin), or its kMaxSegs slots of which the leading ones are used
+  const int seg_first   = p.seg_begin ? p.seg_begin[blockIdx.x] : static_cast<int>(blockIdx.x) * kMaxSegs;
+  const ScreenSeg* gsegs = p.segs + seg_first;
+  const int* seg_col0    = p.seg_col0 ? p.seg_col0 + seg_first : nullptr;
   int nseg               = 0;
-  while (nseg < kMaxSegs && gsegs[nseg].t1 > gsegs[nseg].t0) { ++nseg; }
-  if (nseg == 0) { return; }  // uniform over the CTA
+  if (p.seg_begin) {
+    nseg = min(p.seg_begin[blockIdx.x + 1] - seg_first, kSharedSegs);
+  } else {
+    while (nseg < kMaxSegs && gsegs[nseg].t1 > gsegs[nseg].t0) { ++nseg; }
+  }
+  if (nseg <= 0) { return; }  // uniform over the CTA
 
   // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle)
   const uint32_t base      = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base        = smem_raw + (base - smem_u32(smem_raw));
   const int kb             = p.kb;
-  const int ns             = p.n_stages;
+  const int ns             = WIDE ? kWideStages : p.n_stages;
   const uint32_t panel_off = 0;
-  const uint32_t stage_off = panel_off + static_cast<uint32_t>(p.panel_tiles) * kb * kQTileBytes;
-  const uint32_t init_off  = stage_off + static_cast<uint32_t>(ns) * kb * kBTileBytes;
-  const uint32_t rec_off   = init_off + static_cast<uint32_t>(ns) * kBaseTile * 4;
+  const uint32_t stage_off = WIDE ? 0u : panel_off + static_cast<uint32_t>(p.panel_tiles) * kb * kQTileBytes;
+  const uint32_t init_off  = stage_off + (WIDE ? static_cast<uint32_t>(kWideStages * kWideStage)
+                                               : static_cast<uint32_t>(ns) * kb * kBTileBytes);
+  const uint32_t rec_off   = init_off + static_cast<uint32_t>(WIDE ? kERing : ns) * kBaseTile * 4;
   const uint32_t ctl_off   = rec_off + kEpiWarps * kRecBuf * 8;
   SharedCtl* ctl           = reinterpret_cast<SharedCtl*>(gen_base + ctl_off);
   const int32_t* init_smem = reinterpret_cast<const int32_t*>(gen_base + init_off);
   volatile int* abort_flag = &ctl->abort_flag;
-  constexpr bool kStageE   = MODE != kModeRate;  // e values travel with the tile and are read by the epilogue
+  constexpr bool kStageE   = MODE != kModeRate && !WIDE;  // e values travel with the stage and are read by the epilogue
 
   const ScreenSeg* segs = ctl->segs;
-  if (threadIdx.x < kMaxSegs) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
+  if (threadIdx.x < nseg) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
   if (threadIdx.x == 0) {
     for (int i = 0; i < ns; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
@@ -198,6 +219,10 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     mbar_init(smem_u32(&ctl->panel_full), 1);
     mbar_init(smem_u32(&ctl->panel_empty), 1);
     mbar_init(smem_u32(&ctl->drain), 1);
+    for (int i = 0; i < kERing; ++i) {
+      mbar_init(smem_u32(&ctl->e_full[i]), 1);
+      mbar_init(smem_u32(&ctl->e_empty[i]), kEpiWarps);
+    }
     ctl->abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
@@ -214,7 +239,54 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
 
   if (warp == kTmaWarp) {
     // ================================================================ TMA producer
-    if (lane == 0) {
+    if (WIDE && lane == 0) {
+      int ks = 0, ts = 0;  // K-block stages and tiles issued so far
+      bool aborted = false;
+      for (int s = 0; s < nseg && !aborted; ++s) {
+        const ScreenSeg sg = segs[s];
+        for (int t = sg.t0; t < sg.t1 && !aborted; ++t, ++ts) {
+          const int er = ts % kERing;
+          if (ts >= kERing && !mbar_wait(smem_u32(&ctl->e_empty[er]), ((ts / kERing) - 1) & 1, abort_flag, p.err, 8)) {
+            aborted = true;
+            break;
+          }
+          mbar_arrive_expect_tx(smem_u32(&ctl->e_full[er]), kBaseTile * 4);
+          bulk_load_1d(base + init_off + er * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4,
+                       smem_u32(&ctl->e_full[er]));
+          for (int b = 0; b < kb; ++b, ++ks) {
+            const int st = ks % ns;
+            if (ks >= ns && !mbar_wait(smem_u32(&ctl->empty[st]), ((ks / ns) - 1) & 1, abort_flag, p.err, 2)) {
+              aborted = true;
+              break;
+            }
+            const uint32_t fbar = smem_u32(&ctl->full[st]);
+            const uint32_t dst  = base + stage_off + st * kWideStage;
+            mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(sg.n_qtiles) * kQTileBytes + kBTileBytes);
+            for (int j = 0; j < sg.n_qtiles; ++j) {
+              tma_load_2d(dst + j * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, fbar);
+            }
+            if (MODE == kModeGroupMax && !p.plain_tiles) {
+              tma_load_3d(dst + 2 * kQTileBytes, &tm_x, b * 128, 0, t, fbar);
+            } else {
+              tma_load_2d(dst + 2 * kQTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
+            }
+          }
+        }
+      }
+      if (*abort_flag) {
+        // let the copies that are still in flight land before the CTA leaves (bounded)
+        for (int back = 1; back <= ns && back <= ks; ++back) {
+          const int u        = ks - back;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(smem_u32(&ctl->full[u % ns]), (u / ns) & 1) && clock64() - t0 < (1ll << 24)) {}
+        }
+        for (int back = 1; back <= kERing && back <= ts; ++back) {
+          const int u        = ts - back;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(smem_u32(&ctl->e_full[u % kERing]), (u / kERing) & 1) && clock64() - t0 < (1ll << 24)) {}
+        }
+      }
+    } else if (lane == 0) {
       int ts       = 0;
       bool aborted = false;
       for (int s = 0; s < nseg && !aborted; ++s) {
@@ -236,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           const uint32_t fbar = smem_u32(&ctl->full[st]);
           mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(kb) * kBTileBytes + (kStageE ? kBaseTile * 4 : 0));
           for (int b = 0; b < kb; ++b) {
-            if (MODE == kModeGroupMax) {
+            if (MODE == kModeGroupMax && !p.plain_tiles) {
               // anchors: column c of tile t is anchor c * n_tiles + t, so every group of 64 columns samples the whole
               // (norm-sorted) set; the map is 3-D (bytes, column, tile)
               tma_load_3d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, t, fbar);
@@ -268,7 +340,44 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       const uint64_t b_desc0 = smem_desc_sw128(base + stage_off);
       int gu = 0, ts = 0;
       bool ok = true;
-      for (int s = 0; s < nseg && ok; ++s) {
+      if (WIDE) {
+        int ks = 0;
+        for (int s = 0; s < nseg && ok; ++s) {
+          const ScreenSeg sg = segs[s];
+          for (int t = sg.t0; t < sg.t1 && ok; ++t, gu += sg.n_qtiles) {
+            for (int b = 0; b < kb && ok; ++b, ++ks) {
+              const int st = ks % ns;
+              ok           = mbar_wait(smem_u32(&ctl->full[st]), (ks / ns) & 1, abort_flag, p.err, 4);
+              if (!ok) { break; }
+              tc_fence_after();
+              const uint64_t s_desc = b_desc0 + static_cast<uint64_t>(st) * (kWideStage >> 4);
+              for (int j = 0; j < sg.n_qtiles; ++j) {
+                const int u    = gu + j;
+                const int slot = u & (kSlots - 1);
+                if (b == 0 && u >= kSlots) {  // the slot's previous unit must be in the epilogue's registers
+                  ok = mbar_wait(smem_u32(&ctl->tmem_empty[slot]), ((u >> 1) - 1) & 1, abort_flag, p.err, 5);
+                  if (!ok) { break; }
+                  tc_fence_after();
+                }
+                const uint32_t d_tmem = tmem + static_cast<uint32_t>(slot * kBaseTile);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint64_t ad = s_desc + static_cast<uint64_t>(j * (kQTileBytes >> 4) + k * 2);
+                  const uint64_t bd = s_desc + static_cast<uint64_t>(2 * (kQTileBytes >> 4) + k * 2);
+                  if (F16) {
+                    mma_f16(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
+                  } else {
+                    mma_i8(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
+                  }
+                }
+                if (b == kb - 1) { tc_commit(smem_u32(&ctl->tmem_full[slot])); }
+              }
+              if (ok) { tc_commit(smem_u32(&ctl->empty[st])); }
+            }
+          }
+        }
+      }
+      for (int s = 0; s < nseg && ok && !WIDE; ++s) {
         const ScreenSeg sg = segs[s];
         ok                 = mbar_wait(smem_u32(&ctl->panel_full), s & 1, abort_flag, p.err, 3);
         for (int t = sg.t0; t < sg.t1 && ok; ++t, ++ts) {
@@ -321,8 +430,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     int n_rec                = 0;  // staged records of this warp (warp-uniform)
 
     Cursor cur;
-    cur.s = 0, cur.j = 0, cur.ts = 0;
-    cursor_seg(cur, segs, nseg);
+    cur.s = 0, cur.j = 0, cur.ts = 0, cur.col0 = 0;
+    cursor_seg<MODE == kModeGroupMax>(cur, segs, seg_col0, nseg);
     int gu  = 0;
     bool ok = true;
 
@@ -412,8 +521,12 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         }
         if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
           // the exact e of the tile was staged with it
-          if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
-          const int32_t* e   = init_smem + (cur.ts % ns) * kBaseTile + piece * kGroupRows;
+          const int er = WIDE ? cur.ts % kERing : cur.ts % ns;
+          if (!mbar_wait(WIDE ? smem_u32(&ctl->e_full[er]) : smem_u32(&ctl->full[er]), (cur.ts / (WIDE ? kERing : ns)) & 1,
+                         abort_flag, p.err, 6)) {
+            break;
+          }
+          const int32_t* e   = init_smem + er * kBaseTile + piece * kGroupRows;
           const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
           records(a, h0, thr, q, row0, e);
           records(a + 16, h1, thr, q, row0 + 16, e + 16);
@@ -422,24 +535,30 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         }
       } else {
         // exact group maximum: e of the tile was staged with it
-        if (!mbar_wait(smem_u32(&ctl->full[cur.ts % ns]), (cur.ts / ns) & 1, abort_flag, p.err, 6)) { break; }
-        const int32_t* e = init_smem + (cur.ts % ns) * kBaseTile + piece * kGroupRows;
+        const int er = WIDE ? cur.ts % kERing : cur.ts % ns;
+        if (!mbar_wait(WIDE ? smem_u32(&ctl->e_full[er]) : smem_u32(&ctl->full[er]), (cur.ts / (WIDE ? kERing : ns)) & 1,
+                       abort_flag, p.err, 6)) {
+          break;
+        }
+        const int32_t* e = init_smem + er * kBaseTile + piece * kGroupRows;
         const int m = F16 ? float_key(fmaxf(max32f_plus(a, e), max32f_plus(b, e + 32)))
                           : max(max32_plus(a, e), max32_plus(b, e + 32));
-        if (q < p.nq) { p.gmax[static_cast<size_t>(q) * p.ld_gmax + cur.t * (kBaseTile / kGroupRows) + piece] = m; }
+        if (q < p.nq) {
+          p.gmax[static_cast<size_t>(q) * p.ld_gmax + (cur.t - cur.col0) * (kBaseTile / kGroupRows) + piece] = m;
+        }
       }
       // next unit; a finished tile's e values are released (GROUPMAX)
       ++gu;
       if (++cur.j == cur.nqt) {
         cur.j = 0;
-        if (kStageE) {
+        if (kStageE || WIDE) {
           __syncwarp();
-          if (lane == 0) { mbar_arrive(smem_u32(&ctl->empty[cur.ts % ns])); }
+          if (lane == 0) { mbar_arrive(WIDE ? smem_u32(&ctl->e_empty[cur.ts % kERing]) : smem_u32(&ctl->empty[cur.ts % ns])); }
         }
         ++cur.ts;
         if (++cur.t == cur.t1) {
           ++cur.s;
-          cursor_seg(cur, segs, nseg);
+          cursor_seg<MODE == kModeGroupMax>(cur, segs, seg_col0, nseg);
         }
       }
     }
@@ -455,6 +574,12 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
 
 }  // namespace
 
+size_t screen_smem_bytes_wide()
+{
+  return 1024 + static_cast<size_t>(kWideStages) * kWideStage + static_cast<size_t>(kERing) * kBaseTile * 4 +
+         kEpiWarps * kRecBuf * 8 + sizeof(SharedCtl) + 64;
+}
+
 size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages)
 {
   return 1024 + static_cast<size_t>(panel_tiles) * kb * kQTileBytes + static_cast<size_t>(n_stages) * kb * kBTileBytes +
@@ -463,11 +588,18 @@ size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages)
 
 cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args, int grid, cudaStream_t stream)
 {
-  const size_t smem = screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
+  const size_t smem = args.wide ? screen_smem_bytes_wide() : screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
   // opt-in to large dynamic shared memory (cheap; set on every launch so that every device of the process has it)
-  auto kernel = args.mode == kModeRate       ? screen_i8_kernel<kModeRate, false>
-                : args.mode == kModeScreen   ? (args.f16 ? screen_i8_kernel<kModeScreen, true> : screen_i8_kernel<kModeScreen, false>)
-                                             : (args.f16 ? screen_i8_kernel<kModeGroupMax, true> : screen_i8_kernel<kModeGroupMax, false>);
+  auto kernel = screen_i8_kernel<kModeRate, false, false>;
+  if (args.mode == kModeRate) {
+    if (args.wide) { return cudaErrorInvalidValue; }
+  } else if (args.mode == kModeScreen) {
+    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeScreen, true, true> : screen_i8_kernel<kModeScreen, false, true>)
+                       : (args.f16 ? screen_i8_kernel<kModeScreen, true, false> : screen_i8_kernel<kModeScreen, false, false>);
+  } else {
+    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeGroupMax, true, true> : screen_i8_kernel<kModeGroupMax, false, true>)
+                       : (args.f16 ? screen_i8_kernel<kModeGroupMax, true, false> : screen_i8_kernel<kModeGroupMax, false, false>);
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) { return e; }
   kernel<<<grid, kThreads, smem, stream>>>(tm_q, tm_x, args);

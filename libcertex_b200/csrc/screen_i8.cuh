@@ -55,11 +55,16 @@ struct ScreenArgs {
   int f16;                        // 1: fp16 codes, fp32 accumulators; init / cmax / thr hold float bits, gmax float keys
   uint32_t q_signed;              // 0 = uint8 codes, 1 = int8 codes
   uint32_t x_signed;
-  const ScreenSeg* segs;          // [grid, kMaxSegs]; unused entries have t1 <= t0
+  const ScreenSeg* segs;          // [grid, kMaxSegs]; unused entries have t1 <= t0. With seg_begin: one list
+  const int* seg_begin;           // optional [grid + 1]: CTA b works on segs[seg_begin[b] .. seg_begin[b + 1])
+  const int* seg_col0;            // optional, per segment: the tile whose groups are columns 0..3 of gmax (else tile 0)
+  int wide;                       // 1: rows of more than two K blocks; a segment then has at most two query tiles
+  int plain_tiles;                // GROUPMAX: tile t is rows [256 t, 256 t + 256) of a 2-D map (else the 3-D anchor map)
   int* err;                       // set to a non-zero code when a bounded wait gave up
 };
 
 size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages);
+size_t screen_smem_bytes_wide();
 
 cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args, int grid, cudaStream_t stream);
 

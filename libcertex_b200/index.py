@@ -122,8 +122,9 @@ class _Core:
 class Index:
     """Exact k-NN index; every search returns the exact k nearest stored vectors of every query.
 
-    Same constructor as the reference (certex/index.py:220-238). width, n_lists, local_projections, int8_rows and
-    partition_labels only tune the reference's speed; they are accepted and have no effect here. storage="host" is
+    Same constructor as the reference (certex/index.py:220-238). width, n_lists, local_projections and int8_rows
+    only tune the reference's speed; they are accepted and have no effect here. partition_labels=True keeps the ids
+    grouped by label, so that a search by labels scores only the vectors of the query's label. storage="host" is
     accepted; vectors are kept in GPU memory. The vectors keep the element type of the first addition (float32,
     float16, int8, uint8; other types become float32; cosine needs a float type).
     """
@@ -161,6 +162,7 @@ class Index:
             "storage": self.storage,
             "ntotal": self.ntotal,
             "integer_screen": None if i is None else bool(i.integer_screen),
+            "n_partitioned": 0 if i is None else int(i.n_partitioned),
         }
 
     # ------------------------------------------------------------------ updates
@@ -218,9 +220,23 @@ class Index:
                 L.check(lib.cuvsCertexExtend(res, xt.ref, self.core.handle))
             if lab is not None:
                 L.check(lib.cuvsCertexSetLabels(res, L.Tensor(lab).ref, first, self.core.handle))
-                if self.partition_labels:
+                i = self.core.info()  # the partition is renewed once an eighth of the vectors is newer than it
+                if self.partition_labels and 8 * (int(i.size) - int(i.n_partitioned)) > int(i.size):
                     L.check(lib.cuvsCertexPartitionByLabels(res, self.core.handle))
         return _like_input(torch.arange(first, first + X.shape[0]), kind)
+
+    def set_labels(self, labels, first=0):
+        """Labels of the vectors first, first + 1, ... (cuvsCertexSetLabels); relabeling voids the label partition."""
+        _need(self.core is not None, "add vectors first")
+        lab = _as_torch(labels)[0].reshape(-1).to(device="cuda", dtype=torch.int32).contiguous()
+        with self._writer:
+            L.check(L.lib().cuvsCertexSetLabels(L.resources(), L.Tensor(lab).ref, int(first), self.core.handle))
+
+    def partition_by_labels(self):
+        """Group the ids by label now (cuvsCertexPartitionByLabels); `add` does it by itself as the index grows."""
+        _need(self.core is not None, "add vectors first")
+        with self._writer:
+            L.check(L.lib().cuvsCertexPartitionByLabels(L.resources(), self.core.handle))
 
     def remove(self, ids):
         """Remove vectors by id; they never appear in later results."""

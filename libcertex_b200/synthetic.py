@@ -38,6 +38,30 @@ def mixture_u8(n, dim=128, n_centers=1000, sigma=18.0, seed=0, row0=0, device="c
     return out
 
 
+def clustered_unit_f32(n, dim=768, n_clusters=4096, seed=0, row0=0, device="cuda"):
+    """Rows [row0, row0 + n) of the filtered workload's float32 vectors: a unit-length cluster centre (Gaussian
+    direction) plus noise of length about sigma, sigma log-uniform in [0.05, 0.3] per cluster and unequal over the
+    dimensions (fixed per-dimension scales in [0.25, 1.75]); every row is then scaled to unit length. Chunked and
+    seeded like mixture_u8."""
+    g0 = torch.Generator().manual_seed(7_000_003 + n_clusters)
+    centers = torch.randn((n_clusters, dim), generator=g0)
+    centers /= centers.norm(dim=1, keepdim=True)
+    sigma = torch.exp(torch.rand(n_clusters, generator=g0) * np.log(0.3 / 0.05) + np.log(0.05))
+    scales = (torch.rand(dim, generator=g0) * 1.5 + 0.25) / np.sqrt(dim)
+    centers, sigma, scales = centers.to(device), sigma.to(device), scales.to(device)
+    out = torch.empty((n, dim), dtype=torch.float32, device=device)
+    slab = 1 << 16
+    s0, s1 = row0 // slab, (row0 + n + slab - 1) // slab
+    for c in range(s0, s1):
+        g = torch.Generator(device=device).manual_seed(seed * 1_000_003 + c)
+        which = torch.randint(0, n_clusters, (slab,), generator=g, device=device)
+        rows = centers[which] + torch.randn((slab, dim), generator=g, device=device) * scales * sigma[which, None]
+        rows /= rows.norm(dim=1, keepdim=True)
+        a, b = max(row0, c * slab), min(row0 + n, (c + 1) * slab)
+        out[a - row0 : b - row0] = rows[a - c * slab : b - c * slab]
+    return out
+
+
 def gaussian_f32(n, nq, dim=128, seed=0):
     """The CPU plumbing configuration: base then queries from one numpy default_rng(seed) stream, i.i.d. N(0, 1)."""
     rng = np.random.default_rng(seed)

@@ -39,6 +39,14 @@ CASES = [
     (20000, 128, 100, 10, "cosine", "float16", 1.0, True, 0),
     (25, 32, 50, 10, "l2", "float32", 1.0, False, 0),
     (3000, 33, 40, 2048, "ip", "float32", 1.0, True, 0),
+    # more than 128 float dimensions / 256 bytes: code rows of several K blocks
+    (30000, 200, 300, 10, "l2", "float32", 1.0, False, 0),
+    (20000, 768, 150, 100, "cosine", "float32", 0.5, True, 0),
+    (20000, 768, 50, 10, "ip", "float16", 1.0, True, 0),
+    (12000, 2048, 20, 10, "l2", "float32", 1.0, False, 0),
+    (20000, 1024, 200, 10, "l2", "uint8", 1.0, False, 0),
+    (6000, 4096, 30, 10, "ip", "int8", 1.0, False, 0),
+    (3000, 2100, 10, 10, "l2", "float32", 1.0, False, 0),
 ]
 
 
@@ -94,12 +102,19 @@ def test_which_searches_the_tensor_cores_screen():
     with certex.search_stats() as st:
         check(fidx, xf, qf, 10, "l2")
     assert st.dense_queries == 0 and 1000 <= st.survivors < 100 * 50000 // 10
-    # wider float vectors, tiny sets and filtered searches: every vector is scored
-    xw, qw = make(5000, 200, 10, "float32", False, 0)
+    # float vectors of up to 2048 dimensions are screened too (several K blocks per code row)
+    xw, qw = make(20000, 200, 10, "float32", False, 0)
     widx = certex.Index(200)
     widx.add(xw)
     with certex.search_stats() as st:
         widx.search(qw, k=10)
+    assert st.dense_queries == 0 and st.survivors < 10 * 20000 // 10
+    # wider vectors still, tiny sets and filtered searches: every vector is scored
+    xv, qv = make(3000, 2100, 10, "float32", False, 0)
+    vidx = certex.Index(2100)
+    vidx.add(xv)
+    with certex.search_stats() as st:
+        vidx.search(qv, k=10)
     assert st.dense_queries == 10
     with certex.search_stats() as st:
         fidx.search(qf, k=10, filter=np.ones(50000, dtype=bool))

@@ -26,6 +26,11 @@ SHAPES = [
     (130, 40000, 256, 0),
     (1, 128, 128, 0),
     (513, 255, 128, 0),
+    # rows of more than two K blocks: the K blocks stream through the stage ring
+    (300, 6000, 384, 0),
+    (129, 3000, 512, 1),
+    (50, 2000, 1536, 0),
+    (700, 1500, 4096, 1),
 ]
 
 

@@ -82,6 +82,101 @@ def test_labels_after_extend_and_remove():
     assert (I[ql == 16] == -1).all() and np.isinf(D[ql == 16]).all()
 
 
+def test_label_partition_with_newer_vectors():
+    """The partition made at 20 000 vectors stays while 1 500 more arrive (less than an eighth): the search then scores
+    the label's partition entries and the newer vectors together. Partitioned and unpartitioned searches agree."""
+    x, q = data(21500, 24, 400, "float32", seed=11)
+    rng = np.random.default_rng(12)
+    lab = rng.integers(0, 32, 21500).astype(np.int32)
+    ql = rng.integers(-1, 34, 400).astype(np.int32)  # -1 and the labels 32, 33 match nothing
+    index = certex.Index(24)
+    index.add(x[:20000], labels=lab[:20000])
+    assert index.info()["n_partitioned"] == 20000
+    index.add(x[20000:], labels=lab[20000:])
+    assert index.info()["n_partitioned"] == 20000
+    gone = rng.choice(21500, 1500, replace=False)
+    index.remove(gone)
+    masked = lab.copy()
+    masked[gone] = -1
+    same(index, x, q, 10, row_labels=masked, query_labels=ql, labels=ql)
+    Dp, Ip, Sp = index.search(q, k=10, labels=ql, return_scores=True)
+    index._test_mode(1)  # the label test over every vector instead of the partition
+    Du, Iu, Su = index.search(q, k=10, labels=ql, return_scores=True)
+    index._test_mode(0)
+    assert np.array_equal(Ip, Iu) and np.array_equal(Sp, Su) and np.array_equal(Dp, Du)
+    assert (Ip[(ql < 0) | (ql >= 32)] == -1).all()
+
+
+def test_label_partition_small_labels_and_large_k():
+    """Labels with fewer than k vectors pad with -1; one query per label; labels that are not consecutive numbers."""
+    x, q = data(6000, 16, 64, "uint8", seed=13)
+    rng = np.random.default_rng(14)
+    lab = (rng.integers(0, 300, 6000) * 1000 + 7).astype(np.int32)  # about 20 vectors per label
+    ql = (np.arange(64) * 1000 + 7).astype(np.int32)
+    index = certex.Index(16)
+    index.add(x, labels=lab)
+    _, I, S = index.search(q, k=50, labels=ql, return_scores=True)
+    ids, scores = oracle.knn(x, q, 50, "l2", row_labels=lab, query_labels=ql)
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    assert (I == -1).any() and (I[:, 0] >= 0).all()
+
+
+def test_label_partition_long_labels():
+    """Two labels of about 300 000 vectors each: score rows long enough to be selected from in chunks."""
+    x, q = data(600000, 8, 24, "uint8", seed=15)
+    rng = np.random.default_rng(16)
+    lab = rng.integers(0, 2, 600000).astype(np.int32)
+    ql = rng.integers(0, 2, 24).astype(np.int32)
+    index = certex.Index(8)
+    index.add(x, labels=lab)
+    same(index, x, q, 100, row_labels=lab, query_labels=ql, labels=ql)
+
+
+def test_relabeling_voids_the_partition():
+    x, q = data(8000, 16, 100, "float32", seed=17)
+    rng = np.random.default_rng(18)
+    lab = rng.integers(0, 8, 8000).astype(np.int32)
+    ql = rng.integers(0, 8, 100).astype(np.int32)
+    index = certex.Index(16)
+    index.add(x, labels=lab)
+    assert index.info()["n_partitioned"] == 8000
+    lab2 = rng.integers(0, 8, 8000).astype(np.int32)
+    index.set_labels(lab2, first=0)
+    assert index.info()["n_partitioned"] == 0
+    same(index, x, q, 10, row_labels=lab2, query_labels=ql, labels=ql)
+    index.partition_by_labels()
+    assert index.info()["n_partitioned"] == 8000
+    same(index, x, q, 10, row_labels=lab2, query_labels=ql, labels=ql)
+
+
+def test_labeled_cosine_with_churn():
+    """The shape of the filtered workload at a small scale: unit vectors of dimension 768, cosine, k = 100, one of 64
+    labels per vector and query, and between query batches 1 % of the vectors removed and as many added."""
+    n, dim, nq, k = 20000, 768, 96, 100
+    x = synthetic.clustered_unit_f32(n + 600, dim, n_clusters=256, seed=19).cpu().numpy()
+    q = synthetic.clustered_unit_f32(nq, dim, n_clusters=256, seed=20).cpu().numpy()
+    rng = np.random.default_rng(21)
+    lab = rng.integers(0, 64, n + 600).astype(np.int32)
+    ql = rng.integers(0, 64, nq).astype(np.int32)
+    index = certex.Index(dim, metric="cosine")
+    index.add(x[:n], labels=lab[:n])
+    live = lab.copy()
+    live[n:] = -1
+    size = n
+    for step in range(3):
+        _, I, S = index.search(q, k=k, labels=ql, return_scores=True)
+        ids, scores = oracle.knn(x[:size], q, k, "cosine", row_labels=live[:size], query_labels=ql)
+        assert np.array_equal(I, ids), f"step {step}: {(I != ids).any(1).sum()} queries differ"
+        assert np.array_equal(S, scores)
+        alive = np.flatnonzero(live[:size] >= 0)
+        gone = rng.choice(alive, 200, replace=False)
+        index.remove(gone)
+        live[gone] = -1
+        index.add(x[size:size + 200], labels=lab[size:size + 200])
+        live[size:size + 200] = lab[size:size + 200]
+        size += 200
+
+
 @pytest.mark.parametrize("dtype", ["uint8", "float16"])
 def test_bitset_and_bitmap(dtype):
     x, q = data(15000, 64, 120, dtype)
