@@ -240,9 +240,10 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsC
  *  (cpp/src/neighbors/certex/detail/kernels.hpp:256-263). out[0..3] = queries, survivors of the screen, exact scores
  *  computed, queries answered by the dense (unscreened) path; out[4] = kernels launched; out[5], out[6] = device
  *  time in microseconds of the screen passes and of the anchor (group-maximum) passes, measured with CUDA events on
- *  the launching stream; out[7] = number of screen passes. */
+ *  the launching stream; out[7] = number of screen passes; out[8] = queries whose candidate list overflowed and that
+ *  were screened a second time with a tighter threshold. */
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsBegin(void);
-CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[8]);
+CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[9]);
 
 /** Test hook: mode 0 automatic, 1 always the dense path, 2 screen with candidate lists of `cap` entries per query
  *  (small values exercise the overflow fallback). */

@@ -447,7 +447,7 @@ cuvsError_t certexB200StatsBegin(void)
   });
 }
 
-cuvsError_t certexB200StatsEnd(uint64_t out[8])
+cuvsError_t certexB200StatsEnd(uint64_t out[9])
 {
   return translate([=] {
     Index::stats_sink = nullptr;
@@ -456,6 +456,7 @@ cuvsError_t certexB200StatsEnd(uint64_t out[8])
     out[5] = static_cast<uint64_t>(g_stats.screen_ms * 1000.0);
     out[6] = static_cast<uint64_t>(g_stats.anchor_ms * 1000.0);
     out[7] = g_stats.screen_passes;
+    out[8] = g_stats.rescreened;
   });
 }
 

@@ -446,51 +446,34 @@ void Index::search_dense(const Resources& res, const void* q, size_t qpitch, con
   }
 }
 
-void Index::search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries,
-                            size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
-                            unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
-                            std::vector<cudaEvent_t>* events) const
+// One pass of the screen over all rows with given thresholds, then the exact scores of the survivors and the k best.
+// qcodes: code rows of the nq queries (zero padded to a multiple of 128 rows); queries: their vectors; lists are
+// written at query numbers q0 .. q0 + nq - 1. With `thr2` the queries that end in ovf_list also get a tighter threshold
+// (see Refine).
+void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32_t* thr, const void* queries,
+                        size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
+                        unsigned int* ovf_count, unsigned long long* stats, int* err, int64_t n, int32_t* thr2,
+                        const float* shift, std::vector<cudaEvent_t>* events) const
 {
-  // qbuf: the code rows of all queries of the call, zero padded to [round_up(total, 128), code_pitch_]; this batch is
-  // rows [q0, q0 + nq). shift (fp16 codes only): the rounding allowance of every query.
   Scratch scratch(res.stream);
   const int grid          = res.sm_count;
   const ScreenShape shape = shape_for(kb_);
   const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
-  // anchors: sorted rows 0, stride, 2 stride, ...; only whole tiles of 256 anchors take part
-  const int nt_anchor     = static_cast<int>(n / (static_cast<int64_t>(anchor_stride) * kTile));
   const int nt_all        = static_cast<int>((n + kTile - 1) / kTile);
-  const int n_groups      = nt_anchor * (kBaseTile / kGroupRows);
-  const int64_t ld_g      = round_up(n_groups, 8);
   const uint32_t cap      = test_mode_ == 2 ? static_cast<uint32_t>(test_cap_) : static_cast<uint32_t>(std::max(2048, 2 * k));
   const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
-
-  int32_t* anchor_init = scratch.get<int32_t>(static_cast<size_t>(nt_anchor) * kTile);
-  int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
-  int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
   uint32_t* cnt        = scratch.get<uint32_t>(static_cast<size_t>(nq));
   int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
   uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
   auto* rec_count      = scratch.get<unsigned long long>(1);
-  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs * 2);
-
-  const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
+  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs);
   const std::vector<ScreenSeg> seg_s = plan_segments(nqt, nt_all, shape.panel_tiles, grid);
-  const size_t seg_bytes             = seg_a.size() * sizeof(ScreenSeg);
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs + seg_a.size(), seg_s.data(), seg_bytes, cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_s.data(), seg_s.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
-  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream);  // e of the anchors
-  CERTEX_CUDA(cudaGetLastError());
-
   const size_t cp        = code_pitch_;
-  const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * cp;
-  const CUtensorMap tm_q = make_code_map(qb, cp, static_cast<uint64_t>(round_up(nq, kQTile)), cp, kQueryTile);
-  const CUtensorMap tm_a = make_tile_map(codes_, cp, static_cast<uint64_t>(nt_anchor) * anchor_stride * cp,
-                                         static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor));
+  const CUtensorMap tm_q = make_code_map(qcodes, cp, static_cast<uint64_t>(round_up(nq, kQTile)), cp, kQueryTile);
   const CUtensorMap tm_x = make_code_map(codes_, cp, static_cast<uint64_t>(n), cp, kBaseTile);
-
   ScreenArgs a{};
   a.nq          = nq;
   a.kb          = kb_;
@@ -501,6 +484,14 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   a.q_signed    = dtype_ == kI8 ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.err         = err;
+  a.mode        = kModeScreen;
+  a.init        = init_;
+  a.cmax        = cmax_;
+  a.thr         = thr;
+  a.rec         = rec;
+  a.rec_count   = rec_count;
+  a.rec_cap     = rec_cap;
+  a.segs        = d_segs;
   auto mark = [&] {
     if (events) {
       cudaEvent_t e;
@@ -509,12 +500,78 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
       events->push_back(e);
     }
   };
+  mark();
+  CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
+  mark();
+  launch_expand_records(rec, rec_count, rec_cap, n, perm_, cnt, cand, cap, res.sm_count, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+  Admit adm{};
+  adm.removed = removed_;
+  Refine rf{};
+  rf.thr2  = thr2;
+  rf.thr   = thr;
+  rf.shift = shift;
+  rf.kind  = screen_kind_;
+  launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes, nq, q0, cand, cnt,
+                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf, res.stream);
+  CERTEX_CUDA(cudaGetLastError());
+}
+
+void Index::search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries,
+                            size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
+                            unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
+                            int32_t* thr2, std::vector<cudaEvent_t>* events) const
+{
+  // qbuf: the code rows of all queries of the call, zero padded to [round_up(total, 128), code_pitch_]; this batch is
+  // rows [q0, q0 + nq). shift (fp16 codes only): the rounding allowance of every query.
+  Scratch scratch(res.stream);
+  const int grid          = res.sm_count;
+  const ScreenShape shape = shape_for(kb_);
+  const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
+  // anchors: sorted rows 0, stride, 2 stride, ...; only whole tiles of 256 anchors take part
+  const int nt_anchor     = static_cast<int>(n / (static_cast<int64_t>(anchor_stride) * kTile));
+  const int n_groups      = nt_anchor * (kBaseTile / kGroupRows);
+  const int64_t ld_g      = round_up(n_groups, 8);
+
+  int32_t* anchor_init = scratch.get<int32_t>(static_cast<size_t>(nt_anchor) * kTile);
+  int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
+  int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
+  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs);
+
+  const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_a.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream);  // e of the anchors
+  CERTEX_CUDA(cudaGetLastError());
+
+  const size_t cp        = code_pitch_;
+  const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * cp;
+  const CUtensorMap tm_q = make_code_map(qb, cp, static_cast<uint64_t>(round_up(nq, kQTile)), cp, kQueryTile);
+  const CUtensorMap tm_a = make_tile_map(codes_, cp, static_cast<uint64_t>(nt_anchor) * anchor_stride * cp,
+                                         static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor));
+  ScreenArgs a{};
+  a.nq          = nq;
+  a.kb          = kb_;
+  a.panel_tiles = shape.panel_tiles;
+  a.n_stages    = shape.n_stages;
+  a.f16         = screen_kind_ == 2 ? 1 : 0;
+  a.wide        = kb_ > 2 ? 1 : 0;
+  a.q_signed    = dtype_ == kI8 ? 1u : 0u;
+  a.x_signed    = a.q_signed;
+  a.err         = err;
   // 1 anchors: maximum of acc over every group of 64 anchors
   a.mode    = kModeGroupMax;
   a.init    = anchor_init;
   a.gmax    = gmax;
   a.ld_gmax = ld_g;
   a.segs    = d_segs;
+  auto mark = [&] {
+    if (events) {
+      cudaEvent_t e;
+      CERTEX_CUDA(cudaEventCreate(&e));
+      CERTEX_CUDA(cudaEventRecord(e, res.stream));
+      events->push_back(e);
+    }
+  };
   mark();
   CERTEX_CUDA(screen_i8_launch(tm_q, tm_a, a, grid, res.stream));
   mark();
@@ -522,26 +579,9 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
   if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, res.stream); }
   CERTEX_CUDA(cudaGetLastError());
-  // 3 screen over all rows: survivor records, then per-query candidate lists
-  a.mode      = kModeScreen;
-  a.init      = init_;
-  a.cmax      = cmax_;
-  a.thr       = thr;
-  a.rec       = rec;
-  a.rec_count = rec_count;
-  a.rec_cap   = rec_cap;
-  a.segs      = d_segs + seg_a.size();
-  mark();
-  CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
-  mark();
-  launch_expand_records(rec, rec_count, rec_cap, n, perm_, cnt, cand, cap, res.sm_count, res.stream);
-  CERTEX_CUDA(cudaGetLastError());
-  // 4 exact scores of the candidates and the k best
-  Admit adm{};
-  adm.removed = removed_;
-  launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes, nq, q0, cand, cnt,
-                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, res.stream);
-  CERTEX_CUDA(cudaGetLastError());
+  // 3 screen over all rows, 4 exact scores of the candidates and the k best
+  screen_pass(res, qb, thr, queries, row_bytes, q0, nq, k, best_s, best_row, ovf_list, ovf_count, stats, err, n, thr2, shift,
+              events);
 }
 
 unsigned long long Index::search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k,
@@ -670,7 +710,10 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
 
   // anchors: every stride-th row in whole tiles of 256, and at least 2k groups of 64 anchors, or the threshold would be
   // useless
-  const int stride    = static_cast<int>(std::min<int64_t>(params_.anchor_stride, n / (kTile * ((2 * k + 3) / 4))));
+  // The k-th largest group maximum is roughly the (stride * k)-th best row: for larger k the anchors are taken denser,
+  // so that the candidate lists stay a small multiple of k (the anchor pass costs 1 / stride of a screen pass).
+  const int64_t by_k  = std::max<int64_t>(1, static_cast<int64_t>(params_.anchor_stride) * 32 / k);
+  const int stride    = static_cast<int>(std::min<int64_t>({params_.anchor_stride, by_k, n / (kTile * ((2 * k + 3) / 4))}));
   const bool screened = screen_kind_ != 0 && !code_overflow_ && !filtered && stride >= 1 && test_mode_ != 1;
 
   SearchStats local{};
@@ -697,7 +740,8 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
       CERTEX_CUDA(cudaMemcpy2DAsync(qbuf, code_pitch_, queries, row_bytes, row_bytes, static_cast<size_t>(nq), cudaMemcpyDeviceToDevice, res.stream));
     }
     int32_t* ovf_list      = scratch.get<int32_t>(static_cast<size_t>(nq));
-    unsigned int* d_count  = scratch.get<unsigned int>(4);  // [0] overflowed queries, [1] error code of the passes
+    int32_t* thr2          = scratch.get<int32_t>(static_cast<size_t>(nq));  // tighter thresholds of the queries in ovf_list
+    unsigned int* d_count  = scratch.get<unsigned int>(4);  // [0] overflowed queries, [1] error code, [2] after the 2nd pass
     auto* d_stats          = scratch.get<unsigned long long>(2);
     CERTEX_CUDA(cudaMemsetAsync(d_count, 0, 4 * sizeof(unsigned int), res.stream));
     CERTEX_CUDA(cudaMemsetAsync(d_stats, 0, 2 * sizeof(unsigned long long), res.stream));
@@ -706,7 +750,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     for (int64_t q0 = 0; q0 < nq; q0 += batch) {
       const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
       search_screened(res, qbuf, shift, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
-                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, stats_sink ? &events : nullptr);
+                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, thr2, stats_sink ? &events : nullptr);
       local.launches += screen_kind_ == 2 ? 7 : 6;  // gather_init, GROUPMAX, kth_largest (+ thresholds), SCREEN, expand, verify
     }
     unsigned int h_count[4]       = {0, 0, 0, 0};
@@ -725,6 +769,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
       ++local.screen_passes;
     }
     for (cudaEvent_t e : events) { cudaEventDestroy(e); }
+    events.clear();
     CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
     local.survivors = h_stats[0];
     local.verified  = h_stats[1];
@@ -732,11 +777,54 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
       search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
       local.dense_queries = static_cast<unsigned long long>(nq);
       local.launches += 2;
-    } else if (h_count[0] > 0) {  // candidate lists that overflowed: those queries are searched without the screen
-      search_dense(res, queries, row_bytes, ovf_list, 0, static_cast<int>(h_count[0]), k, adm, best_s, best_row, n);
-      local.dense_queries = h_count[0];
-      local.launches += 2;
-      local.verified += static_cast<unsigned long long>(h_count[0]) * static_cast<unsigned long long>(n);
+    } else if (h_count[0] > 0) {
+      // Candidate lists that overflowed. Each of those queries got a tighter threshold from the candidates it did list;
+      // they are screened once more with it, as a batch of their own. What overflows again is searched without the screen.
+      const int n_ovf        = static_cast<int>(h_count[0]);
+      const int64_t pad      = round_up(n_ovf, kQTile);
+      uint8_t* qcodes2       = scratch.get<uint8_t>(static_cast<size_t>(pad) * code_pitch_);
+      uint8_t* queries2      = scratch.get<uint8_t>(static_cast<size_t>(n_ovf) * row_bytes);
+      float* shift2          = scratch.get<float>(static_cast<size_t>(n_ovf));
+      double* best2_s        = scratch.get<double>(static_cast<size_t>(n_ovf) * k);
+      int32_t* best2_row     = scratch.get<int32_t>(static_cast<size_t>(n_ovf) * k);
+      int32_t* ovf2          = scratch.get<int32_t>(static_cast<size_t>(n_ovf));
+      launch_gather_rows(qbuf, code_pitch_, ovf_list, n_ovf, pad, qcodes2, code_pitch_, code_pitch_, res.stream);
+      launch_gather_rows(queries, row_bytes, ovf_list, n_ovf, n_ovf, queries2, row_bytes, row_bytes, res.stream);
+      if (shift) { launch_gather_rows(shift, 4, ovf_list, n_ovf, n_ovf, shift2, 4, 4, res.stream); }
+      CERTEX_CUDA(cudaGetLastError());
+      events.clear();
+      for (int b0 = 0; b0 < n_ovf; b0 += static_cast<int>(batch)) {
+        const int nb = std::min<int>(static_cast<int>(batch), n_ovf - b0);
+        screen_pass(res, qcodes2 + static_cast<size_t>(b0) * code_pitch_, thr2 + b0, queries2, row_bytes, b0, nb, k, best2_s,
+                    best2_row, ovf2, d_count + 2, d_stats, reinterpret_cast<int*>(d_count + 1), n, nullptr,
+                    shift ? shift2 : nullptr, stats_sink ? &events : nullptr);
+        local.launches += 3;
+      }
+      launch_scatter_best(best2_s, best2_row, ovf_list, n_ovf, k, best_s, best_row, res.stream);
+      launch_compose(ovf2, d_count + 2, n_ovf, ovf_list, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+      local.launches += 5;
+      CERTEX_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+      for (size_t e = 0; e + 1 < events.size(); e += 2) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, events[e], events[e + 1]);
+        local.screen_ms += ms;
+        ++local.screen_passes;
+      }
+      for (cudaEvent_t e : events) { cudaEventDestroy(e); }
+      events.clear();
+      CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
+      local.survivors    = h_stats[0];
+      local.verified     = h_stats[1];
+      local.rescreened   = static_cast<unsigned long long>(n_ovf);
+      if (h_count[2] > 0) {
+        search_dense(res, queries, row_bytes, ovf2, 0, static_cast<int>(h_count[2]), k, adm, best_s, best_row, n);
+        local.dense_queries = h_count[2];
+        local.launches += 2;
+        local.verified += static_cast<unsigned long long>(h_count[2]) * static_cast<unsigned long long>(n);
+      }
     }
   } else {
     search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
@@ -758,6 +846,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     stats_sink->survivors += local.survivors;
     stats_sink->verified += local.verified;
     stats_sink->dense_queries += local.dense_queries;
+    stats_sink->rescreened += local.rescreened;
   }
 }
 

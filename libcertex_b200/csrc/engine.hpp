@@ -75,6 +75,7 @@ struct SearchStats {
   unsigned long long launches = 0;     // kernels of this library launched by the searches
   double screen_ms = 0, anchor_ms = 0; // device time of the SCREEN and GROUPMAX tensor-core passes (CUDA events)
   unsigned long long screen_passes = 0;
+  unsigned long long rescreened = 0;   // queries screened a second time with a tighter threshold
 };
 
 struct Filter {
@@ -133,7 +134,11 @@ class Index {
   void search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries, size_t row_bytes,
                        int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
                        unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
-                       std::vector<cudaEvent_t>* events) const;
+                       int32_t* thr2, std::vector<cudaEvent_t>* events) const;
+  void screen_pass(const Resources& res, const uint8_t* qcodes, const int32_t* thr, const void* queries, size_t row_bytes,
+                   int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
+                   unsigned long long* stats, int* err, int64_t n, int32_t* thr2, const float* shift,
+                   std::vector<cudaEvent_t>* events) const;
   void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
                     const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
   /// Search by label over the label partition; returns the (query, row) pairs scored and counts its launches.

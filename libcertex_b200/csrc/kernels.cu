@@ -565,17 +565,21 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
                                      Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
                                      unsigned int* ovf_count, unsigned long long* stats,
-                                     const unsigned long long* rec_count, unsigned long long rec_cap)
+                                     const unsigned long long* rec_count, unsigned long long rec_cap, Refine rf)
 {
   extern __shared__ double sh[];
   __shared__ double s_qq;
   const int q       = q0 + blockIdx.x;  // number of the query in the call; cand / cnt are those of its batch
-  const uint32_t c  = cnt[blockIdx.x];
-  // a candidate list that overflowed, or a survivor record buffer that did (then no list of the batch is complete)
-  if (c > cap || (rec_count && *rec_count > rec_cap)) {
+  const uint32_t c0 = cnt[blockIdx.x];
+  // a candidate list that overflowed, or a survivor record buffer that did (then no list of the batch is complete):
+  // the query is reported in ovf_list. What its list holds are still rows at or above its threshold, and the k-th best
+  // exact score among them bounds the k-th neighbour: a tighter threshold for a second pass (rf).
+  const bool over   = c0 > cap || (rec_count && *rec_count > rec_cap);
+  if (over && rf.thr2 == nullptr) {
     if (threadIdx.x == 0) { ovf_list[atomicAdd(ovf_count, 1u)] = q; }
     return;
   }
+  const uint32_t c = min(c0, cap);
   double* qd   = sh;
   double* sc   = sh + d;
   int32_t* ids = reinterpret_cast<int32_t*>(sc + n2max);
@@ -599,6 +603,32 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
     ids[i] = row;
   }
   bitonic_sort(sc, ids, n2);
+  if (over) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int pos = atomicAdd(ovf_count, 1u);
+      ovf_list[pos]          = q;
+      int32_t t              = rf.thr[blockIdx.x];
+      const double kth       = k <= n2 ? sc[k - 1] : CUDART_INF;
+      if (kth < CUDART_INF) {
+        // the screen's value of a row as good as the k-th: <q, x> - |x|^2 / 2 (L2), <q, x> (inner product),
+        // <q, x / |x|> (cosine)
+        const double value = METRIC == kCos ? sqrt(s_qq) * (1.0 - 0.5 * kth) : 0.5 * (s_qq - kth);
+        if (rf.kind == 1) {  // integer values: e = -floor(|x|^2 / 2) only raises a row's value
+          const double cv  = ceil(value);
+          const int32_t tv = cv >= 2147483647.0 ? 0x7fffffff : cv <= -2147483648.0 ? static_cast<int32_t>(0x80000000u)
+                                                                                      : static_cast<int32_t>(cv);
+          t = max(t, tv);
+        } else {             // fp16 codes: the value the pass computes may be lower by half the query's allowance
+          float f = __double2float_rd(value - 0.5 * static_cast<double>(rf.shift[q]));
+          f       = nextafterf(f, -CUDART_INF_F);
+          t       = __float_as_int(fmaxf(f, __int_as_float(t)));
+        }
+      }
+      rf.thr2[pos] = t;
+    }
+    return;
+  }
   for (int t = threadIdx.x; t < k; t += blockDim.x) {
     const bool have                         = t < n2 && sc[t] < CUDART_INF;
     best_s[static_cast<size_t>(q) * k + t]   = have ? sc[t] : CUDART_INF;
@@ -608,6 +638,35 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
     atomicAdd(stats + 0, static_cast<unsigned long long>(c));  // survivors of the screen
     atomicAdd(stats + 1, static_cast<unsigned long long>(c));  // exact scores computed
   }
+}
+
+// out row i = in row sel[i] (rows of row_bytes bytes, 16-byte units when aligned); rows [n, n_pad) are zeroed.
+__global__ void gather_rows_kernel(const uint8_t* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad,
+                                   uint8_t* out, size_t out_pitch, size_t row_bytes)
+{
+  const int64_t row = blockIdx.x;
+  const uint8_t* src = row < n ? in + static_cast<size_t>(sel[row]) * in_pitch : nullptr;
+  uint8_t* dst       = out + static_cast<size_t>(row) * out_pitch;
+  for (size_t b = threadIdx.x; b < out_pitch; b += blockDim.x) { dst[b] = (src && b < row_bytes) ? src[b] : 0; }
+  (void)n_pad;
+}
+
+// best lists of the compact queries 0 .. n - 1 -> rows sel[i] of the call's lists
+__global__ void scatter_best_kernel(const double* s2, const int32_t* row2, const int32_t* sel, int k, double* best_s,
+                                    int32_t* best_row)
+{
+  const size_t src = static_cast<size_t>(blockIdx.x) * k, dst = static_cast<size_t>(sel[blockIdx.x]) * k;
+  for (int t = threadIdx.x; t < k; t += blockDim.x) {
+    best_s[dst + t]   = s2[src + t];
+    best_row[dst + t] = row2[src + t];
+  }
+}
+
+// list[i] = sel[list[i]]: compact query numbers back to the numbers of the call
+__global__ void compose_kernel(int32_t* list, const unsigned int* n, const int32_t* sel)
+{
+  const unsigned int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < *n) { list[i] = sel[list[i]]; }
 }
 
 // ------------------------------------------------------------------------------------------- dense path
@@ -1058,7 +1117,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          cudaStream_t s)
+                          Refine rf, cudaStream_t s)
 {
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
@@ -1068,7 +1127,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
     auto go   = [&](auto kernel) {
       allow_smem(kernel, smem);
       kernel<<<nq, 128, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
-                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap);
+                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf);
     };
     if (metric == kL2) {
       go(verify_select_kernel<T, kL2>);
@@ -1078,6 +1137,27 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
       go(verify_select_kernel<T, kCos>);
     }
   });
+}
+
+void launch_gather_rows(const void* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad, void* out,
+                        size_t out_pitch, size_t row_bytes, cudaStream_t s)
+{
+  if (n_pad <= 0) { return; }
+  gather_rows_kernel<<<static_cast<unsigned>(n_pad), 128, 0, s>>>(static_cast<const uint8_t*>(in), in_pitch, sel, n, n_pad,
+                                                                   static_cast<uint8_t*>(out), out_pitch, row_bytes);
+}
+
+void launch_scatter_best(const double* s2, const int32_t* row2, const int32_t* sel, int n, int k, double* best_s,
+                         int32_t* best_row, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  scatter_best_kernel<<<n, 128, 0, s>>>(s2, row2, sel, k, best_s, best_row);
+}
+
+void launch_compose(int32_t* list, const unsigned int* n, int n_max, const int32_t* sel, cudaStream_t s)
+{
+  if (n_max <= 0) { return; }
+  compose_kernel<<<(n_max + 255) / 256, 256, 0, s>>>(list, n, sel);
 }
 
 void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, const void* queries,

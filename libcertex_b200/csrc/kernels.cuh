@@ -71,6 +71,26 @@ void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
                    int32_t* cmax, bool is_float, unsigned long long* n_new, cudaStream_t s);
 
+/// Optional second output of launch_verify_select for queries whose candidate list is incomplete: a tighter threshold
+/// from the k-th best exact score among the candidates that were listed. thr2 is written at the query's position in
+/// ovf_list; thr [nq] are the thresholds of the pass that produced the candidates; kind 1: integer values, 2: fp16
+/// codes (shift [queries of the call] = the rounding allowance, see launch_encode_f16_queries). thr2 == null: off.
+struct Refine {
+  int32_t* thr2;
+  const int32_t* thr;
+  const float* shift;
+  int kind;
+};
+
+/// out [n_pad, out_pitch] = rows sel[0 .. n) of `in` (row_bytes each, zero padded); rows n .. n_pad - 1 are zeros.
+void launch_gather_rows(const void* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad, void* out,
+                        size_t out_pitch, size_t row_bytes, cudaStream_t s);
+/// best_s / best_row rows sel[i] = rows i of s2 / row2, i < n.
+void launch_scatter_best(const double* s2, const int32_t* row2, const int32_t* sel, int n, int k, double* best_s,
+                         int32_t* best_row, cudaStream_t s);
+/// list[i] = sel[list[i]] for i < *n (at most n_max).
+void launch_compose(int32_t* list, const unsigned int* n, int n_max, const int32_t* sel, cudaStream_t s);
+
 /**
  * Exact fp64 scores of every query's candidate rows, then its k best by (score, row). One block per query.
  * cand [nq, cap] rows, cnt [nq] how many (a query with cnt > cap is skipped and its index appended to ovf_list;
@@ -81,7 +101,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          cudaStream_t s);
+                          Refine rf, cudaStream_t s);
 
 /// All-pairs exact fp64 scores of queries qsel[0:nqb] (or q0.. when qsel is null) against rows [0, n): out [nqb, ld].
 /// Rows that `adm` rejects score +inf.

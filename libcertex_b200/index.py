@@ -74,22 +74,24 @@ def pack_mask(mask):
 
 class search_stats:
     """Counters of the calling thread's searches inside the block: queries, survivors (pairs the screen kept),
-    verified (exact scores computed), dense_queries (queries answered without the screen), launches (kernels of the
-    library), and the device time of the tensor-core passes: screen_ms, anchor_ms over screen_passes passes."""
+    verified (exact scores computed), dense_queries (queries answered without the screen), rescreened (queries screened
+    a second time with a tighter threshold), launches (kernels of the library), and the device time of the tensor-core
+    passes: screen_ms, anchor_ms over screen_passes passes."""
 
     def __enter__(self):
         L.check(L.lib().certexB200StatsBegin())
         self.queries = self.survivors = self.verified = self.dense_queries = 0
-        self.launches = self.screen_passes = 0
+        self.launches = self.screen_passes = self.rescreened = 0
         self.screen_ms = self.anchor_ms = 0.0
         return self
 
     def __exit__(self, *exc):
         torch.cuda.current_stream().synchronize()
-        out = (ctypes.c_uint64 * 8)()
+        out = (ctypes.c_uint64 * 9)()
         L.check(L.lib().certexB200StatsEnd(out))
         self.queries, self.survivors, self.verified, self.dense_queries, self.launches = (int(v) for v in out[:5])
         self.screen_ms, self.anchor_ms, self.screen_passes = out[5] / 1000.0, out[6] / 1000.0, int(out[7])
+        self.rescreened = int(out[8])
         return False
 
 

@@ -153,16 +153,24 @@ def test_batch_sizes(batch):
     check(index, x, q, 10, "l2", batch=batch)
 
 
-def test_overflowing_candidate_lists_fall_back_to_the_dense_path():
-    x, q = make(40000, 64, 300, "uint8", False, 0)
-    index = certex.Index(64)
+@pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("int8", "ip"), ("float32", "l2"), ("float32", "cosine"),
+                                          ("float16", "ip")])
+def test_overflowing_candidate_lists_are_screened_again_then_searched_densely(dtype, metric):
+    """A query whose candidate list overflows takes a tighter threshold from the candidates it did list and is screened
+    once more; what overflows again is searched without the screen."""
+    x, q = make(40000, 64, 300, dtype, metric != "l2", 0)
+    index = certex.Index(64, metric=metric)
     index.add(x)
-    index._test_mode(2, cap=16)  # candidate lists of 16 entries: most queries overflow
+    index._test_mode(2, cap=64)  # candidate lists of 64 entries: most queries overflow, the second pass fits
     with certex.search_stats() as st:
-        check(index, x, q, 10, "l2")
-    assert 0 < st.dense_queries <= 300
+        check(index, x, q, 10, metric)
+    assert 0 < st.rescreened <= 300 and st.dense_queries < st.rescreened
+    index._test_mode(2, cap=12)  # hardly more than k entries: the second pass overflows too
+    with certex.search_stats() as st:
+        check(index, x, q, 10, metric)
+    assert 0 < st.dense_queries <= st.rescreened <= 300
     index._test_mode(1)  # dense path only
-    check(index, x, q, 10, "l2")
+    check(index, x, q, 10, metric)
 
 
 def test_dense_path_on_long_rows():
