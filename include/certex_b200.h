@@ -241,12 +241,14 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsC
  *  computed, queries answered by the dense (unscreened) path; out[4] = kernels launched; out[5], out[6] = device
  *  time in microseconds of the screen passes and of the anchor (group-maximum) passes, measured with CUDA events on
  *  the launching stream; out[7] = number of screen passes; out[8] = queries whose candidate list overflowed and that
- *  were screened a second time with a tighter threshold. */
+ *  were screened a second time with a tighter threshold; out[9] = query slots of searches by label that went through
+ *  the routed screen (a label's queries fill whole tiles of 128 slots); out[10..15] = 0, reserved. */
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsBegin(void);
-CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[9]);
+CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[16]);
 
 /** Test hook: mode 0 automatic, 1 always the dense path, 2 screen with candidate lists of `cap` entries per query
- *  (small values exercise the overflow fallback). */
+ *  (small values exercise the overflow fallback), 3 searches by label score their label's rows densely instead of
+ *  screening them. */
 CERTEX_B200_EXPORT cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap);
 
 /**

@@ -447,7 +447,7 @@ cuvsError_t certexB200StatsBegin(void)
   });
 }
 
-cuvsError_t certexB200StatsEnd(uint64_t out[9])
+cuvsError_t certexB200StatsEnd(uint64_t out[16])
 {
   return translate([=] {
     Index::stats_sink = nullptr;
@@ -457,13 +457,15 @@ cuvsError_t certexB200StatsEnd(uint64_t out[9])
     out[6] = static_cast<uint64_t>(g_stats.anchor_ms * 1000.0);
     out[7] = g_stats.screen_passes;
     out[8] = g_stats.rescreened;
+    out[9] = g_stats.routed_queries;
+    for (int i = 10; i < 16; ++i) { out[i] = 0; }
   });
 }
 
 cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap)
 {
   return translate([=] {
-    CERTEX_EXPECTS(mode >= 0 && mode <= 2 && (mode != 2 || cap >= 1), "certex: unknown test mode");
+    CERTEX_EXPECTS(mode >= 0 && mode <= 3 && (mode != 2 || cap >= 1), "certex: unknown test mode");
     as_holder(index).index->set_test_mode(mode, cap);
   });
 }

@@ -215,6 +215,7 @@ Index::~Index()
   cudaFree(removed_);
   cudaFree(labels_);
   cudaFree(part_ids_);
+  cudaFree(lcodes_), cudaFree(linit_), cudaFree(lcmax_), cudaFree(lperm_), cudaFree(linv_);
   cudaFree(codes_);
   cudaFree(perm_);
   cudaFree(inv_);
@@ -348,6 +349,9 @@ void Index::remove(const Resources& res, const int64_t* ids_device, int64_t n_id
   auto* counter = scratch.get<unsigned long long>(1);
   CERTEX_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned long long), res.stream));
   launch_remove(ids_device, n_ids, size_, removed_, init_, inv_, cmax_, screen_kind_ == 2, counter, res.stream);
+  if (linv_ && n_part_ > 0) {  // the same rows in the label-ordered copy (the flags are set: nothing is counted twice)
+    launch_remove(ids_device, n_ids, n_part_, removed_, linit_, linv_, lcmax_, screen_kind_ == 2, counter, res.stream);
+  }
   CERTEX_CUDA(cudaGetLastError());
   unsigned long long n_new = 0;
   CERTEX_CUDA(cudaMemcpyAsync(&n_new, counter, sizeof(n_new), cudaMemcpyDeviceToHost, res.stream));
@@ -411,16 +415,62 @@ void Index::partition_by_labels(const Resources& res)
   }
   std::vector<int64_t> offsets(distinct.size() + 1, 0);
   for (size_t i = 0; i < distinct.size(); ++i) { offsets[i + 1] = offsets[i] + counts[i]; }
-  int32_t* old = nullptr;
+
+  // With a tensor-core screen: a copy of the code rows in label order, every label's block padded to whole tiles of
+  // 256 rows, with its own e, chain maxima and row <-> id maps, so that a label's queries are screened against the
+  // label's rows only (the reference's partition rows, cpp/src/neighbors/certex/certex.cu:1590-1604).
+  void* lcodes = nullptr;
+  int32_t *linit = nullptr, *lcmax = nullptr, *lperm = nullptr, *linv = nullptr;
+  int64_t n_lrows = 0;
+  std::vector<int64_t> tile0(distinct.size(), 0);
+  if (screen_kind_ != 0 && !code_overflow_) {
+    std::vector<int64_t> lrow0(distinct.size(), 0);
+    for (size_t i = 0; i < distinct.size(); ++i) {
+      lrow0[i] = n_lrows;
+      tile0[i] = n_lrows / kTile;
+      n_lrows += round_up(counts[i], kTile);
+    }
+    try {
+      const bool f16      = screen_kind_ == 2;
+      const int32_t never = f16 ? static_cast<int32_t>(0xff800000u) : kNeverInit;
+      CERTEX_CUDA(cudaMalloc(&lcodes, static_cast<size_t>(n_lrows) * code_pitch_));
+      CERTEX_CUDA(cudaMalloc(&linit, static_cast<size_t>(n_lrows) * 4));
+      CERTEX_CUDA(cudaMalloc(&lcmax, static_cast<size_t>(n_lrows / kChainRows) * 4));
+      CERTEX_CUDA(cudaMalloc(&lperm, static_cast<size_t>(n_lrows) * 4));
+      CERTEX_CUDA(cudaMalloc(&linv, static_cast<size_t>(n) * 4));
+      Scratch scratch(res.stream);
+      int32_t* lsrc   = scratch.get<int32_t>(static_cast<size_t>(n_lrows));
+      int64_t* d_off  = scratch.get<int64_t>(offsets.size());
+      int64_t* d_row0 = scratch.get<int64_t>(lrow0.size());
+      CERTEX_CUDA(cudaMemcpyAsync(d_off, offsets.data(), offsets.size() * 8, cudaMemcpyHostToDevice, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(d_row0, lrow0.data(), lrow0.size() * 8, cudaMemcpyHostToDevice, res.stream));
+      launch_fill_i32(linit, n_lrows, never, res.stream);
+      launch_fill_i32(lperm, n_lrows, -1, res.stream);
+      launch_fill_i32(lsrc, n_lrows, -1, res.stream);
+      launch_label_rows(ids, n, d_off, d_row0, static_cast<int>(distinct.size()), inv_, init_, lperm, linv, lsrc, linit,
+                        res.stream);
+      launch_gather_rows(codes_, code_pitch_, lsrc, n_lrows, n_lrows, lcodes, code_pitch_, code_pitch_, res.stream);
+      launch_chain_max(linit, 0, n_lrows / kChainRows, lcmax, f16, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+      res.sync();
+    } catch (...) {
+      cudaFree(ids), cudaFree(lcodes), cudaFree(linit), cudaFree(lcmax), cudaFree(lperm), cudaFree(linv);
+      throw;
+    }
+  }
+  void* old[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   {
     std::unique_lock<std::shared_mutex> lock(rw_);
-    old           = part_ids_;
+    old[0] = part_ids_, old[1] = lcodes_, old[2] = linit_, old[3] = lcmax_, old[4] = lperm_, old[5] = linv_;
     part_ids_     = ids;
     n_part_       = n;
     part_labels_  = std::move(distinct);
     part_offsets_ = std::move(offsets);
+    part_tile0_   = std::move(tile0);
+    lcodes_ = lcodes, linit_ = linit, lcmax_ = lcmax, lperm_ = lperm, linv_ = linv;
+    n_lrows_ = n_lrows;
   }
-  cudaFree(old);
+  for (void* p : old) { cudaFree(p); }
 }
 
 // -------------------------------------------------------------------------------------------- search
@@ -584,14 +634,81 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
               events);
 }
 
+namespace {
+
+/// The queries of one label in a search by labels.
+struct LabelRun {
+  int64_t part_off  = 0;  // the label's entries in the partition
+  int64_t n_in_part = 0;
+  int64_t tile0     = 0;  // its first tile in the label-ordered copy of the screen's rows
+  std::vector<int32_t> queries;
+};
+
+/// Work split of a routed pass: run r pairs the query tiles [q_tile0[r], + nqt[r]) with its label's tiles. Segments of
+/// at most `panel` query tiles are dealt to the CTAs in order, about the same number of units each, at most
+/// `max_segs` per CTA. Returns how many runs fit (all, unless the segment slots ran out).
+size_t plan_routed(const std::vector<LabelRun>& runs, size_t r0, size_t r1, const std::vector<int>& q_tile0, int panel,
+                   int grid, int max_segs, std::vector<ScreenSeg>& segs, std::vector<int>& col0, std::vector<int>& seg_begin)
+{
+  int64_t units = 0;
+  for (size_t r = r0; r < r1; ++r) {
+    const int64_t nqt = (static_cast<int64_t>(runs[r].queries.size()) + kQTile - 1) / kQTile;
+    units += nqt * ((runs[r].n_in_part + kTile - 1) / kTile);
+  }
+  const int64_t target = std::max<int64_t>(1, (units + grid - 1) / grid);
+  segs.clear(), col0.clear(), seg_begin.assign(1, 0);
+  int64_t filled = 0;
+  size_t done    = r1;
+  for (size_t r = r0; r < r1 && done == r1; ++r) {
+    const size_t mark = segs.size();
+    const size_t ctas = seg_begin.size();
+    const int64_t keep = filled;
+    const int nqt = static_cast<int>((runs[r].queries.size() + kQTile - 1) / kQTile);
+    const int nt  = static_cast<int>((runs[r].n_in_part + kTile - 1) / kTile);
+    const int t0  = static_cast<int>(runs[r].tile0);
+    for (int qp = 0; qp < nqt && done == r1; qp += panel) {
+      const int pq = std::min(panel, nqt - qp);
+      for (int t = 0; t < nt;) {
+        const bool last_cta = static_cast<int>(seg_begin.size()) == grid;
+        const int in_cta    = static_cast<int>(segs.size()) - seg_begin.back();
+        if (!last_cta && (filled >= target || in_cta == max_segs)) {
+          seg_begin.push_back(static_cast<int>(segs.size()));
+          filled = 0;
+          continue;
+        }
+        if (last_cta && in_cta == max_segs) {  // no slot left: this run and the later ones wait for another pass
+          done = r;
+          break;
+        }
+        const int64_t room = last_cta ? int64_t(1) << 40 : target - filled;
+        const int tiles    = static_cast<int>(std::min<int64_t>(nt - t, std::max<int64_t>(1, room / pq)));
+        segs.push_back(ScreenSeg{q_tile0[r - r0] + qp, pq, t0 + t, t0 + t + tiles});
+        col0.push_back(t0);
+        filled += static_cast<int64_t>(tiles) * pq;
+        t += tiles;
+      }
+    }
+    if (done != r1) {  // undo the partial run
+      segs.resize(mark), col0.resize(mark), seg_begin.resize(ctas);
+      filled = keep;
+    }
+  }
+  while (static_cast<int>(seg_begin.size()) < grid + 1) { seg_begin.push_back(static_cast<int>(segs.size())); }
+  return done - r0;
+}
+
+}  // namespace
+
 unsigned long long Index::search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k,
                                            const Admit& adm, double* best_s, int32_t* best_row, int64_t n,
-                                           unsigned long long* launches) const
+                                           SearchStats* st) const
 {
-  // The one host decision of the path: which queries share a label. Their labels come to the host, the queries are
-  // ordered by label, and every label becomes a group (queries x that label's partition entries + the rows added
-  // since). Groups are scored, selected from and translated to ids in waves of bounded score memory, three launches
-  // per wave whatever the number of labels.
+  // The one host decision of the path: which queries share a label. Their labels come to the host and the queries are
+  // ordered by label. A label with enough rows for a threshold (k groups of 64) is screened on the tensor cores
+  // against its block of the label-ordered copy of the code rows (routed pass); the other labels, the queries whose
+  // candidate list overflowed, and every label when rows were added after the partition, are scored densely: every
+  // label becomes a group (queries x that label's partition entries + the rows added since), and the groups are
+  // scored, selected from and translated to ids in waves of bounded score memory, three launches per wave.
   std::vector<int32_t> lab(static_cast<size_t>(nq));
   CERTEX_CUDA(cudaMemcpyAsync(lab.data(), adm.query_labels, lab.size() * 4, cudaMemcpyDeviceToHost, res.stream));
   res.sync();
@@ -599,15 +716,220 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
   for (int i = 0; i < nq; ++i) { order[static_cast<size_t>(i)] = i; }
   std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return lab[a] < lab[b]; });
 
-  const int64_t n_tail  = n - n_part_;
+  const int64_t n_tail = n - n_part_;
+  const bool can_route = lcodes_ != nullptr && screen_kind_ != 0 && !code_overflow_ && n_tail == 0 && test_mode_ != 3;
+  std::vector<LabelRun> routed, dense;
+  for (int i = 0; i < nq;) {
+    const int32_t l = lab[order[static_cast<size_t>(i)]];
+    int j           = i;
+    while (j < nq && lab[order[static_cast<size_t>(j)]] == l) { ++j; }
+    LabelRun run;
+    const auto it = std::lower_bound(part_labels_.begin(), part_labels_.end(), l);
+    if (l >= 0 && it != part_labels_.end() && *it == l) {
+      const size_t at = static_cast<size_t>(it - part_labels_.begin());
+      run.part_off    = part_offsets_[at];
+      run.n_in_part   = part_offsets_[at + 1] - part_offsets_[at];
+      run.tile0       = part_tile0_.empty() ? 0 : part_tile0_[at];
+    }
+    run.queries.assign(order.begin() + i, order.begin() + j);
+    const bool route = can_route && run.n_in_part / kGroupRows >= k;
+    (route ? routed : dense).push_back(std::move(run));
+    i = j;
+  }
+  unsigned long long pairs = 0;
+
+  // ------------------------------------------------------------------ routed passes
+  for (size_t r0 = 0; r0 < routed.size();) {
+    // as many runs as fit 32 768 query slots (a label's queries fill whole tiles of 128) and the segment slots
+    size_t r1 = r0;
+    int64_t n_slots = 0;
+    std::vector<int> q_tile0;
+    while (r1 < routed.size()) {
+      const int64_t add = round_up(static_cast<int64_t>(routed[r1].queries.size()), kQTile);
+      if (r1 > r0 && n_slots + add > 32768) { break; }
+      if (add > 32768) {  // more queries of one label than a pass takes: the rest forms another run
+        LabelRun rest = routed[r1];
+        rest.queries.assign(routed[r1].queries.begin() + 32768, routed[r1].queries.end());
+        routed[r1].queries.resize(32768);
+        routed.insert(routed.begin() + static_cast<std::ptrdiff_t>(r1) + 1, std::move(rest));
+        continue;
+      }
+      q_tile0.push_back(static_cast<int>(n_slots / kQTile));
+      n_slots += add;
+      ++r1;
+    }
+    const int grid          = res.sm_count;
+    const ScreenShape shape = shape_for(kb_);
+    std::vector<ScreenSeg> segs;
+    std::vector<int> col0, seg_begin;
+    r1 = r0 + plan_routed(routed, r0, r1, q_tile0, shape.panel_tiles, grid, 64, segs, col0, seg_begin);
+    CERTEX_EXPECTS(r1 > r0, "certex: internal error: a label's queries do not fit one routed pass");
+    n_slots = 0;
+    std::vector<int32_t> slot_query, slot_ng;
+    int64_t max_tiles = 0;
+    for (size_t r = r0; r < r1; ++r) {
+      const LabelRun& run = routed[r];
+      const int64_t nt    = (run.n_in_part + kTile - 1) / kTile;
+      const int64_t add   = round_up(static_cast<int64_t>(run.queries.size()), kQTile);
+      for (int64_t i = 0; i < add; ++i) {
+        const bool real = i < static_cast<int64_t>(run.queries.size());
+        slot_query.push_back(real ? run.queries[static_cast<size_t>(i)] : -1);
+        slot_ng.push_back(real ? static_cast<int32_t>(nt * (kBaseTile / kGroupRows)) : -1);
+      }
+      n_slots += add;
+      max_tiles = std::max(max_tiles, nt);
+      pairs += static_cast<unsigned long long>(run.queries.size()) * static_cast<unsigned long long>(run.n_in_part);
+    }
+    const int ns = static_cast<int>(n_slots);
+
+    Scratch scratch(res.stream);
+    const bool f16       = screen_kind_ == 2;
+    const size_t cp      = code_pitch_;
+    const int n_groups   = static_cast<int>(max_tiles) * (kBaseTile / kGroupRows);
+    const int64_t ld_g   = round_up(n_groups, 8);
+    const uint32_t cap   = static_cast<uint32_t>(std::max(2048, 2 * k));
+    const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(ns) * 1024ull);
+    int32_t* d_slot_q    = scratch.get<int32_t>(static_cast<size_t>(ns));
+    int32_t* d_slot_ng   = scratch.get<int32_t>(static_cast<size_t>(ns));
+    ScreenSeg* d_segs    = scratch.get<ScreenSeg>(segs.size());
+    int* d_col0          = scratch.get<int>(col0.size());
+    int* d_seg_begin     = scratch.get<int>(seg_begin.size());
+    uint8_t* q_rows      = scratch.get<uint8_t>(static_cast<size_t>(ns) * (f16 ? qpitch : cp));  // the queries in slot order
+    uint8_t* q_codes     = f16 ? scratch.get<uint8_t>(static_cast<size_t>(ns) * cp) : q_rows;
+    float* shift         = f16 ? scratch.get<float>(static_cast<size_t>(ns)) : nullptr;
+    int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(ns) * ld_g);
+    int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(ns));
+    uint32_t* cnt        = scratch.get<uint32_t>(static_cast<size_t>(ns));
+    int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(ns) * cap);
+    uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
+    auto* rec_count      = scratch.get<unsigned long long>(1);
+    double* slot_s       = scratch.get<double>(static_cast<size_t>(ns) * k);
+    int32_t* slot_row    = scratch.get<int32_t>(static_cast<size_t>(ns) * k);
+    int32_t* ovf_list    = scratch.get<int32_t>(static_cast<size_t>(ns));
+    unsigned int* d_flag = scratch.get<unsigned int>(4);  // [0] overflowed slots, [1] error code, [2] fp16 overflow
+    auto* d_stats        = scratch.get<unsigned long long>(2);
+    const auto h2d       = cudaMemcpyHostToDevice;
+    CERTEX_CUDA(cudaMemcpyAsync(d_slot_q, slot_query.data(), slot_query.size() * 4, h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_slot_ng, slot_ng.data(), slot_ng.size() * 4, h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_col0, col0.data(), col0.size() * sizeof(int), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, seg_begin.data(), seg_begin.size() * sizeof(int), h2d, res.stream));
+    CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * ns, res.stream));
+    CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
+    CERTEX_CUDA(cudaMemsetAsync(d_flag, 0, 4 * sizeof(unsigned int), res.stream));
+    CERTEX_CUDA(cudaMemsetAsync(d_stats, 0, 2 * sizeof(unsigned long long), res.stream));
+    // queries in slot order (8-bit vectors: zero padded to code rows, which the verification reads as well)
+    const size_t q_rows_pitch = f16 ? qpitch : cp;
+    launch_gather_rows(q, qpitch, d_slot_q, ns, ns, q_rows, q_rows_pitch, qpitch, res.stream);
+    if (f16) {
+      launch_encode_f16_queries(q_rows, qpitch, dtype_, static_cast<int>(dim_), ns, q_codes, cp, n1max_, n2max_, emax_, shift,
+                                d_flag + 2, res.stream);
+    }
+    CERTEX_CUDA(cudaGetLastError());
+    const CUtensorMap tm_q = make_code_map(q_codes, cp, static_cast<uint64_t>(ns), cp, kQueryTile);
+    const CUtensorMap tm_x = make_code_map(lcodes_, cp, static_cast<uint64_t>(n_lrows_), cp, kBaseTile);
+    ScreenArgs a{};
+    a.nq          = ns;
+    a.kb          = kb_;
+    a.panel_tiles = shape.panel_tiles;
+    a.n_stages    = shape.n_stages;
+    a.f16         = f16 ? 1 : 0;
+    a.wide        = kb_ > 2 ? 1 : 0;
+    a.q_signed    = dtype_ == kI8 ? 1u : 0u;
+    a.x_signed    = a.q_signed;
+    a.err         = reinterpret_cast<int*>(d_flag + 1);
+    a.segs        = d_segs;
+    a.seg_begin   = d_seg_begin;
+    a.seg_col0    = d_col0;
+    a.plain_tiles = 1;
+    a.init        = linit_;
+    // 1 group maxima over the label's own rows, 2 the k-th largest of them is the threshold
+    a.mode    = kModeGroupMax;
+    a.gmax    = gmax;
+    a.ld_gmax = ld_g;
+    std::vector<cudaEvent_t> events;
+    auto mark = [&] {
+      if (stats_sink) {
+        cudaEvent_t e;
+        CERTEX_CUDA(cudaEventCreate(&e));
+        CERTEX_CUDA(cudaEventRecord(e, res.stream));
+        events.push_back(e);
+      }
+    };
+    mark();
+    CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
+    mark();
+    launch_kth_largest(gmax, ld_g, n_groups, k, ns, thr, res.stream, d_slot_ng,
+                       f16 ? static_cast<int32_t>(0x7f800000) : static_cast<int32_t>(0x7fffffff));
+    if (f16) { launch_finish_thr_f16(thr, shift, ns, res.stream); }
+    CERTEX_CUDA(cudaGetLastError());
+    // 3 screen, 4 exact scores of the candidates
+    a.mode      = kModeScreen;
+    a.cmax      = lcmax_;
+    a.thr       = thr;
+    a.rec       = rec;
+    a.rec_count = rec_count;
+    a.rec_cap   = rec_cap;
+    mark();
+    CERTEX_CUDA(screen_i8_launch(tm_q, tm_x, a, grid, res.stream));
+    mark();
+    launch_expand_records(rec, rec_count, rec_cap, n_lrows_, lperm_, cnt, cand, cap, res.sm_count, res.stream);
+    Admit plain{};
+    plain.removed = removed_;
+    launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, q_rows, q_rows_pitch, ns, 0, cand,
+                         cnt, cap, k, plain, slot_s, slot_row, ovf_list, d_flag, d_stats, rec_count, rec_cap, Refine{}, res.stream);
+    launch_scatter_best(slot_s, slot_row, d_slot_q, ns, k, best_s, best_row, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    st->launches += f16 ? 10 : 8;
+    unsigned int h_flag[4]        = {0, 0, 0, 0};
+    unsigned long long h_stats[2] = {0, 0};
+    std::vector<int32_t> h_ovf(static_cast<size_t>(ns));
+    CERTEX_CUDA(cudaMemcpyAsync(h_flag, d_flag, sizeof(h_flag), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(h_ovf.data(), ovf_list, h_ovf.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+    for (size_t e = 0; e + 3 < events.size(); e += 4) {
+      float ms = 0;
+      cudaEventElapsedTime(&ms, events[e], events[e + 1]);
+      st->anchor_ms += ms;
+      cudaEventElapsedTime(&ms, events[e + 2], events[e + 3]);
+      st->screen_ms += ms;
+      ++st->screen_passes;
+    }
+    for (cudaEvent_t e : events) { cudaEventDestroy(e); }
+    CERTEX_EXPECTS(h_flag[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_flag[1]) + ")");
+    st->routed_queries += static_cast<unsigned long long>(ns);
+    // slots whose list overflowed (every real slot, when a query coordinate did not fit fp16) go to the dense groups
+    std::vector<char> again(static_cast<size_t>(ns), h_flag[2] != 0 ? 1 : 0);
+    for (unsigned int i = 0; i < h_flag[0] && i < static_cast<unsigned int>(ns); ++i) { again[static_cast<size_t>(h_ovf[i])] = 1; }
+    if (h_flag[0] != 0 || h_flag[2] != 0) {
+      int64_t slot = 0;
+      for (size_t r = r0; r < r1; ++r) {
+        LabelRun redo = routed[r];
+        redo.queries.clear();
+        for (size_t i = 0; i < routed[r].queries.size(); ++i) {
+          if (again[static_cast<size_t>(slot) + i]) { redo.queries.push_back(routed[r].queries[i]); }
+        }
+        slot += round_up(static_cast<int64_t>(routed[r].queries.size()), kQTile);
+        if (!redo.queries.empty()) { dense.push_back(std::move(redo)); }
+      }
+    }
+    r0 = r1;
+  }
+
+  // ------------------------------------------------------------------ dense groups
+  std::vector<int32_t> dorder;
+  for (const LabelRun& run : dense) { dorder.insert(dorder.end(), run.queries.begin(), run.queries.end()); }
+  const int nd = static_cast<int>(dorder.size());
+  if (nd == 0) { return pairs; }
+  st->dense_queries += static_cast<unsigned long long>(nd);
   const int64_t budget  = int64_t(1) << 28;  // doubles of score memory per wave
   std::vector<LabelGroup> groups;
   std::vector<int64_t> row_off;
   std::vector<int32_t> row_n;
-  unsigned long long pairs = 0;
   Scratch keep(res.stream);
-  int32_t* d_order = keep.get<int32_t>(static_cast<size_t>(nq));
-  CERTEX_CUDA(cudaMemcpyAsync(d_order, order.data(), order.size() * 4, cudaMemcpyHostToDevice, res.stream));
+  int32_t* d_order = keep.get<int32_t>(static_cast<size_t>(nd));
+  CERTEX_CUDA(cudaMemcpyAsync(d_order, dorder.data(), dorder.size() * 4, cudaMemcpyHostToDevice, res.stream));
 
   int wave_q0 = 0;           // first query (in label order) of the wave being collected
   int64_t wave_scores = 0, wave_blocks = 0, wave_max_cols = 0;
@@ -633,35 +955,27 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     CERTEX_CUDA(cudaGetLastError());
     launch_group_columns_to_ids(best_row, k, d_order, d_grp, static_cast<int>(groups.size()), part_ids_, n_part_, res.stream);
     CERTEX_CUDA(cudaGetLastError());
-    *launches += 3;
+    st->launches += 3;
     groups.clear();
     row_off.clear();
     row_n.clear();
     wave_q0 = q_end, wave_scores = 0, wave_blocks = 0, wave_max_cols = 0;
   };
 
-  for (int i = 0; i < nq;) {
-    const int32_t l = lab[order[static_cast<size_t>(i)]];
-    int j           = i;
-    while (j < nq && lab[order[static_cast<size_t>(j)]] == l) { ++j; }
-    int64_t part_off = 0, n_in_part = 0;
-    const auto it = std::lower_bound(part_labels_.begin(), part_labels_.end(), l);
-    if (l >= 0 && it != part_labels_.end() && *it == l) {
-      const size_t at = static_cast<size_t>(it - part_labels_.begin());
-      part_off        = part_offsets_[at];
-      n_in_part       = part_offsets_[at + 1] - part_offsets_[at];
-    }
-    const int64_t n_cols = n_in_part + n_tail;
+  int i = 0;
+  for (const LabelRun& run : dense) {
+    const int j          = i + static_cast<int>(run.queries.size());
+    const int64_t n_cols = run.n_in_part + n_tail;
     const int64_t ld     = round_up(n_cols, 4);
-    const int at_most    = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nq, budget / std::max<int64_t>(ld, 1))));
+    const int at_most    = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nd, budget / std::max<int64_t>(ld, 1))));
     for (int a = i; a < j;) {  // the label's queries, in pieces that fit the score memory of a wave
       const int nqg = std::min(j - a, at_most);
       if (wave_scores > 0 && wave_scores + static_cast<int64_t>(nqg) * ld > budget) { flush(a); }
       LabelGroup g{};
       g.q_begin   = a;
       g.nq        = nqg;
-      g.part_off  = part_off;
-      g.n_part    = static_cast<int32_t>(n_in_part);
+      g.part_off  = run.part_off;
+      g.n_part    = static_cast<int32_t>(run.n_in_part);
       g.ld        = static_cast<int32_t>(ld);
       g.score_off = wave_scores;
       g.blk_begin = wave_blocks;
@@ -678,7 +992,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     }
     i = j;
   }
-  flush(nq);
+  flush(nd);
   return pairs;
 }
 
@@ -719,9 +1033,8 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   SearchStats local{};
   local.queries = static_cast<unsigned long long>(nq);
   if (filter.query_labels && !filter.words && n_part_ > 0 && test_mode_ != 1) {
-    local.survivors = search_by_labels(res, queries, row_bytes, static_cast<int>(nq), k, adm, best_s, best_row, n, &local.launches);
-    local.verified      = local.survivors;
-    local.dense_queries = static_cast<unsigned long long>(nq);
+    local.survivors = search_by_labels(res, queries, row_bytes, static_cast<int>(nq), k, adm, best_s, best_row, n, &local);
+    local.verified  = local.survivors;
   } else if (screened) {
     const int64_t nq_pad = round_up(nq, kQTile);
     uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * code_pitch_);
@@ -847,6 +1160,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     stats_sink->verified += local.verified;
     stats_sink->dense_queries += local.dense_queries;
     stats_sink->rescreened += local.rescreened;
+    stats_sink->routed_queries += local.routed_queries;
   }
 }
 
@@ -945,6 +1259,7 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
       int32_t* tmp = scratch.get<int32_t>(static_cast<size_t>(n));
       CERTEX_CUDA(cudaMemcpyAsync(tmp, host.data(), static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, res.stream));
       idx->set_labels(res, tmp, n, 0);
+      idx->partition_by_labels(res);  // not stored: remade from the labels
     }
     res.sync();
   }

@@ -76,6 +76,7 @@ struct SearchStats {
   double screen_ms = 0, anchor_ms = 0; // device time of the SCREEN and GROUPMAX tensor-core passes (CUDA events)
   unsigned long long screen_passes = 0;
   unsigned long long rescreened = 0;   // queries screened a second time with a tighter threshold
+  unsigned long long routed_queries = 0;  // query slots of searches by label that went through the routed screen
 };
 
 struct Filter {
@@ -125,7 +126,8 @@ class Index {
   void save(const Resources& res, std::ostream& os) const;
   static std::unique_ptr<Index> load(const Resources& res, std::istream& is, int dtype);
 
-  /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity.
+  /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity,
+  /// 3 = searches by label score their label's rows densely (no routed screen).
   void set_test_mode(int mode, int cap) { test_mode_ = mode, test_cap_ = cap; }
 
   static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
@@ -143,7 +145,7 @@ class Index {
                     const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
   /// Search by label over the label partition; returns the (query, row) pairs scored and counts its launches.
   unsigned long long search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k, const Admit& adm,
-                                      double* best_s, int32_t* best_row, int64_t n, unsigned long long* launches) const;
+                                      double* best_s, int32_t* best_row, int64_t n, SearchStats* st) const;
 
   IndexParams params_;
   int dtype_;
@@ -169,6 +171,15 @@ class Index {
   int64_t n_part_     = 0;
   std::vector<int32_t> part_labels_;
   std::vector<int64_t> part_offsets_;
+  // label-ordered copy of the screen's rows (made with the partition when the index has a screen): every label's
+  // entries in id order, padded to whole tiles of 256 rows; label i starts at tile part_tile0_[i]
+  void* lcodes_       = nullptr;  // [n_lrows_, code_pitch_]
+  int32_t* linit_     = nullptr;  // [n_lrows_] e (never: padding, removed)
+  int32_t* lcmax_     = nullptr;  // [n_lrows_ / 16]
+  int32_t* lperm_     = nullptr;  // [n_lrows_] row -> id, -1 padding
+  int32_t* linv_      = nullptr;  // [n_part_] id -> row
+  int64_t n_lrows_    = 0;
+  std::vector<int64_t> part_tile0_;
   // screen: the code rows sorted by squared norm (each appended batch on its own), and per sorted row
   void* codes_        = nullptr;  // [capacity, pitch] rows in sorted order
   int32_t* perm_      = nullptr;  // [capacity] sorted row -> id

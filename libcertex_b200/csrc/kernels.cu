@@ -485,9 +485,10 @@ __global__ void expand_records_kernel(const uint64_t* rec, const unsigned long l
     while (mask) {
       const int b = __ffs(mask) - 1;
       mask &= mask - 1;
-      if (row0 + b < n_rows) {
+      const int32_t id = row0 + b < n_rows ? (perm ? perm[row0 + b] : static_cast<int32_t>(row0 + b)) : -1;
+      if (id >= 0) {  // rows beyond the last one and padding rows of a label's block have no id
         const uint32_t pos = atomicAdd(cnt + q, 1u);
-        if (pos < cap) { cand[static_cast<size_t>(q) * cap + pos] = perm ? perm[row0 + b] : static_cast<int32_t>(row0 + b); }
+        if (pos < cap) { cand[static_cast<size_t>(q) * cap + pos] = id; }
       }
     }
   }
@@ -495,12 +496,21 @@ __global__ void expand_records_kernel(const uint64_t* rec, const unsigned long l
 
 // Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk. The row is copied to
 // shared memory first when it fits (vals != global row).
-__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr, int in_smem)
+// With ng_rows the rows have their own lengths; a negative length marks a row without a query: thr = never.
+__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr, int in_smem,
+                                   const int32_t* ng_rows, int32_t never)
 {
   extern __shared__ int32_t row_smem[];
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_remaining;
   const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
+  if (ng_rows) {
+    ng = ng_rows[blockIdx.x];
+    if (ng < 0) {
+      if (threadIdx.x == 0) { thr[blockIdx.x] = never; }
+      return;
+    }
+  }
   if (ng < k) {
     if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(0x80000000u); }
     return;
@@ -640,21 +650,57 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
   }
 }
 
-// out row i = in row sel[i] (rows of row_bytes bytes, 16-byte units when aligned); rows [n, n_pad) are zeroed.
-__global__ void gather_rows_kernel(const uint8_t* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad,
-                                   uint8_t* out, size_t out_pitch, size_t row_bytes)
+// out row i = in row sel[i] (or row i when sel is null), row_bytes of it, the rest of the out_pitch bytes zero; a negative
+// sel[i] and rows [n, n_pad) give zero rows. 16-byte units when everything is 16-byte aligned.
+__global__ void gather_rows_kernel(const uint8_t* in, size_t in_pitch, const int32_t* sel, int64_t n, uint8_t* out,
+                                   size_t out_pitch, size_t row_bytes, int vec16)
 {
   const int64_t row = blockIdx.x;
-  const uint8_t* src = row < n ? in + static_cast<size_t>(sel[row]) * in_pitch : nullptr;
+  int64_t from      = row < n ? (sel ? sel[row] : row) : -1;
+  const uint8_t* src = from >= 0 ? in + static_cast<size_t>(from) * in_pitch : nullptr;
   uint8_t* dst       = out + static_cast<size_t>(row) * out_pitch;
-  for (size_t b = threadIdx.x; b < out_pitch; b += blockDim.x) { dst[b] = (src && b < row_bytes) ? src[b] : 0; }
-  (void)n_pad;
+  if (vec16) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (size_t b = threadIdx.x; b < out_pitch / 16; b += blockDim.x) {
+      reinterpret_cast<uint4*>(dst)[b] = (src && b < row_bytes / 16) ? reinterpret_cast<const uint4*>(src)[b] : zero;
+    }
+  } else {
+    for (size_t b = threadIdx.x; b < out_pitch; b += blockDim.x) { dst[b] = (src && b < row_bytes) ? src[b] : 0; }
+  }
+}
+
+// Label layout of the partition entries: entry p (id part_ids[p], label number i found by its offset) goes to row
+// lrow0[i] + (p - off[i]) of the label-ordered copy. Writes lperm [lrow] = id, linv [id] = lrow, lsrc [lrow] = the
+// sorted row the codes are copied from, linit [lrow] = e of that row.
+__global__ void label_rows_kernel(const int32_t* part_ids, int64_t n, const int64_t* off, const int64_t* lrow0, int n_labels,
+                                  const int32_t* inv, const int32_t* init, int32_t* lperm, int32_t* linv, int32_t* lsrc,
+                                  int32_t* linit)
+{
+  const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (p >= n) { return; }
+  int lo = 0, hi = n_labels - 1;  // last label whose first entry is <= p
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (off[mid] <= p) {
+      lo = mid;
+    } else {
+      hi = mid - 1;
+    }
+  }
+  const int32_t id   = part_ids[p];
+  const int64_t lrow = lrow0[lo] + (p - off[lo]);
+  const int32_t srow = inv[id];
+  lperm[lrow] = id;
+  linv[id]    = static_cast<int32_t>(lrow);
+  lsrc[lrow]  = srow;
+  linit[lrow] = init[srow];
 }
 
 // best lists of the compact queries 0 .. n - 1 -> rows sel[i] of the call's lists
 __global__ void scatter_best_kernel(const double* s2, const int32_t* row2, const int32_t* sel, int k, double* best_s,
                                     int32_t* best_row)
 {
+  if (sel[blockIdx.x] < 0) { return; }
   const size_t src = static_cast<size_t>(blockIdx.x) * k, dst = static_cast<size_t>(sel[blockIdx.x]) * k;
   for (int t = threadIdx.x; t < k; t += blockDim.x) {
     best_s[dst + t]   = s2[src + t];
@@ -1094,13 +1140,14 @@ void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, c
     metric, is_float ? 1 : 0);
 }
 
-void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s)
+void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
+                        const int32_t* ng_rows, int32_t never)
 {
   if (nq <= 0) { return; }
   const size_t bytes = static_cast<size_t>(ng) * 4;
   const int in_smem  = bytes <= 160 * 1024;
   if (in_smem) { allow_smem(kth_largest_kernel, bytes); }
-  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem);
+  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never);
 }
 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
@@ -1143,8 +1190,19 @@ void launch_gather_rows(const void* in, size_t in_pitch, const int32_t* sel, int
                         size_t out_pitch, size_t row_bytes, cudaStream_t s)
 {
   if (n_pad <= 0) { return; }
-  gather_rows_kernel<<<static_cast<unsigned>(n_pad), 128, 0, s>>>(static_cast<const uint8_t*>(in), in_pitch, sel, n, n_pad,
-                                                                   static_cast<uint8_t*>(out), out_pitch, row_bytes);
+  const auto a    = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | in_pitch | out_pitch | row_bytes;
+  gather_rows_kernel<<<static_cast<unsigned>(n_pad), 128, 0, s>>>(static_cast<const uint8_t*>(in), in_pitch, sel, n,
+                                                                   static_cast<uint8_t*>(out), out_pitch, row_bytes,
+                                                                   (a & 15) == 0 ? 1 : 0);
+}
+
+void launch_label_rows(const int32_t* part_ids, int64_t n, const int64_t* off, const int64_t* lrow0, int n_labels,
+                       const int32_t* inv, const int32_t* init, int32_t* lperm, int32_t* linv, int32_t* lsrc, int32_t* linit,
+                       cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  label_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(part_ids, n, off, lrow0, n_labels, inv, init, lperm,
+                                                                            linv, lsrc, linit);
 }
 
 void launch_scatter_best(const double* s2, const int32_t* row2, const int32_t* sel, int n, int k, double* best_s,

@@ -63,8 +63,15 @@ void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_co
                            int64_t n_rows, const int32_t* perm, uint32_t* cnt, int32_t* cand, uint32_t cap, int sm_count,
                            cudaStream_t s);
 
-/// thr[q] = k-th largest of gmax[q, 0:ng]  (INT_MIN when ng < k).
-void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s);
+/// thr[q] = k-th largest of gmax[q, 0:ng]  (INT_MIN when ng < k). With ng_rows [nq] every row has its own length
+/// (at most ng); a negative length gives thr[q] = never.
+void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
+                        const int32_t* ng_rows = nullptr, int32_t never = 0x7fffffff);
+
+/// Label-ordered layout of the partition (see label_rows_kernel in kernels.cu).
+void launch_label_rows(const int32_t* part_ids, int64_t n, const int64_t* off, const int64_t* lrow0, int n_labels,
+                       const int32_t* inv, const int32_t* init, int32_t* lperm, int32_t* linv, int32_t* lsrc, int32_t* linit,
+                       cudaStream_t s);
 
 /// Marks ids as removed: removed[id] = 1, and for the integer screen init[inv[id]] = kNeverInit with the chain maxima
 /// of the touched chains recomputed; *n_new counts first-time removals.
@@ -82,10 +89,11 @@ struct Refine {
   int kind;
 };
 
-/// out [n_pad, out_pitch] = rows sel[0 .. n) of `in` (row_bytes each, zero padded); rows n .. n_pad - 1 are zeros.
+/// out [n_pad, out_pitch] = rows sel[0 .. n) of `in` (row_bytes each, zero padded; sel null: rows 0 .. n - 1; a negative
+/// entry: a zero row); rows n .. n_pad - 1 are zeros.
 void launch_gather_rows(const void* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad, void* out,
                         size_t out_pitch, size_t row_bytes, cudaStream_t s);
-/// best_s / best_row rows sel[i] = rows i of s2 / row2, i < n.
+/// best_s / best_row rows sel[i] = rows i of s2 / row2, i < n (negative sel[i]: skipped).
 void launch_scatter_best(const double* s2, const int32_t* row2, const int32_t* sel, int n, int k, double* best_s,
                          int32_t* best_row, cudaStream_t s);
 /// list[i] = sel[list[i]] for i < *n (at most n_max).

@@ -75,23 +75,24 @@ def pack_mask(mask):
 class search_stats:
     """Counters of the calling thread's searches inside the block: queries, survivors (pairs the screen kept),
     verified (exact scores computed), dense_queries (queries answered without the screen), rescreened (queries screened
-    a second time with a tighter threshold), launches (kernels of the library), and the device time of the tensor-core
+    a second time with a tighter threshold), routed_queries (query slots of searches by label screened against their
+    label's rows), launches (kernels of the library), and the device time of the tensor-core
     passes: screen_ms, anchor_ms over screen_passes passes."""
 
     def __enter__(self):
         L.check(L.lib().certexB200StatsBegin())
         self.queries = self.survivors = self.verified = self.dense_queries = 0
-        self.launches = self.screen_passes = self.rescreened = 0
+        self.launches = self.screen_passes = self.rescreened = self.routed_queries = 0
         self.screen_ms = self.anchor_ms = 0.0
         return self
 
     def __exit__(self, *exc):
         torch.cuda.current_stream().synchronize()
-        out = (ctypes.c_uint64 * 9)()
+        out = (ctypes.c_uint64 * 16)()
         L.check(L.lib().certexB200StatsEnd(out))
         self.queries, self.survivors, self.verified, self.dense_queries, self.launches = (int(v) for v in out[:5])
         self.screen_ms, self.anchor_ms, self.screen_passes = out[5] / 1000.0, out[6] / 1000.0, int(out[7])
-        self.rescreened = int(out[8])
+        self.rescreened, self.routed_queries = int(out[8]), int(out[9])
         return False
 
 
@@ -126,7 +127,8 @@ class Index:
 
     Same constructor as the reference (certex/index.py:220-238). width, n_lists, local_projections and int8_rows
     only tune the reference's speed; they are accepted and have no effect here. partition_labels=True keeps the ids
-    grouped by label, so that a search by labels scores only the vectors of the query's label. storage="host" is
+    grouped by label, so that a search by labels screens and scores only the vectors of the query's label
+    ("lazy": renewed only once an eighth of the vectors is newer than the partition). storage="host" is
     accepted; vectors are kept in GPU memory. The vectors keep the element type of the first addition (float32,
     float16, int8, uint8; other types become float32; cosine needs a float type).
     """
@@ -222,8 +224,13 @@ class Index:
                 L.check(lib.cuvsCertexExtend(res, xt.ref, self.core.handle))
             if lab is not None:
                 L.check(lib.cuvsCertexSetLabels(res, L.Tensor(lab).ref, first, self.core.handle))
-                i = self.core.info()  # the partition is renewed once an eighth of the vectors is newer than it
-                if self.partition_labels and 8 * (int(i.size) - int(i.n_partitioned)) > int(i.size):
+                # The partition (ids grouped by label and a label-ordered copy of the screen's rows) is renewed with
+                # every labeled addition: it costs a sort of the labels and one copy of the code rows.
+                # partition_labels="lazy" keeps the reference's rule instead (certex/index.py:306-311): renew once an
+                # eighth of the vectors is newer than the partition; until then the newer vectors are scored densely.
+                i = self.core.info()
+                lazy = self.partition_labels == "lazy"
+                if self.partition_labels and (not lazy or 8 * (int(i.size) - int(i.n_partitioned)) > int(i.size)):
                     L.check(lib.cuvsCertexPartitionByLabels(res, self.core.handle))
         return _like_input(torch.arange(first, first + X.shape[0]), kind)
 

@@ -89,10 +89,10 @@ def test_label_partition_with_newer_vectors():
     rng = np.random.default_rng(12)
     lab = rng.integers(0, 32, 21500).astype(np.int32)
     ql = rng.integers(-1, 34, 400).astype(np.int32)  # -1 and the labels 32, 33 match nothing
-    index = certex.Index(24)
+    index = certex.Index(24, partition_labels="lazy")
     index.add(x[:20000], labels=lab[:20000])
     assert index.info()["n_partitioned"] == 20000
-    index.add(x[20000:], labels=lab[20000:])
+    index.add(x[20000:], labels=lab[20000:])  # fewer than an eighth of the vectors: the partition stays
     assert index.info()["n_partitioned"] == 20000
     gone = rng.choice(21500, 1500, replace=False)
     index.remove(gone)
@@ -105,6 +105,53 @@ def test_label_partition_with_newer_vectors():
     index._test_mode(0)
     assert np.array_equal(Ip, Iu) and np.array_equal(Sp, Su) and np.array_equal(Dp, Du)
     assert (Ip[(ql < 0) | (ql >= 32)] == -1).all()
+
+
+@pytest.mark.parametrize("dtype,dim,metric,k", [("uint8", 64, "l2", 10), ("int8", 300, "ip", 10), ("float32", 96, "l2", 10),
+                                               ("float32", 768, "cosine", 100), ("float16", 200, "ip", 20)])
+def test_labels_are_screened_against_their_own_rows(dtype, dim, metric, k):
+    """Labels with at least k groups of 64 rows go through the routed tensor-core pass (label-ordered copy of the code
+    rows, one block of whole tiles per label); the answers equal the oracle's and those of the dense label groups.
+    Label 0 is large, label 7 small (dense), some queries ask for labels without rows; rows are removed in between."""
+    n, nq = 60000, 500
+    x, q = data(n, dim, nq, dtype, seed=31)
+    rng = np.random.default_rng(32)
+    lab = rng.choice(8, n, p=[0.4, 0.2, 0.15, 0.1, 0.08, 0.04, 0.0295, 0.0005]).astype(np.int32)
+    ql = rng.integers(0, 10, nq).astype(np.int32)
+    index = certex.Index(dim, metric=metric)
+    index.add(x, labels=lab)
+    with certex.search_stats() as st:
+        same(index, x, q, k, metric=metric, row_labels=lab, query_labels=ql, labels=ql)
+    assert st.routed_queries >= (ql < 6).sum() and 0 < st.dense_queries < nq
+    gone = rng.choice(n, 3000, replace=False)
+    index.remove(gone)
+    masked = lab.copy()
+    masked[gone] = -1
+    with certex.search_stats() as st:
+        _, Ir, Sr = index.search(q, k=k, labels=ql, return_scores=True)
+    assert st.routed_queries > 0
+    ids, scores = oracle.knn(x, q, k, metric, row_labels=masked, query_labels=ql)
+    assert np.array_equal(Ir, ids) and np.array_equal(Sr, scores)
+    index._test_mode(3)  # dense label groups only
+    with certex.search_stats() as st:
+        _, Id, Sd = index.search(q, k=k, labels=ql, return_scores=True)
+    assert st.routed_queries == 0 and np.array_equal(Ir, Id) and np.array_equal(Sr, Sd)
+
+
+def test_routed_pass_with_many_labels_and_uneven_query_counts():
+    """300 labels of about 700 rows (k = 10 needs 640): most are routed, every label's block is a few tiles and the
+    segments of many labels share a CTA; one label has 400 queries (several query tiles), most have one or none."""
+    n, dim, nq = 210000, 32, 1200
+    x, q = data(n, dim, nq, "uint8", seed=33)
+    rng = np.random.default_rng(34)
+    lab = rng.integers(0, 300, n).astype(np.int32)
+    ql = rng.integers(0, 300, nq).astype(np.int32)
+    ql[:400] = 17
+    index = certex.Index(dim)
+    index.add(x, labels=lab)
+    with certex.search_stats() as st:
+        same(index, x, q, 10, row_labels=lab, query_labels=ql, labels=ql)
+    assert st.routed_queries > 400
 
 
 def test_label_partition_small_labels_and_large_k():
