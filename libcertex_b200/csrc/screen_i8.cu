@@ -61,7 +61,7 @@ constexpr int kThreads    = 32 * (2 + kEpiWarps);
 // The two single-thread roles sit in the last two warps; warps 0..15 are the epilogue (TMEM lane quarter = warp % 4).
 constexpr int kTmaWarp    = kEpiWarps;
 constexpr int kMmaWarp    = kEpiWarps + 1;
-constexpr int kRecBuf     = 64;                // staged survivor records per epilogue warp
+constexpr int kRecBuf     = 64;                // staged survivor records per epilogue warp (flushed when half full)
 constexpr int kWideStage  = 2 * kQTileBytes + kBTileBytes;  // WIDE: one K block of two query tiles and a base tile
 constexpr int kWideStages = 3;
 constexpr int kERing      = 4;                 // WIDE: tiles whose e values may be in flight
@@ -79,6 +79,7 @@ struct SharedCtl {
   uint64_t e_empty[kERing];     // WIDE: every epilogue warp is done with them
   uint32_t tmem_base;
   int abort_flag;
+  int rec_n[kEpiWarps];         // fill counts of the warps' record staging buffers
   ScreenSeg segs[kSharedSegs];
 };
 
@@ -224,6 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       mbar_init(smem_u32(&ctl->e_empty[i]), kEpiWarps);
     }
     ctl->abort_flag = 0;
+    for (int i = 0; i < kEpiWarps; ++i) { ctl->rec_n[i] = 0; }
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_x);
@@ -427,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     const int row            = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     uint64_t* rec_buf        = reinterpret_cast<uint64_t*>(gen_base + rec_off) + ew * kRecBuf;
-    int n_rec                = 0;  // staged records of this warp (warp-uniform)
+    volatile int* rec_n      = &ctl->rec_n[ew];  // staged records of this warp
 
     Cursor cur;
     cur.s = 0, cur.j = 0, cur.ts = 0, cur.col0 = 0;
@@ -436,8 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     bool ok = true;
 
     // Staged records -> global memory: one atomic add reserves the range, the lanes copy.
-    auto flush = [&]() {
-      __syncwarp();
+    auto flush = [&](int n_rec) {
       unsigned long long at = 0;
       if (lane == 0) { at = atomicAdd(p.rec_count, static_cast<unsigned long long>(n_rec)); }
       at = __shfl_sync(0xffffffffu, at, 0);
@@ -445,41 +446,41 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         if (at + i < p.rec_cap) { p.rec[at + i] = rec_buf[i]; }
       }
       __syncwarp();
-      n_rec = 0;
+      if (lane == 0) { *rec_n = 0; }
+      __syncwarp();
     };
-    // A chain of 16 columns that may hold survivors of some rows of the warp (`hit`): exact test per element.
-    auto records = [&](const int32_t* v, bool hit, int thr, int q, int64_t row0, const int32_t* e) {
-      const uint32_t ball = __ballot_sync(0xffffffffu, hit);
-      if (ball == 0u) { return; }
-      uint32_t mask = 0;
-      if (hit) {
-        const int4* e4 = reinterpret_cast<const int4*>(e);
+    // A chain of 16 columns that may hold survivors of this thread's query (the conservative test passed): the exact
+    // test per element; the survivors form one record, staged through the warp's buffer in shared memory (its fill
+    // count is a shared-memory atomic: the few threads that get here need no warp-wide step).
+    auto record = [&](const int32_t* v, int thr, int q, int64_t row0, const int32_t* e) {
+      uint32_t mask  = 0;
+      const int4* e4 = reinterpret_cast<const int4*>(e);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int4 t = e4[i];
-          if (F16) {
-            const float tf = __int_as_float(thr);
-            mask |= (__int_as_float(v[4 * i]) + __int_as_float(t.x) >= tf ? 1u : 0u) << (4 * i);
-            mask |= (__int_as_float(v[4 * i + 1]) + __int_as_float(t.y) >= tf ? 1u : 0u) << (4 * i + 1);
-            mask |= (__int_as_float(v[4 * i + 2]) + __int_as_float(t.z) >= tf ? 1u : 0u) << (4 * i + 2);
-            mask |= (__int_as_float(v[4 * i + 3]) + __int_as_float(t.w) >= tf ? 1u : 0u) << (4 * i + 3);
-          } else {
-            mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
-            mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
-            mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
-            mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
-          }
+      for (int i = 0; i < 4; ++i) {
+        const int4 t = e4[i];
+        if (F16) {
+          const float tf = __int_as_float(thr);
+          mask |= (__int_as_float(v[4 * i]) + __int_as_float(t.x) >= tf ? 1u : 0u) << (4 * i);
+          mask |= (__int_as_float(v[4 * i + 1]) + __int_as_float(t.y) >= tf ? 1u : 0u) << (4 * i + 1);
+          mask |= (__int_as_float(v[4 * i + 2]) + __int_as_float(t.z) >= tf ? 1u : 0u) << (4 * i + 2);
+          mask |= (__int_as_float(v[4 * i + 3]) + __int_as_float(t.w) >= tf ? 1u : 0u) << (4 * i + 3);
+        } else {
+          mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
+          mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
+          mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
+          mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
         }
       }
-      const uint32_t keep = __ballot_sync(0xffffffffu, mask != 0u);
-      if (keep == 0u) { return; }
-      const int n_new = __popc(keep);
-      if (n_rec + n_new > kRecBuf) { flush(); }
       if (mask != 0u) {
-        rec_buf[n_rec + __popc(keep & ((1u << lane) - 1u))] =
-          make_record(static_cast<uint32_t>(q), static_cast<uint32_t>(row0 / kChainRows), mask);
+        const uint64_t r = make_record(static_cast<uint32_t>(q), static_cast<uint32_t>(row0 / kChainRows), mask);
+        const int pos    = atomicAdd(const_cast<int*>(rec_n), 1);
+        if (pos < kRecBuf) {
+          rec_buf[pos] = r;
+        } else {  // the staging buffer is full: straight to global memory
+          const unsigned long long at = atomicAdd(p.rec_count, 1ull);
+          if (at < p.rec_cap) { p.rec[at] = r; }
+        }
       }
-      n_rec += n_new;
     };
 
     while (ok && cur.valid) {
@@ -528,10 +529,13 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           }
           const int32_t* e   = init_smem + er * kBaseTile + piece * kGroupRows;
           const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
-          records(a, h0, thr, q, row0, e);
-          records(a + 16, h1, thr, q, row0 + 16, e + 16);
-          records(b, h2, thr, q, row0 + 32, e + 32);
-          records(b + 16, h3, thr, q, row0 + 48, e + 48);
+          if (h0) { record(a, thr, q, row0, e); }
+          if (h1) { record(a + 16, thr, q, row0 + 16, e + 16); }
+          if (h2) { record(b, thr, q, row0 + 32, e + 32); }
+          if (h3) { record(b + 16, thr, q, row0 + 48, e + 48); }
+          __syncwarp();
+          const int staged = min(*rec_n, kRecBuf);
+          if (staged > kRecBuf / 2) { flush(staged); }
         }
       } else {
         // exact group maximum: e of the tile was staged with it
@@ -562,7 +566,11 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
         }
       }
     }
-    if (MODE == kModeScreen && n_rec > 0) { flush(); }
+    if (MODE == kModeScreen) {
+      __syncwarp();
+      const int staged = min(*rec_n, kRecBuf);
+      if (staged > 0) { flush(staged); }
+    }
   }
 
   // ---- teardown: all roles meet here, also when a wait gave up
