@@ -167,8 +167,9 @@ CERTEX_B200_EXPORT cuvsError_t cuvsCertexRemove(cuvsResources_t res, DLManagedTe
 /** certex.h:157-160: labels (int32 device vector) of the vectors first, first + 1, ... */
 CERTEX_B200_EXPORT cuvsError_t cuvsCertexSetLabels(cuvsResources_t res, DLManagedTensor* labels, int64_t first,
                                                    cuvsCertexIndex_t index);
-/** certex.h:164: in the reference a speed-only re-ordering of the screening rows by label; results are the same
- *  with or without it, and here it only records that the call was made. */
+/** certex.h:164: groups the ids by label and, when the index has a tensor-core screen, copies the code rows in label
+ *  order, so that searches by label screen and score only the rows of the query's label. Speed only: results are the
+ *  same with or without it. Vectors added later are found too (scored densely) until the next call. */
 CERTEX_B200_EXPORT cuvsError_t cuvsCertexPartitionByLabels(cuvsResources_t res, cuvsCertexIndex_t index);
 
 /** certex.h:184-190: exact k nearest neighbours, k = neighbors.shape[1]. queries [nq, dim] (device, index dtype),
