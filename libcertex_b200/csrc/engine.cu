@@ -778,7 +778,6 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
       }
       n_slots += add;
       max_tiles = std::max(max_tiles, nt);
-      pairs += static_cast<unsigned long long>(run.queries.size()) * static_cast<unsigned long long>(run.n_in_part);
     }
     const int ns = static_cast<int>(n_slots);
 
@@ -899,6 +898,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     for (cudaEvent_t e : events) { cudaEventDestroy(e); }
     CERTEX_EXPECTS(h_flag[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_flag[1]) + ")");
     st->routed_queries += static_cast<unsigned long long>(ns);
+    pairs += h_stats[0];  // pairs the routed screen kept and the verification scored
     // slots whose list overflowed (every real slot, when a query coordinate did not fit fp16) go to the dense groups
     std::vector<char> again(static_cast<size_t>(ns), h_flag[2] != 0 ? 1 : 0);
     for (unsigned int i = 0; i < h_flag[0] && i < static_cast<unsigned int>(ns); ++i) { again[static_cast<size_t>(h_ovf[i])] = 1; }

@@ -25,20 +25,6 @@ namespace certex_b200 {
 namespace {
 
 // ------------------------------------------------------------------------------------------- element access
-// 8-bit coordinates become doubles without the conversion instruction: I2F / F2F to a 64-bit type issue on the XU
-// pipe at about two results per clock and SM, an order of magnitude below the fp64 add unit (the verification of
-// float32 rows runs at 76 % of that pipe's peak). The integer is planted in the mantissa of 2^52 and 2^52 is
-// subtracted, which is exact. (For floats the same idea, re-biasing the exponent with integer instructions, measured
-// slower than the conversion instruction and is not used.)
-__device__ __forceinline__ double u32_to_f64(uint32_t n)  // exact for every n
-{
-  return __dsub_rn(__hiloint2double(0x43300000, static_cast<int>(n)), 4503599627370496.0);
-}
-__device__ __forceinline__ double i8_to_f64(uint32_t byte)  // byte = the two's complement bits of an int8
-{
-  return __dsub_rn(__hiloint2double(0x43300000, static_cast<int>((byte ^ 0x80u) & 0xffu)), 4503599627370624.0);  // 2^52 + 128
-}
-
 template <typename T>
 struct Elems;
 template <>
@@ -73,9 +59,9 @@ struct Elems<int8_t> {
   {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i] = i8_to_f64((u[i >> 2] >> (8 * (i & 3))) & 0xffu); }
+    for (int i = 0; i < 16; ++i) { o[i] = double(int(int8_t((u[i >> 2] >> (8 * (i & 3))) & 0xffu))); }
   }
-  __device__ static double one(const void* p, int64_t i) { return i8_to_f64(static_cast<const uint8_t*>(p)[i]); }
+  __device__ static double one(const void* p, int64_t i) { return double(static_cast<const int8_t*>(p)[i]); }
 };
 template <>
 struct Elems<uint8_t> {
@@ -84,9 +70,9 @@ struct Elems<uint8_t> {
   {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i] = u32_to_f64((u[i >> 2] >> (8 * (i & 3))) & 0xffu); }
+    for (int i = 0; i < 16; ++i) { o[i] = double(int((u[i >> 2] >> (8 * (i & 3))) & 0xffu)); }
   }
-  __device__ static double one(const void* p, int64_t i) { return u32_to_f64(static_cast<const uint8_t*>(p)[i]); }
+  __device__ static double one(const void* p, int64_t i) { return double(static_cast<const uint8_t*>(p)[i]); }
 };
 
 __device__ __forceinline__ bool admitted(const Admit& a, int64_t q, int64_t row)
