@@ -247,6 +247,18 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsC
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsBegin(void);
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[16]);
 
+/** Exchange of thresholds between the row shards of one set: the reference's threshold hooks
+ *  (cpp/src/neighbors/certex/detail/kernels.hpp:271-277) and the first round of its sharded search
+ *  (cpp/src/neighbors/certex/certex_shards.cu:136-141). While a hook is set for the calling thread, every unfiltered
+ *  screened search calls it once per batch of queries, between the anchor pass and the screen: keys [n] (device) are
+ *  monotone int32 images of scores that k rows of this shard certainly reach for the n queries of the batch (larger =
+ *  tighter). The hook may raise a key to what another shard of the same set certainly reaches, e.g. take the maximum
+ *  over the shards with an all-reduce; it must enqueue its work on `stream`. certexB200IndexWillScreen tells whether a
+ *  search for k neighbours will call it (every shard must agree before a collective is used). NULL removes the hook. */
+typedef void (*certexB200ThresholdHook)(void* ctx, int32_t* keys, int64_t n, void* stream /* cudaStream_t */);
+CERTEX_B200_EXPORT cuvsError_t certexB200SetThresholdHook(certexB200ThresholdHook hook, void* ctx);
+CERTEX_B200_EXPORT cuvsError_t certexB200IndexWillScreen(cuvsCertexIndex_t index, int32_t k, int32_t* out);
+
 /** Test hook: mode 0 automatic, 1 always the dense path, 2 screen with candidate lists of `cap` entries per query
  *  (small values exercise the overflow fallback), 3 searches by label score their label's rows densely instead of
  *  screening them. */

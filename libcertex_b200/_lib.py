@@ -110,7 +110,11 @@ SYMBOLS = [
     "certexB200SearchEx", "certexB200MergeShards", "certexB200IndexGetInfo", "certexB200IndexReserve",
     "certexB200StatsBegin", "certexB200StatsEnd", "certexB200IndexSetTestMode", "certexB200ScreenRaw",
     "certexB200PlanSegments", "certexB200SearchStatic", "certexB200Version",
+    "certexB200SetThresholdHook", "certexB200IndexWillScreen",
 ]
+
+# void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
+ThresholdHook = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p)
 
 _lib = None
 _lock = threading.Lock()
@@ -163,6 +167,8 @@ def lib():
                 L.certexB200StatsBegin.argtypes = []
                 L.certexB200StatsEnd.argtypes = [P(ctypes.c_uint64)]
                 L.certexB200IndexSetTestMode.argtypes = [P(IndexHandle), ctypes.c_int32, ctypes.c_int32]
+                L.certexB200SetThresholdHook.argtypes = [ThresholdHook, vp]
+                L.certexB200IndexWillScreen.argtypes = [P(IndexHandle), ctypes.c_int32, P(ctypes.c_int32)]
                 L.certexB200ScreenRaw.argtypes = [
                     vp, vp, i64, vp, i64, i64, ctypes.c_int32, vp, ctypes.c_int32, vp, vp, i64, vp, vp,
                     ctypes.c_uint32, P(ctypes.c_float),

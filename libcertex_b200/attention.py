@@ -18,31 +18,41 @@ def _as_half_or_float(x):
 
 class KeyCache:
     """n_kv_heads, head_dim: the shape of the keys; k: the largest k searches will ask for; capacity: expected keys
-    per head (reserves memory once)."""
+    per head (reserves memory once).
+
+    All KV heads live in one labeled inner-product index (label = KV head), so that one search call answers the
+    queries of every head: each query is screened and scored against the keys of its own head only."""
 
     def __init__(self, n_kv_heads, head_dim, k=2048, capacity=None):
         _need(n_kv_heads >= 1 and head_dim >= 1, "n_kv_heads and head_dim must be positive")
         _need(1 <= k <= 2048, f"k must be between 1 and 2048, not {k}")
         self.n_kv_heads, self.head_dim, self.k, self.capacity = int(n_kv_heads), int(head_dim), int(k), capacity
-        self.heads, self.dtype, self.size = None, None, 0
+        self.index, self.dtype, self.size = None, None, 0
+        self._position = None  # id of the index -> position of the key inside its head
 
     def append(self, keys):
-        """Append keys of shape (n_kv_heads, n, head_dim); ids continue from the keys appended before."""
+        """Append keys of shape (n_kv_heads, n, head_dim); positions continue from the keys appended before."""
         K = _as_half_or_float(keys)
         _need(K.ndim == 3 and K.shape[0] == self.n_kv_heads and K.shape[2] == self.head_dim,
               f"keys must have shape ({self.n_kv_heads}, n, {self.head_dim}), not {tuple(K.shape)}")
-        if self.heads is None:
+        n_new = K.shape[1]
+        if self.index is None:
             self.dtype = K.dtype
-            self.heads = [Index(self.head_dim, metric="ip", capacity=self.capacity) for _ in range(self.n_kv_heads)]
-        for g, idx in enumerate(self.heads):
-            idx.add(K[g].to(self.dtype).contiguous())
-        self.size += K.shape[1]
+            cap = None if self.capacity is None else int(self.capacity) * self.n_kv_heads
+            # the partition by head is renewed once an eighth of the keys is newer than it: appending a few keys per
+            # decoding step must not copy the whole cache
+            self.index = Index(self.head_dim, metric="ip", capacity=cap, partition_labels="lazy")
+        heads = torch.arange(self.n_kv_heads, dtype=torch.int32, device="cuda").repeat_interleave(n_new)
+        self.index.add(K.to(self.dtype).reshape(self.n_kv_heads * n_new, self.head_dim).contiguous(), labels=heads)
+        pos = torch.arange(self.size, self.size + n_new, dtype=torch.int64, device="cuda").repeat(self.n_kv_heads)
+        self._position = pos if self._position is None else torch.cat([self._position, pos])
+        self.size += n_new
         return self
 
     def topk(self, q, k=None, batch=2048):
         """q: (n_heads, m, head_dim) or (n_heads, head_dim), n_heads a multiple of n_kv_heads. Returns (scores, ids) of
-        shape (n_heads, m, k) or (n_heads, k), scores descending."""
-        _need(self.heads is not None, "the cache is empty: append keys first")
+        shape (n_heads, m, k) or (n_heads, k), scores descending, ids = key positions."""
+        _need(self.index is not None, "the cache is empty: append keys first")
         k = self.k if k is None else int(k)
         _need(1 <= k <= min(2048, self.size), f"k must be between 1 and {min(2048, self.size)}, not {k}")
         Q = _as_half_or_float(q)
@@ -53,13 +63,10 @@ class KeyCache:
               f"queries must have shape (n_heads, m, {self.head_dim}) with n_heads a multiple of {self.n_kv_heads}")
         H, m, d = Q.shape
         group = H // self.n_kv_heads
-        scores = torch.empty((H, m, k), dtype=torch.float32, device="cuda")
-        ids = torch.empty((H, m, k), dtype=torch.int64, device="cuda")
-        for g, idx in enumerate(self.heads):
-            rows = slice(g * group, (g + 1) * group)
-            D, I = idx.search(Q[rows].reshape(group * m, d).to(self.dtype), k=k, batch=batch)
-            scores[rows] = D.reshape(group, m, k)
-            ids[rows] = I.reshape(group, m, k)
+        heads = (torch.arange(H, dtype=torch.int32, device="cuda") // group).repeat_interleave(m)
+        D, I = self.index.search(Q.reshape(H * m, d).to(self.dtype).contiguous(), k=k, batch=batch, labels=heads)
+        ids = self._position[I.clamp_(min=0)]  # every head holds at least k keys: no entry is missing
+        scores, ids = D.reshape(H, m, k), ids.reshape(H, m, k)
         return (scores[:, 0], ids[:, 0]) if single else (scores, ids)
 
 

@@ -462,6 +462,22 @@ cuvsError_t certexB200StatsEnd(uint64_t out[16])
   });
 }
 
+cuvsError_t certexB200SetThresholdHook(certexB200ThresholdHook hook, void* ctx)
+{
+  return translate([=] {
+    Index::threshold_hook     = reinterpret_cast<Index::ThresholdHook>(hook);
+    Index::threshold_hook_ctx = ctx;
+  });
+}
+
+cuvsError_t certexB200IndexWillScreen(cuvsCertexIndex_t index, int32_t k, int32_t* out)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(out != nullptr, "certex: out is null");
+    *out = as_holder(index).index->will_screen(k) ? 1 : 0;
+  });
+}
+
 cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap)
 {
   return translate([=] {

@@ -25,6 +25,8 @@
 namespace certex_b200 {
 
 thread_local SearchStats* Index::stats_sink = nullptr;
+thread_local Index::ThresholdHook Index::threshold_hook = nullptr;
+thread_local void* Index::threshold_hook_ctx = nullptr;
 
 namespace {
 
@@ -511,7 +513,8 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
   const int nt_all        = static_cast<int>((n + kTile - 1) / kTile);
   const uint32_t cap      = test_mode_ == 2 ? static_cast<uint32_t>(test_cap_) : static_cast<uint32_t>(std::max(2048, 2 * k));
-  const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
+  // a record holds the survivors of one chain of 16 rows: as many records as candidate slots always suffice
+  const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * cap);
   uint32_t* cnt        = scratch.get<uint32_t>(static_cast<size_t>(nq));
   int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
   uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
@@ -627,7 +630,11 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   mark();
   // 2 threshold: the k-th largest group maximum
   launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
-  if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, res.stream); }
+  if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, 0, res.stream); }
+  CERTEX_CUDA(cudaGetLastError());
+  // thr now holds, per query, (a key of) a score k rows of this index certainly reach: other shards may tighten it
+  if (threshold_hook) { threshold_hook(threshold_hook_ctx, thr, nq, res.stream); }
+  if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, 1, res.stream); }
   CERTEX_CUDA(cudaGetLastError());
   // 3 screen over all rows, 4 exact scores of the candidates and the k best
   screen_pass(res, qb, thr, queries, row_bytes, q0, nq, k, best_s, best_row, ovf_list, ovf_count, stats, err, n, thr2, shift,
@@ -704,7 +711,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
                                            SearchStats* st) const
 {
   // The one host decision of the path: which queries share a label. Their labels come to the host and the queries are
-  // ordered by label. A label with enough rows for a threshold (k groups of 64) is screened on the tensor cores
+  // ordered by label. A label with enough rows for a threshold (2k groups of 64) is screened on the tensor cores
   // against its block of the label-ordered copy of the code rows (routed pass); the other labels, the queries whose
   // candidate list overflowed, and every label when rows were added after the partition, are scored densely: every
   // label becomes a group (queries x that label's partition entries + the rows added since), and the groups are
@@ -718,7 +725,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
 
   const int64_t n_tail = n - n_part_;
   const bool can_route = lcodes_ != nullptr && screen_kind_ != 0 && !code_overflow_ && n_tail == 0 && test_mode_ != 3;
-  std::vector<LabelRun> routed, dense;
+  std::vector<LabelRun> routed, routed_fine, dense;
   for (int i = 0; i < nq;) {
     const int32_t l = lab[order[static_cast<size_t>(i)]];
     int j           = i;
@@ -732,13 +739,23 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
       run.tile0       = part_tile0_.empty() ? 0 : part_tile0_[at];
     }
     run.queries.assign(order.begin() + i, order.begin() + j);
-    const bool route = can_route && run.n_in_part / kGroupRows >= k;
-    (route ? routed : dense).push_back(std::move(run));
+    // a threshold worth the passes needs about 2k groups: the k-th largest of them then sits near the best 1 % of the
+    // label. Groups are 64 rows, or single chains of 16 rows for labels too small for that.
+    const int64_t need = 2 * static_cast<int64_t>(k);
+    if (can_route && run.n_in_part / kGroupRows >= need) {
+      routed.push_back(std::move(run));
+    } else if (can_route && run.n_in_part / kChainRows >= need) {
+      routed_fine.push_back(std::move(run));
+    } else {
+      dense.push_back(std::move(run));
+    }
     i = j;
   }
   unsigned long long pairs = 0;
 
   // ------------------------------------------------------------------ routed passes
+  auto run_routed = [&](std::vector<LabelRun>& routed, const bool fine) {
+  const int per_tile = fine ? kBaseTile / kChainRows : kBaseTile / kGroupRows;  // columns of gmax per tile
   for (size_t r0 = 0; r0 < routed.size();) {
     // as many runs as fit 32 768 query slots (a label's queries fill whole tiles of 128) and the segment slots
     size_t r1 = r0;
@@ -774,7 +791,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
       for (int64_t i = 0; i < add; ++i) {
         const bool real = i < static_cast<int64_t>(run.queries.size());
         slot_query.push_back(real ? run.queries[static_cast<size_t>(i)] : -1);
-        slot_ng.push_back(real ? static_cast<int32_t>(nt * (kBaseTile / kGroupRows)) : -1);
+        slot_ng.push_back(real ? static_cast<int32_t>(nt * per_tile) : -1);
       }
       n_slots += add;
       max_tiles = std::max(max_tiles, nt);
@@ -784,10 +801,10 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     Scratch scratch(res.stream);
     const bool f16       = screen_kind_ == 2;
     const size_t cp      = code_pitch_;
-    const int n_groups   = static_cast<int>(max_tiles) * (kBaseTile / kGroupRows);
+    const int n_groups   = static_cast<int>(max_tiles) * per_tile;
     const int64_t ld_g   = round_up(n_groups, 8);
     const uint32_t cap   = static_cast<uint32_t>(std::max(2048, 2 * k));
-    const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(ns) * 1024ull);
+    const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(ns) * cap);
     int32_t* d_slot_q    = scratch.get<int32_t>(static_cast<size_t>(ns));
     int32_t* d_slot_ng   = scratch.get<int32_t>(static_cast<size_t>(ns));
     ScreenSeg* d_segs    = scratch.get<ScreenSeg>(segs.size());
@@ -841,6 +858,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     a.seg_begin   = d_seg_begin;
     a.seg_col0    = d_col0;
     a.plain_tiles = 1;
+    a.fine_groups = fine ? 1 : 0;
     a.init        = linit_;
     // 1 group maxima over the label's own rows, 2 the k-th largest of them is the threshold
     a.mode    = kModeGroupMax;
@@ -860,7 +878,10 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     mark();
     launch_kth_largest(gmax, ld_g, n_groups, k, ns, thr, res.stream, d_slot_ng,
                        f16 ? static_cast<int32_t>(0x7f800000) : static_cast<int32_t>(0x7fffffff));
-    if (f16) { launch_finish_thr_f16(thr, shift, ns, res.stream); }
+    if (f16) {
+      launch_finish_thr_f16(thr, shift, ns, 0, res.stream);
+      launch_finish_thr_f16(thr, shift, ns, 1, res.stream);
+    }
     CERTEX_CUDA(cudaGetLastError());
     // 3 screen, 4 exact scores of the candidates
     a.mode      = kModeScreen;
@@ -916,6 +937,9 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     }
     r0 = r1;
   }
+  };
+  run_routed(routed, false);
+  run_routed(routed_fine, true);
 
   // ------------------------------------------------------------------ dense groups
   std::vector<int32_t> dorder;
@@ -996,6 +1020,21 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
   return pairs;
 }
 
+int Index::anchor_stride_for(int64_t n, int k) const
+{
+  // anchors: every stride-th row in whole tiles of 256, and at least 2k groups of 64 anchors, or the threshold would be
+  // useless. The k-th largest group maximum is roughly the (stride * k)-th best row: for larger k the anchors are taken
+  // denser, so that the candidate lists stay a small multiple of k (the anchor pass costs 1 / stride of a screen pass).
+  const int64_t by_k = std::max<int64_t>(1, static_cast<int64_t>(params_.anchor_stride) * 32 / k);
+  return static_cast<int>(std::min<int64_t>({params_.anchor_stride, by_k, n / (kTile * ((2 * k + 3) / 4))}));
+}
+
+bool Index::will_screen(int k) const
+{
+  std::shared_lock<std::shared_mutex> lock(rw_);
+  return screen_kind_ != 0 && !code_overflow_ && test_mode_ != 1 && k >= 1 && anchor_stride_for(size_, k) >= 1;
+}
+
 void Index::search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
                    int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base) const
 {
@@ -1022,12 +1061,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   adm.query_labels    = filter.query_labels;
   const bool filtered = filter.words != nullptr || filter.query_labels != nullptr;
 
-  // anchors: every stride-th row in whole tiles of 256, and at least 2k groups of 64 anchors, or the threshold would be
-  // useless
-  // The k-th largest group maximum is roughly the (stride * k)-th best row: for larger k the anchors are taken denser,
-  // so that the candidate lists stay a small multiple of k (the anchor pass costs 1 / stride of a screen pass).
-  const int64_t by_k  = std::max<int64_t>(1, static_cast<int64_t>(params_.anchor_stride) * 32 / k);
-  const int stride    = static_cast<int>(std::min<int64_t>({params_.anchor_stride, by_k, n / (kTile * ((2 * k + 3) / 4))}));
+  const int stride    = anchor_stride_for(n, k);
   const bool screened = screen_kind_ != 0 && !code_overflow_ && !filtered && stride >= 1 && test_mode_ != 1;
 
   SearchStats local{};

@@ -132,6 +132,18 @@ class Index {
 
   static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
 
+  /// Exchange of thresholds between the row shards of one set (the reference's threshold hooks,
+  /// cpp/src/neighbors/certex/detail/kernels.hpp:271-277, and the first round of its sharded search,
+  /// certex_shards.cu:136-141). Between the anchor pass and the screen of every batch the hook of the calling thread
+  /// gets keys [n] on the device: key i is a monotone int32 image of a score that k rows of this shard certainly reach
+  /// for query i of the batch (larger = tighter). It may raise keys to what another shard of the same set certainly
+  /// reaches (e.g. the maximum over the shards); it must enqueue its work on `stream`. Plain unfiltered searches only.
+  using ThresholdHook = void (*)(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream);
+  static thread_local ThresholdHook threshold_hook;
+  static thread_local void* threshold_hook_ctx;
+  /// Whether an unfiltered search for k neighbours goes through the tensor-core screen (and calls the hook).
+  bool will_screen(int k) const;
+
  private:
   void search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries, size_t row_bytes,
                        int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
@@ -141,6 +153,7 @@ class Index {
                    int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                    unsigned long long* stats, int* err, int64_t n, int32_t* thr2, const float* shift,
                    std::vector<cudaEvent_t>* events) const;
+  int anchor_stride_for(int64_t n, int k) const;
   void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,
                     const Admit& adm, double* best_s, int32_t* best_row, int64_t n) const;
   /// Search by label over the label partition; returns the (query, row) pairs scored and counts its launches.

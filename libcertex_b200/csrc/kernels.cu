@@ -19,6 +19,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace certex_b200 {
 
@@ -451,15 +452,19 @@ __global__ void encode_f16_queries_kernel(const uint8_t* queries, size_t qpitch,
   }
 }
 
-// thr[q]: the key of the k-th largest group maximum (see float_key in the screen kernel) -> float bits of the
-// screen's threshold, value - shift[q], rounded down.
-__global__ void finish_thr_f16_kernel(int32_t* thr, const float* shift, int nq)
+// fp16 codes, in two steps around the optional exchange of thresholds between shards. Step 0: thr[q] = the key of the
+// k-th largest group maximum (see float_key in the screen kernel) -> the key of value - shift[q] / 2, a score that k
+// rows of this index certainly reach in exact arithmetic. Step 1: such a key -> float bits of the screen's
+// threshold, bound - shift[q] / 2. Both subtractions round down.
+__global__ void finish_thr_f16_kernel(int32_t* thr, const float* shift, int nq, int step)
 {
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
   if (q >= nq) { return; }
   const int32_t key = thr[q];
   const float v     = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
-  thr[q]            = __float_as_int(__fadd_rd(v, -shift[q]));
+  const float r     = __fadd_rd(v, -__fmul_ru(0.5f, shift[q]));
+  const int32_t b   = __float_as_int(r);
+  thr[q]            = step == 0 ? (b ^ ((b >> 31) & 0x7fffffff)) : b;
 }
 
 __global__ void chain_max_f32_kernel(const float* init, int64_t c0, int64_t n, float* cmax)
@@ -568,6 +573,48 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
   if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(prefix ^ 0x80000000u); }
 }
 
+// Exact score of an 8-bit row against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot
+// products (int32 is enough: 255^2 * 4096 < 2^31), the score |q|^2 + |x|^2 - 2 <q, x> (L2) or |q|^2 - 2 <q, x> in
+// int64. Every partial sum of the fp64 loop over the coordinates is an integer below 2^53, so that loop returns this
+// very integer: the results are bit-identical, without one conversion to double per coordinate.
+// qb: the query's bytes in shared memory, zero padded to whole 16-byte vectors like the stored row.
+template <typename T, int METRIC>
+__device__ __forceinline__ double int_row_score(const uint8_t* row, int d, const uint4* qb, long long qq)
+{
+  const uint4* p  = reinterpret_cast<const uint4*>(row);
+  const int n_vec = (d + 15) / 16;
+  int ip = 0, xx = 0;
+  for (int c = 0; c < n_vec; ++c) {
+    const uint4 w = __ldg(p + c);
+    const uint4 a = qb[c];
+    if constexpr (std::is_same<T, int8_t>::value) {
+      ip = __dp4a(static_cast<int>(w.x), static_cast<int>(a.x), ip);
+      ip = __dp4a(static_cast<int>(w.y), static_cast<int>(a.y), ip);
+      ip = __dp4a(static_cast<int>(w.z), static_cast<int>(a.z), ip);
+      ip = __dp4a(static_cast<int>(w.w), static_cast<int>(a.w), ip);
+      if constexpr (METRIC == kL2) {
+        xx = __dp4a(static_cast<int>(w.x), static_cast<int>(w.x), xx);
+        xx = __dp4a(static_cast<int>(w.y), static_cast<int>(w.y), xx);
+        xx = __dp4a(static_cast<int>(w.z), static_cast<int>(w.z), xx);
+        xx = __dp4a(static_cast<int>(w.w), static_cast<int>(w.w), xx);
+      }
+    } else {
+      ip = static_cast<int>(__dp4a(w.x, a.x, static_cast<unsigned>(ip)));
+      ip = static_cast<int>(__dp4a(w.y, a.y, static_cast<unsigned>(ip)));
+      ip = static_cast<int>(__dp4a(w.z, a.z, static_cast<unsigned>(ip)));
+      ip = static_cast<int>(__dp4a(w.w, a.w, static_cast<unsigned>(ip)));
+      if constexpr (METRIC == kL2) {
+        xx = static_cast<int>(__dp4a(w.x, w.x, static_cast<unsigned>(xx)));
+        xx = static_cast<int>(__dp4a(w.y, w.y, static_cast<unsigned>(xx)));
+        xx = static_cast<int>(__dp4a(w.z, w.z, static_cast<unsigned>(xx)));
+        xx = static_cast<int>(__dp4a(w.w, w.w, static_cast<unsigned>(xx)));
+      }
+    }
+  }
+  const long long s = qq + static_cast<long long>(xx) - 2ll * static_cast<long long>(ip);
+  return __ll2double_rn(s);
+}
+
 // ------------------------------------------------------------------------------------------- verify + select
 // Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap).
 template <typename T, int METRIC>
@@ -594,7 +641,29 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
   double* sc   = sh + d;
   int32_t* ids = reinterpret_cast<int32_t*>(sc + n2max);
   const int64_t qi = q;
-  load_queries<T>(queries, qpitch, &qi, 1, d, qd, d, &s_qq);
+  constexpr bool kBytes = std::is_same<T, int8_t>::value || std::is_same<T, uint8_t>::value;
+  __shared__ long long s_qq_int;
+  if constexpr (kBytes) {
+    // the query's bytes, zero padded to whole 16-byte vectors, in the space of qd; |q|^2 as an integer
+    uint8_t* qbytes    = reinterpret_cast<uint8_t*>(qd);
+    const uint8_t* src = static_cast<const uint8_t*>(queries) + static_cast<size_t>(q) * qpitch;
+    const int padded   = (d + 15) / 16 * 16;
+    for (int t = threadIdx.x; t < padded; t += blockDim.x) { qbytes[t] = t < d ? src[t] : 0; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      long long a = 0;
+      for (int t = 0; t < d; ++t) {
+        const long long v = std::is_same<T, int8_t>::value ? static_cast<long long>(static_cast<int8_t>(qbytes[t]))
+                                                           : static_cast<long long>(qbytes[t]);
+        a += v * v;
+      }
+      s_qq_int = a;
+      s_qq     = __ll2double_rn(a);
+    }
+    __syncthreads();
+  } else {
+    load_queries<T>(queries, qpitch, &qi, 1, d, qd, d, &s_qq);
+  }
   const int n2 = max(next_pow2(static_cast<int>(c)), 2);
   const int32_t* mine = cand + static_cast<size_t>(blockIdx.x) * cap;
   for (int i = threadIdx.x; i < n2; i += blockDim.x) {
@@ -603,10 +672,14 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
     if (i < static_cast<int>(c)) {
       row = mine[i];
       if (admitted(adm, q, row)) {
-        Acc<METRIC, 1> acc;
-        acc.clear();
-        scan_row<T, METRIC, 1>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);
-        s = acc.result(0, s_qq);
+        if constexpr (kBytes) {
+          s = int_row_score<T, METRIC>(vectors + static_cast<size_t>(row) * pitch, d, reinterpret_cast<const uint4*>(qd), s_qq_int);
+        } else {
+          Acc<METRIC, 1> acc;
+          acc.clear();
+          scan_row<T, METRIC, 1>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);
+          s = acc.result(0, s_qq);
+        }
       }
     }
     sc[i]  = s;
@@ -1107,10 +1180,10 @@ void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, in
   }
 }
 
-void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, cudaStream_t s)
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s)
 {
   if (nq <= 0) { return; }
-  finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq);
+  finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq, step);
 }
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s)

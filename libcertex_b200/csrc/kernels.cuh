@@ -42,8 +42,9 @@ void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, in
                                size_t code_pitch, float n1max, float n2max, float emax, float* shift,
                                unsigned int* overflow, cudaStream_t s);
 
-/// thr [nq]: float keys of the k-th largest group maxima -> float bits of (value - shift), rounded down.
-void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, cudaStream_t s);
+/// thr [nq] of fp16 codes. step 0: float keys of the k-th largest group maxima -> keys of (value - shift / 2), scores
+/// that k rows certainly reach; step 1: such keys -> float bits of the screen's threshold (bound - shift / 2).
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s);
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s);
 

@@ -163,6 +163,37 @@ __device__ __forceinline__ float max32f_plus(const int32_t (&v)[32], const int32
   return fmaxf(m, n);
 }
 
+// Maximum of v[i] + e[i] over one chain of 16 columns.
+__device__ __forceinline__ int max16_plus(const int32_t* v, const int32_t* e)
+{
+  const int4* e4 = reinterpret_cast<const int4*>(e);
+  int m = kNeverInit * 2 + 1, n = m;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int4 t = e4[i];
+    m = addmax(v[4 * i], t.x, m);
+    n = addmax(v[4 * i + 1], t.y, n);
+    m = addmax(v[4 * i + 2], t.z, m);
+    n = addmax(v[4 * i + 3], t.w, n);
+  }
+  return max(m, n);
+}
+
+__device__ __forceinline__ float max16f_plus(const int32_t* v, const int32_t* e)
+{
+  const float4* e4 = reinterpret_cast<const float4*>(e);
+  float m = -CUDART_INF_F, n = m;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 t = e4[i];
+    m = fmaxf(m, __int_as_float(v[4 * i]) + t.x);
+    n = fmaxf(n, __int_as_float(v[4 * i + 1]) + t.y);
+    m = fmaxf(m, __int_as_float(v[4 * i + 2]) + t.z);
+    n = fmaxf(n, __int_as_float(v[4 * i + 3]) + t.w);
+  }
+  return fmaxf(m, n);
+}
+
 /// Monotone map of a float to an int32 (and back), so that integer selection kernels can rank floats.
 __device__ __forceinline__ int32_t float_key(float f)
 {
@@ -545,10 +576,30 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           break;
         }
         const int32_t* e = init_smem + er * kBaseTile + piece * kGroupRows;
-        const int m = F16 ? float_key(fmaxf(max32f_plus(a, e), max32f_plus(b, e + 32)))
-                          : max(max32_plus(a, e), max32_plus(b, e + 32));
-        if (q < p.nq) {
-          p.gmax[static_cast<size_t>(q) * p.ld_gmax + (cur.t - cur.col0) * (kBaseTile / kGroupRows) + piece] = m;
+        if (p.fine_groups) {
+          // one maximum per chain of 16 rows: four times as many groups, for labels too small for 2k groups of 64
+          int4 m4;
+          if (F16) {
+            m4.x = float_key(max16f_plus(a, e));
+            m4.y = float_key(max16f_plus(a + 16, e + 16));
+            m4.z = float_key(max16f_plus(b, e + 32));
+            m4.w = float_key(max16f_plus(b + 16, e + 48));
+          } else {
+            m4.x = max16_plus(a, e);
+            m4.y = max16_plus(a + 16, e + 16);
+            m4.z = max16_plus(b, e + 32);
+            m4.w = max16_plus(b + 16, e + 48);
+          }
+          if (q < p.nq) {
+            *reinterpret_cast<int4*>(p.gmax + static_cast<size_t>(q) * p.ld_gmax +
+                                     (cur.t - cur.col0) * (kBaseTile / kChainRows) + piece * 4) = m4;
+          }
+        } else {
+          const int m = F16 ? float_key(fmaxf(max32f_plus(a, e), max32f_plus(b, e + 32)))
+                            : max(max32_plus(a, e), max32_plus(b, e + 32));
+          if (q < p.nq) {
+            p.gmax[static_cast<size_t>(q) * p.ld_gmax + (cur.t - cur.col0) * (kBaseTile / kGroupRows) + piece] = m;
+          }
         }
       }
       // next unit; a finished tile's e values are released (GROUPMAX)

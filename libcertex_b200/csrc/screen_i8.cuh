@@ -60,6 +60,7 @@ struct ScreenArgs {
   const int* seg_col0;            // optional, per segment: the tile whose groups are columns 0..3 of gmax (else tile 0)
   int wide;                       // 1: rows of more than two K blocks; a segment then has at most two query tiles
   int plain_tiles;                // GROUPMAX: tile t is rows [256 t, 256 t + 256) of a 2-D map (else the 3-D anchor map)
+  int fine_groups;                // GROUPMAX: one maximum per 16 rows (16 columns of gmax per tile) instead of per 64 (4)
   int* err;                       // set to a non-zero code when a bounded wait gave up
 };
 

@@ -7,10 +7,39 @@ sorts on the CPU; here every rank contributes k (fp64 score, int64 id) pairs per
 gathered lists with a device kernel. No kernel reads another GPU's memory.
 """
 
+import contextlib
+import ctypes
+
 import torch
 import torch.distributed as dist
 
+from . import _lib as L
 from .index import Index, _need, merge_shards
+
+
+class _DeviceInts:
+    """int32 device memory that the library owns, seen through the CUDA array interface."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (int(n),), "typestr": "<i4", "data": (int(ptr), False), "version": 2}
+
+
+@contextlib.contextmanager
+def threshold_hook(fn):
+    """Inside the block every unfiltered screened search of the calling thread hands `fn` its thresholds once per batch
+    of queries, between the anchor pass and the screen: an int32 tensor of monotone keys (larger = tighter), one per
+    query, each a score that k rows of the searched shard certainly reach. `fn` may raise them in place."""
+
+    def call(_ctx, ptr, n, _stream):
+        # the library runs on torch's current stream, which is where fn's work is enqueued
+        fn(torch.as_tensor(_DeviceInts(ptr, n), device="cuda"))
+
+    c_hook = L.ThresholdHook(call)
+    L.check(L.lib().certexB200SetThresholdHook(c_hook, None))
+    try:
+        yield
+    finally:
+        L.check(L.lib().certexB200SetThresholdHook(ctypes.cast(None, L.ThresholdHook), None))
 
 
 def shard_bounds(n, world, rank):
@@ -33,15 +62,33 @@ class DistributedIndex:
     """One shard per rank of the process group. add_shard() takes this rank's rows and the global id of its first
     row; search() returns the same (distances, ids) on every rank."""
 
-    def __init__(self, dim, metric="l2", anchor_stride=16, group=None):
+    def __init__(self, dim, metric="l2", anchor_stride=16, group=None, share_thresholds=True):
         self.d, self.metric, self.group = dim, metric, group
         self.local = Index(dim, metric=metric, anchor_stride=anchor_stride)
         self.first = 0
+        self.share_thresholds = share_thresholds
+        self._all_screen = {}  # k -> every rank's search for k neighbours goes through the screen
 
     def add_shard(self, rows, first_id):
         self.local.add(rows)
         self.first = int(first_id)
+        self._all_screen.clear()
         return self
+
+    def _shared(self, k):
+        """Whether the ranks exchange thresholds for this k: the reference's first round (certex_shards.cu:136-141).
+        Any k rows of one shard bound the k-th neighbour of the whole set, so every rank may screen with the tightest
+        bound any rank found: the maximum of the keys, one all-reduce of n_queries int32 per batch. It needs every rank
+        to reach the hook, i.e. to screen; that is agreed once per k."""
+        if not self.share_thresholds or dist.get_world_size(self.group) == 1:
+            return False
+        if k not in self._all_screen:
+            mine = ctypes.c_int32(0)
+            L.check(L.lib().certexB200IndexWillScreen(self.local.core.handle, int(k), ctypes.byref(mine)))
+            flag = torch.tensor([mine.value], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            self._all_screen[k] = bool(flag.item())
+        return self._all_screen[k]
 
     def add(self, x):
         """x: the full set (same array on every rank); this rank keeps its contiguous shard."""
@@ -52,6 +99,10 @@ class DistributedIndex:
         _need(self.local.core is not None, "add vectors first")
         _need(k <= int(self.local.core.info().size), "every shard needs at least k vectors")
         Q = q.cuda().contiguous()
-        _, I, S = self.local.search(Q, k=k, batch=batch, return_scores=True, id_base=self.first)
+        if self._shared(k):
+            with threshold_hook(lambda keys: dist.all_reduce(keys, op=dist.ReduceOp.MAX, group=self.group)):
+                _, I, S = self.local.search(Q, k=k, batch=batch, return_scores=True, id_base=self.first)
+        else:
+            _, I, S = self.local.search(Q, k=k, batch=batch, return_scores=True, id_base=self.first)
         all_s, all_i = gather_lists(S, I, self.group)
         return merge_shards(Q.to(self.local.dtype), all_s, all_i, self.metric, return_scores=return_scores)

@@ -45,6 +45,50 @@ def test_device_merge_equals_oracle_merge_with_missing_entries():
     assert np.array_equal(I.cpu().numpy(), wi) and np.array_equal(S.cpu().numpy(), ws)
 
 
+@pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("float32", "l2"), ("float32", "cosine"), ("int8", "ip")])
+def test_thresholds_exchanged_between_shards(dtype, metric):
+    """The exchange a process group does with one all-reduce, replayed on one GPU: two shards, every shard's
+    thresholds raised to the maximum over both. The merged answer stays exact and fewer pairs survive the screens."""
+    from libcertex_b200 import distributed
+
+    x = synthetic.correlated(60000, 48, seed=21, dtype=dtype, unequal_norms=metric != "l2")
+    q = synthetic.correlated(300, 48, seed=22, dtype=dtype)
+    xt, qt = torch.from_numpy(x).cuda(), torch.from_numpy(q).cuda()
+    shards = [certex.Index(48, metric=metric), certex.Index(48, metric=metric)]
+    shards[0].add(xt[:30000])
+    shards[1].add(xt[30000:])
+    seen = [None, None]
+
+    def search_all(exchange):
+        lists, survivors = [], 0
+        for s, index in enumerate(shards):
+            def hook(keys, s=s):
+                if exchange:
+                    keys.copy_(torch.maximum(keys, seen[1 - s]))
+                else:
+                    seen[s] = keys.clone()
+            with distributed.threshold_hook(hook), certex.search_stats() as st:
+                _, I, S = index.search(qt, k=10, return_scores=True, id_base=30000 * s)
+            assert st.dense_queries == 0
+            survivors += st.survivors
+            lists.append((S, I))
+        S = torch.stack([l[0] for l in lists])
+        I = torch.stack([l[1] for l in lists])
+        _, Im, Sm = certex.merge_shards(qt, S, I, metric, return_scores=True)
+        return Im.cpu().numpy(), Sm.cpu().numpy(), survivors
+
+    ids, scores = oracle.knn(x, q, 10, metric)
+    I0, S0, n0 = search_all(exchange=False)
+    assert seen[0] is not None and seen[0].shape == (300,) and seen[0].dtype == torch.int32
+    I1, S1, n1 = search_all(exchange=True)
+    assert np.array_equal(I0, ids) and np.array_equal(S0, scores)
+    assert np.array_equal(I1, ids) and np.array_equal(S1, scores)
+    assert n1 < n0
+    with certex.search_stats() as st:  # the hook is gone after the block
+        shards[0].search(qt, k=10)
+    assert st.survivors > 0
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_one_process_per_gpu_over_nccl(tmp_path):
     script = tmp_path / "rank.py"
@@ -60,6 +104,12 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
         "D, I, S = idx.search(torch.from_numpy(q), k=10, return_scores=True)\n"
         "ids, scores = oracle.knn(x, q, 10, 'l2')\n"
         "assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores)\n"
+        "xf = synthetic.correlated(40000, 96, seed=5, dtype='float32'); qf = synthetic.correlated(100, 96, seed=6, dtype='float32')\n"
+        "for share in (True, False):\n"
+        "    fidx = distributed.DistributedIndex(96, metric='cosine', share_thresholds=share).add(torch.from_numpy(xf))\n"
+        "    D, I, S = fidx.search(torch.from_numpy(qf), k=20, return_scores=True)\n"
+        "    ids, scores = oracle.knn(xf, qf, 20, 'cosine')\n"
+        "    assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores)\n"
         "dist.barrier(); dist.destroy_process_group(); print('rank', rank, 'ok')\n"
     )
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
