@@ -100,7 +100,7 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
         "rank = int(os.environ['RANK']); torch.cuda.set_device(int(os.environ['LOCAL_RANK']))\n"
         "dist.init_process_group('nccl')\n"
         "x = synthetic.correlated(40000, 32, seed=3, dtype='uint8'); q = synthetic.correlated(100, 32, seed=4, dtype='uint8')\n"
-        "idx = distributed.DistributedIndex(32).add(torch.from_numpy(x))\n"
+        "idx = distributed.DistributedIndex(32, share_thresholds=True).add(torch.from_numpy(x))\n"
         "D, I, S = idx.search(torch.from_numpy(q), k=10, return_scores=True)\n"
         "ids, scores = oracle.knn(x, q, 10, 'l2')\n"
         "assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores)\n"
