@@ -12,13 +12,15 @@
 // with N = 128 the operand reads from shared memory cap the rate at about 60 % of peak).
 //   value[q][x] = <q, x> + e[x]
 //   e[x] = -floor(|x|^2 / 2) for L2, 0 for inner product, -2^30 for removed rows and padding
-// SCREEN keeps (q, x) iff value >= thr[q]. The stored rows are kept sorted by |x|^2 (per appended batch), so e is
-// almost constant over 16 adjacent rows and the epilogue never touches e per element: a thread (one query row, 64
+// SCREEN keeps every (q, x) with value >= thr[q]. The stored rows are kept sorted by |x|^2 (per appended batch), so e
+// is almost constant over 16 adjacent rows and the epilogue never touches e per element: a thread (one query row, 64
 // columns of the unit) takes the maximum of the raw products over each chain of 16 columns (3-input integer max, half
 // an instruction per element) and tests  max + cmax[chain] >= thr  with cmax = max of e over the chain. That test
-// never rejects a pair that should be kept. Only a chain that passes it (rare) is looked at element by element with
-// the exact e[x]; its survivors form one record (query, chain, 16-bit mask) in the warp's staging buffer in shared
-// memory, and a full buffer goes to global memory with one atomic add for the whole batch.
+// never rejects a pair that should be kept. Only in a chain that passes it (rare) the columns are looked at one by
+// one, still with cmax in place of their own e: what is kept is a superset of the pairs at or above the threshold,
+// larger by the few rows whose e is below their chain's maximum, and the exact scores of the verification sort those
+// out. The kept columns of a chain form one record (query, chain, 16-bit mask) in the warp's staging buffer in shared
+// memory, and a half-full buffer goes to global memory with one atomic add for the whole batch.
 // GROUPMAX writes gmax[q][group] = max over 64 anchors of value (exact, e is staged in shared memory with the tile);
 // the k-th largest group maximum of a query is its threshold: k distinct stored rows are at least that close. The
 // anchors of one tile are spread over the whole sorted set (column c of tile t is anchor c * n_tiles + t), so that the
@@ -235,7 +237,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   SharedCtl* ctl           = reinterpret_cast<SharedCtl*>(gen_base + ctl_off);
   const int32_t* init_smem = reinterpret_cast<const int32_t*>(gen_base + init_off);
   volatile int* abort_flag = &ctl->abort_flag;
-  constexpr bool kStageE   = MODE != kModeRate && !WIDE;  // e values travel with the stage and are read by the epilogue
+  constexpr bool kNeedE    = MODE == kModeGroupMax;   // only the group maxima need the exact e of every row
+  constexpr bool kStageE   = kNeedE && !WIDE;          // resident panel: e travels with the stage; WIDE: in its own ring
 
   const ScreenSeg* segs = ctl->segs;
   if (threadIdx.x < nseg) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
@@ -278,14 +281,16 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       for (int s = 0; s < nseg && !aborted; ++s) {
         const ScreenSeg sg = segs[s];
         for (int t = sg.t0; t < sg.t1 && !aborted; ++t, ++ts) {
-          const int er = ts % kERing;
-          if (ts >= kERing && !mbar_wait(smem_u32(&ctl->e_empty[er]), ((ts / kERing) - 1) & 1, abort_flag, p.err, 8)) {
-            aborted = true;
-            break;
+          if (kNeedE) {
+            const int er = ts % kERing;
+            if (ts >= kERing && !mbar_wait(smem_u32(&ctl->e_empty[er]), ((ts / kERing) - 1) & 1, abort_flag, p.err, 8)) {
+              aborted = true;
+              break;
+            }
+            mbar_arrive_expect_tx(smem_u32(&ctl->e_full[er]), kBaseTile * 4);
+            bulk_load_1d(base + init_off + er * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4,
+                         smem_u32(&ctl->e_full[er]));
           }
-          mbar_arrive_expect_tx(smem_u32(&ctl->e_full[er]), kBaseTile * 4);
-          bulk_load_1d(base + init_off + er * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4,
-                       smem_u32(&ctl->e_full[er]));
           for (int b = 0; b < kb; ++b, ++ks) {
             const int st = ks % ns;
             if (ks >= ns && !mbar_wait(smem_u32(&ctl->empty[st]), ((ks / ns) - 1) & 1, abort_flag, p.err, 2)) {
@@ -313,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           const long long t0 = clock64();
           while (!mbar_try_wait(smem_u32(&ctl->full[u % ns]), (u / ns) & 1) && clock64() - t0 < (1ll << 24)) {}
         }
-        for (int back = 1; back <= kERing && back <= ts; ++back) {
+        for (int back = 1; kNeedE && back <= kERing && back <= ts; ++back) {
           const int u        = ts - back;
           const long long t0 = clock64();
           while (!mbar_try_wait(smem_u32(&ctl->e_full[u % kERing]), (u / kERing) & 1) && clock64() - t0 < (1ll << 24)) {}
@@ -480,37 +485,29 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       if (lane == 0) { *rec_n = 0; }
       __syncwarp();
     };
-    // A chain of 16 columns that may hold survivors of this thread's query (the conservative test passed): the exact
-    // test per element; the survivors form one record, staged through the warp's buffer in shared memory (its fill
-    // count is a shared-memory atomic: the few threads that get here need no warp-wide step).
-    auto record = [&](const int32_t* v, int thr, int q, int64_t row0, const int32_t* e) {
-      uint32_t mask  = 0;
-      const int4* e4 = reinterpret_cast<const int4*>(e);
+    // A chain of 16 columns whose maximum reached the query's threshold with the chain's largest e: the columns that
+    // reach it with that same e form one record. (Rows are kept sorted by norm, so e is almost constant over a chain
+    // and hardly any row is kept that the exact e would drop; the exact scores sort that out.) The record is staged
+    // through the warp's buffer in shared memory, whose fill count is a shared-memory atomic: the few threads that get
+    // here need no warp-wide step.
+    auto record = [&](const int32_t* v, int thr, int ce, int q, int64_t row0) {
+      uint32_t mask = 0;
+      if (F16) {
+        const float tf = __int_as_float(thr), cf = __int_as_float(ce);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int4 t = e4[i];
-        if (F16) {
-          const float tf = __int_as_float(thr);
-          mask |= (__int_as_float(v[4 * i]) + __int_as_float(t.x) >= tf ? 1u : 0u) << (4 * i);
-          mask |= (__int_as_float(v[4 * i + 1]) + __int_as_float(t.y) >= tf ? 1u : 0u) << (4 * i + 1);
-          mask |= (__int_as_float(v[4 * i + 2]) + __int_as_float(t.z) >= tf ? 1u : 0u) << (4 * i + 2);
-          mask |= (__int_as_float(v[4 * i + 3]) + __int_as_float(t.w) >= tf ? 1u : 0u) << (4 * i + 3);
-        } else {
-          mask |= (v[4 * i] + t.x >= thr ? 1u : 0u) << (4 * i);
-          mask |= (v[4 * i + 1] + t.y >= thr ? 1u : 0u) << (4 * i + 1);
-          mask |= (v[4 * i + 2] + t.z >= thr ? 1u : 0u) << (4 * i + 2);
-          mask |= (v[4 * i + 3] + t.w >= thr ? 1u : 0u) << (4 * i + 3);
-        }
+        for (int i = 0; i < 16; ++i) { mask |= (__int_as_float(v[i]) + cf >= tf ? 1u : 0u) << i; }
+      } else {
+        const int t = thr - ce;  // no overflow: |thr|, |ce| <= 2^30 wherever a chain passed the test
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { mask |= (v[i] >= t ? 1u : 0u) << i; }
       }
-      if (mask != 0u) {
-        const uint64_t r = make_record(static_cast<uint32_t>(q), static_cast<uint32_t>(row0 / kChainRows), mask);
-        const int pos    = atomicAdd(const_cast<int*>(rec_n), 1);
-        if (pos < kRecBuf) {
-          rec_buf[pos] = r;
-        } else {  // the staging buffer is full: straight to global memory
-          const unsigned long long at = atomicAdd(p.rec_count, 1ull);
-          if (at < p.rec_cap) { p.rec[at] = r; }
-        }
+      const uint64_t r = make_record(static_cast<uint32_t>(q), static_cast<uint32_t>(row0 / kChainRows), mask);
+      const int pos    = atomicAdd(const_cast<int*>(rec_n), 1);
+      if (pos < kRecBuf) {
+        rec_buf[pos] = r;
+      } else {  // the staging buffer is full: straight to global memory
+        const unsigned long long at = atomicAdd(p.rec_count, 1ull);
+        if (at < p.rec_cap) { p.rec[at] = r; }
       }
     };
 
@@ -552,18 +549,11 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           h3 = max16(b + 16) + ce.w >= thr;
         }
         if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
-          // the exact e of the tile was staged with it
-          const int er = WIDE ? cur.ts % kERing : cur.ts % ns;
-          if (!mbar_wait(WIDE ? smem_u32(&ctl->e_full[er]) : smem_u32(&ctl->full[er]), (cur.ts / (WIDE ? kERing : ns)) & 1,
-                         abort_flag, p.err, 6)) {
-            break;
-          }
-          const int32_t* e   = init_smem + er * kBaseTile + piece * kGroupRows;
           const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
-          if (h0) { record(a, thr, q, row0, e); }
-          if (h1) { record(a + 16, thr, q, row0 + 16, e + 16); }
-          if (h2) { record(b, thr, q, row0 + 32, e + 32); }
-          if (h3) { record(b + 16, thr, q, row0 + 48, e + 48); }
+          if (h0) { record(a, thr, ce.x, q, row0); }
+          if (h1) { record(a + 16, thr, ce.y, q, row0 + 16); }
+          if (h2) { record(b, thr, ce.z, q, row0 + 32); }
+          if (h3) { record(b + 16, thr, ce.w, q, row0 + 48); }
           __syncwarp();
           const int staged = min(*rec_n, kRecBuf);
           if (staged > kRecBuf / 2) { flush(staged); }
@@ -606,7 +596,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       ++gu;
       if (++cur.j == cur.nqt) {
         cur.j = 0;
-        if (kStageE || WIDE) {
+        if (kNeedE) {
           __syncwarp();
           if (lane == 0) { mbar_arrive(WIDE ? smem_u32(&ctl->e_empty[cur.ts % kERing]) : smem_u32(&ctl->empty[cur.ts % ns])); }
         }
