@@ -520,20 +520,56 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
     if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(0x80000000u); }
     return;
   }
+  // The row goes to shared memory (when it fits) and its smallest and largest key are found on the way: the radix walk
+  // then runs on key - smallest and starts at the highest byte in which the keys differ. Group maxima of one query lie
+  // close together; walking all 32 bits would put nearly every value into one bin of the first passes, and the
+  // shared-memory atomics on that bin would serialise.
+  __shared__ uint32_t s_lo, s_hi;
+  if (threadIdx.x == 0) {
+    s_lo = 0xffffffffu;
+    s_hi = 0u;
+  }
+  __syncthreads();
+  uint32_t lo = 0xffffffffu, hi = 0u;
+  auto see = [&](int32_t v) {
+    const uint32_t key = static_cast<uint32_t>(v) ^ 0x80000000u;
+    lo                 = min(lo, key);
+    hi                 = max(hi, key);
+  };
   if (in_smem) {
     const int n4 = ng >> 2;  // rows start 16-byte aligned (ld is a multiple of 8)
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      reinterpret_cast<int4*>(row_smem)[i] = __ldg(reinterpret_cast<const int4*>(row) + i);
+      const int4 v                         = __ldg(reinterpret_cast<const int4*>(row) + i);
+      reinterpret_cast<int4*>(row_smem)[i] = v;
+      see(v.x), see(v.y), see(v.z), see(v.w);
     }
-    for (int i = (n4 << 2) + threadIdx.x; i < ng; i += blockDim.x) { row_smem[i] = row[i]; }
+    for (int i = (n4 << 2) + threadIdx.x; i < ng; i += blockDim.x) {
+      row_smem[i] = row[i];
+      see(row_smem[i]);
+    }
     row = row_smem;
+  } else {
+    for (int i = threadIdx.x; i < ng; i += blockDim.x) { see(row[i]); }
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicMin(&s_lo, lo);
+    atomicMax(&s_hi, hi);
+  }
+  __syncthreads();
+  const uint32_t base  = s_lo;
+  const uint32_t range = s_hi - base;
+  const int top        = range == 0u ? 0 : 32 - __clz(range);  // bits in which key - base can be set
   uint32_t prefix = 0, mask = 0, remaining = static_cast<uint32_t>(k);
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  for (int shift = ((top + 7) / 8 - 1) * 8; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) { hist[i] = 0; }
     __syncthreads();
     for (int i = threadIdx.x; i < ng; i += blockDim.x) {
-      const uint32_t key = static_cast<uint32_t>(row[i]) ^ 0x80000000u;
+      const uint32_t key = (static_cast<uint32_t>(row[i]) ^ 0x80000000u) - base;
       if ((key & mask) == prefix) { atomicAdd(&hist[(key >> shift) & 255u], 1u); }
     }
     __syncthreads();
@@ -570,7 +606,7 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
     remaining = s_remaining;
     mask |= 0xffu << shift;
   }
-  if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(prefix ^ 0x80000000u); }
+  if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>((prefix + base) ^ 0x80000000u); }
 }
 
 // Exact score of an 8-bit row against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot
