@@ -266,6 +266,8 @@ def main():
                 "unit": "TFLOP/s", "frac": None if achieved is None else achieved / peak, "traffic": None,
                 "note": f"int8 tensor ops (2 x nq x rows x 128) / CUDA-event time of the screen passes on rank 0; "
                         f"peak = 2 x the {pk['source']} sustained bf16 cuBLAS rate (int8 nominal is twice bf16)",
+                "traffic_note": "not captured at full size; a 2048-query x 1M-row launch moved 251 MB of DRAM traffic "
+                                "under ncu, 0.65 x its algorithmic bytes (query panels share rows in L2)",
                 "screen_ms_per_step": st.screen_ms / args.steps, "anchor_ms_per_step": st.anchor_ms / args.steps,
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},

@@ -287,6 +287,16 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const vo
 CERTEX_B200_EXPORT cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
                                                       int32_t grid, int32_t* out);
 
+/** Test hook (host only): the work split of a routed pass (searches by label). Run r pairs n_query_tiles[r] query
+ *  tiles with its own n_base_tiles[r] base tiles; runs follow one another in both directions. segs receives 5 ints
+ *  per segment (first query tile, query tiles <= panel_tiles, first base tile, end base tile, first base tile of the
+ *  run), *n_segs their number (at most cap_segs), seg_begin [grid + 1] the range of every CTA (at most max_segs
+ *  segments each), *runs_done how many runs fit (the rest waits for another pass). */
+CERTEX_B200_EXPORT cuvsError_t certexB200PlanRouted(int32_t n_runs, const int32_t* n_query_tiles,
+                                                    const int32_t* n_base_tiles, int32_t panel_tiles, int32_t grid,
+                                                    int32_t max_segs, int32_t* segs, int32_t cap_segs, int32_t* n_segs,
+                                                    int32_t* seg_begin, int32_t* runs_done);
+
 /**
  * Exact search that allocates no device memory. It has no counterpart in the reference, whose searches take their
  * temporaries from a memory pool. It exists for callers that cannot allocate on the GPU at search time: a process in

@@ -110,7 +110,7 @@ SYMBOLS = [
     "certexB200SearchEx", "certexB200MergeShards", "certexB200IndexGetInfo", "certexB200IndexReserve",
     "certexB200StatsBegin", "certexB200StatsEnd", "certexB200IndexSetTestMode", "certexB200ScreenRaw",
     "certexB200PlanSegments", "certexB200SearchStatic", "certexB200Version",
-    "certexB200SetThresholdHook", "certexB200IndexWillScreen",
+    "certexB200SetThresholdHook", "certexB200IndexWillScreen", "certexB200PlanRouted",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -174,6 +174,9 @@ def lib():
                     ctypes.c_uint32, P(ctypes.c_float),
                 ]
                 L.certexB200PlanSegments.argtypes = [ctypes.c_int32] * 4 + [P(ctypes.c_int32)]
+                L.certexB200PlanRouted.argtypes = [ctypes.c_int32, P(ctypes.c_int32), P(ctypes.c_int32), ctypes.c_int32,
+                                                   ctypes.c_int32, ctypes.c_int32, P(ctypes.c_int32), ctypes.c_int32,
+                                                   P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32)]
                 L.certexB200SearchStatic.argtypes = [vp, ctypes.c_int, DLDataType, vp, i64, vp, i64, i64, ctypes.c_int32, vp, vp]
                 _lib = L
     return _lib

@@ -1313,6 +1313,33 @@ void merge_shards(const Resources& res, const double* scores, const int64_t* ids
   CERTEX_CUDA(cudaGetLastError());
 }
 
+int plan_routed_flat(int n_runs, const int32_t* n_query_tiles, const int32_t* n_base_tiles, int panel_tiles, int grid,
+                     int max_segs, int32_t* segs_out, int cap_segs, int32_t* n_segs, int32_t* seg_begin)
+{
+  std::vector<LabelRun> runs(static_cast<size_t>(n_runs));
+  std::vector<int> q_tile0(static_cast<size_t>(n_runs));
+  int64_t tile = 0, slot = 0;
+  for (int r = 0; r < n_runs; ++r) {
+    runs[r].queries.assign(static_cast<size_t>(n_query_tiles[r]) * kQTile, 0);
+    runs[r].n_in_part = static_cast<int64_t>(n_base_tiles[r]) * kTile;
+    runs[r].tile0     = tile;
+    q_tile0[r]        = static_cast<int>(slot);
+    tile += n_base_tiles[r];
+    slot += n_query_tiles[r];
+  }
+  std::vector<ScreenSeg> segs;
+  std::vector<int> col0, begin;
+  const size_t done = plan_routed(runs, 0, runs.size(), q_tile0, panel_tiles, grid, max_segs, segs, col0, begin);
+  CERTEX_EXPECTS(static_cast<int>(segs.size()) <= cap_segs, "certex: more segments than the output holds");
+  for (size_t i = 0; i < segs.size(); ++i) {
+    segs_out[5 * i + 0] = segs[i].q_tile0, segs_out[5 * i + 1] = segs[i].n_qtiles;
+    segs_out[5 * i + 2] = segs[i].t0, segs_out[5 * i + 3] = segs[i].t1, segs_out[5 * i + 4] = col0[i];
+  }
+  *n_segs = static_cast<int32_t>(segs.size());
+  for (int b = 0; b <= grid; ++b) { seg_begin[b] = begin[static_cast<size_t>(b)]; }
+  return static_cast<int>(done);
+}
+
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out)
 {
   CERTEX_EXPECTS(nqt >= 1 && nt >= 1 && panel_tiles >= 1 && grid >= 1, "certex: sizes must be positive");

@@ -214,6 +214,13 @@ void merge_shards(const Resources& res, const double* scores, const int64_t* ids
 /// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);
 
+/// Host-side work split of a routed pass (searches by label): run r pairs n_query_tiles[r] query tiles with its own
+/// n_base_tiles[r] base tiles (runs are laid out one after the other in both directions). Writes the segments (5 ints
+/// each: first query tile, query tiles, first base tile, end base tile, first base tile of the run), their number and
+/// the per-CTA ranges seg_begin [grid + 1]; returns how many runs fit.
+int plan_routed_flat(int n_runs, const int32_t* n_query_tiles, const int32_t* n_base_tiles, int panel_tiles, int grid,
+                     int max_segs, int32_t* segs_out, int cap_segs, int32_t* n_segs, int32_t* seg_begin);
+
 /// The tensor-core pass alone on caller buffers (see certexB200ScreenRaw in the public header). Synchronises.
 void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n, int64_t code_len,
                 bool is_signed, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,

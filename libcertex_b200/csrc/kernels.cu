@@ -196,6 +196,24 @@ __device__ void bitonic_sort(double* s, IdT* id, int n2)
   __syncthreads();
 }
 
+// In-place bitonic sort of n2 (a power of two) 64-bit keys in shared memory, ascending.
+__device__ void bitonic_sort_keys(unsigned long long* key, int n2)
+{
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < (n2 >> 1); i += blockDim.x) {
+        const int lo                 = 2 * i - (i & (stride - 1));
+        const int hi                 = lo + stride;
+        const unsigned long long a   = key[lo], b = key[hi];
+        const bool asc               = (lo & size) == 0;
+        if (asc ? b < a : a < b) { key[lo] = b, key[hi] = a; }
+      }
+    }
+  }
+  __syncthreads();
+}
+
 __device__ __forceinline__ unsigned long long ordered_key(double v)
 {
   const unsigned long long b = static_cast<unsigned long long>(__double_as_longlong(v));
@@ -612,10 +630,10 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
 // Exact score of an 8-bit row against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot
 // products (int32 is enough: 255^2 * 4096 < 2^31), the score |q|^2 + |x|^2 - 2 <q, x> (L2) or |q|^2 - 2 <q, x> in
 // int64. Every partial sum of the fp64 loop over the coordinates is an integer below 2^53, so that loop returns this
-// very integer: the results are bit-identical, without one conversion to double per coordinate.
+// very integer: the results are bit-identical, without one conversion to double per coordinate. |score| < 2^31.
 // qb: the query's bytes in shared memory, zero padded to whole 16-byte vectors like the stored row.
 template <typename T, int METRIC>
-__device__ __forceinline__ double int_row_score(const uint8_t* row, int d, const uint4* qb, long long qq)
+__device__ __forceinline__ long long int_row_score(const uint8_t* row, int d, const uint4* qb, long long qq)
 {
   const uint4* p  = reinterpret_cast<const uint4*>(row);
   const int n_vec = (d + 15) / 16;
@@ -647,8 +665,7 @@ __device__ __forceinline__ double int_row_score(const uint8_t* row, int d, const
       }
     }
   }
-  const long long s = qq + static_cast<long long>(xx) - 2ll * static_cast<long long>(ip);
-  return __ll2double_rn(s);
+  return qq + static_cast<long long>(xx) - 2ll * static_cast<long long>(ip);
 }
 
 // ------------------------------------------------------------------------------------------- verify + select
@@ -702,26 +719,47 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
   }
   const int n2 = max(next_pow2(static_cast<int>(c)), 2);
   const int32_t* mine = cand + static_cast<size_t>(blockIdx.x) * cap;
-  for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-    double s    = CUDART_INF;
-    int32_t row = 0x7fffffff;
-    if (i < static_cast<int>(c)) {
-      row = mine[i];
-      if (admitted(adm, q, row)) {
-        if constexpr (kBytes) {
-          s = int_row_score<T, METRIC>(vectors + static_cast<size_t>(row) * pitch, d, reinterpret_cast<const uint4*>(qd), s_qq_int);
-        } else {
+  if constexpr (kBytes) {
+    // integer scores (below 2^31 in magnitude) and ids sort as one 64-bit key: (score + 2^31) << 32 | id
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(sc);
+    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+      unsigned long long key = ~0ull;
+      if (i < static_cast<int>(c)) {
+        const int32_t row = mine[i];
+        if (admitted(adm, q, row)) {
+          const long long v = int_row_score<T, METRIC>(vectors + static_cast<size_t>(row) * pitch, d,
+                                                      reinterpret_cast<const uint4*>(qd), s_qq_int);
+          key = (static_cast<unsigned long long>(v + 2147483648ll) << 32) | static_cast<uint32_t>(row);
+        }
+      }
+      keys[i] = key;
+    }
+    bitonic_sort_keys(keys, n2);
+    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+      const unsigned long long key = keys[i];
+      const bool have              = key != ~0ull;  // sc[i] occupies the bytes of keys[i]: read, then overwritten, by this thread
+      sc[i]  = have ? __ll2double_rn(static_cast<long long>(key >> 32) - 2147483648ll) : CUDART_INF;
+      ids[i] = have ? static_cast<int32_t>(key & 0xffffffffull) : 0x7fffffff;
+    }
+    __syncthreads();
+  } else {
+    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+      double s    = CUDART_INF;
+      int32_t row = 0x7fffffff;
+      if (i < static_cast<int>(c)) {
+        row = mine[i];
+        if (admitted(adm, q, row)) {
           Acc<METRIC, 1> acc;
           acc.clear();
           scan_row<T, METRIC, 1>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);
           s = acc.result(0, s_qq);
         }
       }
+      sc[i]  = s;
+      ids[i] = row;
     }
-    sc[i]  = s;
-    ids[i] = row;
+    bitonic_sort(sc, ids, n2);
   }
-  bitonic_sort(sc, ids, n2);
   if (over) {
     __syncthreads();
     if (threadIdx.x == 0) {

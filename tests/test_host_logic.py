@@ -38,6 +38,46 @@ def test_plan_segments_covers_every_unit_once(built_library, nqt, nt, panel, gri
     assert max(units) - nqt * nt / grid <= panel
 
 
+@pytest.mark.parametrize(
+    "runs,panel,grid,max_segs",
+    [([(2, 62)] * 64, 2, 148, 64),                      # 64 labels, two query tiles and 62 base tiles each
+     ([(1, 3)] * 300 + [(4, 3)], 7, 148, 64),           # many small labels, one with several query tiles
+     ([(9, 500), (1, 1), (2, 40)], 2, 148, 64),         # more query tiles than a panel holds
+     ([(1, 5)] * 40, 7, 3, 4),                          # few CTAs with few slots: not everything fits one pass
+     ([(3, 1000)], 2, 7, 64), ([(1, 1)], 7, 148, 64)],
+)
+def test_plan_routed_covers_every_unit_of_the_runs_it_takes(built_library, runs, panel, grid, max_segs):
+    n = len(runs)
+    nqt = (ctypes.c_int32 * n)(*[r[0] for r in runs])
+    nt = (ctypes.c_int32 * n)(*[r[1] for r in runs])
+    cap = 100000
+    segs = (ctypes.c_int32 * (5 * cap))()
+    n_segs, done = ctypes.c_int32(), ctypes.c_int32()
+    begin = (ctypes.c_int32 * (grid + 1))()
+    assert built_library.certexB200PlanRouted(n, nqt, nt, panel, grid, max_segs, segs, cap, ctypes.byref(n_segs), begin,
+                                              ctypes.byref(done)) == 1
+    done, n_segs = done.value, n_segs.value
+    assert 1 <= done <= n and (done == n or grid * max_segs < 10 * n)
+    seg = np.frombuffer(segs, dtype=np.int32)[: 5 * n_segs].reshape(n_segs, 5)
+    begin = np.frombuffer(begin, dtype=np.int32)
+    assert begin[0] == 0 and begin[-1] == n_segs and (np.diff(begin) >= 0).all() and (np.diff(begin) <= max_segs).all()
+    q0 = np.concatenate([[0], np.cumsum([r[0] for r in runs])])
+    t0 = np.concatenate([[0], np.cumsum([r[1] for r in runs])])
+    cover = {}
+    for a, w, lo, hi, col0 in seg:
+        r = int(np.searchsorted(t0, lo, side="right") - 1)  # the run this segment belongs to
+        assert r < done and col0 == t0[r] and 1 <= w <= panel
+        assert q0[r] <= a and a + w <= q0[r + 1] and t0[r] <= lo < hi <= t0[r + 1]
+        for qt in range(a, a + w):
+            for t in range(lo, hi):
+                cover[(qt, t)] = cover.get((qt, t), 0) + 1
+    want = sum(runs[r][0] * runs[r][1] for r in range(done))
+    assert len(cover) == want and all(v == 1 for v in cover.values())
+    if done == n:  # balanced: no CTA but the last (which takes what is left) is more than a panel above its share
+        units = [sum(int(w) * int(hi - lo) for a, w, lo, hi, _ in seg[begin[b] : begin[b + 1]]) for b in range(grid)]
+        assert max(units[:-1], default=0) <= -(-want // grid) + panel
+
+
 def test_shard_bounds_partition_rows():
     for n, world in [(10_000_000, 8), (1001, 3), (7, 7), (5, 2)]:
         bounds = [distributed.shard_bounds(n, world, r) for r in range(world)]
