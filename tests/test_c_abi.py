@@ -56,6 +56,36 @@ def test_errors_are_reported_not_raised(built_library):
         assert L.cuvsGetLastErrorText()
 
 
+def _build_c_caller(tmp_path):
+    """tests/c/exact_search.c compiled as C11 with gcc against the public header and linked to the library."""
+    import shutil
+    import subprocess
+
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    lib_dir = os.path.join(ROOT, "libcertex_b200", "lib")
+    exe = str(tmp_path / "exact_search_c")
+    cmd = [shutil.which("gcc") or "gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-O1",
+           "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(cuda, "include"),
+           os.path.join(ROOT, "tests", "c", "exact_search.c"), "-o", exe, "-L" + lib_dir, "-lcertex_b200",
+           "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-Wl,-rpath," + lib_dir]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    return exe
+
+
+def test_header_is_plain_c_and_a_c_caller_links(built_library, tmp_path):
+    _build_c_caller(tmp_path)
+
+
+@pytest.mark.gpu
+def test_c_caller_gets_exact_answers(built_library, tmp_path):
+    import subprocess
+
+    exe = _build_c_caller(tmp_path)
+    r = subprocess.run([exe, str(tmp_path / "index.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", (r.returncode, r.stdout[-500:], r.stderr[-2000:])
+
+
 @pytest.mark.gpu
 def test_plain_c_call_sequence(tmp_path):
     from oracle import oracle
