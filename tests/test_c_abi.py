@@ -67,7 +67,8 @@ def _build_c_caller(tmp_path):
     cmd = [shutil.which("gcc") or "gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-O1",
            "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(cuda, "include"),
            os.path.join(ROOT, "tests", "c", "exact_search.c"), "-o", exe, "-L" + lib_dir, "-lcertex_b200",
-           "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-Wl,-rpath," + lib_dir]
+           "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-Wl,-rpath," + lib_dir,
+           "-Wl,-rpath," + os.path.join(cuda, "lib64")]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
     return exe
