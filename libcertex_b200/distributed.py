@@ -48,14 +48,17 @@ def shard_bounds(n, world, rank):
 
 
 def gather_lists(scores, ids, group=None):
-    """All-gather of per-rank answer lists: ([world, nq, k] scores, [world, nq, k] ids) on every rank."""
+    """All-gather of per-rank answer lists: ([world, nq, k] scores, [world, nq, k] ids) on every rank. The fp64 scores
+    travel as their int64 bit patterns next to the ids, so that one collective moves both."""
     world = dist.get_world_size(group)
     nq, k = scores.shape
-    all_s = torch.empty((world * nq, k), dtype=scores.dtype, device=scores.device)  # rank-major concatenation
-    all_i = torch.empty((world * nq, k), dtype=ids.dtype, device=ids.device)
-    dist.all_gather_into_tensor(all_s, scores.contiguous(), group=group)
-    dist.all_gather_into_tensor(all_i, ids.contiguous(), group=group)
-    return all_s.view(world, nq, k), all_i.view(world, nq, k)
+    mine = torch.empty((2, nq, k), dtype=torch.int64, device=scores.device)
+    mine[0] = scores.contiguous().view(torch.int64)
+    mine[1] = ids
+    both = torch.empty((world * 2 * nq, k), dtype=torch.int64, device=scores.device)  # rank-major concatenation
+    dist.all_gather_into_tensor(both, mine.view(2 * nq, k), group=group)
+    both = both.view(world, 2, nq, k)
+    return both[:, 0].contiguous().view(torch.float64), both[:, 1].contiguous()
 
 
 class DistributedIndex:
