@@ -51,3 +51,20 @@ def test_one_call_topk_large_k_bf16_with_outliers():
     assert np.isfinite(kf).all()
     want = exact_topk(kf, qf, 2048, 2)
     assert np.array_equal(ids.cpu().numpy(), want)
+
+
+def test_keys_appended_after_the_partition_are_found():
+    """A few keys appended after the cache was partitioned by head stay outside the partition (it is renewed once an
+    eighth of the keys is newer); they are scored next to the partitioned keys of their head."""
+    g = torch.Generator().manual_seed(2)
+    n_kv, n_heads, d, m, k = 2, 4, 32, 6, 20
+    keys = torch.randn(n_kv, 9000, d, generator=g).half()
+    q = torch.randn(n_heads, m, d, generator=g).half()
+    cache = certex.KeyCache(n_kv, d, k=k)
+    cache.append(keys[:, :8500].cuda())
+    for lo in range(8500, 9000, 100):  # decoding steps
+        cache.append(keys[:, lo : lo + 100].cuda())
+    assert cache.index.info()["n_partitioned"] < 2 * 9000
+    scores, ids = cache.topk(q.cuda())
+    want = exact_topk(keys.numpy(), q.numpy(), k, n_heads // n_kv)
+    assert np.array_equal(ids.cpu().numpy(), want)

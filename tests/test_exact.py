@@ -173,6 +173,17 @@ def test_overflowing_candidate_lists_are_screened_again_then_searched_densely(dt
     check(index, x, q, 10, metric)
 
 
+@pytest.mark.parametrize("dtype,dim,metric", [("uint8", 300, "l2"), ("float32", 200, "cosine")])
+def test_second_pass_on_rows_of_several_k_blocks(dtype, dim, metric):
+    x, q = make(20000, dim, 150, dtype, metric != "l2", 0)
+    index = certex.Index(dim, metric=metric)
+    index.add(x)
+    index._test_mode(2, cap=64)
+    with certex.search_stats() as st:
+        check(index, x, q, 10, metric)
+    assert st.rescreened > 0
+
+
 def test_dense_path_on_long_rows():
     """Rows longer than 2^18 are selected from in chunks by separate blocks and merged; ties across chunks go to the
     smaller id."""

@@ -156,6 +156,22 @@ def test_routed_pass_with_many_labels_and_uneven_query_counts(n):
     assert st.routed_queries > 400
 
 
+def test_more_queries_of_one_label_than_a_routed_pass_takes():
+    """36 000 queries of one label (a routed pass holds 32 768 query slots) and 1 000 of another."""
+    n, dim = 200000, 16
+    x = synthetic.correlated(n, dim, seed=41, dtype="uint8")
+    q = synthetic.correlated(37000, dim, seed=42, dtype="uint8")
+    rng = np.random.default_rng(43)
+    lab = rng.integers(0, 2, n).astype(np.int32)
+    ql = np.zeros(37000, dtype=np.int32)
+    ql[rng.choice(37000, 1000, replace=False)] = 1
+    index = certex.Index(dim)
+    index.add(x, labels=lab)
+    with certex.search_stats() as st:
+        same(index, x, q, 10, row_labels=lab, query_labels=ql, labels=ql)
+    assert st.routed_queries >= 37000
+
+
 def test_label_partition_small_labels_and_large_k():
     """Labels with fewer than k vectors pad with -1; one query per label; labels that are not consecutive numbers."""
     x, q = data(6000, 16, 64, "uint8", seed=13)
