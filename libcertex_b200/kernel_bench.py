@@ -34,6 +34,10 @@ def main():
     init = torch.full((n_pad,), -(1 << 30), dtype=torch.int32, device="cuda")
     for i in range(0, n, 1 << 20):  # chunked: the int64 squares of a large x would not fit
         init[i : i + (1 << 20)][: min(1 << 20, n - i)] = -((x[i : i + (1 << 20)].long() ** 2).sum(1) >> 1).int()
+    # rows in the order the engine keeps them: sorted by norm, so that e is almost constant over a chain of 16 rows
+    order = torch.argsort(init[:n], descending=True, stable=True)
+    x = x[order].contiguous()
+    init[:n] = init[:n][order]
     ld = -(-(n_pad // 64) // 8) * 8
     need_gmax = args.mode == "groupmax" or args.survivors > 0
     gmax = torch.zeros((nq if need_gmax else 1, ld), dtype=torch.int32, device="cuda")
