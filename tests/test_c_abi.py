@@ -74,8 +74,39 @@ def _build_c_caller(tmp_path):
     return exe
 
 
+def _build_cpp_caller(tmp_path):
+    """tests/cpp/exact_search.cpp compiled as C++17 with g++ against include/certex_b200.hpp."""
+    import shutil
+    import subprocess
+
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    lib_dir = os.path.join(ROOT, "libcertex_b200", "lib")
+    exe = str(tmp_path / "exact_search_cpp")
+    cmd = [shutil.which("g++") or "g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-O1",
+           "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(cuda, "include"),
+           os.path.join(ROOT, "tests", "cpp", "exact_search.cpp"), "-o", exe, "-L" + lib_dir, "-lcertex_b200",
+           "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-Wl,-rpath," + lib_dir,
+           "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    return exe
+
+
 def test_header_is_plain_c_and_a_c_caller_links(built_library, tmp_path):
     _build_c_caller(tmp_path)
+
+
+def test_cpp_header_compiles_and_a_cpp_caller_links(built_library, tmp_path):
+    _build_cpp_caller(tmp_path)
+
+
+@pytest.mark.gpu
+def test_cpp_caller_gets_exact_answers(built_library, tmp_path):
+    import subprocess
+
+    exe = _build_cpp_caller(tmp_path)
+    r = subprocess.run([exe, str(tmp_path / "index.bin")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", (r.returncode, r.stdout[-500:], r.stderr[-2000:])
 
 
 @pytest.mark.gpu
