@@ -781,12 +781,30 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     std::vector<int> col0, seg_begin;
     r1 = r0 + plan_routed(routed, r0, r1, q_tile0, shape.panel_tiles, grid, 64, segs, col0, seg_begin);
     CERTEX_EXPECTS(r1 > r0, "certex: internal error: a label's queries do not fit one routed pass");
+    // The thresholds of a large label come from its leading tiles only (its rows are in id order: a sample like any
+    // other, and the group maxima of any subset of rows are valid): at least 1024 tiles (smaller labels take part
+    // whole: every tile left out costs survivors, and their exact scores cost more than the tile), enough tiles for
+    // 2k groups, for a sixteenth of the label, and for candidate lists that stay within half their capacity (about
+    // 1.2 k rows per sampled fraction).
+    const uint32_t cap = static_cast<uint32_t>(std::max(2048, 2 * k));
+    std::vector<LabelRun> heads(routed.begin() + static_cast<std::ptrdiff_t>(r0), routed.begin() + static_cast<std::ptrdiff_t>(r1));
+    for (LabelRun& h : heads) {
+      const int64_t nt     = (h.n_in_part + kTile - 1) / kTile;
+      const int64_t enough = (2 * static_cast<int64_t>(k) + per_tile - 1) / per_tile;
+      const int64_t by_cap = (24 * static_cast<int64_t>(k) * nt + 10 * cap - 1) / (10 * static_cast<int64_t>(cap));
+      const int64_t take   = std::min(nt, std::max({int64_t(1024), enough, (nt + 15) / 16, by_cap}));
+      h.n_in_part          = std::min(h.n_in_part, take * kTile);
+    }
+    std::vector<ScreenSeg> segs_g;
+    std::vector<int> col0_g, seg_begin_g;
+    const size_t fit = plan_routed(heads, 0, heads.size(), q_tile0, shape.panel_tiles, grid, 64, segs_g, col0_g, seg_begin_g);
+    CERTEX_EXPECTS(fit == heads.size(), "certex: internal error: the threshold pass of a routed search does not fit");
     n_slots = 0;
     std::vector<int32_t> slot_query, slot_ng;
     int64_t max_tiles = 0;
     for (size_t r = r0; r < r1; ++r) {
       const LabelRun& run = routed[r];
-      const int64_t nt    = (run.n_in_part + kTile - 1) / kTile;
+      const int64_t nt    = (heads[r - r0].n_in_part + kTile - 1) / kTile;  // tiles that take part in the thresholds
       const int64_t add   = round_up(static_cast<int64_t>(run.queries.size()), kQTile);
       for (int64_t i = 0; i < add; ++i) {
         const bool real = i < static_cast<int64_t>(run.queries.size());
@@ -803,13 +821,15 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     const size_t cp      = code_pitch_;
     const int n_groups   = static_cast<int>(max_tiles) * per_tile;
     const int64_t ld_g   = round_up(n_groups, 8);
-    const uint32_t cap   = static_cast<uint32_t>(std::max(2048, 2 * k));
     const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(ns) * cap);
     int32_t* d_slot_q    = scratch.get<int32_t>(static_cast<size_t>(ns));
     int32_t* d_slot_ng   = scratch.get<int32_t>(static_cast<size_t>(ns));
     ScreenSeg* d_segs    = scratch.get<ScreenSeg>(segs.size());
     int* d_col0          = scratch.get<int>(col0.size());
     int* d_seg_begin     = scratch.get<int>(seg_begin.size());
+    ScreenSeg* d_segs_g  = scratch.get<ScreenSeg>(segs_g.size());  // the threshold pass: leading tiles of every label
+    int* d_col0_g        = scratch.get<int>(col0_g.size());
+    int* d_seg_begin_g   = scratch.get<int>(seg_begin_g.size());
     uint8_t* q_rows      = scratch.get<uint8_t>(static_cast<size_t>(ns) * (f16 ? qpitch : cp));  // the queries in slot order
     uint8_t* q_codes     = f16 ? scratch.get<uint8_t>(static_cast<size_t>(ns) * cp) : q_rows;
     float* shift         = f16 ? scratch.get<float>(static_cast<size_t>(ns)) : nullptr;
@@ -830,6 +850,9 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), h2d, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(d_col0, col0.data(), col0.size() * sizeof(int), h2d, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, seg_begin.data(), seg_begin.size() * sizeof(int), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_segs_g, segs_g.data(), segs_g.size() * sizeof(ScreenSeg), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_col0_g, col0_g.data(), col0_g.size() * sizeof(int), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin_g, seg_begin_g.data(), seg_begin_g.size() * sizeof(int), h2d, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * ns, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
     CERTEX_CUDA(cudaMemsetAsync(d_flag, 0, 4 * sizeof(unsigned int), res.stream));
@@ -854,9 +877,9 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     a.q_signed    = dtype_ == kI8 ? 1u : 0u;
     a.x_signed    = a.q_signed;
     a.err         = reinterpret_cast<int*>(d_flag + 1);
-    a.segs        = d_segs;
-    a.seg_begin   = d_seg_begin;
-    a.seg_col0    = d_col0;
+    a.segs        = d_segs_g;
+    a.seg_begin   = d_seg_begin_g;
+    a.seg_col0    = d_col0_g;
     a.plain_tiles = 1;
     a.fine_groups = fine ? 1 : 0;
     a.init        = linit_;
@@ -883,8 +906,11 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
       launch_finish_thr_f16(thr, shift, ns, 1, res.stream);
     }
     CERTEX_CUDA(cudaGetLastError());
-    // 3 screen, 4 exact scores of the candidates
+    // 3 screen over all tiles of every label, 4 exact scores of the candidates
     a.mode      = kModeScreen;
+    a.segs      = d_segs;
+    a.seg_begin = d_seg_begin;
+    a.seg_col0  = d_col0;
     a.cmax      = lcmax_;
     a.thr       = thr;
     a.rec       = rec;

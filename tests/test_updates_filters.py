@@ -187,13 +187,16 @@ def test_label_partition_small_labels_and_large_k():
 
 
 def test_label_partition_long_labels():
-    """Two labels of about 300 000 vectors each: score rows long enough to be selected from in chunks."""
+    """Two labels of about 300 000 vectors each (1 172 tiles: the thresholds come from the leading 1 024); with the
+    dense label groups the score rows are long enough to be selected from in chunks."""
     x, q = data(600000, 8, 24, "uint8", seed=15)
     rng = np.random.default_rng(16)
     lab = rng.integers(0, 2, 600000).astype(np.int32)
     ql = rng.integers(0, 2, 24).astype(np.int32)
     index = certex.Index(8)
     index.add(x, labels=lab)
+    same(index, x, q, 100, row_labels=lab, query_labels=ql, labels=ql)
+    index._test_mode(3)  # dense label groups
     same(index, x, q, 100, row_labels=lab, query_labels=ql, labels=ql)
 
 
