@@ -205,6 +205,17 @@ def test_dense_path_on_long_rows():
     check(ii, xi, qi, 10, "l2")
 
 
+def test_gaussian_configuration_at_full_size():
+    """100 000 base and 1 000 query vectors of dimension 128, float32 i.i.d. N(0, 1) from one default_rng(0) stream,
+    k = 10, L2: ids and fp64 scores equal the exhaustive CPU search, through the fp16 screen."""
+    xb, xq = synthetic.gaussian_f32(100_000, 1000, 128, seed=0)
+    index = certex.Index(128)
+    index.add(xb)
+    with certex.search_stats() as st:
+        check(index, xb, xq, 10, "l2")
+    assert st.dense_queries == 0 and st.survivors < 1000 * 100_000 // 50
+
+
 def test_mixture_sample():
     """The benchmark's data distribution at a size the oracle finishes quickly."""
     xb = synthetic.mixture_u8(1_000_000, seed=0)
