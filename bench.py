@@ -101,12 +101,13 @@ def cpu_baseline(xb_host, xq_host, target_seconds=15.0):
     the workload; the sample is sized from a short probe so that it takes roughly `target_seconds`."""
     from oracle import oracle
 
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     t0 = time.perf_counter()
-    oracle.knn(xb_host, xq_host[:8], K, "l2")
+    oracle.knn(xb_host, xq_host[:8], K, "l2", threads=cores)
     probe = time.perf_counter() - t0
     nqs = int(max(8, min(xq_host.shape[0], 8 * target_seconds / max(probe, 1e-3))))
     t0 = time.perf_counter()
-    oracle.knn(xb_host, xq_host[:nqs], K, "l2")
+    oracle.knn(xb_host, xq_host[:nqs], K, "l2", threads=cores)
     dt = time.perf_counter() - t0
     return {"value": nqs / dt, "unit": "queries/s", "cores": int(oracle.knn.threads_used), "kind": "port",
             "sample": f"first {nqs} of {xq_host.shape[0]} queries against all {xb_host.shape[0]} rows, {dt:.1f} s"}
@@ -124,17 +125,19 @@ def run_reference(args):
     n_base = args.n_base
     xb = synthetic.mixture_u8(n_base, seed=0, device=dev).cpu().numpy()
     xq = synthetic.mixture_u8(args.n_queries, seed=1, device=dev).cpu().numpy()
-    oracle.knn(xb, xq[:4], K, "l2")
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    # every host core, also under a launcher that sets OMP_NUM_THREADS=1 for its ranks (the other ranks do nothing)
+    oracle.knn(xb, xq[:4], K, "l2", threads=cores)
     t0 = time.perf_counter()
-    oracle.knn(xb, xq[:8], K, "l2")
+    oracle.knn(xb, xq[:8], K, "l2", threads=cores)
     per_query = (time.perf_counter() - t0) / 8
     budget = 150.0 / max(args.steps + args.warmup, 1)  # seconds per step so that the whole run takes a few minutes
     nqs = int(max(4, min(args.n_queries, budget / per_query)))
     for _ in range(args.warmup):
-        oracle.knn(xb, xq[:nqs], K, "l2")
+        oracle.knn(xb, xq[:nqs], K, "l2", threads=cores)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.knn(xb, xq[:nqs], K, "l2")
+        oracle.knn(xb, xq[:nqs], K, "l2", threads=cores)
     dt = time.perf_counter() - t0
     qps = nqs * args.steps / dt
     cores = int(oracle.knn.threads_used)
