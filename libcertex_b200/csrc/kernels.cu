@@ -1316,11 +1316,15 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
   const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) + sizeof(int32_t) * n2max;
+  // a thread walks one candidate row: float rows are long walks bound by latency and the conversion pipe, more
+  // resident threads hide more of it
+  // (measured on 768-dimensional rows: 512 threads per query beat 128 by 8 to 13 %, 1024 only when k is large)
+  const int threads = (dtype == kF32 || dtype == kF16) ? (k >= 1024 ? 1024 : 512) : 128;
   by_dtype(dtype, [&](auto tag) {
     using T   = decltype(tag);
     auto go   = [&](auto kernel) {
       allow_smem(kernel, smem);
-      kernel<<<nq, 128, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
+      kernel<<<nq, threads, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
                                    n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf);
     };
     if (metric == kL2) {
