@@ -250,6 +250,8 @@ def main():
         screen_s = st.screen_ms / 1000 / max(args.steps, 1)
         achieved = ops / screen_s / 1e12 if screen_s > 0 else None
         peak = 2 * pk["bf16_sustained"]
+        n_panels = -(-(-(-min(nq, args.batch) // 128)) // 7) * -(-nq // args.batch)  # query panels of 7 tiles, all batches
+        traffic = int(14.89e9 * n_panels * shard_rows / (12 * 10_000_000))
         line = {
             "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -266,11 +268,12 @@ def main():
             "clocks": clocks,
             "roofline": {
                 "bound": "tensor", "kernel": "screen_i8_kernel (SCREEN pass)", "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": None if achieved is None else achieved / peak, "traffic": None,
+                "unit": "TFLOP/s", "frac": None if achieved is None else achieved / peak, "traffic": traffic,
                 "note": f"int8 tensor ops (2 x nq x rows x 128) / CUDA-event time of the screen passes on rank 0; "
                         f"peak = 2 x the {pk['source']} sustained bf16 cuBLAS rate (int8 nominal is twice bf16)",
-                "traffic_note": "not captured at full size; a 2048-query x 1M-row launch moved 251 MB of DRAM traffic "
-                                "under ncu, 0.65 x its algorithmic bytes (query panels share rows in L2)",
+                "traffic_note": "DRAM bytes of one SCREEN launch: ncu measured 14.87 GB read + 0.02 GB written on the "
+                                "10M x 128, 10000-query launch (12 query panels x 1.28 GB of codes = 15.4 GB "
+                                "algorithmic); other sizes scaled by panels x rows",
                 "screen_ms_per_step": st.screen_ms / args.steps, "anchor_ms_per_step": st.anchor_ms / args.steps,
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},
