@@ -641,8 +641,6 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
               events);
 }
 
-namespace {
-
 /// The queries of one label in a search by labels.
 struct LabelRun {
   int64_t part_off  = 0;  // the label's entries in the partition
@@ -650,6 +648,8 @@ struct LabelRun {
   int64_t tile0     = 0;  // its first tile in the label-ordered copy of the screen's rows
   std::vector<int32_t> queries;
 };
+
+namespace {
 
 /// Work split of a routed pass: run r pairs the query tiles [q_tile0[r], + nqt[r]) with its label's tiles. Segments of
 /// at most `panel` query tiles are dealt to the CTAs in order, about the same number of units each, at most
@@ -706,55 +706,13 @@ size_t plan_routed(const std::vector<LabelRun>& runs, size_t r0, size_t r1, cons
 
 }  // namespace
 
-unsigned long long Index::search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k,
-                                           const Admit& adm, double* best_s, int32_t* best_row, int64_t n,
-                                           SearchStats* st) const
+// One class of routed runs (groups of 64 rows, or with `fine` of 16): passes of at most 32 768 query slots. Returns the
+// pairs the screens kept; runs' queries whose candidate list overflowed are appended to `dense`.
+unsigned long long Index::search_routed(const Resources& res, const void* q, size_t qpitch, int k,
+                                        std::vector<LabelRun>& routed, const bool fine, double* best_s, int32_t* best_row,
+                                        SearchStats* st, std::vector<LabelRun>& dense) const
 {
-  // The one host decision of the path: which queries share a label. Their labels come to the host and the queries are
-  // ordered by label. A label with enough rows for a threshold (2k groups of 64) is screened on the tensor cores
-  // against its block of the label-ordered copy of the code rows (routed pass); the other labels, the queries whose
-  // candidate list overflowed, and every label when rows were added after the partition, are scored densely: every
-  // label becomes a group (queries x that label's partition entries + the rows added since), and the groups are
-  // scored, selected from and translated to ids in waves of bounded score memory, three launches per wave.
-  std::vector<int32_t> lab(static_cast<size_t>(nq));
-  CERTEX_CUDA(cudaMemcpyAsync(lab.data(), adm.query_labels, lab.size() * 4, cudaMemcpyDeviceToHost, res.stream));
-  res.sync();
-  std::vector<int32_t> order(static_cast<size_t>(nq));
-  for (int i = 0; i < nq; ++i) { order[static_cast<size_t>(i)] = i; }
-  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return lab[a] < lab[b]; });
-
-  const int64_t n_tail = n - n_part_;
-  const bool can_route = lcodes_ != nullptr && screen_kind_ != 0 && !code_overflow_ && n_tail == 0 && test_mode_ != 3;
-  std::vector<LabelRun> routed, routed_fine, dense;
-  for (int i = 0; i < nq;) {
-    const int32_t l = lab[order[static_cast<size_t>(i)]];
-    int j           = i;
-    while (j < nq && lab[order[static_cast<size_t>(j)]] == l) { ++j; }
-    LabelRun run;
-    const auto it = std::lower_bound(part_labels_.begin(), part_labels_.end(), l);
-    if (l >= 0 && it != part_labels_.end() && *it == l) {
-      const size_t at = static_cast<size_t>(it - part_labels_.begin());
-      run.part_off    = part_offsets_[at];
-      run.n_in_part   = part_offsets_[at + 1] - part_offsets_[at];
-      run.tile0       = part_tile0_.empty() ? 0 : part_tile0_[at];
-    }
-    run.queries.assign(order.begin() + i, order.begin() + j);
-    // a threshold worth the passes needs about 2k groups: the k-th largest of them then sits near the best 1 % of the
-    // label. Groups are 64 rows, or single chains of 16 rows for labels too small for that.
-    const int64_t need = 2 * static_cast<int64_t>(k);
-    if (can_route && run.n_in_part / kGroupRows >= need) {
-      routed.push_back(std::move(run));
-    } else if (can_route && run.n_in_part / kChainRows >= need) {
-      routed_fine.push_back(std::move(run));
-    } else {
-      dense.push_back(std::move(run));
-    }
-    i = j;
-  }
   unsigned long long pairs = 0;
-
-  // ------------------------------------------------------------------ routed passes
-  auto run_routed = [&](std::vector<LabelRun>& routed, const bool fine) {
   const int per_tile = fine ? kBaseTile / kChainRows : kBaseTile / kGroupRows;  // columns of gmax per tile
   for (size_t r0 = 0; r0 < routed.size();) {
     // as many runs as fit 32 768 query slots (a label's queries fill whole tiles of 128) and the segment slots
@@ -963,9 +921,59 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
     }
     r0 = r1;
   }
-  };
-  run_routed(routed, false);
-  run_routed(routed_fine, true);
+  return pairs;
+}
+
+unsigned long long Index::search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k,
+                                           const Admit& adm, double* best_s, int32_t* best_row, int64_t n,
+                                           SearchStats* st) const
+{
+  // The one host decision of the path: which queries share a label. Their labels come to the host and the queries are
+  // ordered by label. A label with enough rows for a threshold (2k groups of 64) is screened on the tensor cores
+  // against its block of the label-ordered copy of the code rows (routed pass); the other labels, the queries whose
+  // candidate list overflowed, and every label when rows were added after the partition, are scored densely: every
+  // label becomes a group (queries x that label's partition entries + the rows added since), and the groups are
+  // scored, selected from and translated to ids in waves of bounded score memory, three launches per wave.
+  std::vector<int32_t> lab(static_cast<size_t>(nq));
+  CERTEX_CUDA(cudaMemcpyAsync(lab.data(), adm.query_labels, lab.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+  res.sync();
+  std::vector<int32_t> order(static_cast<size_t>(nq));
+  for (int i = 0; i < nq; ++i) { order[static_cast<size_t>(i)] = i; }
+  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return lab[a] < lab[b]; });
+
+  const int64_t n_tail = n - n_part_;
+  const bool can_route = lcodes_ != nullptr && screen_kind_ != 0 && !code_overflow_ && n_tail == 0 && test_mode_ != 3;
+  std::vector<LabelRun> routed, routed_fine, dense;
+  for (int i = 0; i < nq;) {
+    const int32_t l = lab[order[static_cast<size_t>(i)]];
+    int j           = i;
+    while (j < nq && lab[order[static_cast<size_t>(j)]] == l) { ++j; }
+    LabelRun run;
+    const auto it = std::lower_bound(part_labels_.begin(), part_labels_.end(), l);
+    if (l >= 0 && it != part_labels_.end() && *it == l) {
+      const size_t at = static_cast<size_t>(it - part_labels_.begin());
+      run.part_off    = part_offsets_[at];
+      run.n_in_part   = part_offsets_[at + 1] - part_offsets_[at];
+      run.tile0       = part_tile0_.empty() ? 0 : part_tile0_[at];
+    }
+    run.queries.assign(order.begin() + i, order.begin() + j);
+    // a threshold worth the passes needs about 2k groups: the k-th largest of them then sits near the best 1 % of the
+    // label. Groups are 64 rows, or single chains of 16 rows for labels too small for that.
+    const int64_t need = 2 * static_cast<int64_t>(k);
+    if (can_route && run.n_in_part / kGroupRows >= need) {
+      routed.push_back(std::move(run));
+    } else if (can_route && run.n_in_part / kChainRows >= need) {
+      routed_fine.push_back(std::move(run));
+    } else {
+      dense.push_back(std::move(run));
+    }
+    i = j;
+  }
+  unsigned long long pairs = 0;
+
+  // ------------------------------------------------------------------ routed passes
+  pairs += search_routed(res, q, qpitch, k, routed, false, best_s, best_row, st, dense);
+  pairs += search_routed(res, q, qpitch, k, routed_fine, true, best_s, best_row, st, dense);
 
   // ------------------------------------------------------------------ dense groups
   std::vector<int32_t> dorder;

@@ -79,6 +79,8 @@ struct SearchStats {
   unsigned long long routed_queries = 0;  // query slots of searches by label that went through the routed screen
 };
 
+struct LabelRun;  // the queries of one label in a search by labels (engine.cu)
+
 struct Filter {
   const uint32_t* words = nullptr;  // device words, bit j of word i is entry 32 i + j, set = keep
   int64_t bitmap_cols   = 0;        // 0: bitset over the ids; > 0: bitmap [n_queries, bitmap_cols]
@@ -159,6 +161,10 @@ class Index {
   /// Search by label over the label partition; returns the (query, row) pairs scored and counts its launches.
   unsigned long long search_by_labels(const Resources& res, const void* q, size_t qpitch, int nq, int k, const Admit& adm,
                                       double* best_s, int32_t* best_row, int64_t n, SearchStats* st) const;
+  /// The routed (screened) part of a search by labels for one class of labels; see engine.cu.
+  unsigned long long search_routed(const Resources& res, const void* q, size_t qpitch, int k, std::vector<LabelRun>& routed,
+                                   bool fine, double* best_s, int32_t* best_row, SearchStats* st,
+                                   std::vector<LabelRun>& dense) const;
 
   IndexParams params_;
   int dtype_;
