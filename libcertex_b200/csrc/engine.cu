@@ -505,7 +505,7 @@ void Index::search_dense(const Resources& res, const void* q, size_t qpitch, con
 void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32_t* thr, const void* queries,
                         size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
                         unsigned int* ovf_count, unsigned long long* stats, int* err, int64_t n, int32_t* thr2,
-                        const float* shift, std::vector<cudaEvent_t>* events) const
+                        const float* shift, const Admit& adm, std::vector<cudaEvent_t>* events) const
 {
   Scratch scratch(res.stream);
   const int grid          = res.sm_count;
@@ -558,8 +558,6 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   mark();
   launch_expand_records(rec, rec_count, rec_cap, n, perm_, cnt, cand, cap, res.sm_count, res.stream);
   CERTEX_CUDA(cudaGetLastError());
-  Admit adm{};
-  adm.removed = removed_;
   Refine rf{};
   rf.thr2  = thr2;
   rf.thr   = thr;
@@ -573,7 +571,7 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
 void Index::search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries,
                             size_t row_bytes, int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
                             unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
-                            int32_t* thr2, std::vector<cudaEvent_t>* events) const
+                            int32_t* thr2, const Admit& adm, std::vector<cudaEvent_t>* events) const
 {
   // qbuf: the code rows of all queries of the call, zero padded to [round_up(total, 128), code_pitch_]; this batch is
   // rows [q0, q0 + nq). shift (fp16 codes only): the rounding allowance of every query.
@@ -593,7 +591,9 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
 
   const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
   CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_a.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
-  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream);  // e of the anchors
+  // e of the anchors; with a bitset filter the anchors it drops do not count
+  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream, adm.bits, perm_,
+                     screen_kind_ == 2 ? static_cast<int32_t>(0xff800000u) : kNeverInit);
   CERTEX_CUDA(cudaGetLastError());
 
   const size_t cp        = code_pitch_;
@@ -638,7 +638,7 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   CERTEX_CUDA(cudaGetLastError());
   // 3 screen over all rows, 4 exact scores of the candidates and the k best
   screen_pass(res, qb, thr, queries, row_bytes, q0, nq, k, best_s, best_row, ovf_list, ovf_count, stats, err, n, thr2, shift,
-              events);
+              adm, events);
 }
 
 /// The queries of one label in a search by labels.
@@ -1093,7 +1093,10 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   adm.bitmap_cols     = filter.bitmap_cols;
   adm.row_labels      = filter.query_labels ? labels_ : nullptr;
   adm.query_labels    = filter.query_labels;
-  const bool filtered = filter.words != nullptr || filter.query_labels != nullptr;
+  // A bitset (one bit per id for all queries) keeps the screen: the anchors it drops are left out of the thresholds and
+  // the exact stage applies it to the kept pairs, as the reference does (cpp/src/neighbors/certex/detail/kernels.hpp:
+  // 39-62). A bitmap (a row of bits per query) and label searches without a partition score every vector.
+  const bool filtered = (filter.words != nullptr && filter.bitmap_cols > 0) || filter.query_labels != nullptr;
 
   const int stride    = anchor_stride_for(n, k);
   const bool screened = screen_kind_ != 0 && !code_overflow_ && !filtered && stride >= 1 && test_mode_ != 1;
@@ -1131,7 +1134,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     for (int64_t q0 = 0; q0 < nq; q0 += batch) {
       const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
       search_screened(res, qbuf, shift, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
-                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, thr2, stats_sink ? &events : nullptr);
+                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, thr2, adm, stats_sink ? &events : nullptr);
       local.launches += screen_kind_ == 2 ? 7 : 6;  // gather_init, GROUPMAX, kth_largest (+ thresholds), SCREEN, expand, verify
     }
     unsigned int h_count[4]       = {0, 0, 0, 0};
@@ -1178,7 +1181,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
         const int nb = std::min<int>(static_cast<int>(batch), n_ovf - b0);
         screen_pass(res, qcodes2 + static_cast<size_t>(b0) * code_pitch_, thr2 + b0, queries2, row_bytes, b0, nb, k, best2_s,
                     best2_row, ovf2, d_count + 2, d_stats, reinterpret_cast<int*>(d_count + 1), n, nullptr,
-                    shift ? shift2 : nullptr, stats_sink ? &events : nullptr);
+                    shift ? shift2 : nullptr, adm, stats_sink ? &events : nullptr);
         local.launches += 3;
       }
       launch_scatter_best(best2_s, best2_row, ovf_list, n_ovf, k, best_s, best_row, res.stream);

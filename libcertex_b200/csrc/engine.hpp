@@ -150,10 +150,10 @@ class Index {
   void search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries, size_t row_bytes,
                        int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
                        unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,
-                       int32_t* thr2, std::vector<cudaEvent_t>* events) const;
+                       int32_t* thr2, const Admit& adm, std::vector<cudaEvent_t>* events) const;
   void screen_pass(const Resources& res, const uint8_t* qcodes, const int32_t* thr, const void* queries, size_t row_bytes,
                    int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
-                   unsigned long long* stats, int* err, int64_t n, int32_t* thr2, const float* shift,
+                   unsigned long long* stats, int* err, int64_t n, int32_t* thr2, const float* shift, const Admit& adm,
                    std::vector<cudaEvent_t>* events) const;
   int anchor_stride_for(int64_t n, int k) const;
   void search_dense(const Resources& res, const void* q, size_t qpitch, const int32_t* qsel, int q0, int nqb, int k,

@@ -263,12 +263,21 @@ __global__ void row_init_kernel(const uint8_t* vectors, size_t pitch, int d, int
 }
 
 // e of the anchors in tile order: out[t * 256 + c] = init[(c * n_tiles + t) * stride].
-__global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out)
+// With a bitset (one bit per id, set = keep) the anchors the filter drops get `never`, like removed rows: the threshold
+// then comes from anchors the search may return.
+__global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, const uint32_t* bits,
+                                   const int32_t* perm, int32_t never)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (j < n_tiles * kBaseTile) {
     const int64_t t = j / kBaseTile, c = j % kBaseTile;
-    out[j]          = init[(c * n_tiles + t) * stride];
+    const int64_t r = (c * n_tiles + t) * stride;
+    int32_t e       = init[r];
+    if (bits) {
+      const int32_t id = perm[r];
+      if (((bits[id >> 5] >> (id & 31)) & 1u) == 0u) { e = never; }
+    }
+    out[j] = e;
   }
 }
 
@@ -1201,10 +1210,11 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
   }
 }
 
-void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s)
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s,
+                        const uint32_t* bits, const int32_t* perm, int32_t never)
 {
   if (n_tiles <= 0) { return; }
-  gather_init_kernel<<<static_cast<unsigned>(n_tiles), kBaseTile, 0, s>>>(init, stride, n_tiles, out);
+  gather_init_kernel<<<static_cast<unsigned>(n_tiles), kBaseTile, 0, s>>>(init, stride, n_tiles, out, bits, perm, never);
 }
 
 void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,

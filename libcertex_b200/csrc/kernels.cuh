@@ -26,7 +26,9 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
                      int64_t row0, int64_t n, int64_t n_pad, int32_t* init, cudaStream_t s);
 
 /// e of the anchors of the threshold stage in tile order: out[t * 256 + c] = init[(c * n_tiles + t) * stride].
-void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s);
+/// With `bits` (a bitset over the ids, set = keep; perm: sorted row -> id) dropped anchors get `never`.
+void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s,
+                        const uint32_t* bits = nullptr, const int32_t* perm = nullptr, int32_t never = 0);
 
 /// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1 (int32 values, or float bits).
 void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, bool is_float, cudaStream_t s);

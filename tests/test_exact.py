@@ -117,7 +117,10 @@ def test_which_searches_the_tensor_cores_screen():
         vidx.search(qv, k=10)
     assert st.dense_queries == 10
     with certex.search_stats() as st:
-        fidx.search(qf, k=10, filter=np.ones(50000, dtype=bool))
+        fidx.search(qf, k=10, filter=np.ones(50000, dtype=bool))  # one mask for all queries keeps the screen
+    assert st.dense_queries == 0
+    with certex.search_stats() as st:
+        fidx.search(qf, k=10, filter=np.ones((100, 50000), dtype=bool))  # a mask per query does not
     assert st.dense_queries == 100
 
 

@@ -252,7 +252,11 @@ def test_bitset_and_bitmap(dtype):
     index = certex.Index(64)
     index.add(x)
     mask = rng.random(15000) < 0.3
-    same(index, x, q, 10, keep_row=mask.astype(np.uint8), filter=mask)
+    with certex.search_stats() as st:
+        same(index, x, q, 10, keep_row=mask.astype(np.uint8), filter=mask)
+    assert st.dense_queries == 0 and st.survivors < 120 * 15000 // 4  # screened: thresholds from the kept anchors
+    rare = rng.random(15000) < 0.004  # about 60 kept vectors: too few anchors pass, the lists overflow
+    same(index, x, q, 10, keep_row=rare.astype(np.uint8), filter=rare)
     per_query = rng.random((120, 15000)) < 0.05
     per_query[7] = False  # a query with no admitted vector
     per_query[8, :3] = True
@@ -261,6 +265,11 @@ def test_bitset_and_bitmap(dtype):
     ids, scores = oracle.knn(x, q, 10, "l2", keep_pair=per_query.astype(np.uint8))
     assert np.array_equal(I, ids) and np.array_equal(S, scores)
     assert (I[7] == -1).all() and (I[8, 3:] == -1).all() and (I[8, :3] >= 0).all()
+    gone = rng.choice(15000, 3000, replace=False)  # removed vectors and a mask together
+    index.remove(gone)
+    both = mask.copy()
+    both[gone] = False
+    same(index, x, q, 10, keep_row=both.astype(np.uint8), filter=mask)
 
 
 @pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("float32", "cosine")])
