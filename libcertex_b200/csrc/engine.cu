@@ -449,7 +449,15 @@ void Index::partition_by_labels(const Resources& res)
       launch_fill_i32(linit, n_lrows, never, res.stream);
       launch_fill_i32(lperm, n_lrows, -1, res.stream);
       launch_fill_i32(lsrc, n_lrows, -1, res.stream);
-      launch_label_rows(ids, n, d_off, d_row0, static_cast<int>(distinct.size()), inv_, init_, lperm, linv, lsrc, linit,
+      // inside a label the copy is ordered by norm, like the main copy of the code rows: the screen's keep rule relies
+      // on e being almost constant over 16 adjacent rows
+      auto* keys_in   = scratch.get<unsigned long long>(static_cast<size_t>(n));
+      auto* keys_out  = scratch.get<unsigned long long>(static_cast<size_t>(n));
+      int32_t* order  = scratch.get<int32_t>(static_cast<size_t>(n));
+      const size_t tb = label_norm_order_temp_bytes(n);
+      void* temp      = scratch.get<uint8_t>(tb);
+      launch_label_norm_order(ids, n, labels_, inv_, init_, f16, keys_in, keys_out, order, temp, tb, res.stream);
+      launch_label_rows(order, n, d_off, d_row0, static_cast<int>(distinct.size()), inv_, init_, lperm, linv, lsrc, linit,
                         res.stream);
       launch_gather_rows(codes_, code_pitch_, lsrc, n_lrows, n_lrows, lcodes, code_pitch_, code_pitch_, res.stream);
       launch_chain_max(linit, 0, n_lrows / kChainRows, lcmax, f16, res.stream);
@@ -739,24 +747,34 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     std::vector<int> col0, seg_begin;
     r1 = r0 + plan_routed(routed, r0, r1, q_tile0, shape.panel_tiles, grid, 64, segs, col0, seg_begin);
     CERTEX_EXPECTS(r1 > r0, "certex: internal error: a label's queries do not fit one routed pass");
-    // The thresholds of a large label come from its leading tiles only (its rows are in id order: a sample like any
-    // other, and the group maxima of any subset of rows are valid): at least 1024 tiles (smaller labels take part
+    // The thresholds of a large label come from a strided sample of its tiles (its rows are sorted by norm, so the sample
+    // spans all norms; the group maxima of any subset of rows are valid): at least 1024 tiles (smaller labels take part
     // whole: every tile left out costs survivors, and their exact scores cost more than the tile), enough tiles for
     // 2k groups, for a sixteenth of the label, and for candidate lists that stay within half their capacity (about
     // 1.2 k rows per sampled fraction).
     const uint32_t cap = static_cast<uint32_t>(std::max(2048, 2 * k));
     std::vector<LabelRun> heads(routed.begin() + static_cast<std::ptrdiff_t>(r0), routed.begin() + static_cast<std::ptrdiff_t>(r1));
-    for (LabelRun& h : heads) {
+    std::vector<int> steps(heads.size(), 1);  // the sample of a large label: every steps[r]-th tile
+    for (size_t r = 0; r < heads.size(); ++r) {
+      LabelRun& h          = heads[r];
       const int64_t nt     = (h.n_in_part + kTile - 1) / kTile;
       const int64_t enough = (2 * static_cast<int64_t>(k) + per_tile - 1) / per_tile;
       const int64_t by_cap = (24 * static_cast<int64_t>(k) * nt + 10 * cap - 1) / (10 * static_cast<int64_t>(cap));
       const int64_t take   = std::min(nt, std::max({int64_t(1024), enough, (nt + 15) / 16, by_cap}));
-      h.n_in_part          = std::min(h.n_in_part, take * kTile);
+      if (take < nt) {
+        steps[r]    = static_cast<int>(nt / take);  // tiles tile0, tile0 + step, ... stay inside the label
+        h.n_in_part = take * kTile;
+      }
     }
     std::vector<ScreenSeg> segs_g;
     std::vector<int> col0_g, seg_begin_g;
     const size_t fit = plan_routed(heads, 0, heads.size(), q_tile0, shape.panel_tiles, grid, 64, segs_g, col0_g, seg_begin_g);
     CERTEX_EXPECTS(fit == heads.size(), "certex: internal error: the threshold pass of a routed search does not fit");
+    std::vector<int> step_g(segs_g.size(), 1);
+    for (size_t i = 0, r = 0; i < segs_g.size(); ++i) {  // segments come in the order of the runs
+      while (heads[r].tile0 != col0_g[i]) { ++r; }
+      step_g[i] = steps[r];
+    }
     n_slots = 0;
     std::vector<int32_t> slot_query, slot_ng;
     int64_t max_tiles = 0;
@@ -788,6 +806,7 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     ScreenSeg* d_segs_g  = scratch.get<ScreenSeg>(segs_g.size());  // the threshold pass: leading tiles of every label
     int* d_col0_g        = scratch.get<int>(col0_g.size());
     int* d_seg_begin_g   = scratch.get<int>(seg_begin_g.size());
+    int* d_step_g        = scratch.get<int>(step_g.size());
     uint8_t* q_rows      = scratch.get<uint8_t>(static_cast<size_t>(ns) * (f16 ? qpitch : cp));  // the queries in slot order
     uint8_t* q_codes     = f16 ? scratch.get<uint8_t>(static_cast<size_t>(ns) * cp) : q_rows;
     float* shift         = f16 ? scratch.get<float>(static_cast<size_t>(ns)) : nullptr;
@@ -811,6 +830,7 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     CERTEX_CUDA(cudaMemcpyAsync(d_segs_g, segs_g.data(), segs_g.size() * sizeof(ScreenSeg), h2d, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(d_col0_g, col0_g.data(), col0_g.size() * sizeof(int), h2d, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin_g, seg_begin_g.data(), seg_begin_g.size() * sizeof(int), h2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(d_step_g, step_g.data(), step_g.size() * sizeof(int), h2d, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * ns, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
     CERTEX_CUDA(cudaMemsetAsync(d_flag, 0, 4 * sizeof(unsigned int), res.stream));
@@ -838,6 +858,7 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     a.segs        = d_segs_g;
     a.seg_begin   = d_seg_begin_g;
     a.seg_col0    = d_col0_g;
+    a.seg_step    = d_step_g;
     a.plain_tiles = 1;
     a.fine_groups = fine ? 1 : 0;
     a.init        = linit_;
@@ -869,6 +890,7 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     a.segs      = d_segs;
     a.seg_begin = d_seg_begin;
     a.seg_col0  = d_col0;
+    a.seg_step  = nullptr;
     a.cmax      = lcmax_;
     a.thr       = thr;
     a.rec       = rec;

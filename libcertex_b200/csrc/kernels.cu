@@ -1494,6 +1494,40 @@ __global__ void iota_kernel(int32_t* p, int64_t n)
   if (i < n) { p[i] = static_cast<int32_t>(i); }
 }
 
+// Order of the label-ordered copy of the screen's rows: by label, and inside a label by norm (the per-row term e of the
+// screen), so that e is almost constant over 16 adjacent rows there too. keys [n]: (label, -e) of the partition
+// entries; the sorted ids go to `order`. labels_of_ids: the label of every id; e is init[inv[id]].
+__global__ void label_norm_keys_kernel(const int32_t* part_ids, int64_t n, const int32_t* labels_of_ids, const int32_t* inv,
+                                       const int32_t* init, int is_float, unsigned long long* keys)
+{
+  const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (p >= n) { return; }
+  const int32_t id   = part_ids[p];
+  const int32_t e    = init[inv[id]];
+  const uint32_t low = is_float ? __float_as_uint(-__int_as_float(e)) : static_cast<uint32_t>(-e);  // e <= 0
+  const uint32_t top = static_cast<uint32_t>(labels_of_ids[id]) ^ 0x80000000u;                       // signed order
+  keys[p]            = (static_cast<unsigned long long>(top) << 32) | low;
+}
+
+size_t label_norm_order_temp_bytes(int64_t n)
+{
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const unsigned long long*>(nullptr),
+                                  static_cast<unsigned long long*>(nullptr), static_cast<const int32_t*>(nullptr),
+                                  static_cast<int32_t*>(nullptr), n);
+  return bytes;
+}
+
+void launch_label_norm_order(const int32_t* part_ids, int64_t n, const int32_t* labels_of_ids, const int32_t* inv,
+                             const int32_t* init, bool is_float, unsigned long long* keys_in, unsigned long long* keys_out,
+                             int32_t* order, void* temp, size_t temp_bytes, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  label_norm_keys_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(part_ids, n, labels_of_ids, inv, init,
+                                                                                is_float ? 1 : 0, keys_in);
+  cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys_in, keys_out, part_ids, order, n, 0, 64, s);
+}
+
 size_t label_partition_temp_bytes(int64_t n)
 {
   size_t a = 0, b = 0;

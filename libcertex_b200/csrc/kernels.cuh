@@ -71,6 +71,13 @@ void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_co
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
                         const int32_t* ng_rows = nullptr, int32_t never = 0x7fffffff);
 
+/// order [n] = the partition entries by (label, norm): inside a label the rows sorted by their term e of the screen
+/// (stable: equal norms keep ascending ids). keys_in / keys_out: scratch of n; temp of label_norm_order_temp_bytes(n).
+size_t label_norm_order_temp_bytes(int64_t n);
+void launch_label_norm_order(const int32_t* part_ids, int64_t n, const int32_t* labels_of_ids, const int32_t* inv,
+                             const int32_t* init, bool is_float, unsigned long long* keys_in, unsigned long long* keys_out,
+                             int32_t* order, void* temp, size_t temp_bytes, cudaStream_t s);
+
 /// Label-ordered layout of the partition (see label_rows_kernel in kernels.cu).
 void launch_label_rows(const int32_t* part_ids, int64_t n, const int64_t* off, const int64_t* lrow0, int n_labels,
                        const int32_t* inv, const int32_t* init, int32_t* lperm, int32_t* linv, int32_t* lsrc, int32_t* linit,

@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   const int seg_first   = p.seg_begin ? p.seg_begin[blockIdx.x] : static_cast<int>(blockIdx.x) * kMaxSegs;
   const ScreenSeg* gsegs = p.segs + seg_first;
   const int* seg_col0    = p.seg_col0 ? p.seg_col0 + seg_first : nullptr;
+  const int* seg_step    = p.seg_step ? p.seg_step + seg_first : nullptr;  // GROUPMAX over a strided sample of tiles
   int nseg               = 0;
   if (p.seg_begin) {
     nseg = min(p.seg_begin[blockIdx.x + 1] - seg_first, kSharedSegs);
@@ -280,7 +281,10 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       bool aborted = false;
       for (int s = 0; s < nseg && !aborted; ++s) {
         const ScreenSeg sg = segs[s];
+        const int c0       = (kNeedE && seg_col0) ? seg_col0[s] : 0;
+        const int stp      = (kNeedE && seg_step) ? seg_step[s] : 1;
         for (int t = sg.t0; t < sg.t1 && !aborted; ++t, ++ts) {
+          const int ta = c0 + (t - c0) * stp;  // the tile that is read
           if (kNeedE) {
             const int er = ts % kERing;
             if (ts >= kERing && !mbar_wait(smem_u32(&ctl->e_empty[er]), ((ts / kERing) - 1) & 1, abort_flag, p.err, 8)) {
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
               break;
             }
             mbar_arrive_expect_tx(smem_u32(&ctl->e_full[er]), kBaseTile * 4);
-            bulk_load_1d(base + init_off + er * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4,
+            bulk_load_1d(base + init_off + er * kBaseTile * 4, p.init + static_cast<size_t>(ta) * kBaseTile, kBaseTile * 4,
                          smem_u32(&ctl->e_full[er]));
           }
           for (int b = 0; b < kb; ++b, ++ks) {
@@ -304,9 +308,9 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
               tma_load_2d(dst + j * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, fbar);
             }
             if (MODE == kModeGroupMax && !p.plain_tiles) {
-              tma_load_3d(dst + 2 * kQTileBytes, &tm_x, b * 128, 0, t, fbar);
+              tma_load_3d(dst + 2 * kQTileBytes, &tm_x, b * 128, 0, ta, fbar);
             } else {
-              tma_load_2d(dst + 2 * kQTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
+              tma_load_2d(dst + 2 * kQTileBytes, &tm_x, b * 128, ta * kBaseTile, fbar);
             }
           }
         }
@@ -337,7 +341,10 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             tma_load_2d(base + panel_off + (j * kb + b) * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, pbar);
           }
         }
+        const int c0  = (kNeedE && seg_col0) ? seg_col0[s] : 0;
+        const int stp = (kNeedE && seg_step) ? seg_step[s] : 1;
         for (int t = sg.t0; t < sg.t1; ++t, ++ts) {
+          const int ta = c0 + (t - c0) * stp;  // the tile that is read
           const int st = ts % ns;
           if (ts >= ns && !mbar_wait(smem_u32(&ctl->empty[st]), ((ts / ns) - 1) & 1, abort_flag, p.err, 2)) {
             aborted = true;
@@ -349,13 +356,13 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             if (MODE == kModeGroupMax && !p.plain_tiles) {
               // anchors: column c of tile t is anchor c * n_tiles + t, so every group of 64 columns samples the whole
               // (norm-sorted) set; the map is 3-D (bytes, column, tile)
-              tma_load_3d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, t, fbar);
+              tma_load_3d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, ta, fbar);
             } else {
-              tma_load_2d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, t * kBaseTile, fbar);
+              tma_load_2d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, ta * kBaseTile, fbar);
             }
           }
           if (kStageE) {
-            bulk_load_1d(base + init_off + st * kBaseTile * 4, p.init + static_cast<size_t>(t) * kBaseTile, kBaseTile * 4, fbar);
+            bulk_load_1d(base + init_off + st * kBaseTile * 4, p.init + static_cast<size_t>(ta) * kBaseTile, kBaseTile * 4, fbar);
           }
         }
       }

@@ -58,6 +58,7 @@ struct ScreenArgs {
   const ScreenSeg* segs;          // [grid, kMaxSegs]; unused entries have t1 <= t0. With seg_begin: one list
   const int* seg_begin;           // optional [grid + 1]: CTA b works on segs[seg_begin[b] .. seg_begin[b + 1])
   const int* seg_col0;            // optional, per segment: the tile whose groups are columns 0..3 of gmax (else tile 0)
+  const int* seg_step;            // optional, GROUPMAX: tile t of a segment stands for tile col0 + (t - col0) * step
   int wide;                       // 1: rows of more than two K blocks; a segment then has at most two query tiles
   int plain_tiles;                // GROUPMAX: tile t is rows [256 t, 256 t + 256) of a 2-D map (else the 3-D anchor map)
   int fine_groups;                // GROUPMAX: one maximum per 16 rows (16 columns of gmax per tile) instead of per 64 (4)

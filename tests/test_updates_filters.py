@@ -187,11 +187,11 @@ def test_label_partition_small_labels_and_large_k():
 
 
 def test_label_partition_long_labels():
-    """Two labels of about 300 000 vectors each (1 172 tiles: the thresholds come from the leading 1 024); with the
+    """Two labels of about 600 000 vectors each (2 344 tiles: the thresholds come from every second tile); with the
     dense label groups the score rows are long enough to be selected from in chunks."""
-    x, q = data(600000, 8, 24, "uint8", seed=15)
+    x, q = data(1200000, 8, 24, "uint8", seed=15)
     rng = np.random.default_rng(16)
-    lab = rng.integers(0, 2, 600000).astype(np.int32)
+    lab = rng.integers(0, 2, 1200000).astype(np.int32)
     ql = rng.integers(0, 2, 24).astype(np.int32)
     index = certex.Index(8)
     index.add(x, labels=lab)
