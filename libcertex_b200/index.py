@@ -349,6 +349,7 @@ class ShardedIndex:
         self.d, self.devices, self.metric = dim, list(devices), metric
         self.anchor_stride = anchor_stride
         self.shards, self.first, self._dtype, self._n = [], [], None, 0
+        self._pool = None
 
     def add(self, x):
         _need(not self.shards, "a sharded index is built by one addition")
@@ -376,12 +377,23 @@ class ShardedIndex:
         Q = _to_dtype(_as_torch(q)[0].cpu(), self._dtype).contiguous()
         for idx in self.shards:
             _need(k <= int(idx.core.info().size), "every shard needs at least k vectors")
-        parts_s, parts_i = [], []
-        for dev, idx, lo in zip(self.devices, self.shards, self.first):
+        def one(shard):  # a host thread per shard, like the reference (certex_shards.cu:105-135): the GPUs work at once
+            dev, idx, lo = shard
             with torch.cuda.device(dev):
                 _, I, Sc = idx.search(Q.cuda(), k=k, batch=batch, return_scores=True, id_base=lo)
-                parts_s.append(Sc)
-                parts_i.append(I)
+                torch.cuda.current_stream().synchronize()
+            return Sc, I
+
+        shards = list(zip(self.devices, self.shards, self.first))
+        if len(shards) == 1:
+            results = [one(shards[0])]
+        else:
+            if self._pool is None:  # the threads live as long as the index: each keeps its resource handles
+                from concurrent.futures import ThreadPoolExecutor
+
+                self._pool = ThreadPoolExecutor(max_workers=len(shards))
+            results = list(self._pool.map(one, shards))
+        parts_s, parts_i = [r[0] for r in results], [r[1] for r in results]
         with torch.cuda.device(self.devices[0]):
             ps = torch.stack([p.cuda() for p in parts_s])
             pi = torch.stack([p.cuda() for p in parts_i])
