@@ -1,5 +1,5 @@
-// Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA (cp.async.bulk[.tensor], never
-// with cluster multicast), tensor memory (tcgen05.alloc/ld) and the fifth-generation tensor-core MMA
+// Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA (cp.async.bulk[.tensor], every load
+// for the issuing CTA alone), tensor memory (tcgen05.alloc/ld) and the fifth-generation tensor-core MMA
 // (tcgen05.mma / tcgen05.commit). Every wait in here is bounded; see `mbar_wait`.
 #pragma once
 

@@ -42,7 +42,7 @@
 // every unit), warp 16 lane 0 issues TMA loads (query panel once per segment, base tiles through a ring of stages),
 // warp 17 lane 0 issues tcgen05.mma. TMEM holds two accumulator slots of 256 columns: the MMAs of one unit run while the
 // epilogue reads the other; a slot goes back to the MMA warp as soon as its columns are in registers. No cluster
-// launch, no multicast: each CTA loads its own tiles from its GPU's memory.
+// launch: each CTA loads its own tiles from its GPU's memory.
 #include "screen_i8.cuh"
 
 #include "ptx.cuh"
