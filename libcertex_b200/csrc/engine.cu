@@ -298,34 +298,51 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
     CERTEX_CUDA(cudaMemcpy2DAsync(dst, pitch_, rows, row_bytes, row_bytes, static_cast<size_t>(n), kind, res.stream));
   }
   if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
+  std::unique_lock<std::shared_mutex> lock(rw_, std::defer_lock);
   if (screen_kind_) {
-    // The batch goes into sorted rows [size, size + n), ordered by squared norm. Rows beyond the published size are
-    // invisible to running searches, which bound tiles and candidates by their own size.
+    // The batch goes into sorted rows [size, size + n), ordered by squared norm; rows beyond the published size are
+    // invisible to running searches, which bound tiles and candidates by their own size. With the L2 metric small
+    // batches are not left as sorted runs of their own (chains of 16 rows would mix norms and the screen's keep rule
+    // would loosen): the runs at the end of the index that are no longer than twice what follows them are sorted again
+    // together with the batch, until a run reaches kFrozenRun rows. Those rows are visible, so searches wait meanwhile.
+    int64_t a = size_, m = n;
+    if (params_.metric == kL2) {
+      while (!runs_.empty() && runs_.back().second <= 2 * m && runs_.back().second < kFrozenRun) {
+        a = runs_.back().first;
+        m += runs_.back().second;
+        runs_.pop_back();
+      }
+      m = size_ + n - a;
+      if (m < kFrozenRun) { runs_.emplace_back(a, m); }
+    }
+    if (a < size_) { lock.lock(); }
     Scratch scratch(res.stream);
     const bool f16     = screen_kind_ == 2;
-    int32_t* e         = scratch.get<int32_t>(static_cast<size_t>(n));
-    uint32_t* keys_in  = scratch.get<uint32_t>(static_cast<size_t>(n));
-    uint32_t* keys_out = scratch.get<uint32_t>(static_cast<size_t>(n));
-    int32_t* ids_in    = scratch.get<int32_t>(static_cast<size_t>(n));
-    int32_t* ids_out   = scratch.get<int32_t>(static_cast<size_t>(n));
-    const size_t tb    = sort_batch_temp_bytes(n);
+    int32_t* e         = scratch.get<int32_t>(static_cast<size_t>(m));
+    uint32_t* keys_in  = scratch.get<uint32_t>(static_cast<size_t>(m));
+    uint32_t* keys_out = scratch.get<uint32_t>(static_cast<size_t>(m));
+    int32_t* ids_in    = scratch.get<int32_t>(static_cast<size_t>(m));
+    int32_t* ids_out   = scratch.get<int32_t>(static_cast<size_t>(m));
+    const size_t tb    = sort_batch_temp_bytes(m);
     void* temp         = scratch.get<uint8_t>(tb);
     const void* src    = vectors_;  // code rows by id: the stored rows themselves (8-bit), or fresh fp16 codes
     int64_t src_id0    = 0;
+    const uint8_t* from = static_cast<const uint8_t*>(vectors_) + static_cast<size_t>(a) * pitch_;
     if (f16) {
-      uint8_t* fresh = scratch.get<uint8_t>(static_cast<size_t>(n) * code_pitch_);
-      launch_encode_f16_rows(dst, pitch_, dtype_, static_cast<int>(dim_), params_.metric, n, fresh, code_pitch_,
+      uint8_t* fresh = scratch.get<uint8_t>(static_cast<size_t>(m) * code_pitch_);
+      launch_encode_f16_rows(from, pitch_, dtype_, static_cast<int>(dim_), params_.metric, m, fresh, code_pitch_,
                              reinterpret_cast<float*>(e), maxima_, res.stream);
       src     = fresh;
-      src_id0 = size_;
+      src_id0 = a;
     } else {
-      launch_row_init(dst, pitch_, dtype_, static_cast<int>(dim_), kL2, nullptr, 0, n, n, e, res.stream);
+      launch_row_init(from, pitch_, dtype_, static_cast<int>(dim_), kL2, nullptr, 0, m, m, e, res.stream);
     }
+    if (a < size_ && n_removed_ > 0) { launch_mask_removed(e, removed_ + a, size_ - a, f16, res.stream); }
     CERTEX_CUDA(cudaGetLastError());
-    launch_sort_batch(e, n, static_cast<int32_t>(size_), size_, src, src_id0, code_pitch_, params_.metric, f16, keys_in,
-                      keys_out, ids_in, ids_out, temp, tb, codes_, perm_, inv_, init_, res.stream);
+    launch_sort_batch(e, m, static_cast<int32_t>(a), a, src, src_id0, code_pitch_, params_.metric, f16, keys_in, keys_out,
+                      ids_in, ids_out, temp, tb, codes_, perm_, inv_, init_, res.stream);
     CERTEX_CUDA(cudaGetLastError());
-    const int64_t c0 = size_ / kChainRows, c1 = (size_ + n + kChainRows - 1) / kChainRows;
+    const int64_t c0 = a / kChainRows, c1 = (size_ + n + kChainRows - 1) / kChainRows;
     launch_chain_max(init_, c0, c1 - c0, cmax_, f16, res.stream);
     CERTEX_CUDA(cudaGetLastError());
     if (f16) {
@@ -339,7 +356,7 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
     }
   }
   res.sync();
-  std::unique_lock<std::shared_mutex> lock(rw_);
+  if (!lock.owns_lock()) { lock.lock(); }
   size_ += n;
 }
 

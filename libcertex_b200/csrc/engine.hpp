@@ -13,6 +13,7 @@
 #include <shared_mutex>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "kernels.cuh"
@@ -199,12 +200,17 @@ class Index {
   int32_t* linv_      = nullptr;  // [n_part_] id -> row
   int64_t n_lrows_    = 0;
   std::vector<int64_t> part_tile0_;
-  // screen: the code rows sorted by squared norm (each appended batch on its own), and per sorted row
+  // screen: the code rows sorted by squared norm run by run (a run: one appended batch, or several small ones of an
+  // L2 index sorted together), and per sorted row
   void* codes_        = nullptr;  // [capacity, pitch] rows in sorted order
   int32_t* perm_      = nullptr;  // [capacity] sorted row -> id
   int32_t* inv_       = nullptr;  // [capacity] id -> sorted row
   int32_t* init_      = nullptr;  // [capacity rounded up to 256] e of the sorted row (kNeverInit: removed / padding)
   int32_t* cmax_      = nullptr;  // [capacity rounded up to 256, / 16] maximum of e over each chain of 16 sorted rows
+  // L2 only: the sorted runs [first row, rows) at the end of the index that a later append may still sort again with
+  // its own rows; a run of kFrozenRun rows or more stays as it is
+  std::vector<std::pair<int64_t, int64_t>> runs_;
+  static constexpr int64_t kFrozenRun = 65536;
   int test_mode_      = 0;
   int test_cap_       = 0;
   mutable std::shared_mutex rw_;  // searches hold it shared per call; size/pointer publication holds it exclusive

@@ -363,6 +363,12 @@ __global__ void place_sorted_kernel(const uint32_t* keys, const int32_t* ids, in
   }
 }
 
+__global__ void mask_removed_kernel(int32_t* e, const uint8_t* removed, int64_t n, int32_t never)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j < n && removed[j]) { e[j] = never; }
+}
+
 __global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t v)
 {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -1274,6 +1280,13 @@ void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s)
 {
   if (n <= 0) { return; }
   fill_i32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p, n, v);
+}
+
+void launch_mask_removed(int32_t* e, const uint8_t* removed, int64_t n, bool is_float, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  const int32_t never = is_float ? static_cast<int32_t>(0xff800000u) : kNeverInit;
+  mask_removed_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e, removed, n, never);
 }
 
 size_t sort_batch_temp_bytes(int64_t n)

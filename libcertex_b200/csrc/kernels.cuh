@@ -30,6 +30,9 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
 void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s,
                         const uint32_t* bits = nullptr, const int32_t* perm = nullptr, int32_t never = 0);
 
+/// e[j] = never (-2^30, or -inf as float bits) where removed[j] is set, j < n.
+void launch_mask_removed(int32_t* e, const uint8_t* removed, int64_t n, bool is_float, cudaStream_t s);
+
 /// cmax[c] = max of init over rows [16c, 16c + 16), chains c0 .. c0 + n - 1 (int32 values, or float bits).
 void launch_chain_max(const int32_t* init, int64_t c0, int64_t n, int32_t* cmax, bool is_float, cudaStream_t s);
 

@@ -156,6 +156,16 @@ def test_batch_sizes(batch):
     check(index, x, q, 10, "l2", batch=batch)
 
 
+def test_more_queries_than_one_pass_takes():
+    """40 000 queries in one call: a pass holds at most 32 768, whatever batch size is asked for."""
+    x, q = make(50000, 16, 40000, "uint8", False, 0)
+    index = certex.Index(16)
+    index.add(x)
+    with certex.search_stats() as st:
+        check(index, x, q, 10, "l2", batch=100000)
+    assert st.screen_passes == 2 and st.dense_queries == 0
+
+
 @pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("int8", "ip"), ("float32", "l2"), ("float32", "cosine"),
                                           ("float16", "ip")])
 def test_overflowing_candidate_lists_are_screened_again_then_searched_densely(dtype, metric):

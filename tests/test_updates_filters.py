@@ -51,6 +51,37 @@ def test_remove_then_add(dtype):
     same(index, x, q, 10, keep_row=keep)
 
 
+@pytest.mark.parametrize("dtype", ["uint8", "float32"])
+def test_many_small_appends_keep_the_screen_tight(dtype):
+    """An L2 index grown by a thousand appends of a few dozen rows, with removals in between: the answers are the
+    oracle's, and the screen keeps about as many pairs as on the same rows added in one call (small sorted runs are
+    sorted together as the index grows)."""
+    n, step, dim = 60000, 37, 128
+    x = synthetic.mixture_u8(n, seed=3).cpu().numpy()
+    q = synthetic.mixture_u8(400, seed=4).cpu().numpy()
+    if dtype == "float32":
+        x, q = x.astype(np.float32) / 16, q.astype(np.float32) / 16
+    grown = certex.Index(dim)
+    grown.add(x[:20000])
+    rng = np.random.default_rng(2)
+    keep = np.ones(n, dtype=np.uint8)
+    for lo in range(20000, n, step):
+        grown.add(x[lo : lo + step])
+        if lo % (step * 100) == 20000 % (step * 100):  # every hundredth append: some of the newest rows go
+            gone = rng.choice(np.arange(max(lo - 2000, 0), lo + step), 50, replace=False)
+            grown.remove(gone)
+            keep[gone] = 0
+    whole = certex.Index(dim)
+    whole.add(x)
+    whole.remove(np.flatnonzero(keep == 0))
+    with certex.search_stats() as st_grown:
+        same(grown, x, q, 10, keep_row=keep)
+    with certex.search_stats() as st_whole:
+        same(whole, x, q, 10, keep_row=keep)
+    assert st_grown.dense_queries == 0 and st_grown.rescreened == 0
+    assert st_grown.survivors <= 1.25 * st_whole.survivors + 400 * 16
+
+
 @pytest.mark.parametrize("n_labels", [5, 50, 500, 5000])
 def test_search_by_label(n_labels):
     x, q = data(20000, 32, 200, "uint8")
