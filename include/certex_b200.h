@@ -322,6 +322,29 @@ CERTEX_B200_EXPORT cuvsError_t certexB200SearchStatic(cuvsResources_t res, cuvsD
                                                       int64_t n_queries, int64_t dim, int32_t k, int64_t* neighbors,
                                                       float* distances);
 
+/* ------------------------------------------------------------------------------- row shards on the GPUs of one process */
+/** An index split into contiguous row shards, one index per device: cuvs::neighbors::certex::sharded_index<T>
+ *  (cpp/include/cuvs/neighbors/certex_shards.hpp:39-60). */
+typedef struct certexB200Sharded* certexB200ShardedIndex_t;
+
+/** build_sharded (certex_shards.hpp:70-90, cpp/src/neighbors/certex/certex_shards.cu:56-83): `dataset` is a host matrix
+ *  [n, dim] of float32, float16, int8 or uint8; shard s is built on devices[s] from the rows
+ *  [n s / S, n (s + 1) / S), all shards at the same time on one host thread each. A device may appear more than once.
+ *  Of `params` the metric and anchor_stride are used. */
+CERTEX_B200_EXPORT cuvsError_t certexB200ShardedBuild(const int32_t* devices, int32_t n_shards,
+                                                      cuvsCertexIndexParams_t params, DLManagedTensor* dataset,
+                                                      certexB200ShardedIndex_t* index);
+CERTEX_B200_EXPORT cuvsError_t certexB200ShardedDestroy(certexB200ShardedIndex_t index);
+/** Number of vectors over all shards (sharded_index<T>::size, certex_shards.hpp:51-58). */
+CERTEX_B200_EXPORT cuvsError_t certexB200ShardedGetSize(certexB200ShardedIndex_t index, int64_t* size);
+/** search on a sharded index (certex_shards.hpp:104-120, certex_shards.cu:85-167): queries [nq, dim], neighbors int64
+ *  [nq, k] and distances float32 [nq, k] are HOST matrices. Every shard finds its exact k best on its own device (one
+ *  host thread per shard), the lists are merged by (score, global id). Every shard must hold at least k vectors.
+ *  Synchronous: the outputs are complete on return. */
+CERTEX_B200_EXPORT cuvsError_t certexB200ShardedSearch(cuvsCertexSearchParams_t params, certexB200ShardedIndex_t index,
+                                                       DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                                       DLManagedTensor* distances);
+
 /** Version string "major.minor.patch". */
 CERTEX_B200_EXPORT const char* certexB200Version(void);
 

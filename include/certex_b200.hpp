@@ -1,7 +1,8 @@
 // C++ face of libcertex_b200: the names, argument order and meaning of the reference's
 // cuvs::neighbors::certex API (cpp/include/cuvs/neighbors/certex.hpp: index_params 43-87, search_params 97-107,
 // index<T> 131-423, build 481-511, extend 534-557, set_labels 579-591, partition_by_labels 609-612, remove 632-641,
-// search 668-735, serialize / deserialize 764-767), header-only over the C ABI of certex_b200.h.
+// search 668-735, serialize / deserialize 764-767; cpp/include/cuvs/neighbors/certex_shards.hpp: sharded_index<T>,
+// build_sharded, search), header-only over the C ABI of certex_b200.h.
 //
 // The reference passes raft::resources and raft mdspan views; this header has no RAFT dependency and declares the two
 // small view types it needs (a pointer and extents, the same accessors: data_handle(), extent(i)). A caller that
@@ -14,6 +15,7 @@
 #include <string>
 #include <type_traits>
 #include <utility>
+#include <vector>
 
 #include "certex_b200.h"
 
@@ -300,6 +302,67 @@ void deserialize(resources const& res, const std::string& filename, index<T>* id
 {
   *idx = index<T>();
   detail::check(cuvsCertexDeserialize(res.handle(), filename.c_str(), idx->handle()));
+}
+
+/// certex_shards.hpp:39-60: contiguous row shards, one index per device; movable, not copyable.
+template <typename T>
+class sharded_index {
+ public:
+  sharded_index() = default;
+  explicit sharded_index(certexB200ShardedIndex_t h) : handle_(h) {}
+  ~sharded_index()
+  {
+    if (handle_) { certexB200ShardedDestroy(handle_); }
+  }
+  sharded_index(sharded_index&& o) noexcept : handle_(std::exchange(o.handle_, nullptr)) {}
+  sharded_index& operator=(sharded_index&& o) noexcept
+  {
+    if (this != &o) {
+      if (handle_) { certexB200ShardedDestroy(handle_); }
+      handle_ = std::exchange(o.handle_, nullptr);
+    }
+    return *this;
+  }
+  sharded_index(const sharded_index&)            = delete;
+  sharded_index& operator=(const sharded_index&) = delete;
+  int64_t size() const
+  {
+    int64_t n = 0;
+    detail::check(certexB200ShardedGetSize(handle_, &n));
+    return n;
+  }
+  certexB200ShardedIndex_t handle() const { return handle_; }
+
+ private:
+  certexB200ShardedIndex_t handle_ = nullptr;
+};
+
+/// certex_shards.hpp:70-90: one shard per entry of `devices` (a device may appear more than once), built in parallel.
+template <typename T>
+sharded_index<std::remove_cv_t<T>> build_sharded(std::vector<int> const& devices, index_params const& params,
+                                                 host_matrix_view<T> dataset)
+{
+  cuvsCertexIndexParams ip{};
+  ip.metric        = params.metric;
+  ip.anchor_stride = params.anchor_stride;
+  std::vector<int32_t> dev(devices.begin(), devices.end());
+  detail::tensor x(dataset.data, detail::dl_type<T>(), 2, dataset.rows, dataset.cols, true);
+  certexB200ShardedIndex_t h = nullptr;
+  detail::check(certexB200ShardedBuild(dev.data(), static_cast<int32_t>(dev.size()), &ip, x.ptr(), &h));
+  return sharded_index<std::remove_cv_t<T>>(h);
+}
+
+/// certex_shards.hpp:104-120: queries, neighbors and distances are host matrices; complete on return.
+template <typename T, typename U>
+void search(search_params const& params, sharded_index<T> const& idx, host_matrix_view<U> queries,
+            host_matrix_view<int64_t> neighbors, host_matrix_view<float> distances)
+{
+  static_assert(std::is_same_v<std::remove_cv_t<U>, T>, "the queries must have the element type of the index");
+  cuvsCertexSearchParams sp{params.anchors, params.batch_size, params.probe_lists};
+  detail::tensor q(queries.data, detail::dl_type<T>(), 2, queries.rows, queries.cols, true);
+  detail::tensor nb(neighbors.data, detail::dl_type<int64_t>(), 2, neighbors.rows, neighbors.cols, true);
+  detail::tensor ds(distances.data, detail::dl_type<float>(), 2, distances.rows, distances.cols, true);
+  detail::check(certexB200ShardedSearch(&sp, idx.handle(), q.ptr(), nb.ptr(), ds.ptr()));
 }
 
 }  // namespace certex_b200

@@ -111,6 +111,7 @@ SYMBOLS = [
     "certexB200StatsBegin", "certexB200StatsEnd", "certexB200IndexSetTestMode", "certexB200ScreenRaw",
     "certexB200PlanSegments", "certexB200SearchStatic", "certexB200Version",
     "certexB200SetThresholdHook", "certexB200IndexWillScreen", "certexB200PlanRouted",
+    "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -177,6 +178,10 @@ def lib():
                 L.certexB200PlanRouted.argtypes = [ctypes.c_int32, P(ctypes.c_int32), P(ctypes.c_int32), ctypes.c_int32,
                                                    ctypes.c_int32, ctypes.c_int32, P(ctypes.c_int32), ctypes.c_int32,
                                                    P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32)]
+                L.certexB200ShardedBuild.argtypes = [P(ctypes.c_int32), ctypes.c_int32, P(IndexParams), mt, P(vp)]
+                L.certexB200ShardedDestroy.argtypes = [vp]
+                L.certexB200ShardedGetSize.argtypes = [vp, P(i64)]
+                L.certexB200ShardedSearch.argtypes = [P(SearchParams), vp, mt, mt, mt]
                 L.certexB200SearchStatic.argtypes = [vp, ctypes.c_int, DLDataType, vp, i64, vp, i64, i64, ctypes.c_int32, vp, vp]
                 _lib = L
     return _lib

@@ -7,9 +7,12 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+#include <exception>
 #include <fstream>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 namespace {
@@ -148,6 +151,54 @@ void search_impl(cuvsResources_t res, cuvsCertexSearchParams_t params, cuvsCerte
   CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
   h.index->search(r, sp, q, nq, static_cast<int>(k), nb, ds, sc, f, id_base);
 }
+
+// ------------------------------------------------------------------------------------------- row shards on several GPUs
+/// One row shard: a device, a stream on it and the index of the shard's rows.
+struct Shard {
+  int device = 0;
+  Resources res;
+  std::unique_ptr<Index> index;
+  int64_t first_id = 0;
+};
+
+/// Restores the calling thread's current device when it goes out of scope.
+struct DeviceGuard {
+  int old = 0;
+  DeviceGuard() { CERTEX_CUDA(cudaGetDevice(&old)); }
+  ~DeviceGuard() { cudaSetDevice(old); }
+};
+
+/// Runs work(s) for every shard on a host thread of its own (the GPUs work at the same time, as in the reference's
+/// cpp/src/neighbors/certex/certex_shards.cu:105-135) and rethrows the first failure.
+template <typename Work>
+void for_each_shard(size_t n_shards, Work&& work)
+{
+  std::vector<std::exception_ptr> failed(n_shards);
+  std::vector<std::thread> threads;
+  for (size_t s = 0; s < n_shards; ++s) {
+    threads.emplace_back([&, s] {
+      try {
+        work(s);
+      } catch (...) {
+        failed[s] = std::current_exception();
+      }
+    });
+  }
+  for (auto& t : threads) { t.join(); }
+  for (auto& f : failed) {
+    if (f) { std::rethrow_exception(f); }
+  }
+}
+
+/// Device memory of one call from the stream's pool.
+struct PoolBuffer {
+  void* p = nullptr;
+  cudaStream_t stream;
+  PoolBuffer(size_t bytes, cudaStream_t s) : stream(s) { CERTEX_CUDA(cudaMallocAsync(&p, std::max<size_t>(bytes, 16), s)); }
+  ~PoolBuffer() { cudaFreeAsync(p, stream); }
+  PoolBuffer(const PoolBuffer&)            = delete;
+  PoolBuffer& operator=(const PoolBuffer&) = delete;
+};
 
 const char* prefix_of(int dtype)
 {
@@ -512,6 +563,138 @@ cuvsError_t certexB200PlanRouted(int32_t n_runs, const int32_t* n_query_tiles, c
   return translate([=] {
     *runs_done = plan_routed_flat(n_runs, n_query_tiles, n_base_tiles, panel_tiles, grid, max_segs, segs, cap_segs, n_segs,
                                   seg_begin);
+  });
+}
+
+struct certexB200Sharded {
+  std::vector<std::unique_ptr<Shard>> shards;
+  int dtype   = 0;
+  int64_t dim = 0;
+  int metric  = kL2;
+};
+
+cuvsError_t certexB200ShardedBuild(const int32_t* devices, int32_t n_shards, cuvsCertexIndexParams_t params,
+                                   DLManagedTensor* dataset, certexB200ShardedIndex_t* out)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(out != nullptr && devices != nullptr && n_shards >= 1, "certex: one device per shard, at least one");
+    CERTEX_EXPECTS(params != nullptr, "certex: null index parameters");
+    auto* x           = static_cast<const char*>(checked(dataset, 2, -1, 0, false, "the dataset"));
+    const DLTensor& t = dataset->dl_tensor;
+    CERTEX_EXPECTS(on_host(t), "certex: a sharded index is built from a host matrix");
+    const int dtype  = dtype_of(t.dtype);
+    const int64_t n  = t.shape[0], dim = t.shape[1];
+    CERTEX_EXPECTS(n >= n_shards, "certex: fewer vectors than shards");
+    IndexParams p;
+    p.metric        = metric_of(params->metric);
+    p.anchor_stride = params->anchor_stride;
+    auto sharded    = std::make_unique<certexB200Sharded>();
+    sharded->dtype  = dtype;
+    sharded->dim    = dim;
+    sharded->metric = p.metric;
+    sharded->shards.resize(static_cast<size_t>(n_shards));
+    const size_t row_bytes = static_cast<size_t>(dim) * (dtype == kF32 ? 4 : dtype == kF16 ? 2 : 1);
+    for_each_shard(static_cast<size_t>(n_shards), [&](size_t s) {
+      CERTEX_CUDA(cudaSetDevice(devices[s]));
+      auto sh    = std::make_unique<Shard>();  // Resources() reads the device that is current now
+      sh->device = devices[s];
+      CERTEX_CUDA(cudaStreamCreateWithFlags(&sh->res.stream, cudaStreamNonBlocking));
+      // shard s owns the ids [n s / S, n (s + 1) / S) (certex_shards.cu:70-75)
+      const int64_t lo = n * static_cast<int64_t>(s) / n_shards, hi = n * static_cast<int64_t>(s + 1) / n_shards;
+      sh->first_id     = lo;
+      sh->index        = std::make_unique<Index>(sh->res, p, dtype, dim);
+      sh->index->extend(sh->res, x + static_cast<size_t>(lo) * row_bytes, hi - lo, true);
+      sharded->shards[s] = std::move(sh);
+    });
+    *out = sharded.release();
+  });
+}
+
+cuvsError_t certexB200ShardedDestroy(certexB200ShardedIndex_t index)
+{
+  return translate([=] {
+    if (index == nullptr) { return; }
+    DeviceGuard guard;
+    for (auto& sh : index->shards) {
+      if (!sh) { continue; }
+      cudaSetDevice(sh->device);
+      sh->index.reset();
+      if (sh->res.stream) { cudaStreamDestroy(sh->res.stream); }
+    }
+    delete index;
+  });
+}
+
+cuvsError_t certexB200ShardedGetSize(certexB200ShardedIndex_t index, int64_t* size)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(index != nullptr && size != nullptr, "certex: null sharded index");
+    int64_t n = 0;
+    for (auto& sh : index->shards) { n += sh->index->size(); }
+    *size = n;
+  });
+}
+
+cuvsError_t certexB200ShardedSearch(cuvsCertexSearchParams_t params, certexB200ShardedIndex_t index,
+                                    DLManagedTensor* queries, DLManagedTensor* neighbors, DLManagedTensor* distances)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(index != nullptr && !index->shards.empty(), "certex: null sharded index");
+    CERTEX_EXPECTS(params != nullptr, "certex: null search parameters");
+    const void* q = checked(queries, 2, -1, 0, false, "the queries");
+    auto* nb      = static_cast<int64_t*>(checked(neighbors, 2, kDLInt, 64, false, "the neighbors"));
+    auto* ds      = static_cast<float*>(checked(distances, 2, kDLFloat, 32, false, "the distances"));
+    CERTEX_EXPECTS(on_host(queries->dl_tensor) && on_host(neighbors->dl_tensor) && on_host(distances->dl_tensor),
+                   "certex: a sharded search takes and returns host matrices");
+    CERTEX_EXPECTS(dtype_of(queries->dl_tensor.dtype) == index->dtype && queries->dl_tensor.shape[1] == index->dim,
+                   "certex: the queries must have the vector type and the dimension of the index");
+    const int64_t nq = queries->dl_tensor.shape[0], k = neighbors->dl_tensor.shape[1];
+    CERTEX_EXPECTS(neighbors->dl_tensor.shape[0] == nq && distances->dl_tensor.shape[0] == nq &&
+                     distances->dl_tensor.shape[1] == k,
+                   "certex: neighbors and distances must be [n_queries, k]");
+    CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
+    for (auto& sh : index->shards) {
+      CERTEX_EXPECTS(sh->index->size() >= k, "certex: every shard must hold at least k vectors");  // certex_shards.cu:97-99
+    }
+    if (nq == 0) { return; }
+    SearchParams sp;
+    sp.anchors     = params->anchors;
+    sp.batch_size  = params->batch_size;
+    sp.probe_lists = params->probe_lists;
+    const size_t S       = index->shards.size();
+    const size_t q_bytes = static_cast<size_t>(nq) * static_cast<size_t>(index->dim) *
+                           (index->dtype == kF32 ? 4 : index->dtype == kF16 ? 2 : 1);
+    const size_t cells = static_cast<size_t>(nq) * static_cast<size_t>(k);
+    std::vector<double> part_scores(S * cells);
+    std::vector<int64_t> part_ids(S * cells);
+    // every shard: its exact k best with global ids and fp64 scores
+    for_each_shard(S, [&](size_t s) {
+      Shard& sh = *index->shards[s];
+      CERTEX_CUDA(cudaSetDevice(sh.device));
+      cudaStream_t st = sh.res.stream;
+      PoolBuffer dq(q_bytes, st), ids(cells * 8, st), dist(cells * 4, st), scores(cells * 8, st);
+      CERTEX_CUDA(cudaMemcpyAsync(dq.p, q, q_bytes, cudaMemcpyHostToDevice, st));
+      sh.index->search(sh.res, sp, dq.p, nq, static_cast<int>(k), static_cast<int64_t*>(ids.p), static_cast<float*>(dist.p),
+                       static_cast<double*>(scores.p), Filter{}, sh.first_id);
+      CERTEX_CUDA(cudaMemcpyAsync(part_scores.data() + s * cells, scores.p, cells * 8, cudaMemcpyDeviceToHost, st));
+      CERTEX_CUDA(cudaMemcpyAsync(part_ids.data() + s * cells, ids.p, cells * 8, cudaMemcpyDeviceToHost, st));
+      sh.res.sync();
+    });
+    // merge by (score, id) on the first shard's device (the reference merges on the host, certex_shards.cu:144-166)
+    DeviceGuard guard;
+    Shard& first = *index->shards[0];
+    CERTEX_CUDA(cudaSetDevice(first.device));
+    cudaStream_t st = first.res.stream;
+    PoolBuffer dq(q_bytes, st), ps(S * cells * 8, st), pi(S * cells * 8, st), ids(cells * 8, st), dist(cells * 4, st);
+    CERTEX_CUDA(cudaMemcpyAsync(dq.p, q, q_bytes, cudaMemcpyHostToDevice, st));
+    CERTEX_CUDA(cudaMemcpyAsync(ps.p, part_scores.data(), S * cells * 8, cudaMemcpyHostToDevice, st));
+    CERTEX_CUDA(cudaMemcpyAsync(pi.p, part_ids.data(), S * cells * 8, cudaMemcpyHostToDevice, st));
+    merge_shards(first.res, static_cast<const double*>(ps.p), static_cast<const int64_t*>(pi.p), static_cast<int>(S),
+                 static_cast<int>(nq), static_cast<int>(k), dq.p, index->dtype, index->dim, index->metric,
+                 static_cast<int64_t*>(ids.p), static_cast<float*>(dist.p), nullptr);
+    CERTEX_CUDA(cudaMemcpyAsync(nb, ids.p, cells * 8, cudaMemcpyDeviceToHost, st));
+    CERTEX_CUDA(cudaMemcpyAsync(ds, dist.p, cells * 4, cudaMemcpyDeviceToHost, st));
+    first.res.sync();
   });
 }
 

@@ -339,66 +339,54 @@ def merge_shards(queries, part_scores, part_ids, metric="l2", return_scores=Fals
 
 class ShardedIndex:
     """Exact k-NN over several GPUs of one process: contiguous row shards, one index per device, shard s owning the
-    ids [n s / S, n (s + 1) / S) (the reference's ShardedIndex, certex/index.py:400-457). Every shard computes its
-    exact local top-k, the per-shard lists are copied to the first device and merged there by (score, id). The vectors
-    and the queries are host arrays; results are numpy arrays. For one process per GPU use `DistributedIndex`."""
+    ids [n s / S, n (s + 1) / S) (the reference's ShardedIndex, certex/index.py:400-457). The library runs one host
+    thread per shard, so the GPUs build and search at the same time; every shard computes its exact local top-k and
+    the lists are merged by (score, id) on the first device. The vectors and the queries are host arrays; results are
+    numpy arrays. For one process per GPU use `DistributedIndex`."""
 
     def __init__(self, dim, devices, metric="l2", width="auto", storage="device", anchor_stride=16, n_lists=0,
                  local_projections=False):
         _need(metric in METRICS and storage in ("device", "host"), "unknown metric or storage")
         self.d, self.devices, self.metric = dim, list(devices), metric
         self.anchor_stride = anchor_stride
-        self.shards, self.first, self._dtype, self._n = [], [], None, 0
-        self._pool = None
+        self._handle, self._dtype, self._n = None, None, 0
+
+    def __del__(self):
+        if getattr(self, "_handle", None) is not None:
+            L.lib().certexB200ShardedDestroy(self._handle)
+            self._handle = None
 
     def add(self, x):
-        _need(not self.shards, "a sharded index is built by one addition")
+        _need(self._handle is None, "a sharded index is built by one addition")
         t, _ = _as_torch(x)
         _need(t.ndim == 2 and t.shape[1] == self.d and not t.is_cuda, "a host matrix (n, dim)")
         if t.dtype not in _INDEX_DTYPES or (self.metric == "cosine" and not t.dtype.is_floating_point):
             t = t.float()
-        n, S = t.shape[0], len(self.devices)
-        for s, dev in enumerate(self.devices):
-            lo, hi = n * s // S, n * (s + 1) // S
-            with torch.cuda.device(dev):
-                idx = Index(self.d, metric=self.metric, anchor_stride=self.anchor_stride)
-                idx.add(t[lo:hi].contiguous().cuda())
-            self.shards.append(idx)
-            self.first.append(lo)
-        self._dtype, self._n = t.dtype, n
-        return np.arange(n)
+        t = t.contiguous()
+        params = L.IndexParams(metric=L.METRIC_CODE[self.metric], anchor_stride=self.anchor_stride)
+        devices = (ctypes.c_int32 * len(self.devices))(*self.devices)
+        handle = ctypes.c_void_p()
+        L.check(L.lib().certexB200ShardedBuild(devices, len(self.devices), ctypes.byref(params), L.Tensor(t).ref,
+                                               ctypes.byref(handle)))
+        self._handle, self._dtype, self._n = handle, t.dtype, t.shape[0]
+        return np.arange(self._n)
 
     @property
     def ntotal(self):
         return self._n
 
     def search(self, q, k=10, batch=2048, anchors=128, probe_lists=2):
-        _need(bool(self.shards), "add vectors first")
+        _need(self._handle is not None, "add vectors first")
         Q = _to_dtype(_as_torch(q)[0].cpu(), self._dtype).contiguous()
-        for idx in self.shards:
-            _need(k <= int(idx.core.info().size), "every shard needs at least k vectors")
-        def one(shard):  # a host thread per shard, like the reference (certex_shards.cu:105-135): the GPUs work at once
-            dev, idx, lo = shard
-            with torch.cuda.device(dev):
-                _, I, Sc = idx.search(Q.cuda(), k=k, batch=batch, return_scores=True, id_base=lo)
-                torch.cuda.current_stream().synchronize()
-            return Sc, I
-
-        shards = list(zip(self.devices, self.shards, self.first))
-        if len(shards) == 1:
-            results = [one(shards[0])]
-        else:
-            if self._pool is None:  # the threads live as long as the index: each keeps its resource handles
-                from concurrent.futures import ThreadPoolExecutor
-
-                self._pool = ThreadPoolExecutor(max_workers=len(shards))
-            results = list(self._pool.map(one, shards))
-        parts_s, parts_i = [r[0] for r in results], [r[1] for r in results]
-        with torch.cuda.device(self.devices[0]):
-            ps = torch.stack([p.cuda() for p in parts_s])
-            pi = torch.stack([p.cuda() for p in parts_i])
-            D, I = merge_shards(Q.cuda(), ps, pi, self.metric)
-        return D.cpu().numpy(), I.cpu().numpy()
+        _need(Q.ndim == 2 and Q.shape[1] == self.d, "queries must be a matrix (nq, dim)")
+        I = torch.empty((Q.shape[0], k), dtype=torch.int64)
+        D = torch.empty((Q.shape[0], k), dtype=torch.float32)
+        sp = L.SearchParams(anchors, batch, probe_lists)
+        L.check(L.lib().certexB200ShardedSearch(ctypes.byref(sp), self._handle, L.Tensor(Q).ref, L.Tensor(I).ref,
+                                                L.Tensor(D).ref))
+        if self.metric == "cosine":
+            D = 1 - D
+        return D.numpy(), I.numpy()
 
 
 def search(xb, xq=None, k=10, metric="l2", **index_options):

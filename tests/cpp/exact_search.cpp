@@ -1,6 +1,6 @@
 // A C++ caller of include/certex_b200.hpp in the shape of the reference's examples/cpp/exact_search.cu: build from a
-// host matrix, extend from device memory, remove, search with and without a bitset filter and by label, compare with
-// an fp64 loop over all vectors (ties to the smaller id). Prints "ok" and returns 0 when everything agrees.
+// host matrix, extend from device memory, remove, search with and without a bitset filter and by label, search three
+// row shards, compare with an fp64 loop over all vectors (ties to the smaller id). Prints "ok" and returns 0 when everything agrees.
 #include <cuda_runtime_api.h>
 
 #include <algorithm>
@@ -140,6 +140,33 @@ int main(int argc, char** argv)
       cx::search(res, sp, loaded, queries, cx::device_vector_view<const int32_t>{d_qlab, kNq}, neighbors, distances);
       res.sync();
       if (loaded.size() != kN || !same("search by labels after reload", x, q, &keep, &lab, &qlab, d_ids, d_dist)) { return 8; }
+    }
+
+    // row shards: three shards on this device, host matrices in and out, merged by (score, id)
+    {
+      cx::host_matrix_view<const float> all;
+      all.data = x.data(), all.rows = kN, all.cols = kDim;
+      auto sharded = cx::build_sharded(std::vector<int>{0, 0, 0}, ip, all);
+      if (sharded.size() != kN) { return 10; }
+      std::vector<int64_t> h_ids(kNq * kK);
+      std::vector<float> h_dist(kNq * kK);
+      cx::host_matrix_view<const float> hq;
+      hq.data = q.data(), hq.rows = kNq, hq.cols = kDim;
+      cx::host_matrix_view<int64_t> hn;
+      hn.data = h_ids.data(), hn.rows = kNq, hn.cols = kK;
+      cx::host_matrix_view<float> hd;
+      hd.data = h_dist.data(), hd.rows = kNq, hd.cols = kK;
+      cx::search(sp, sharded, hq, hn, hd);
+      const std::vector<char> everything(kN, 1);
+      for (int i = 0; i < kNq; ++i) {
+        const auto want = brute(x, q.data() + i * kDim, everything);
+        for (int j = 0; j < kK; ++j) {
+          if (h_ids[i * kK + j] != want[j].second || h_dist[i * kK + j] != float(want[j].first)) {
+            std::fprintf(stderr, "sharded search: query %d entry %d differs\n", i, j);
+            return 11;
+          }
+        }
+      }
     }
 
     // errors are exceptions with the library's message
