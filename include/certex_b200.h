@@ -186,9 +186,11 @@ CERTEX_B200_EXPORT cuvsError_t cuvsCertexSearchWithLabels(cuvsResources_t res, c
                                                           DLManagedTensor* query_labels, DLManagedTensor* neighbors,
                                                           DLManagedTensor* distances);
 /** certex.h:214-216: save the index with its vectors. The file starts with the reference's 4-byte NumPy dtype
- *  prefix; the rest is this library's own layout (not interchangeable with files of the reference). */
+ *  prefix; the rest is this library's own layout (the reference cannot read it). */
 CERTEX_B200_EXPORT cuvsError_t cuvsCertexSerialize(cuvsResources_t res, const char* filename, cuvsCertexIndex_t index);
-/** certex.h:220-222: load into an empty handle; the vector type comes from the file. */
+/** certex.h:220-222: load into an empty handle; the vector type comes from the file. Reads this library's files and
+ *  files in the reference's layout (cpp/src/neighbors/certex/certex_serialize.cu:40-132, without k-means lists): their
+ *  vectors, removal flags and labels; the screening data is made anew. */
 CERTEX_B200_EXPORT cuvsError_t cuvsCertexDeserialize(cuvsResources_t res, const char* filename,
                                                      cuvsCertexIndex_t index);
 

@@ -1323,8 +1323,87 @@ void Index::save(const Resources& res, std::ostream& os) const
   CERTEX_EXPECTS(os.good(), "certex: cannot write the index file");
 }
 
+// An .npy record as RAFT's serialize_scalar / serialize_mdspan write it (the reference's files are a sequence of
+// them): "\x93NUMPY", version, header length, a Python dict with 'descr', 'fortran_order' and 'shape', then the data.
+namespace {
+struct NpyRecord {
+  size_t item  = 0;  // bytes per element
+  size_t count = 1;  // elements
+  char kind    = 0;  // 'i', 'u', 'f', ...
+  int ndim     = 0;
+  bool fortran = false;
+};
+
+NpyRecord npy_header(std::istream& is)
+{
+  char magic[8];
+  is.read(magic, 8);
+  CERTEX_EXPECTS(is.good() && std::memcmp(magic, "\x93NUMPY", 6) == 0, "certex: the index file is damaged (no array record)");
+  uint32_t len = 0;
+  if (magic[6] == 1) {
+    len = take<uint16_t>(is);
+  } else {
+    len = take<uint32_t>(is);
+  }
+  CERTEX_EXPECTS(len > 0 && len < (1u << 20), "certex: the index file is damaged (array header)");
+  std::string text(len, '\0');
+  is.read(text.data(), len);
+  CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+  NpyRecord r;
+  const size_t at = text.find("'descr'");
+  CERTEX_EXPECTS(at != std::string::npos, "certex: the index file is damaged (array type)");
+  const size_t q0 = text.find('\'', text.find(':', at));
+  const size_t q1 = text.find('\'', q0 + 1);
+  CERTEX_EXPECTS(q0 != std::string::npos && q1 != std::string::npos && q1 > q0 + 2, "certex: the index file is damaged (array type)");
+  const std::string descr = text.substr(q0 + 1, q1 - q0 - 1);  // e.g. "<i4", "|u1", "<f8"
+  CERTEX_EXPECTS(descr[0] != '>', "certex: big-endian index files are not supported");
+  r.kind = descr[1];
+  r.item = static_cast<size_t>(std::stoul(descr.substr(2)));
+  const size_t sh = text.find("'shape'");
+  CERTEX_EXPECTS(sh != std::string::npos, "certex: the index file is damaged (array shape)");
+  const size_t p0 = text.find('(', sh), p1 = text.find(')', sh);
+  CERTEX_EXPECTS(p0 != std::string::npos && p1 != std::string::npos, "certex: the index file is damaged (array shape)");
+  size_t c = p0 + 1;
+  while (c < p1) {
+    while (c < p1 && (text[c] == ' ' || text[c] == ',')) { ++c; }
+    if (c >= p1) { break; }
+    size_t used = 0;
+    r.count *= static_cast<size_t>(std::stoull(text.substr(c, p1 - c), &used));
+    c += used;
+    ++r.ndim;
+  }
+  r.fortran = text.find("'fortran_order': True") != std::string::npos;
+  return r;
+}
+
+template <typename T>
+T npy_scalar(std::istream& is)
+{
+  const NpyRecord r = npy_header(is);
+  CERTEX_EXPECTS(r.count == 1 && r.item == sizeof(T), "certex: the index file is damaged (scalar of another type)");
+  return take<T>(is);
+}
+
+void npy_skip(std::istream& is)
+{
+  const NpyRecord r = npy_header(is);
+  is.ignore(static_cast<std::streamsize>(r.item * r.count));
+  CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+}
+
+void npy_read(std::istream& is, char* dst, size_t bytes)
+{
+  const NpyRecord r = npy_header(is);
+  CERTEX_EXPECTS(r.item * r.count == bytes, "certex: the index file is damaged (array of another size)");
+  CERTEX_EXPECTS(r.ndim < 2 || !r.fortran, "certex: column-major arrays in an index file are not supported");
+  is.read(dst, static_cast<std::streamsize>(bytes));
+  CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+}
+}  // namespace
+
 std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int dtype)
 {
+  if (is.peek() == 0x93) { return load_reference_file(res, is, dtype); }
   CERTEX_EXPECTS(take<uint32_t>(is) == kFileMagic, "certex: not an index file of this library");
   CERTEX_EXPECTS(take<uint32_t>(is) == kFileVersion, "certex: unknown index file version");
   IndexParams p;
@@ -1334,15 +1413,63 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
   const int64_t n     = take<int64_t>(is);
   const int64_t n_rem = take<int64_t>(is);
   const bool labeled  = take<int32_t>(is) != 0;
-  auto idx            = std::make_unique<Index>(res, p, dtype, dim);
+  return from_blocks(res, p, dtype, dim, n, n_rem, labeled, [&](char* dst, size_t bytes) {
+    is.read(dst, static_cast<std::streamsize>(bytes));
+    CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+  });
+}
+
+// A file written by the reference's serialize (cpp/src/neighbors/certex/certex_serialize.cu:40-132, format "CERX"
+// version 1, read back at 135-240). Of its records the engine needs the vectors, the removal flags and the labels;
+// the projection, the certificate rows and the anchors are the reference's screening data and are skipped (this
+// engine screens with its own codes, made from the vectors on load).
+std::unique_ptr<Index> Index::load_reference_file(const Resources& res, std::istream& is, int dtype)
+{
+  CERTEX_EXPECTS(npy_scalar<int32_t>(is) == 0x43455258, "certex: not a CertEx index file");
+  CERTEX_EXPECTS(npy_scalar<int32_t>(is) == 1, "certex: unsupported CertEx serialization version");
+  IndexParams p;
+  const int metric = npy_scalar<int32_t>(is);  // cuvs::distance::DistanceType
+  CERTEX_EXPECTS(metric == 0 || metric == 2 || metric == 6, "certex: the file's metric is not L2Expanded, InnerProduct or CosineExpanded");
+  p.metric            = metric == 0 ? kL2 : metric == 6 ? kIP : kCos;
+  const int64_t dim   = npy_scalar<int64_t>(is);
+  p.width             = npy_scalar<int32_t>(is);
+  p.anchor_stride     = npy_scalar<int32_t>(is);
+  p.host_vectors      = npy_scalar<int32_t>(is) != 0;
+  const int64_t n     = npy_scalar<int64_t>(is);
+  const int64_t n_rem = npy_scalar<int64_t>(is);
+  const bool labeled  = npy_scalar<int32_t>(is) != 0;
+  p.int8_rows         = npy_scalar<int32_t>(is) != 0;
+  for (int i = 0; i < 6; ++i) { (void)npy_scalar<double>(is); }  // alpha and the five certificate maxima
+  npy_skip(is);  // center
+  npy_skip(is);  // basis
+  if (p.int8_rows) {
+    (void)npy_scalar<double>(is);  // largest lifted squared norm
+    npy_skip(is);                  // int8 codes
+    npy_skip(is);                  // their scalars
+  } else {
+    npy_skip(is);  // fp16 certificate rows
+  }
+  npy_skip(is);  // anchor rows
+  npy_skip(is);  // anchor vectors
+  auto idx = from_blocks(res, p, dtype, dim, n, n_rem, labeled, [&](char* dst, size_t bytes) { npy_read(is, dst, bytes); });
+  // k-means lists come last; with lists the reference keeps its rows in list order, which is not read here
+  CERTEX_EXPECTS(npy_scalar<int32_t>(is) == 0, "certex: index files with k-means lists are not supported");
+  return idx;
+}
+
+// The index of n vectors from three blocks in this order: the vectors [n, dim] dense, the removal flags [n] bytes,
+// and (labeled) the labels [n] int32.
+std::unique_ptr<Index> Index::from_blocks(const Resources& res, const IndexParams& p, int dtype, int64_t dim, int64_t n,
+                                          int64_t n_rem, bool labeled, const std::function<void(char*, size_t)>& next_block)
+{
+  CERTEX_EXPECTS(n >= 0 && n_rem >= 0 && n_rem <= n, "certex: the index file is damaged (sizes)");
+  auto idx = std::make_unique<Index>(res, p, dtype, dim);
   if (n > 0) {
     const size_t row_bytes = static_cast<size_t>(dim) * dtype_size(dtype);
     std::vector<char> host(static_cast<size_t>(n) * std::max(row_bytes, sizeof(int32_t)));
-    is.read(host.data(), static_cast<std::streamsize>(static_cast<size_t>(n) * row_bytes));
-    CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+    next_block(host.data(), static_cast<size_t>(n) * row_bytes);
     idx->extend(res, host.data(), n, true);
-    is.read(host.data(), static_cast<std::streamsize>(n));
-    CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+    next_block(host.data(), static_cast<size_t>(n));
     CERTEX_CUDA(cudaMemcpyAsync(idx->removed_, host.data(), static_cast<size_t>(n), cudaMemcpyHostToDevice, res.stream));
     res.sync();
     idx->n_removed_ = n_rem;
@@ -1363,8 +1490,7 @@ std::unique_ptr<Index> Index::load(const Resources& res, std::istream& is, int d
       res.sync();
     }
     if (labeled) {
-      is.read(host.data(), static_cast<std::streamsize>(n * 4));
-      CERTEX_EXPECTS(is.good(), "certex: the index file is truncated");
+      next_block(host.data(), static_cast<size_t>(n) * 4);
       Scratch scratch(res.stream);
       int32_t* tmp = scratch.get<int32_t>(static_cast<size_t>(n));
       CERTEX_CUDA(cudaMemcpyAsync(tmp, host.data(), static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, res.stream));

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <functional>
 #include <iosfwd>
 #include <memory>
 #include <mutex>
@@ -127,6 +128,7 @@ class Index {
 
   /// Writes / reads the index (parameters, vectors, removed flags, labels) after the 4-byte dtype prefix of a file.
   void save(const Resources& res, std::ostream& os) const;
+  /// load() also reads a file written by the reference (format "CERX" version 1): its vectors, removal flags and labels.
   static std::unique_ptr<Index> load(const Resources& res, std::istream& is, int dtype);
 
   /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity,
@@ -148,6 +150,10 @@ class Index {
   bool will_screen(int k) const;
 
  private:
+  static std::unique_ptr<Index> load_reference_file(const Resources& res, std::istream& is, int dtype);
+  static std::unique_ptr<Index> from_blocks(const Resources& res, const IndexParams& p, int dtype, int64_t dim, int64_t n,
+                                            int64_t n_rem, bool labeled,
+                                            const std::function<void(char*, size_t)>& next_block);
   void search_screened(const Resources& res, const uint8_t* qbuf, const float* shift, const void* queries, size_t row_bytes,
                        int q0, int nq, int k, double* best_s, int32_t* best_row, int32_t* ovf_list,
                        unsigned int* ovf_count, unsigned long long* stats, int* err, int anchor_stride, int64_t n,

@@ -369,3 +369,59 @@ def test_removed_rows_exceeding_k_leave_missing_entries():
     index.remove(np.arange(60))
     D, I = index.search(q, k=10)
     assert (I[:, 4:] == -1).all() and (I[:, :4] >= 60).all() and np.isinf(D[:, 4:]).all()
+
+
+def _write_reference_file(path, x, metric_code, removed, labels, int8_rows, width=27, stride=16):
+    """A file in the layout the reference's serialize writes (cpp/src/neighbors/certex/certex_serialize.cu:40-132):
+    the 4-byte dtype prefix, then one .npy record per scalar and array, in its order. The projection, certificate rows
+    and anchors hold filler values: they are the reference's own screening data."""
+    from numpy.lib import format as npy
+
+    n, d = x.shape
+    prefix = {"uint8": b"|u1\0", "int8": b"|i1\0", "float32": b"<f4\0", "float16": b"<f2\0"}[str(x.dtype)]
+    mp = 64
+    with open(path, "wb") as f:
+        def put(value, dtype=None):
+            npy.write_array(f, np.asarray(value, dtype=dtype), version=(1, 0))
+
+        f.write(prefix)
+        put(0x43455258, np.int32), put(1, np.int32), put(metric_code, np.int32), put(d, np.int64), put(width, np.int32)
+        put(stride, np.int32), put(0, np.int32), put(n, np.int64), put(int(removed.sum()), np.int64)
+        put(0 if labels is None else 1, np.int32), put(1 if int8_rows else 0, np.int32)
+        for v in (0.5, 1.0, 2.0, 3.0, 4.0, 5.0):  # alpha and the certificate maxima
+            put(v, np.float64)
+        put(np.zeros(d, np.float32)), put(np.zeros((width, d), np.float32))  # center, basis
+        if int8_rows:
+            put(7.0, np.float64), put(np.zeros((n, 64), np.int8)), put(np.zeros((n, 5), np.float32))
+        else:
+            put(np.zeros((n, mp), np.float16))
+        na = (n + stride - 1) // stride
+        put(np.zeros((na, mp), np.float16)), put(np.zeros((na, d), x.dtype))
+        put(x), put(removed.astype(np.uint8))
+        if labels is not None:
+            put(labels.astype(np.int32))
+        put(0, np.int32)  # no k-means lists
+
+
+@pytest.mark.parametrize("dtype,metric,int8_rows,labeled", [("uint8", "l2", True, True), ("float32", "cosine", False, False),
+                                                            ("float16", "ip", False, True)])
+def test_load_a_file_in_the_reference_layout(tmp_path, dtype, metric, int8_rows, labeled):
+    x, q = data(15000, 40, 100, dtype, seed=21)
+    rng = np.random.default_rng(4)
+    removed = (rng.random(15000) < 0.03)
+    lab = rng.integers(0, 6, 15000).astype(np.int32) if labeled else None
+    path = tmp_path / "reference_layout.bin"
+    _write_reference_file(path, x, {"l2": 0, "cosine": 2, "ip": 6}[metric], removed, lab, int8_rows)
+    loaded = certex.Index.load(path)
+    assert loaded.ntotal == 15000 - int(removed.sum()) and loaded.metric == metric
+    keep = (~removed).astype(np.uint8)
+    same(loaded, x, q, 10, metric, keep_row=keep)
+    if labeled:
+        ql = rng.integers(0, 6, 100).astype(np.int32)
+        same(loaded, x, q, 10, metric, keep_row=keep, row_labels=lab, query_labels=ql, labels=ql)
+    # a file with k-means lists is refused, not misread
+    with open(path, "r+b") as f:
+        f.seek(-4, 2)
+        f.write(np.int32(3).tobytes())
+    with pytest.raises(Exception, match="lists"):
+        certex.Index.load(path)
