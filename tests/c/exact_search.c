@@ -171,6 +171,28 @@ int main(int argc, char** argv)
     if (compare("search by labels after reload", x, lab, q, qlab, ids, dist)) { return 6; }
   }
 
+  /* two row shards on this device: host matrices in and out */
+  {
+    int64_t xs[2] = {N, DIM}, qs[2] = {NQ, DIM}, os[2] = {NQ, K};
+    DLManagedTensor hx, hq, hn, hd;
+    tensor(&hx, (void*)x, xs, 2, kDLUInt, 8);
+    tensor(&hq, (void*)q, qs, 2, kDLUInt, 8);
+    tensor(&hn, ids, os, 2, kDLInt, 64);
+    tensor(&hd, dist, os, 2, kDLFloat, 32);
+    hx.dl_tensor.device.device_type = hq.dl_tensor.device.device_type = kDLCPU;
+    hn.dl_tensor.device.device_type = hd.dl_tensor.device.device_type = kDLCPU;
+    const int32_t devices[2]        = {0, 0};
+    certexB200ShardedIndex_t sharded = NULL;
+    int64_t total                    = 0;
+    CHECK(certexB200ShardedBuild(devices, 2, ip, &hx, &sharded));
+    CHECK(certexB200ShardedGetSize(sharded, &total));
+    if (total != N) { return 8; }
+    memset(ids, 0, sizeof(int64_t) * NQ * K);
+    CHECK(certexB200ShardedSearch(sp, sharded, &hq, &hn, &hd));
+    if (compare("sharded search", x, lab, q, NULL, ids, dist)) { return 9; }
+    CHECK(certexB200ShardedDestroy(sharded));
+  }
+
   /* an error comes back as a code and a message */
   int64_t bad_shape[2] = {NQ, DIM + 1};
   DLManagedTensor tbad;
