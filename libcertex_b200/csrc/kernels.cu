@@ -642,49 +642,122 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
   if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>((prefix + base) ^ 0x80000000u); }
 }
 
-// Exact score of an 8-bit row against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot
-// products (int32 is enough: 255^2 * 4096 < 2^31), the score |q|^2 + |x|^2 - 2 <q, x> (L2) or |q|^2 - 2 <q, x> in
-// int64. Every partial sum of the fp64 loop over the coordinates is an integer below 2^53, so that loop returns this
-// very integer: the results are bit-identical, without one conversion to double per coordinate. |score| < 2^31.
-// qb: the query's bytes in shared memory, zero padded to whole 16-byte vectors like the stored row.
+// Exact scores of 8-bit rows against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot products
+// (int32 is enough: 255^2 * 4096 < 2^31), the score |q|^2 + |x|^2 - 2 <q, x> (L2) or |q|^2 - 2 <q, x> in int64. Every
+// partial sum of the fp64 loop over the coordinates is an integer below 2^53, so that loop returns this very integer:
+// the results are bit-identical, without one conversion to double per coordinate. |score| < 2^31.
+// A row is spread over kRowLanes adjacent lanes of a warp: lane `sub` takes the 16-byte pieces sub, sub + 8, ..., so
+// that the lanes of a row read one 128-byte line together and a warp's load covers four whole lines; the partial sums
+// are added across the lanes by shuffles (integers: exact in any order). kRowUnroll rows per lane group are in flight
+// at once. Every lane of the warp must call it; row < 0 = no row. The results are valid in all lanes of a row.
+// qb: the query's bytes in shared memory, zero padded to whole 16-byte vectors like the stored rows.
+constexpr int kRowLanes  = 8;
+constexpr int kRowUnroll = 4;
 template <typename T, int METRIC>
-__device__ __forceinline__ long long int_row_score(const uint8_t* row, int d, const uint4* qb, long long qq)
+__device__ __forceinline__ void int_row_scores(const uint8_t* vectors, size_t pitch, const int32_t (&row)[kRowUnroll], int d,
+                                               const uint4* qb, long long qq, int sub, long long (&score)[kRowUnroll])
 {
-  const uint4* p  = reinterpret_cast<const uint4*>(row);
   const int n_vec = (d + 15) / 16;
-  int ip = 0, xx = 0;
-  for (int c = 0; c < n_vec; ++c) {
-    const uint4 w = __ldg(p + c);
+  int ip[kRowUnroll], xx[kRowUnroll];
+  const uint4* p[kRowUnroll];
+#pragma unroll
+  for (int u = 0; u < kRowUnroll; ++u) {
+    ip[u] = 0, xx[u] = 0;
+    p[u] = reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(max(row[u], 0)) * pitch);
+  }
+  for (int c = sub; c < n_vec; c += kRowLanes) {
     const uint4 a = qb[c];
-    if constexpr (std::is_same<T, int8_t>::value) {
-      ip = __dp4a(static_cast<int>(w.x), static_cast<int>(a.x), ip);
-      ip = __dp4a(static_cast<int>(w.y), static_cast<int>(a.y), ip);
-      ip = __dp4a(static_cast<int>(w.z), static_cast<int>(a.z), ip);
-      ip = __dp4a(static_cast<int>(w.w), static_cast<int>(a.w), ip);
-      if constexpr (METRIC == kL2) {
-        xx = __dp4a(static_cast<int>(w.x), static_cast<int>(w.x), xx);
-        xx = __dp4a(static_cast<int>(w.y), static_cast<int>(w.y), xx);
-        xx = __dp4a(static_cast<int>(w.z), static_cast<int>(w.z), xx);
-        xx = __dp4a(static_cast<int>(w.w), static_cast<int>(w.w), xx);
-      }
-    } else {
-      ip = static_cast<int>(__dp4a(w.x, a.x, static_cast<unsigned>(ip)));
-      ip = static_cast<int>(__dp4a(w.y, a.y, static_cast<unsigned>(ip)));
-      ip = static_cast<int>(__dp4a(w.z, a.z, static_cast<unsigned>(ip)));
-      ip = static_cast<int>(__dp4a(w.w, a.w, static_cast<unsigned>(ip)));
-      if constexpr (METRIC == kL2) {
-        xx = static_cast<int>(__dp4a(w.x, w.x, static_cast<unsigned>(xx)));
-        xx = static_cast<int>(__dp4a(w.y, w.y, static_cast<unsigned>(xx)));
-        xx = static_cast<int>(__dp4a(w.z, w.z, static_cast<unsigned>(xx)));
-        xx = static_cast<int>(__dp4a(w.w, w.w, static_cast<unsigned>(xx)));
+    uint4 w[kRowUnroll];
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u) { w[u] = row[u] >= 0 ? __ldg(p[u] + c) : make_uint4(0, 0, 0, 0); }
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u) {
+      if constexpr (std::is_same<T, int8_t>::value) {
+        ip[u] = __dp4a(static_cast<int>(w[u].x), static_cast<int>(a.x), ip[u]);
+        ip[u] = __dp4a(static_cast<int>(w[u].y), static_cast<int>(a.y), ip[u]);
+        ip[u] = __dp4a(static_cast<int>(w[u].z), static_cast<int>(a.z), ip[u]);
+        ip[u] = __dp4a(static_cast<int>(w[u].w), static_cast<int>(a.w), ip[u]);
+        if constexpr (METRIC == kL2) {
+          xx[u] = __dp4a(static_cast<int>(w[u].x), static_cast<int>(w[u].x), xx[u]);
+          xx[u] = __dp4a(static_cast<int>(w[u].y), static_cast<int>(w[u].y), xx[u]);
+          xx[u] = __dp4a(static_cast<int>(w[u].z), static_cast<int>(w[u].z), xx[u]);
+          xx[u] = __dp4a(static_cast<int>(w[u].w), static_cast<int>(w[u].w), xx[u]);
+        }
+      } else {
+        ip[u] = static_cast<int>(__dp4a(w[u].x, a.x, static_cast<unsigned>(ip[u])));
+        ip[u] = static_cast<int>(__dp4a(w[u].y, a.y, static_cast<unsigned>(ip[u])));
+        ip[u] = static_cast<int>(__dp4a(w[u].z, a.z, static_cast<unsigned>(ip[u])));
+        ip[u] = static_cast<int>(__dp4a(w[u].w, a.w, static_cast<unsigned>(ip[u])));
+        if constexpr (METRIC == kL2) {
+          xx[u] = static_cast<int>(__dp4a(w[u].x, w[u].x, static_cast<unsigned>(xx[u])));
+          xx[u] = static_cast<int>(__dp4a(w[u].y, w[u].y, static_cast<unsigned>(xx[u])));
+          xx[u] = static_cast<int>(__dp4a(w[u].z, w[u].z, static_cast<unsigned>(xx[u])));
+          xx[u] = static_cast<int>(__dp4a(w[u].w, w[u].w, static_cast<unsigned>(xx[u])));
+        }
       }
     }
   }
-  return qq + static_cast<long long>(xx) - 2ll * static_cast<long long>(ip);
+#pragma unroll
+  for (int u = 0; u < kRowUnroll; ++u) {
+#pragma unroll
+    for (int o = 1; o < kRowLanes; o <<= 1) {
+      ip[u] += __shfl_xor_sync(0xffffffffu, ip[u], o);
+      if constexpr (METRIC == kL2) { xx[u] += __shfl_xor_sync(0xffffffffu, xx[u], o); }
+    }
+    score[u] = qq + static_cast<long long>(xx[u]) - 2ll * static_cast<long long>(ip[u]);
+  }
+}
+
+__device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v                              = other < v ? other : v;
+  }
+  return v;
+}
+
+// The k smallest of n2 distinct 64-bit keys in shared memory (~0 = none), ascending into out [k], for small k and a
+// block of at most kSelectWarps warps: every warp draws the k smallest of its share of the keys by k rounds of a warp
+// minimum, then the first warp draws the k smallest of those lists the same way. No key moves in shared memory.
+constexpr int kSelectWarps = 4;
+constexpr int kSelectMaxK  = 32;
+__device__ void select_smallest_keys(const unsigned long long* key, int n2, int k, unsigned long long* lists,
+                                     unsigned long long* out)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  unsigned long long lo = 0;  // keys below lo are taken already
+  for (int r = 0; r < k; ++r) {
+    unsigned long long best = ~0ull;
+    for (int j = warp * 32 + lane; j < n2; j += n_warps * 32) {
+      const unsigned long long v = key[j];
+      if (v >= lo && v < best) { best = v; }
+    }
+    best = warp_min_u64(best);
+    if (lane == 0) { lists[warp * kSelectMaxK + r] = best; }
+    lo = best == ~0ull ? best : best + 1;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    lo = 0;
+    for (int r = 0; r < k; ++r) {
+      unsigned long long best = ~0ull;
+      for (int j = lane; j < n_warps * kSelectMaxK; j += 32) {
+        const unsigned long long v = (j % kSelectMaxK) < k ? lists[j] : ~0ull;
+        if (v >= lo && v < best) { best = v; }
+      }
+      best = warp_min_u64(best);
+      if (lane == 0) { out[r] = best; }
+      lo = best == ~0ull ? best : best + 1;
+    }
+  }
+  __syncthreads();
 }
 
 // ------------------------------------------------------------------------------------------- verify + select
-// Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap).
+// Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap); for 8-bit rows
+// the query's bytes (in the space of qd) | n2 64-bit keys.
 template <typename T, int METRIC>
 __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
@@ -718,15 +791,19 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
     const int padded   = (d + 15) / 16 * 16;
     for (int t = threadIdx.x; t < padded; t += blockDim.x) { qbytes[t] = t < d ? src[t] : 0; }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      long long a = 0;
-      for (int t = 0; t < d; ++t) {
-        const long long v = std::is_same<T, int8_t>::value ? static_cast<long long>(static_cast<int8_t>(qbytes[t]))
-                                                           : static_cast<long long>(qbytes[t]);
-        a += v * v;
+    if (threadIdx.x < 32) {  // |q|^2: 255^2 * 4096 < 2^31
+      int a = 0;
+      for (int t = threadIdx.x; t < padded / 4; t += 32) {
+        const uint32_t w = reinterpret_cast<const uint32_t*>(qbytes)[t];
+        a = std::is_same<T, int8_t>::value ? __dp4a(static_cast<int>(w), static_cast<int>(w), a)
+                                           : static_cast<int>(__dp4a(w, w, static_cast<unsigned>(a)));
       }
-      s_qq_int = a;
-      s_qq     = __ll2double_rn(a);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); }
+      if (threadIdx.x == 0) {
+        s_qq_int = a;
+        s_qq     = __ll2double_rn(static_cast<long long>(a));
+      }
     }
     __syncthreads();
   } else {
@@ -734,29 +811,85 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
   }
   const int n2 = max(next_pow2(static_cast<int>(c)), 2);
   const int32_t* mine = cand + static_cast<size_t>(blockIdx.x) * cap;
+  // One thread reports an overflowed query with the tighter threshold that the k-th best exact score `kth` among the
+  // listed candidates gives (+inf: fewer than k).
+  auto report_overflow = [&](double kth) {
+    const unsigned int pos = atomicAdd(ovf_count, 1u);
+    ovf_list[pos]          = q;
+    int32_t t              = rf.thr[blockIdx.x];
+    if (kth < CUDART_INF) {
+      // the screen's value of a row as good as the k-th: <q, x> - |x|^2 / 2 (L2), <q, x> (inner product),
+      // <q, x / |x|> (cosine)
+      const double value = METRIC == kCos ? sqrt(s_qq) * (1.0 - 0.5 * kth) : 0.5 * (s_qq - kth);
+      if (rf.kind == 1) {  // integer values: e = -floor(|x|^2 / 2) only raises a row's value
+        const double cv  = ceil(value);
+        const int32_t tv = cv >= 2147483647.0 ? 0x7fffffff : cv <= -2147483648.0 ? static_cast<int32_t>(0x80000000u)
+                                                                                    : static_cast<int32_t>(cv);
+        t = max(t, tv);
+      } else {             // fp16 codes: the value the pass computes may be lower by half the query's allowance
+        float f = __double2float_rd(value - 0.5 * static_cast<double>(rf.shift[q]));
+        f       = nextafterf(f, -CUDART_INF_F);
+        t       = __float_as_int(fmaxf(f, __int_as_float(t)));
+      }
+    }
+    rf.thr2[pos] = t;
+  };
   if constexpr (kBytes) {
     // integer scores (below 2^31 in magnitude) and ids sort as one 64-bit key: (score + 2^31) << 32 | id
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(sc);
-    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-      unsigned long long key = ~0ull;
-      if (i < static_cast<int>(c)) {
-        const int32_t row = mine[i];
-        if (admitted(adm, q, row)) {
-          const long long v = int_row_score<T, METRIC>(vectors + static_cast<size_t>(row) * pitch, d,
-                                                      reinterpret_cast<const uint4*>(qd), s_qq_int);
-          key = (static_cast<unsigned long long>(v + 2147483648ll) << 32) | static_cast<uint32_t>(row);
+    __shared__ unsigned long long s_lists[kSelectWarps * kSelectMaxK], s_best[kSelectMaxK];
+    constexpr int kGroups = 32 / kRowLanes;  // rows a warp's load covers
+    const int sub         = threadIdx.x & (kRowLanes - 1);
+    const int group       = (threadIdx.x >> 5) * kGroups + ((threadIdx.x & 31) / kRowLanes);
+    const int n_groups    = (blockDim.x >> 5) * kGroups;
+    for (int i = static_cast<int>(c) + threadIdx.x; i < n2; i += blockDim.x) { keys[i] = ~0ull; }
+    for (int i0 = 0; i0 < static_cast<int>(c); i0 += n_groups * kRowUnroll) {  // the same trips for every lane of a warp
+      int32_t row[kRowUnroll];
+      bool ok[kRowUnroll];
+      long long v[kRowUnroll];
+#pragma unroll
+      for (int u = 0; u < kRowUnroll; ++u) {
+        const int i = i0 + u * n_groups + group;
+        row[u]      = i < static_cast<int>(c) ? mine[i] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < kRowUnroll; ++u) { ok[u] = row[u] >= 0 && admitted(adm, q, row[u]); }
+      int_row_scores<T, METRIC>(vectors, pitch, row, d, reinterpret_cast<const uint4*>(qd), s_qq_int, sub, v);
+#pragma unroll
+      for (int u = 0; u < kRowUnroll; ++u) {
+        const int i = i0 + u * n_groups + group;
+        if (sub == 0 && row[u] >= 0) {
+          keys[i] = ok[u] ? (static_cast<unsigned long long>(v[u] + 2147483648ll) << 32) | static_cast<uint32_t>(row[u]) : ~0ull;
         }
       }
-      keys[i] = key;
     }
-    bitonic_sort_keys(keys, n2);
-    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-      const unsigned long long key = keys[i];
-      const bool have              = key != ~0ull;  // sc[i] occupies the bytes of keys[i]: read, then overwritten, by this thread
-      sc[i]  = have ? __ll2double_rn(static_cast<long long>(key >> 32) - 2147483648ll) : CUDART_INF;
-      ids[i] = have ? static_cast<int32_t>(key & 0xffffffffull) : 0x7fffffff;
-    }
+    const bool small = k <= kSelectMaxK && n2 <= 512 && blockDim.x <= kSelectWarps * 32;
     __syncthreads();
+    if (small) {
+      select_smallest_keys(keys, n2, k, s_lists, s_best);
+    } else {
+      bitonic_sort_keys(keys, n2);
+    }
+    // entry t of the ranking, t < k: straight from the keys
+    auto entry = [&](int t) { return small ? s_best[t] : (t < n2 ? keys[t] : ~0ull); };
+    if (over) {
+      if (threadIdx.x == 0) {
+        const unsigned long long kk = entry(k - 1);
+        report_overflow(kk != ~0ull ? __ll2double_rn(static_cast<long long>(kk >> 32) - 2147483648ll) : CUDART_INF);
+      }
+      return;
+    }
+    for (int t = threadIdx.x; t < k; t += blockDim.x) {
+      const unsigned long long key             = entry(t);
+      const bool have                          = key != ~0ull;
+      best_s[static_cast<size_t>(q) * k + t]   = have ? __ll2double_rn(static_cast<long long>(key >> 32) - 2147483648ll) : CUDART_INF;
+      best_row[static_cast<size_t>(q) * k + t] = have ? static_cast<int32_t>(key & 0xffffffffull) : -1;
+    }
+    if (threadIdx.x == 0 && stats) {
+      atomicAdd(stats + 0, static_cast<unsigned long long>(c));  // survivors of the screen
+      atomicAdd(stats + 1, static_cast<unsigned long long>(c));  // exact scores computed
+    }
+    return;
   } else {
     for (int i = threadIdx.x; i < n2; i += blockDim.x) {
       double s    = CUDART_INF;
@@ -777,28 +910,7 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
   }
   if (over) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-      const unsigned int pos = atomicAdd(ovf_count, 1u);
-      ovf_list[pos]          = q;
-      int32_t t              = rf.thr[blockIdx.x];
-      const double kth       = k <= n2 ? sc[k - 1] : CUDART_INF;
-      if (kth < CUDART_INF) {
-        // the screen's value of a row as good as the k-th: <q, x> - |x|^2 / 2 (L2), <q, x> (inner product),
-        // <q, x / |x|> (cosine)
-        const double value = METRIC == kCos ? sqrt(s_qq) * (1.0 - 0.5 * kth) : 0.5 * (s_qq - kth);
-        if (rf.kind == 1) {  // integer values: e = -floor(|x|^2 / 2) only raises a row's value
-          const double cv  = ceil(value);
-          const int32_t tv = cv >= 2147483647.0 ? 0x7fffffff : cv <= -2147483648.0 ? static_cast<int32_t>(0x80000000u)
-                                                                                      : static_cast<int32_t>(cv);
-          t = max(t, tv);
-        } else {             // fp16 codes: the value the pass computes may be lower by half the query's allowance
-          float f = __double2float_rd(value - 0.5 * static_cast<double>(rf.shift[q]));
-          f       = nextafterf(f, -CUDART_INF_F);
-          t       = __float_as_int(fmaxf(f, __int_as_float(t)));
-        }
-      }
-      rf.thr2[pos] = t;
-    }
+    if (threadIdx.x == 0) { report_overflow(k <= n2 ? sc[k - 1] : CUDART_INF); }
     return;
   }
   for (int t = threadIdx.x; t < k; t += blockDim.x) {
@@ -1195,7 +1307,8 @@ void by_dtype(int dtype, F&& f)
 template <typename Kernel>
 void allow_smem(Kernel kernel, size_t bytes)
 {
-  if (bytes > 48 * 1024) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)); }
+  // the 48 KB that need no opt-in include the kernel's static shared memory: leave room for it
+  if (bytes > 32 * 1024) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)); }
 }
 
 }  // namespace
@@ -1338,7 +1451,8 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
 {
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
-  const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) + sizeof(int32_t) * n2max;
+  const bool bytes  = dtype == kI8 || dtype == kU8;  // 8-bit rows rank 64-bit keys: no separate id array
+  const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) + (bytes ? 0 : sizeof(int32_t) * n2max);
   // a thread walks one candidate row: float rows are long walks bound by latency and the conversion pipe, more
   // resident threads hide more of it
   // (measured on 768-dimensional rows: 512 threads per query beat 128 by 8 to 13 %, 1024 only when k is large)
