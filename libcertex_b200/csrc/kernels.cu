@@ -28,6 +28,17 @@ namespace {
 // ------------------------------------------------------------------------------------------- element access
 template <typename T>
 struct Elems;
+// The double of a FINITE float32 (bits f) without the conversion instruction, whose pipe does about two per clock and
+// SM: the float's sign, exponent field and mantissa are placed in a double's fields as they are, which gives
+// x * 2^-896 (a subnormal float lands on a subnormal double, zero on zero), and one multiplication by 2^896 - exact,
+// a power of two - restores x. Infinities and NaNs would come out finite: callers use it only on stored rows that
+// passed the fp16 range check of the screen.
+__device__ __forceinline__ double widen_finite(uint32_t f)
+{
+  const uint32_t hi = ((f & 0x7fffffffu) >> 3) | (f & 0x80000000u);
+  return __dmul_rn(__hiloint2double(static_cast<int>(hi), static_cast<int>(f << 29)), 0x1p896);
+}
+
 template <>
 struct Elems<float> {
   static constexpr int kPerVec = 4;
@@ -35,6 +46,10 @@ struct Elems<float> {
   {
     o[0] = double(__uint_as_float(w.x)), o[1] = double(__uint_as_float(w.y));
     o[2] = double(__uint_as_float(w.z)), o[3] = double(__uint_as_float(w.w));
+  }
+  __device__ static void unpack_finite(const uint4& w, double (&o)[4])
+  {
+    o[0] = widen_finite(w.x), o[1] = widen_finite(w.y), o[2] = widen_finite(w.z), o[3] = widen_finite(w.w);
   }
   __device__ static double one(const void* p, int64_t i) { return double(static_cast<const float*>(p)[i]); }
 };
@@ -49,6 +64,16 @@ struct Elems<__half> {
       const __half2 h = *reinterpret_cast<const __half2*>(&u[i]);
       o[2 * i]        = double(__low2float(h));
       o[2 * i + 1]    = double(__high2float(h));
+    }
+  }
+  __device__ static void unpack_finite(const uint4& w, double (&o)[8])
+  {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = *reinterpret_cast<const __half2*>(&u[i]);
+      o[2 * i]        = widen_finite(__float_as_uint(__low2float(h)));
+      o[2 * i + 1]    = widen_finite(__float_as_uint(__high2float(h)));
     }
   }
   __device__ static double one(const void* p, int64_t i) { return double(__half2float(static_cast<const __half*>(p)[i])); }
@@ -129,8 +154,9 @@ struct Acc {
   }
 };
 
-// Walks one stored row (16-byte loads) and feeds every coordinate to `acc`.
-template <typename T, int METRIC, int NQ>
+// Walks one stored row (16-byte loads) and feeds every coordinate to `acc`. FINITE: the row holds no infinity or NaN
+// (float types; see widen_finite).
+template <typename T, int METRIC, int NQ, bool FINITE = false>
 __device__ __forceinline__ void scan_row(const uint8_t* row, int d, const double* qd, int ldq, Acc<METRIC, NQ>& acc)
 {
   constexpr int V   = Elems<T>::kPerVec;
@@ -139,7 +165,11 @@ __device__ __forceinline__ void scan_row(const uint8_t* row, int d, const double
   for (int c = 0; c < n_full; ++c) {
     const uint4 w = __ldg(p + c);
     double x[V];
-    Elems<T>::unpack(w, x);
+    if constexpr (FINITE) {
+      Elems<T>::unpack_finite(w, x);
+    } else {
+      Elems<T>::unpack(w, x);
+    }
 #pragma unroll
     for (int e = 0; e < V; ++e) { acc.add(x[e], qd, ldq, c * V + e); }
   }
@@ -899,7 +929,7 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
         if (admitted(adm, q, row)) {
           Acc<METRIC, 1> acc;
           acc.clear();
-          scan_row<T, METRIC, 1>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);
+          scan_row<T, METRIC, 1, true>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);  // screened rows are finite
           s = acc.result(0, s_qq);
         }
       }
