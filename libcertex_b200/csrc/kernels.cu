@@ -786,10 +786,17 @@ __device__ void select_smallest_keys(const unsigned long long* key, int n2, int 
 }
 
 // ------------------------------------------------------------------------------------------- verify + select
+// Staging tiles of the float rows: per warp 32 rows of a 128-byte slab, 144 bytes apart (a lane's 16-byte reads of its
+// own row then fall on distinct banks within every quarter warp).
+constexpr int kStageStride = 144;
+__device__ __forceinline__ uint8_t* stage_of(void* after_the_arrays)
+{
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(after_the_arrays) + 15) & ~static_cast<uintptr_t>(15));
+}
 // Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap); for 8-bit rows
 // the query's bytes (in the space of qd) | n2 64-bit keys.
 template <typename T, int METRIC>
-__global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
+__global__ void __launch_bounds__(1024) verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
                                      Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
                                      unsigned int* ovf_count, unsigned long long* stats,
@@ -921,20 +928,65 @@ __global__ void verify_select_kernel(const uint8_t* vectors, size_t pitch, int d
     }
     return;
   } else {
-    for (int i = threadIdx.x; i < n2; i += blockDim.x) {
-      double s    = CUDART_INF;
-      int32_t row = 0x7fffffff;
+    // Float rows: a thread sums its candidate's coordinates in order (the order of the fp64 reference loop), but the
+    // rows come through shared memory: a warp fetches a 128-byte slab of 32 candidate rows with eight loads that each
+    // cover four whole lines (eight lanes per row), parks it in its tile, and every lane then walks its own row's slab.
+    // Per 512 bytes that is 4 + 4 + 4 memory wavefronts instead of the 32 of a warp whose lanes each load 16 bytes of
+    // a different row.
+    constexpr int V       = Elems<T>::kPerVec;  // coordinates per 16-byte piece
+    const int lane        = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int n_pieces    = static_cast<int>((static_cast<size_t>(d) * sizeof(T) + 15) / 16);  // rows are zero padded to the pitch
+    uint8_t* tile         = stage_of(ids + n2max) + static_cast<size_t>(warp) * 32 * kStageStride;
+    const int piece       = lane & 7, row_in_load = lane >> 3;
+    for (int g = warp; g * 32 < n2; g += n_warps) {
+      const int i   = g * 32 + lane;
+      int32_t row   = 0x7fffffff;
+      bool ok       = false;
       if (i < static_cast<int>(c)) {
         row = mine[i];
-        if (admitted(adm, q, row)) {
-          Acc<METRIC, 1> acc;
-          acc.clear();
-          scan_row<T, METRIC, 1, true>(vectors + static_cast<size_t>(row) * pitch, d, qd, d, acc);  // screened rows are finite
-          s = acc.result(0, s_qq);
+        ok  = admitted(adm, q, row);
+      }
+      Acc<METRIC, 1> acc;
+      acc.clear();
+      if (g * 32 < static_cast<int>(c)) {  // the same for every lane of the warp
+        int32_t from[8];  // the rows this lane fetches pieces of
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { from[j] = __shfl_sync(0xffffffffu, ok ? row : -1, 4 * j + row_in_load); }
+        for (int p0 = 0; p0 < n_pieces; p0 += 8) {
+          uint4 w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            w[j] = (from[j] >= 0 && p0 + piece < n_pieces)
+                     ? __ldg(reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(from[j]) * pitch) + p0 + piece)
+                     : make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();  // every lane is done with the slab before
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            *reinterpret_cast<uint4*>(tile + (4 * j + row_in_load) * kStageStride + piece * 16) = w[j];
+          }
+          __syncwarp();
+          if (ok) {
+            const int np = min(8, n_pieces - p0);
+            for (int p = 0; p < np; ++p) {
+              const uint4 x4 = *reinterpret_cast<const uint4*>(tile + lane * kStageStride + p * 16);
+              double x[V];
+              Elems<T>::unpack_finite(x4, x);  // screened rows are finite
+              const int t0 = (p0 + p) * V;
+              if (t0 + V <= d) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) { acc.add(x[e], qd, d, t0 + e); }
+              } else {
+                for (int e = 0; e < V && t0 + e < d; ++e) { acc.add(x[e], qd, d, t0 + e); }
+              }
+            }
+          }
         }
       }
-      sc[i]  = s;
-      ids[i] = row;
+      if (i < n2) {
+        sc[i]  = ok ? acc.result(0, s_qq) : CUDART_INF;
+        ids[i] = row;
+      }
     }
     bitonic_sort(sc, ids, n2);
   }
@@ -1482,11 +1534,13 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
   const bool bytes  = dtype == kI8 || dtype == kU8;  // 8-bit rows rank 64-bit keys: no separate id array
-  const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) + (bytes ? 0 : sizeof(int32_t) * n2max);
-  // a thread walks one candidate row: float rows are long walks bound by latency and the conversion pipe, more
-  // resident threads hide more of it
-  // (measured on 768-dimensional rows: 512 threads per query beat 128 by 8 to 13 %, 1024 only when k is large)
-  const int threads = (dtype == kF32 || dtype == kF16) ? (k >= 1024 ? 1024 : 512) : 128;
+  // float rows: a warp scores 32 candidates at a time, so a query with a few hundred candidates keeps 8 warps busy;
+  // larger blocks leave warps idle at the barrier before the sort (measured on 768-dimensional rows with 153 and 664
+  // candidates per query and on 128-dimensional keys with 2 394: 256 threads beat 128, 512 and 1024 in all three)
+  const int threads = (dtype == kF32 || dtype == kF16) ? 256 : 128;
+  // float rows: + 16 bytes of alignment and one staging tile per warp
+  const size_t smem = sizeof(double) * (static_cast<size_t>(d) + n2max) +
+                      (bytes ? 0 : sizeof(int32_t) * n2max + 16 + static_cast<size_t>(threads / 32) * 32 * kStageStride);
   by_dtype(dtype, [&](auto tag) {
     using T   = decltype(tag);
     auto go   = [&](auto kernel) {
