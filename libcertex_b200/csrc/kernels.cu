@@ -614,6 +614,60 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
   } else {
     for (int i = threadIdx.x; i < ng; i += blockDim.x) { see(row[i]); }
   }
+  const uint32_t my_hi = hi;  // the largest key this thread saw (0: none)
+  // Small k: the k-th largest of the maxima of G groups of threads is a value that k elements reach (the k groups at
+  // or above it hold one each), so only the few elements at or above it can be the k-th largest of the row: they are
+  // collected in one more pass over the row and ranked by counting. No histogram, no contended atomics. When the list
+  // does not hold them (many equal values), the radix walk below takes over.
+  constexpr int kCollect = 1024;
+  __shared__ uint32_t s_group[512], s_list[kCollect];
+  __shared__ uint32_t s_bound, s_count, s_answer;
+  const int n_threads = blockDim.x;
+  if (in_smem && n_threads == 512 && 2 * k <= 512) {
+    int groups = 16;
+    while (groups < 2 * k) { groups <<= 1; }
+    const int per_group = n_threads / groups;  // 32, 16, ..., 1 threads
+    uint32_t g_hi       = my_hi;
+    for (int o = 1; o < per_group; o <<= 1) { g_hi = max(g_hi, __shfl_xor_sync(0xffffffffu, g_hi, o)); }
+    if ((threadIdx.x & (per_group - 1)) == 0) { s_group[threadIdx.x / per_group] = g_hi; }
+    if (threadIdx.x == 0) { s_count = 0; }
+    __syncthreads();
+    if (threadIdx.x < groups) {
+      const uint32_t u = s_group[threadIdx.x];
+      int rank         = 0;
+      for (int j = 0; j < groups; ++j) {
+        const uint32_t v = s_group[j];
+        rank += (v > u || (v == u && j < static_cast<int>(threadIdx.x))) ? 1 : 0;
+      }
+      if (rank == k - 1) { s_bound = u; }
+    }
+    __syncthreads();
+    const uint32_t bound = s_bound;
+    for (int i = threadIdx.x; i < ng; i += n_threads) {
+      const uint32_t key = static_cast<uint32_t>(row[i]) ^ 0x80000000u;
+      if (key >= bound) {
+        const uint32_t pos = atomicAdd(&s_count, 1u);
+        if (pos < kCollect) { s_list[pos] = key; }
+      }
+    }
+    __syncthreads();
+    const int n_list = static_cast<int>(s_count);
+    if (n_list <= kCollect) {  // n_list >= k: the k group maxima at or above the bound are k elements of the row
+      for (int i = threadIdx.x; i < n_list; i += n_threads) {
+        const uint32_t u = s_list[i];
+        int greater = 0, at_least = 0;
+        for (int j = 0; j < n_list; ++j) {
+          const uint32_t v = s_list[j];
+          greater += v > u ? 1 : 0;
+          at_least += v >= u ? 1 : 0;
+        }
+        if (greater < k && k <= at_least) { s_answer = u; }  // every thread that gets here holds the same value
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(s_answer ^ 0x80000000u); }
+      return;
+    }
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
