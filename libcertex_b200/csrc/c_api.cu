@@ -159,6 +159,18 @@ struct Shard {
   Resources res;
   std::unique_ptr<Index> index;
   int64_t first_id = 0;
+  Shard()                        = default;
+  Shard(const Shard&)            = delete;
+  Shard& operator=(const Shard&) = delete;
+  ~Shard()
+  {
+    int old = 0;
+    cudaGetDevice(&old);
+    cudaSetDevice(device);
+    index.reset();
+    if (res.stream) { cudaStreamDestroy(res.stream); }
+    cudaSetDevice(old);
+  }
 };
 
 /// Restores the calling thread's current device when it goes out of scope.
@@ -613,15 +625,7 @@ cuvsError_t certexB200ShardedBuild(const int32_t* devices, int32_t n_shards, cuv
 cuvsError_t certexB200ShardedDestroy(certexB200ShardedIndex_t index)
 {
   return translate([=] {
-    if (index == nullptr) { return; }
-    DeviceGuard guard;
-    for (auto& sh : index->shards) {
-      if (!sh) { continue; }
-      cudaSetDevice(sh->device);
-      sh->index.reset();
-      if (sh->res.stream) { cudaStreamDestroy(sh->res.stream); }
-    }
-    delete index;
+    delete index;  // every shard frees its index and its stream on its own device
   });
 }
 
