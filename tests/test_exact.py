@@ -47,6 +47,10 @@ CASES = [
     (20000, 1024, 200, 10, "l2", "uint8", 1.0, False, 0),
     (6000, 4096, 30, 10, "ip", "int8", 1.0, False, 0),
     (3000, 2100, 10, 10, "l2", "float32", 1.0, False, 0),
+    # three quarters of the rows identical: thousands of equal group maxima and equal scores
+    (20000, 64, 100, 10, "l2", "uint8", 1.0, False, 15000),
+    (20000, 64, 100, 10, "ip", "float32", 1.0, True, 15000),
+    (20000, 64, 60, 300, "l2", "int8", 1.0, False, 15000),
 ]
 
 
