@@ -42,6 +42,8 @@ class KeyCache:
             # the partition by head is renewed once an eighth of the keys is newer than it: appending a few keys per
             # decoding step must not copy the whole cache
             self.index = Index(self.head_dim, metric="ip", capacity=cap, partition_labels="lazy")
+        _need(not (self.dtype == torch.float16 and K.dtype == torch.float32),
+              "these keys do not fit float16 but the cache was started with float16 keys: start it with float32 keys")
         heads = torch.arange(self.n_kv_heads, dtype=torch.int32, device="cuda").repeat_interleave(n_new)
         self.index.add(K.to(self.dtype).reshape(self.n_kv_heads * n_new, self.head_dim).contiguous(), labels=heads)
         pos = torch.arange(self.size, self.size + n_new, dtype=torch.int64, device="cuda").repeat(self.n_kv_heads)

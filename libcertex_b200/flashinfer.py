@@ -57,6 +57,8 @@ class ExactTopK:
             self.dtype = K.dtype
             cap = None if self.capacity is None else int(self.capacity) * self.num_kv_heads
             self.index = Index(self.head_dim, metric="ip", capacity=cap, partition_labels="lazy")
+        _need(not (self.dtype == torch.float16 and K.dtype == torch.float32),
+              "these keys do not fit float16 but the selector was started with float16 keys: start it with float32 keys")
         if slot not in self._number:
             self._number[slot], self._next = self._next, self._next + 1
             self._length[slot], self._ids[slot] = 0, []
