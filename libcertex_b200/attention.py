@@ -63,6 +63,8 @@ class KeyCache:
             Q = Q[:, None, :]
         _need(Q.ndim == 3 and Q.shape[2] == self.head_dim and Q.shape[0] % self.n_kv_heads == 0,
               f"queries must have shape (n_heads, m, {self.head_dim}) with n_heads a multiple of {self.n_kv_heads}")
+        _need(not (self.dtype == torch.float16 and Q.dtype == torch.float32),
+              "these queries do not fit float16 but the cache holds float16 keys: start the cache with float32 keys")
         H, m, d = Q.shape
         group = H // self.n_kv_heads
         heads = (torch.arange(H, dtype=torch.int32, device="cuda") // group).repeat_interleave(m)

@@ -120,7 +120,10 @@ class ExactTopK:
         if rows.numel() > 0:
             head = torch.arange(H, dtype=torch.int32, device="cuda") // group
             labels = (number[rows][:, None] * self.num_kv_heads + head[None, :]).reshape(-1).contiguous()
-            Qs = _as_half_or_float(Q[rows]).to(self.dtype).reshape(rows.numel() * H, d).contiguous()
+            Qs = _as_half_or_float(Q[rows])
+            _need(not (self.dtype == torch.float16 and Qs.dtype == torch.float32),
+                  "these queries do not fit float16 but the selector holds float16 keys: start it with float32 keys")
+            Qs = Qs.to(self.dtype).reshape(rows.numel() * H, d).contiguous()
             _, I = self.index.search(Qs, k=k, labels=labels)
             out[rows] = self._position[I.clamp_(min=0)].reshape(rows.numel(), H, k)
         return out[:, 0] if single else out
