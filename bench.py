@@ -3,7 +3,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 A step is one search of all queries (every stage: anchor pass, threshold, screen, exact fp64 verification, top-k,
-and for N > 1 the all-gather + merge of the per-rank lists). Inputs are seeded synthetic Gaussian-mixture rows with the
+and for N > 1 the all-gather + merge of the per-rank lists); for N > 1 a step repeats that search `--searches-per-step`
+times (default 4, stated in `config`), so that the timed region stays long enough for a stable number when a search
+takes a few milliseconds. Inputs are seeded synthetic Gaussian-mixture rows with the
 shape and value range of the reference's benchmark set (which is not available offline). For N > 1 (launched with
 torch.distributed.run, one rank per GPU) the 10 M rows are split into N contiguous shards: total work is fixed
 (strong scaling). Rank 0 prints one JSON line.
@@ -27,6 +29,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "exact 10-NN QPS, 10Mx128 u8"
+# DRAM bytes per (query panel x stored row) of a SCREEN launch: 14.89 GB measured by ncu over 12 panels x 10 M rows
+TRAFFIC_PER_PANEL_ROW = 14.89e9 / (12 * 10_000_000)
 N_BASE, N_QUERIES, DIM, K = 10_000_000, 10_000, 128, 10
 
 
@@ -96,9 +100,45 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def config_of(args):
+    """The `config` object of the JSON line; both arms print the same one."""
+    per_step = args.searches_per_step or (1 if args.gpus == 1 else 4)
+    return {
+        "workload": f"{args.n_base}x{DIM} uint8 Gaussian mixture (1000 centres in [20,235], sigma 18), "
+                    f"{args.n_queries} queries, k={K}, L2, {args.gpus} row shard(s)",
+        "batch": args.batch, "anchor_stride": args.anchor_stride, "searches_per_step": per_step,
+        "l2_policy": "inputs exceed L2: every step streams the whole shard (>= 160 MB) from HBM",
+    }
+
+
+def measure_i8_peak(iters=5):
+    """int8 tensor-pipe rate of this GPU with the screen's own tiling: the pass's TMA + tcgen05.mma stream (M128 x
+    N256 x K32 instructions, uint8 operands, int32 accumulators in TMEM) with no epilogue, over 2048 queries x 1 M
+    rows, best of `iters` (CUDA events around the launch, inside the library). TOP/s."""
+    import ctypes
+
+    from libcertex_b200 import _lib
+
+    L, res = _lib.lib(), _lib.resources()
+    nq, n, cl = 2048, 1_000_000, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randint(0, 256, (nq, cl), generator=g, device="cuda", dtype=torch.uint8)
+    x = torch.randint(0, 256, (n, cl), generator=g, device="cuda", dtype=torch.uint8)
+    init = torch.zeros((-(-n // 256) * 256,), dtype=torch.int32, device="cuda")
+    dummy = torch.zeros((nq,), dtype=torch.int32, device="cuda")
+    ms, best = ctypes.c_float(), None
+    for _ in range(iters):
+        _lib.check(L.certexB200ScreenRaw(res, q.data_ptr(), nq, x.data_ptr(), n, cl, 0, init.data_ptr(), 2,
+                                         dummy.data_ptr(), dummy.data_ptr(), 8, dummy.data_ptr(), dummy.data_ptr(), 1,
+                                         ctypes.byref(ms)))
+        best = ms.value if best is None else min(best, ms.value)
+    return 2.0 * nq * n * cl / (best / 1e3) / 1e12
+
+
 def cpu_baseline(xb_host, xq_host, target_seconds=15.0):
     """The oracle (a restatement of the reference's fp64 exhaustive check) on all host cores, on the first queries of
-    the workload; the sample is sized from a short probe so that it takes roughly `target_seconds`."""
+    the workload; the sample is sized from a short probe so that it takes roughly `target_seconds`. Also returns the
+    sample's answers (number of queries, ids, fp64 scores) for the parity check."""
     from oracle import oracle
 
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
@@ -107,10 +147,11 @@ def cpu_baseline(xb_host, xq_host, target_seconds=15.0):
     probe = time.perf_counter() - t0
     nqs = int(max(8, min(xq_host.shape[0], 8 * target_seconds / max(probe, 1e-3))))
     t0 = time.perf_counter()
-    oracle.knn(xb_host, xq_host[:nqs], K, "l2", threads=cores)
+    ids, scores = oracle.knn(xb_host, xq_host[:nqs], K, "l2", threads=cores)
     dt = time.perf_counter() - t0
     return {"value": nqs / dt, "unit": "queries/s", "cores": int(oracle.knn.threads_used), "kind": "port",
-            "sample": f"first {nqs} of {xq_host.shape[0]} queries against all {xb_host.shape[0]} rows, {dt:.1f} s"}
+            "sample": f"first {nqs} of {xq_host.shape[0]} queries against all {xb_host.shape[0]} rows, {dt:.1f} s"}, \
+        (np.arange(nqs), ids, scores)
 
 
 def run_reference(args):
@@ -146,7 +187,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * dt / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": f"{n_base}x{DIM} uint8 Gaussian mixture, {args.n_queries} queries, k={K}, L2"},
+        "config": config_of(args),
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -163,6 +204,9 @@ def main():
     ap.add_argument("--batch", type=int, default=10240, help="queries that share one pass over the stored rows")
     ap.add_argument("--anchor-stride", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--searches-per-step", type=int, default=0,
+                    help="searches of all queries per step (default: 1 on one GPU, 4 on several)")
+    ap.add_argument("--parity-queries", type=int, default=16, help="queries checked against the CPU oracle at N > 1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -182,18 +226,19 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     n_base, nq = args.n_base, args.n_queries
+    per_step = args.searches_per_step or (1 if world == 1 else 4)
     lo, hi = distributed.shard_bounds(n_base, world, rank)
     xb = synthetic.mixture_u8(hi - lo, seed=0, row0=lo)
     xq = synthetic.mixture_u8(nq, seed=1)
     if world > 1:
         index = distributed.DistributedIndex(DIM, anchor_stride=args.anchor_stride).add_shard(xb, lo)
-        search = lambda q: index.search(q, k=K, batch=args.batch)  # noqa: E731
     else:
         index = certex.Index(DIM, anchor_stride=args.anchor_stride)
         index.add(xb)
-        search = lambda q: index.search(q, k=K, batch=args.batch)  # noqa: E731
+    search = lambda q, **kw: index.search(q, k=K, batch=args.batch, **kw)  # noqa: E731
     del xb
     torch.cuda.synchronize()
+    i8_peak = measure_i8_peak() if rank == 0 else None  # a few ms of the screen's own MMA stream, before the timed region
 
     def barrier():
         if world > 1:
@@ -201,11 +246,12 @@ def main():
         torch.cuda.synchronize()
 
     def timed(fn, steps):
-        """Device time of `steps` calls (CUDA events on the launching stream), max over ranks, in ms."""
+        """Device time of `steps` steps of `per_step` calls each (CUDA events on the launching stream), max over ranks,
+        in ms."""
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        for _ in range(steps):
+        for _ in range(steps * per_step):
             out = fn()
         e1.record()
         barrier()
@@ -215,15 +261,16 @@ def main():
         return float(ms.item()), out
 
     # ---- device-resident inputs
-    for _ in range(args.warmup):
+    for _ in range(args.warmup * per_step):
         search(xq)
     sampler = ClockSampler(local)
     sampler.start()
     with certex.search_stats() as st:
         ms, (D, I) = timed(lambda: search(xq), args.steps)
     clocks = sampler.stop()
-    qps = nq * args.steps / (ms / 1000)
-    launches = st.launches + (args.steps if world > 1 else 0) * 2  # merge + finish kernels of the distributed search
+    n_searches = args.steps * per_step
+    qps = nq * n_searches / (ms / 1000)
+    launches = st.launches + (n_searches if world > 1 else 0) * 2  # merge + finish kernels of the distributed search
 
     # ---- end to end through the public API with host buffers: H2D of the queries, search, D2H of ids + distances
     hq = xq.cpu().pin_memory()
@@ -240,51 +287,73 @@ def main():
     for _ in range(2):
         e2e_step()
     ms_e2e, _ = timed(e2e_step, args.steps)
-    e2e_qps = nq * args.steps / (ms_e2e / 1000)
+    e2e_qps = nq * n_searches / (ms_e2e / 1000)
     assert torch.equal(hI, I.cpu()), "end-to-end ids differ from the device-resident run"
+
+    # ---- parity, outside the timed regions: the answers of this run against the CPU oracle on all rows
+    _, I_all, S_all = search(xq, return_scores=True)
+    torch.cuda.synchronize()
+    assert torch.equal(I_all, I), "two searches of the same queries returned different ids"
 
     if rank == 0:
         pk = peaks()
         shard_rows = hi - lo
-        ops = 2.0 * nq * shard_rows * 128  # int8 multiply-adds x 2 of one screen pass set on this rank, per step
-        screen_s = st.screen_ms / 1000 / max(args.steps, 1)
+        ops = 2.0 * nq * shard_rows * 128  # int8 multiply-adds x 2 of one screen pass set on this rank, per search
+        screen_s = st.screen_ms / 1000 / max(n_searches, 1)
         achieved = ops / screen_s / 1e12 if screen_s > 0 else None
-        peak = 2 * pk["bf16_sustained"]
+        proxy = 2 * pk["bf16_burst"]
         n_panels = -(-(-(-min(nq, args.batch) // 128)) // 7) * -(-nq // args.batch)  # query panels of 7 tiles, all batches
-        traffic = int(14.89e9 * n_panels * shard_rows / (12 * 10_000_000))
+        traffic = int(TRAFFIC_PER_PANEL_ROW * n_panels * shard_rows)
         line = {
             "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {
-                "workload": f"{n_base}x{DIM} uint8 Gaussian mixture (1000 centres in [20,235], sigma 18), "
-                            f"{nq} queries, k={K}, L2, {world} row shard(s)",
-                "batch": args.batch, "anchor_stride": args.anchor_stride,
-                "l2_policy": "inputs exceed L2: every step streams the whole shard (>= 160 MB) from HBM",
-            },
-            "e2e": {"value": e2e_qps, "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel()),
-                    "d2h_bytes_per_step": int(hI.numel() * 8 + hD.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+            "config": config_of(args),
+            "e2e": {"value": e2e_qps, "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel()) * per_step,
+                    "d2h_bytes_per_step": int(hI.numel() * 8 + hD.numel() * 4) * per_step,
+                    "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {
-                "bound": "tensor", "kernel": "screen_i8_kernel (SCREEN pass)", "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": None if achieved is None else achieved / peak, "traffic": traffic,
-                "note": f"int8 tensor ops (2 x nq x rows x 128) / CUDA-event time of the screen passes on rank 0; "
-                        f"peak = 2 x the {pk['source']} sustained bf16 cuBLAS rate (int8 nominal is twice bf16)",
-                "traffic_note": "DRAM bytes of one SCREEN launch: ncu measured 14.87 GB read + 0.02 GB written on the "
-                                "10M x 128, 10000-query launch (12 query panels x 1.28 GB of codes = 15.4 GB "
-                                "algorithmic); other sizes scaled by panels x rows",
-                "screen_ms_per_step": st.screen_ms / args.steps, "anchor_ms_per_step": st.anchor_ms / args.steps,
+                "bound": "tensor", "kernel": "screen_i8_kernel (SCREEN pass)", "achieved": achieved, "peak": i8_peak,
+                "unit": "TFLOP/s", "frac": None if achieved is None else achieved / i8_peak, "traffic": traffic,
+                "peak_measured_i8": i8_peak, "peak_nominal": 4500.0,
+                "frac_of_nominal": None if achieved is None else achieved / 4500.0,
+                "peak_2x_bf16_burst": proxy,
+                "note": "int8 tensor ops (2 x nq x rows x 128) / CUDA-event time of the screen passes on rank 0; peak = "
+                        "the int8 rate measured in this run directly before the timed region by the pass's own TMA + "
+                        "tcgen05.mma stream without epilogue (M128 x N256 x K32, 2048 queries x 1 M rows, best of 5); "
+                        f"peak_2x_bf16_burst = twice the {pk['source']} burst bf16 cuBLAS rate, for comparison only",
+                "traffic_note": "DRAM bytes of one SCREEN launch, scaled by query panels x rows from the ncu capture of "
+                                "the 10M x 128, 10000-query launch under profiles/ (codes are read once per query "
+                                "panel)",
+                "screen_ms_per_search": st.screen_ms / n_searches, "anchor_ms_per_search": st.anchor_ms / n_searches,
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},
         }
+        xb_host = synthetic.mixture_u8(n_base, seed=0).cpu().numpy()
+        xq_host = xq.cpu().numpy()
         if world == 1 and not args.no_cpu_baseline:
-            xb_host = synthetic.mixture_u8(n_base, seed=0).cpu().numpy()
-            line["cpu_baseline"] = cpu_baseline(xb_host, xq.cpu().numpy())
+            line["cpu_baseline"], (pick, ids, scores) = cpu_baseline(xb_host, xq_host)
+        else:
+            from oracle import oracle
+
+            pick = np.arange(0, nq, max(1, nq // max(args.parity_queries, 1)))[: args.parity_queries]
+            cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+            ids, scores = oracle.knn(xb_host, xq_host[pick], K, "l2", threads=cores)
+        ids_equal = bool(np.array_equal(I_all[pick].cpu().numpy(), ids))
+        scores_equal = bool(np.array_equal(S_all[pick].cpu().numpy(), scores))
+        line["parity"] = {"queries": int(len(pick)), "ids_equal": ids_equal, "scores_equal": scores_equal,
+                          "against": "CPU oracle (fp64 exhaustive over all rows), ids and fp64 scores bit for bit"}
         print(json.dumps(line))
+        ok = ids_equal and scores_equal
+    else:
+        ok = True
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        sys.exit("parity check failed: the answers differ from the CPU oracle")
 
 
 if __name__ == "__main__":

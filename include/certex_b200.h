@@ -348,6 +348,36 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ShardedSearch(cuvsCertexSearchParams_t 
                                                        DLManagedTensor* distances);
 
 /** Version string "major.minor.patch". */
+/* ------------------------------------------------------------------------------------------------------------------
+ * Row shards over several processes, one GPU and one shard each, exchanged over NCCL. The reference's sharded search
+ * (cpp/include/cuvs/neighbors/certex_shards.hpp:39-60, cpp/src/neighbors/certex/certex_shards.cu:85-167) keeps its
+ * shards in one process and merges on the host; these entry points are the same search for one process per GPU:
+ * every rank computes the exact local top-k of all queries, one ncclAllGather moves k (fp64 score, int64 id) pairs per
+ * query and rank, and every rank merges by (score, id). NCCL is loaded at run time (the copy already in the process,
+ * else libnccl.so.2); the library loads without it.
+ *
+ * certexB200CommGetUniqueId: one rank fills id (128 bytes, an ncclUniqueId) and the application sends it to the others.
+ * certexB200CommInitRank: every rank, with its device current (ncclCommInitRank). certexB200CommAdopt wraps an
+ * ncclComm_t that the application made and keeps. certexB200CommDestroy frees the buffers (and a communicator made by
+ * InitRank).
+ * certexB200DistributedSearch: called by every rank with the same queries (device, [nq, dim]), k, parameters and
+ * share_thresholds; `index` is the rank's shard and id_base the global id of its first row; neighbors / distances /
+ * scores (scores may be NULL) are device [nq, k] and receive the same merged answer on every rank. Every shard must
+ * hold at least k vectors. share_thresholds != 0 adds the reference's first round (certex_shards.cu:136-141) as one
+ * ncclAllReduce(max) over the per-query threshold keys of every batch. The call waits for its stream once, at its end.
+ * If the local search of a rank fails, every rank returns CUVS_ERROR for the call.
+ */
+typedef struct certexB200Comm* certexB200Comm_t;
+CERTEX_B200_EXPORT cuvsError_t certexB200CommGetUniqueId(void* id /* 128 bytes */);
+CERTEX_B200_EXPORT cuvsError_t certexB200CommInitRank(const void* id, int32_t n_ranks, int32_t rank, certexB200Comm_t* comm);
+CERTEX_B200_EXPORT cuvsError_t certexB200CommAdopt(void* nccl_comm /* ncclComm_t */, certexB200Comm_t* comm);
+CERTEX_B200_EXPORT cuvsError_t certexB200CommDestroy(certexB200Comm_t comm);
+CERTEX_B200_EXPORT cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t comm,
+                                                           cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
+                                                           DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                                           DLManagedTensor* distances, DLManagedTensor* scores,
+                                                           int64_t id_base, int32_t share_thresholds);
+
 CERTEX_B200_EXPORT const char* certexB200Version(void);
 
 #ifdef __cplusplus

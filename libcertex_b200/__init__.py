@@ -11,5 +11,5 @@ PyTorch fallback.
 from .attention import KeyCache, topk
 from .index import Index, ShardedIndex, merge_shards, search, search_stats, verify
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 __all__ = ["KeyCache", "topk", "Index", "ShardedIndex", "merge_shards", "search", "search_stats", "verify", "__version__"]

@@ -112,6 +112,8 @@ SYMBOLS = [
     "certexB200PlanSegments", "certexB200SearchStatic", "certexB200Version",
     "certexB200SetThresholdHook", "certexB200IndexWillScreen", "certexB200PlanRouted",
     "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
+    "certexB200CommGetUniqueId", "certexB200CommInitRank", "certexB200CommAdopt", "certexB200CommDestroy",
+    "certexB200DistributedSearch",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)

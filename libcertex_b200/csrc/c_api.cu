@@ -106,10 +106,14 @@ Filter filter_of(const cuvsFilter& f, int64_t nq, int64_t size)
   auto* words_t = reinterpret_cast<DLManagedTensor*>(f.addr);
   out.words     = static_cast<const uint32_t*>(checked(words_t, 1, kDLUInt, 32, true, "the filter words"));
   const int64_t have = words_t->dl_tensor.shape[0];
+  // the index may grow between this look at its size and the search's own (taken under its reader lock): the search
+  // checks covered_ids against the size it works with
   if (f.type == BITSET) {
     CERTEX_EXPECTS(have * 32 >= size, "certex: the bitset must cover every id of the index");
+    out.covered_ids = have * 32;
   } else {
     out.bitmap_cols = size;
+    out.covered_ids = size;
     CERTEX_EXPECTS(have * 32 >= nq * size, "certex: the bitmap must hold one row of size() bits per query");
   }
   return out;
@@ -702,6 +706,73 @@ cuvsError_t certexB200ShardedSearch(cuvsCertexSearchParams_t params, certexB200S
   });
 }
 
-const char* certexB200Version(void) { return "0.1.0"; }
+// ------------------------------------------------------------------------------------------- row shards over NCCL ranks
+cuvsError_t certexB200CommGetUniqueId(void* id128)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(id128 != nullptr, "certex: null id buffer");
+    comm_unique_id(id128);
+  });
+}
+
+cuvsError_t certexB200CommInitRank(const void* id128, int32_t n_ranks, int32_t rank, certexB200Comm_t* comm)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(comm != nullptr, "certex: null communicator handle");
+    *comm = reinterpret_cast<certexB200Comm_t>(comm_create(id128, n_ranks, rank, nullptr));
+  });
+}
+
+cuvsError_t certexB200CommAdopt(void* nccl_comm, certexB200Comm_t* comm)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(comm != nullptr && nccl_comm != nullptr, "certex: null communicator");
+    *comm = reinterpret_cast<certexB200Comm_t>(comm_create(nullptr, 0, 0, nccl_comm));
+  });
+}
+
+cuvsError_t certexB200CommDestroy(certexB200Comm_t comm)
+{
+  return translate([=] { comm_destroy(reinterpret_cast<Comm*>(comm)); });
+}
+
+cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t comm, cuvsCertexSearchParams_t params,
+                                        cuvsCertexIndex_t index, DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                        DLManagedTensor* distances, DLManagedTensor* scores, int64_t id_base,
+                                        int32_t share_thresholds)
+{
+  return translate([=] {
+    Resources& r = as_res(res);
+    Holder& h    = as_holder(index);
+    CERTEX_EXPECTS(comm != nullptr, "certex: null communicator");
+    CERTEX_EXPECTS(params != nullptr, "certex: null search parameters");
+    CERTEX_EXPECTS(queries != nullptr && queries->dl_tensor.dtype.code == index->dtype.code &&
+                     queries->dl_tensor.dtype.bits == index->dtype.bits,
+                   "certex: the queries must have the vector type of the index");
+    const void* q    = checked(queries, 2, -1, 0, true, "the queries");
+    const int64_t nq = queries->dl_tensor.shape[0];
+    CERTEX_EXPECTS(queries->dl_tensor.shape[1] == h.index->dim(), "certex: the queries must have the dimension of the index");
+    auto* nb        = static_cast<int64_t*>(checked(neighbors, 2, kDLInt, 64, true, "the neighbors"));
+    auto* ds        = static_cast<float*>(checked(distances, 2, kDLFloat, 32, true, "the distances"));
+    const int64_t k = neighbors->dl_tensor.shape[1];
+    CERTEX_EXPECTS(neighbors->dl_tensor.shape[0] == nq && distances->dl_tensor.shape[0] == nq && distances->dl_tensor.shape[1] == k,
+                   "certex: neighbors and distances must be [n_queries, k]");
+    double* sc = nullptr;
+    if (scores) {
+      sc = static_cast<double*>(checked(scores, 2, kDLFloat, 64, true, "the scores"));
+      CERTEX_EXPECTS(scores->dl_tensor.shape[0] == nq && scores->dl_tensor.shape[1] == k, "certex: scores must be [n_queries, k]");
+    }
+    CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
+    CERTEX_EXPECTS(h.index->size() >= k, "certex: every shard must hold at least k vectors");  // certex_shards.cu:97-99
+    SearchParams sp;
+    sp.anchors     = params->anchors;
+    sp.batch_size  = params->batch_size;
+    sp.probe_lists = params->probe_lists;
+    distributed_search(r, *reinterpret_cast<Comm*>(comm), *h.index, sp, q, nq, static_cast<int>(k), nb, ds, sc, id_base,
+                       share_thresholds != 0);
+  });
+}
+
+const char* certexB200Version(void) { return "0.2.0"; }
 
 }  // extern "C"

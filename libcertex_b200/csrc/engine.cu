@@ -48,8 +48,14 @@ struct Scratch {
   template <typename T>
   T* get(size_t count)
   {
-    void* p = nullptr;
-    CERTEX_CUDA(cudaMallocAsync(&p, std::max<size_t>(count, 1) * sizeof(T), stream));
+    void* p             = nullptr;
+    const size_t bytes  = std::max<size_t>(count, 1) * sizeof(T);
+    const cudaError_t e = cudaMallocAsync(&p, bytes, stream);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();  // the failed allocation leaves nothing behind: the error is reported, not kept
+      throw OutOfMemory("certex: out of device memory (" + std::to_string(bytes) + " bytes of scratch)");
+    }
+    CERTEX_CUDA(e);
     ptrs.push_back(p);
     return static_cast<T*>(p);
   }
@@ -179,7 +185,18 @@ Resources::Resources()
   CERTEX_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
 }
 
+Resources::~Resources()
+{
+  if (pinned_) { cudaFreeHost(pinned_); }
+}
+
 void Resources::sync() const { CERTEX_CUDA(cudaStreamSynchronize(stream)); }
+
+void* Resources::pinned_block() const
+{
+  if (!pinned_) { CERTEX_CUDA(cudaHostAlloc(&pinned_, 256, cudaHostAllocDefault)); }
+  return pinned_;
+}
 
 // ============================================================================================ Index
 Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t dim)
@@ -1108,23 +1125,80 @@ bool Index::will_screen(int k) const
   return screen_kind_ != 0 && !code_overflow_ && test_mode_ != 1 && k >= 1 && anchor_stride_for(size_, k) >= 1;
 }
 
-void Index::search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
-                   int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base) const
+/// Counters of a screened search as the device leaves them, copied to page-locked host memory behind the search.
+struct HostCounters {
+  unsigned int count[4];          // [0] queries whose list overflowed, [1] error code of a pass, [2] after the second pass
+  unsigned long long stats[2];    // pairs the screen kept, pairs the verification scored
+  unsigned int q_ovf;             // a query coordinate beyond the fp16 range
+};
+
+/// A search between search_begin and search_end: the reader lock, the temporaries and what the repair needs.
+struct Index::Pending {
+  const Resources* res;
+  std::shared_lock<std::shared_mutex> lock;
+  Scratch scratch;
+  SearchStats local{};
+  SearchParams sp;
+  const void* queries = nullptr;
+  int64_t nq = 0, n = 0, id_base = 0, batch = 0;
+  int k = 0;
+  size_t row_bytes = 0;
+  int64_t* neighbors = nullptr;
+  float* distances   = nullptr;
+  double* scores_out = nullptr;
+  Admit adm{};
+  double* best_s    = nullptr;
+  int32_t* best_row = nullptr;
+  bool screened     = false;  // the tensor-core screen ran: the counters decide whether the outputs stand
+  uint8_t* qbuf     = nullptr;
+  float* shift      = nullptr;
+  unsigned int* q_ovf = nullptr;
+  int32_t* ovf_list = nullptr;
+  int32_t* thr2     = nullptr;
+  unsigned int* d_count = nullptr;
+  unsigned long long* d_stats = nullptr;
+  std::vector<cudaEvent_t> events;
+  cudaEvent_t ready = nullptr;
+  Pending(const Resources& r, std::shared_mutex& m) : res(&r), lock(m), scratch(r.stream) {}
+  ~Pending()
+  {
+    for (cudaEvent_t e : events) { cudaEventDestroy(e); }
+    if (ready) { cudaEventDestroy(ready); }
+    res->search_in_flight_ = false;
+  }
+};
+
+Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
+                                    int64_t* neighbors, float* distances, double* scores_out, const Filter& filter,
+                                    int64_t id_base, unsigned long long* status_out) const
 {
-  std::shared_lock<std::shared_mutex> lock(rw_);
-  const int64_t n = size_;
+  CERTEX_EXPECTS(!res.search_in_flight_, "certex: a search is already in flight on these resources (search_end it first)");
+  auto pending = std::make_unique<Pending>(res, rw_);
+  res.search_in_flight_ = true;
+  Pending& P            = *pending;
+  const int64_t n       = size_;
   CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
   CERTEX_EXPECTS(n >= k, "certex: k exceeds the number of vectors added to the index");
   CERTEX_EXPECTS(sp.batch_size >= 1, "certex: batch_size must be positive");
   CERTEX_EXPECTS(nq >= 0 && nq < (int64_t(1) << 31), "certex: too many queries in one call");
   CERTEX_EXPECTS(!filter.query_labels || has_labels_, "certex: the index has no labels");
-  if (nq == 0) { return; }
+  // the filter must cover the rows of this snapshot (the size is read under the reader lock the call holds)
+  CERTEX_EXPECTS(filter.words == nullptr || filter.covered_ids >= n,
+                 filter.bitmap_cols > 0 ? "certex: the bitmap must hold one row of size() bits per query"
+                                        : "certex: the bitset must cover every id of the index");
+  if (status_out) { CERTEX_CUDA(cudaMemsetAsync(status_out, 0, sizeof(unsigned long long), res.stream)); }
+  P.sp = sp, P.queries = queries, P.nq = nq, P.n = n, P.k = k, P.id_base = id_base;
+  P.neighbors = neighbors, P.distances = distances, P.scores_out = scores_out;
+  if (nq == 0) { return pending.release(); }
+  if (test_mode_ == 4 && nq > test_cap_) { throw OutOfMemory("certex: out of device memory (simulated for a test)"); }
 
-  Scratch scratch(res.stream);
+  Scratch& scratch       = P.scratch;
   const int d            = static_cast<int>(dim_);
   const size_t row_bytes = static_cast<size_t>(d) * dtype_size(dtype_);
+  P.row_bytes            = row_bytes;
   double* best_s         = scratch.get<double>(static_cast<size_t>(nq) * k);
   int32_t* best_row      = scratch.get<int32_t>(static_cast<size_t>(nq) * k);
+  P.best_s = best_s, P.best_row = best_row;
 
   Admit adm{};
   adm.removed         = removed_;
@@ -1132,6 +1206,7 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   adm.bitmap_cols     = filter.bitmap_cols;
   adm.row_labels      = filter.query_labels ? labels_ : nullptr;
   adm.query_labels    = filter.query_labels;
+  P.adm               = adm;
   // A bitset (one bit per id for all queries) keeps the screen: the anchors it drops are left out of the thresholds and
   // the exact stage applies it to the kept pairs, as the reference does (cpp/src/neighbors/certex/detail/kernels.hpp:
   // 39-62). A bitmap (a row of bits per query) and label searches without a partition score every vector.
@@ -1140,12 +1215,13 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
   const int stride    = anchor_stride_for(n, k);
   const bool screened = screen_kind_ != 0 && !code_overflow_ && !filtered && stride >= 1 && test_mode_ != 1;
 
-  SearchStats local{};
-  local.queries = static_cast<unsigned long long>(nq);
+  SearchStats& local = P.local;
+  local.queries      = static_cast<unsigned long long>(nq);
   if (filter.query_labels && !filter.words && n_part_ > 0 && test_mode_ != 1) {
     local.survivors = search_by_labels(res, queries, row_bytes, static_cast<int>(nq), k, adm, best_s, best_row, n, &local);
     local.verified  = local.survivors;
   } else if (screened) {
+    P.screened           = true;
     const int64_t nq_pad = round_up(nq, kQTile);
     uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * code_pitch_);
     float* shift         = nullptr;
@@ -1169,85 +1245,23 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     CERTEX_CUDA(cudaMemsetAsync(d_count, 0, 4 * sizeof(unsigned int), res.stream));
     CERTEX_CUDA(cudaMemsetAsync(d_stats, 0, 2 * sizeof(unsigned long long), res.stream));
     const int64_t batch = std::min<int64_t>(sp.batch_size, 32768);
-    std::vector<cudaEvent_t> events;
+    P.qbuf = qbuf, P.shift = shift, P.q_ovf = q_ovf, P.ovf_list = ovf_list, P.thr2 = thr2, P.d_count = d_count;
+    P.d_stats = d_stats, P.batch = batch;
     for (int64_t q0 = 0; q0 < nq; q0 += batch) {
       const int nb = static_cast<int>(std::min<int64_t>(batch, nq - q0));
       search_screened(res, qbuf, shift, queries, row_bytes, static_cast<int>(q0), nb, k, best_s, best_row, ovf_list, d_count,
-                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, thr2, adm, stats_sink ? &events : nullptr);
+                      d_stats, reinterpret_cast<int*>(d_count + 1), stride, n, thr2, adm, stats_sink ? &P.events : nullptr);
       local.launches += screen_kind_ == 2 ? 7 : 6;  // gather_init, GROUPMAX, kth_largest (+ thresholds), SCREEN, expand, verify
     }
-    unsigned int h_count[4]       = {0, 0, 0, 0};
-    unsigned long long h_stats[2] = {0, 0};
-    CERTEX_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
-    unsigned int h_q_ovf = 0;
-    CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(&h_q_ovf, q_ovf, sizeof(h_q_ovf), cudaMemcpyDeviceToHost, res.stream));
-    res.sync();  // the one host round trip of a search call
-    for (size_t e = 0; e + 3 < events.size(); e += 4) {
-      float ms = 0;
-      cudaEventElapsedTime(&ms, events[e], events[e + 1]);
-      local.anchor_ms += ms;
-      cudaEventElapsedTime(&ms, events[e + 2], events[e + 3]);
-      local.screen_ms += ms;
-      ++local.screen_passes;
-    }
-    for (cudaEvent_t e : events) { cudaEventDestroy(e); }
-    events.clear();
-    CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
-    local.survivors = h_stats[0];
-    local.verified  = h_stats[1];
-    if (h_q_ovf) {  // a query coordinate beyond the fp16 range: no threshold of this call is trusted
-      search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
-      local.dense_queries = static_cast<unsigned long long>(nq);
-      local.launches += 2;
-    } else if (h_count[0] > 0) {
-      // Candidate lists that overflowed. Each of those queries got a tighter threshold from the candidates it did list;
-      // they are screened once more with it, as a batch of their own. What overflows again is searched without the screen.
-      const int n_ovf        = static_cast<int>(h_count[0]);
-      const int64_t pad      = round_up(n_ovf, kQTile);
-      uint8_t* qcodes2       = scratch.get<uint8_t>(static_cast<size_t>(pad) * code_pitch_);
-      uint8_t* queries2      = scratch.get<uint8_t>(static_cast<size_t>(n_ovf) * row_bytes);
-      float* shift2          = scratch.get<float>(static_cast<size_t>(n_ovf));
-      double* best2_s        = scratch.get<double>(static_cast<size_t>(n_ovf) * k);
-      int32_t* best2_row     = scratch.get<int32_t>(static_cast<size_t>(n_ovf) * k);
-      int32_t* ovf2          = scratch.get<int32_t>(static_cast<size_t>(n_ovf));
-      launch_gather_rows(qbuf, code_pitch_, ovf_list, n_ovf, pad, qcodes2, code_pitch_, code_pitch_, res.stream);
-      launch_gather_rows(queries, row_bytes, ovf_list, n_ovf, n_ovf, queries2, row_bytes, row_bytes, res.stream);
-      if (shift) { launch_gather_rows(shift, 4, ovf_list, n_ovf, n_ovf, shift2, 4, 4, res.stream); }
-      CERTEX_CUDA(cudaGetLastError());
-      events.clear();
-      for (int b0 = 0; b0 < n_ovf; b0 += static_cast<int>(batch)) {
-        const int nb = std::min<int>(static_cast<int>(batch), n_ovf - b0);
-        screen_pass(res, qcodes2 + static_cast<size_t>(b0) * code_pitch_, thr2 + b0, queries2, row_bytes, b0, nb, k, best2_s,
-                    best2_row, ovf2, d_count + 2, d_stats, reinterpret_cast<int*>(d_count + 1), n, nullptr,
-                    shift ? shift2 : nullptr, adm, stats_sink ? &events : nullptr);
-        local.launches += 3;
-      }
-      launch_scatter_best(best2_s, best2_row, ovf_list, n_ovf, k, best_s, best_row, res.stream);
-      launch_compose(ovf2, d_count + 2, n_ovf, ovf_list, res.stream);
-      CERTEX_CUDA(cudaGetLastError());
-      local.launches += 5;
-      CERTEX_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
-      CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
-      res.sync();
-      for (size_t e = 0; e + 1 < events.size(); e += 2) {
-        float ms = 0;
-        cudaEventElapsedTime(&ms, events[e], events[e + 1]);
-        local.screen_ms += ms;
-        ++local.screen_passes;
-      }
-      for (cudaEvent_t e : events) { cudaEventDestroy(e); }
-      events.clear();
-      CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
-      local.survivors    = h_stats[0];
-      local.verified     = h_stats[1];
-      local.rescreened   = static_cast<unsigned long long>(n_ovf);
-      if (h_count[2] > 0) {
-        search_dense(res, queries, row_bytes, ovf2, 0, static_cast<int>(h_count[2]), k, adm, best_s, best_row, n);
-        local.dense_queries = h_count[2];
-        local.launches += 2;
-        local.verified += static_cast<unsigned long long>(h_count[2]) * static_cast<unsigned long long>(n);
-      }
+    // The outputs are written now, as if no list had overflowed; the counters follow them to the host and search_end
+    // looks at them once the caller has enqueued what it wanted behind the search.
+    auto* host = static_cast<HostCounters*>(res.pinned_block());
+    CERTEX_CUDA(cudaMemcpyAsync(host->count, d_count, sizeof(host->count), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(host->stats, d_stats, sizeof(host->stats), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(&host->q_ovf, q_ovf, sizeof(host->q_ovf), cudaMemcpyDeviceToHost, res.stream));
+    if (status_out) {
+      launch_search_status(d_count, q_ovf, status_out, res.stream);
+      local.launches += 1;
     }
   } else {
     search_dense(res, queries, row_bytes, nullptr, 0, static_cast<int>(nq), k, adm, best_s, best_row, n);
@@ -1260,7 +1274,102 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
                 distances, scores_out, res.stream);
   CERTEX_CUDA(cudaGetLastError());
   local.launches += 1;  // finish
-  if (stats_sink) {
+  if (P.screened) {
+    CERTEX_CUDA(cudaEventCreateWithFlags(&P.ready, cudaEventDisableTiming));
+    CERTEX_CUDA(cudaEventRecord(P.ready, res.stream));
+  }
+  return pending.release();
+}
+
+bool Index::search_end(Pending* raw) const
+{
+  std::unique_ptr<Pending> pending(raw);
+  CERTEX_EXPECTS(raw != nullptr, "certex: no search to finish");
+  Pending& P          = *pending;
+  const Resources& res = *P.res;
+  SearchStats& local  = P.local;
+  bool changed        = false;
+  if (P.screened && P.nq > 0) {
+    CERTEX_CUDA(cudaEventSynchronize(P.ready));  // the one host round trip of a search call
+    const HostCounters h = *static_cast<const HostCounters*>(res.pinned_block());
+    auto add_times = [&](size_t per_pass) {
+      for (size_t e = 0; e + per_pass - 1 < P.events.size(); e += per_pass) {
+        float ms = 0;
+        if (per_pass == 4) {
+          cudaEventElapsedTime(&ms, P.events[e], P.events[e + 1]);
+          local.anchor_ms += ms;
+        }
+        cudaEventElapsedTime(&ms, P.events[e + per_pass - 2], P.events[e + per_pass - 1]);
+        local.screen_ms += ms;
+        ++local.screen_passes;
+      }
+      for (cudaEvent_t e : P.events) { cudaEventDestroy(e); }
+      P.events.clear();
+    };
+    add_times(4);
+    CERTEX_EXPECTS(h.count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h.count[1]) + ")");
+    local.survivors = h.stats[0];
+    local.verified  = h.stats[1];
+    const int k     = P.k;
+    const int64_t n = P.n, nq = P.nq;
+    Scratch& scratch = P.scratch;
+    if (h.q_ovf) {  // a query coordinate beyond the fp16 range: no threshold of this call is trusted
+      search_dense(res, P.queries, P.row_bytes, nullptr, 0, static_cast<int>(nq), k, P.adm, P.best_s, P.best_row, n);
+      local.dense_queries = static_cast<unsigned long long>(nq);
+      local.launches += 2;
+      changed = true;
+    } else if (h.count[0] > 0) {
+      // Candidate lists that overflowed. Each of those queries got a tighter threshold from the candidates it did list;
+      // they are screened once more with it, as a batch of their own. What overflows again is searched without the screen.
+      const int n_ovf        = static_cast<int>(h.count[0]);
+      const int64_t pad      = round_up(n_ovf, kQTile);
+      uint8_t* qcodes2       = scratch.get<uint8_t>(static_cast<size_t>(pad) * code_pitch_);
+      uint8_t* queries2      = scratch.get<uint8_t>(static_cast<size_t>(n_ovf) * P.row_bytes);
+      float* shift2          = scratch.get<float>(static_cast<size_t>(n_ovf));
+      double* best2_s        = scratch.get<double>(static_cast<size_t>(n_ovf) * k);
+      int32_t* best2_row     = scratch.get<int32_t>(static_cast<size_t>(n_ovf) * k);
+      int32_t* ovf2          = scratch.get<int32_t>(static_cast<size_t>(n_ovf));
+      launch_gather_rows(P.qbuf, code_pitch_, P.ovf_list, n_ovf, pad, qcodes2, code_pitch_, code_pitch_, res.stream);
+      launch_gather_rows(P.queries, P.row_bytes, P.ovf_list, n_ovf, n_ovf, queries2, P.row_bytes, P.row_bytes, res.stream);
+      if (P.shift) { launch_gather_rows(P.shift, 4, P.ovf_list, n_ovf, n_ovf, shift2, 4, 4, res.stream); }
+      CERTEX_CUDA(cudaGetLastError());
+      for (int b0 = 0; b0 < n_ovf; b0 += static_cast<int>(P.batch)) {
+        const int nb = std::min<int>(static_cast<int>(P.batch), n_ovf - b0);
+        screen_pass(res, qcodes2 + static_cast<size_t>(b0) * code_pitch_, P.thr2 + b0, queries2, P.row_bytes, b0, nb, k, best2_s,
+                    best2_row, ovf2, P.d_count + 2, P.d_stats, reinterpret_cast<int*>(P.d_count + 1), n, nullptr,
+                    P.shift ? shift2 : nullptr, P.adm, stats_sink ? &P.events : nullptr);
+        local.launches += 3;
+      }
+      launch_scatter_best(best2_s, best2_row, P.ovf_list, n_ovf, k, P.best_s, P.best_row, res.stream);
+      launch_compose(ovf2, P.d_count + 2, n_ovf, P.ovf_list, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+      local.launches += 5;
+      unsigned int h_count[4]       = {0, 0, 0, 0};
+      unsigned long long h_stats[2] = {0, 0};
+      CERTEX_CUDA(cudaMemcpyAsync(h_count, P.d_count, sizeof(h_count), cudaMemcpyDeviceToHost, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(h_stats, P.d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+      add_times(2);
+      CERTEX_EXPECTS(h_count[1] == 0, "certex: the screening pass gave up on a wait (code " + std::to_string(h_count[1]) + ")");
+      local.survivors    = h_stats[0];
+      local.verified     = h_stats[1];
+      local.rescreened   = static_cast<unsigned long long>(n_ovf);
+      if (h_count[2] > 0) {
+        search_dense(res, P.queries, P.row_bytes, ovf2, 0, static_cast<int>(h_count[2]), k, P.adm, P.best_s, P.best_row, n);
+        local.dense_queries = h_count[2];
+        local.launches += 2;
+        local.verified += static_cast<unsigned long long>(h_count[2]) * static_cast<unsigned long long>(n);
+      }
+      changed = true;
+    }
+    if (changed) {
+      launch_finish(P.best_s, P.best_row, P.id_base, P.queries, P.row_bytes, dtype_, static_cast<int>(dim_), params_.metric,
+                    static_cast<int>(nq), k, P.neighbors, P.distances, P.scores_out, res.stream);
+      CERTEX_CUDA(cudaGetLastError());
+      local.launches += 1;
+    }
+  }
+  if (stats_sink && P.nq > 0) {
     stats_sink->launches += local.launches;
     stats_sink->screen_ms += local.screen_ms;
     stats_sink->anchor_ms += local.anchor_ms;
@@ -1271,6 +1380,32 @@ void Index::search(const Resources& res, const SearchParams& sp, const void* que
     stats_sink->dense_queries += local.dense_queries;
     stats_sink->rescreened += local.rescreened;
     stats_sink->routed_queries += local.routed_queries;
+  }
+  return changed;
+}
+
+void Index::search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
+                   int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base) const
+{
+  try {
+    search_end(search_begin(res, sp, queries, nq, k, neighbors, distances, scores_out, filter, id_base, nullptr));
+    return;
+  } catch (const OutOfMemory&) {
+    // no room for the temporaries of this many queries: the two halves one after the other, recursively
+    // (cpp/src/neighbors/certex/certex.cu:1477-1502); a bitmap filter is cut at a whole word of query rows
+    if (nq < 2 || (filter.bitmap_cols > 0 && nq < 64)) { throw; }
+  }
+  int64_t half = nq / 2;
+  if (filter.bitmap_cols > 0) { half = half / 32 * 32; }
+  const size_t row_bytes = static_cast<size_t>(dim_) * dtype_size(dtype_);
+  for (int part = 0; part < 2; ++part) {
+    const int64_t q0 = part == 0 ? 0 : half, m = part == 0 ? half : nq - half;
+    Filter f = filter;
+    if (f.query_labels) { f.query_labels += q0; }
+    if (f.bitmap_cols > 0) { f.words += static_cast<size_t>(q0) * static_cast<size_t>(f.bitmap_cols) / 32; }
+    search(res, sp, static_cast<const uint8_t*>(queries) + static_cast<size_t>(q0) * row_bytes, m, k,
+           neighbors + static_cast<size_t>(q0) * k, distances + static_cast<size_t>(q0) * k,
+           scores_out ? scores_out + static_cast<size_t>(q0) * k : nullptr, f, id_base);
   }
 }
 
@@ -1504,14 +1639,35 @@ std::unique_ptr<Index> Index::from_blocks(const Resources& res, const IndexParam
 
 void merge_shards(const Resources& res, const double* scores, const int64_t* ids, int parts, int nq, int k,
                   const void* queries, int dtype, int64_t dim, int metric, int64_t* neighbors, float* distances,
-                  double* scores_out)
+                  double* scores_out, int64_t part_stride)
 {
-  CERTEX_EXPECTS(parts >= 1 && k >= 1 && static_cast<int64_t>(parts) * k <= 8192,
-                 "certex: a merge takes at most 8192 candidates per query");
+  CERTEX_EXPECTS(parts >= 1 && k >= 1 && k <= 2048, "certex: a merge takes at least one part and k up to 2048");
   Scratch scratch(res.stream);
-  double* out_s = scores_out ? scores_out : scratch.get<double>(static_cast<size_t>(nq) * k);
-  launch_merge(scores, ids, parts, nq, k, queries, static_cast<size_t>(dim) * dtype_size(dtype), dtype, static_cast<int>(dim),
-               metric, neighbors, distances, out_s, res.stream);
+  double* out_s        = scores_out ? scores_out : scratch.get<double>(static_cast<size_t>(nq) * k);
+  const size_t qpitch  = static_cast<size_t>(dim) * dtype_size(dtype);
+  const int64_t cells  = static_cast<int64_t>(nq) * k;
+  if (part_stride == 0) { part_stride = cells; }
+  // One block sorts at most 8192 candidates per query. More parts than that are merged in rounds: groups of
+  // floor(8192 / k) lists each give one exact list of k (any of the final k best is among the k best of its group),
+  // until one round takes what is left. The order is (score, id) in every round, so the result does not depend on the
+  // grouping.
+  constexpr int kMaxCandidates = 8192;
+  while (static_cast<int64_t>(parts) * k > kMaxCandidates) {
+    const int group   = kMaxCandidates / k;  // at least 4
+    const int n_next  = (parts + group - 1) / group;
+    double* next_s    = scratch.get<double>(static_cast<size_t>(n_next) * cells);
+    int64_t* next_id  = scratch.get<int64_t>(static_cast<size_t>(n_next) * cells);
+    for (int g = 0; g < n_next; ++g) {
+      const int first = g * group, count = std::min(group, parts - first);
+      launch_merge(scores + static_cast<size_t>(first) * part_stride, ids + static_cast<size_t>(first) * part_stride, count, nq, k,
+                   queries, qpitch, dtype, static_cast<int>(dim), metric, next_id + static_cast<size_t>(g) * cells, nullptr,
+                   next_s + static_cast<size_t>(g) * cells, res.stream, part_stride, false);
+    }
+    CERTEX_CUDA(cudaGetLastError());
+    scores = next_s, ids = next_id, parts = n_next, part_stride = cells;
+  }
+  launch_merge(scores, ids, parts, nq, k, queries, qpitch, dtype, static_cast<int>(dim), metric, neighbors, distances, out_s,
+               res.stream, part_stride, true);
   CERTEX_CUDA(cudaGetLastError());
 }
 

@@ -25,6 +25,12 @@ struct Error : std::runtime_error {
   using std::runtime_error::runtime_error;
 };
 
+/// Device memory for a call's temporaries could not be had. A search answers it by splitting its queries in halves,
+/// like the reference (cpp/src/neighbors/certex/certex.cu:1477-1502).
+struct OutOfMemory : Error {
+  using Error::Error;
+};
+
 #define CERTEX_EXPECTS(cond, msg)                                \
   do {                                                           \
     if (!(cond)) { throw ::certex_b200::Error(std::string(msg)); } \
@@ -45,7 +51,18 @@ struct Resources {
   cudaStream_t stream = nullptr;
   int sm_count        = 0;
   Resources();
+  ~Resources();
+  Resources(const Resources&)            = delete;
+  Resources& operator=(const Resources&) = delete;
   void sync() const;
+  /// A small block of page-locked host memory (256 bytes) that the counters of a search in flight are copied to; made
+  /// on first use. One search at a time may be in flight per Resources (search_begin .. search_end).
+  void* pinned_block() const;
+
+ private:
+  mutable void* pinned_ = nullptr;
+  friend class Index;
+  mutable bool search_in_flight_ = false;
 };
 
 /// cuvs::neighbors::certex::index_params (cpp/include/cuvs/neighbors/certex.hpp:43-87). Every setting returns the same
@@ -87,6 +104,8 @@ struct Filter {
   const uint32_t* words = nullptr;  // device words, bit j of word i is entry 32 i + j, set = keep
   int64_t bitmap_cols   = 0;        // 0: bitset over the ids; > 0: bitmap [n_queries, bitmap_cols]
   const int32_t* query_labels = nullptr;  // device [n_queries]: search by label
+  int64_t covered_ids         = 0;        // ids the words cover (bits of a bitset, columns of a bitmap): checked against
+                                          // the index size under the search's reader lock
 };
 
 class Index {
@@ -113,6 +132,23 @@ class Index {
   void search(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k, int64_t* neighbors,
               float* distances, double* scores_out, const Filter& filter, int64_t id_base = 0) const;
 
+  /**
+   * The same search in two steps, for callers that have more device work to enqueue behind it (the all-gather and the
+   * merge of a sharded search) before the host looks at anything. search_begin enqueues the whole search on res.stream,
+   * outputs included, and returns without waiting for the device; it assumes that no candidate list overflows, which
+   * is what nearly every call sees. status_out (optional, device) receives a non-zero word when the assumption did not
+   * hold for this call. search_end waits for the stream, and only then, if a list did overflow, enqueues the repair
+   * (second pass or dense scan of the queries concerned) and writes the outputs again; it returns true in that case:
+   * whatever the caller derived from the outputs in between must be derived again. Every search_begin needs its
+   * search_end on the same thread (it holds the index's reader lock and the call's temporaries); one search may be in
+   * flight per Resources. search() is search_begin + search_end (plus the halving on allocation failure).
+   */
+  struct Pending;
+  Pending* search_begin(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
+                        int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base,
+                        unsigned long long* status_out) const;
+  bool search_end(Pending* pending) const;
+
   int64_t size() const { return size_; }
   int64_t dim() const { return dim_; }
   int64_t capacity() const { return capacity_; }
@@ -132,7 +168,8 @@ class Index {
   static std::unique_ptr<Index> load(const Resources& res, std::istream& is, int dtype);
 
   /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity,
-  /// 3 = searches by label score their label's rows densely (no routed screen).
+  /// 3 = searches by label score their label's rows densely (no routed screen), 4 = a search call of more than `cap`
+  /// queries fails as if the device were out of memory (exercises the halving, on the host, without exhausting a GPU).
   void set_test_mode(int mode, int cap) { test_mode_ = mode, test_cap_ = cap; }
 
   static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
@@ -227,7 +264,21 @@ class Index {
 /// order of the reference's sharded merge (cpp/src/neighbors/certex/certex_shards.cu:144-166).
 void merge_shards(const Resources& res, const double* scores, const int64_t* ids, int parts, int nq, int k,
                   const void* queries, int dtype, int64_t dim, int metric, int64_t* neighbors, float* distances,
-                  double* scores_out);
+                  double* scores_out, int64_t part_stride = 0);
+
+/// Row shards over several processes, one GPU each (nccl_shards.cu): a communicator with its exchange buffers, and the
+/// sharded search over it. comm_create: from a 128-byte id that one rank made with comm_unique_id and the application
+/// sent to the others (ncclCommInitRank on the current device), or adopting an ncclComm_t the application owns.
+struct Comm;
+void comm_unique_id(void* id128);
+Comm* comm_create(const void* id128, int n_ranks, int rank, void* adopt);
+void comm_destroy(Comm* c);
+int comm_ranks(const Comm* c);
+/// Every rank calls it with the same queries, k and parameters: local exact top-k of its shard (ids + id_base),
+/// ncclAllGather of the lists, merge by (score, id); the same answer on every rank. Device pointers.
+void distributed_search(const Resources& res, Comm& c, const Index& index, const SearchParams& sp, const void* queries,
+                        int64_t nq, int k, int64_t* neighbors, float* distances, double* scores_out, int64_t id_base,
+                        bool share_thresholds);
 
 /// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);

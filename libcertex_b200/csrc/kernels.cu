@@ -1400,8 +1400,13 @@ __global__ void finish_kernel(const double* best_s, const int32_t* best_row, con
 }
 
 // Block per query; shared memory: s [n2] doubles | id [n2] int64.
+__global__ void search_status_kernel(const unsigned int* count, const unsigned int* q_ovf, unsigned long long* status)
+{
+  *status = (count[0] != 0 ? 1ull : 0ull) | (count[1] != 0 ? 2ull : 0ull) | (*q_ovf != 0 ? 4ull : 0ull);
+}
+
 __global__ void merge_kernel(const double* in_s, const int64_t* in_id, int parts, int nq, int k, int n2, double* out_s,
-                             int64_t* out_id)
+                             int64_t* out_id, int64_t part_stride)
 {
   extern __shared__ double sh[];
   double* s   = sh;
@@ -1412,7 +1417,7 @@ __global__ void merge_kernel(const double* in_s, const int64_t* in_id, int parts
     double v   = CUDART_INF;
     int64_t ii = 0x7fffffffffffffffll;
     if (i < m) {
-      const size_t o = (static_cast<size_t>(i / k) * nq + q) * k + (i % k);
+      const size_t o = static_cast<size_t>(i / k) * part_stride + static_cast<size_t>(q) * k + (i % k);
       if (in_id[o] >= 0) {
         v  = in_s[o];
         ii = in_id[o];
@@ -1824,15 +1829,23 @@ void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_bas
   });
 }
 
+void launch_search_status(const unsigned int* count, const unsigned int* q_ovf, unsigned long long* status, cudaStream_t s)
+{
+  search_status_kernel<<<1, 1, 0, s>>>(count, q_ovf, status);
+}
+
 void launch_merge(const double* in_s, const int64_t* in_id, int parts, int nq, int k, const void* queries, size_t qpitch,
-                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s)
+                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s,
+                  int64_t part_stride, bool finish)
 {
   if (nq <= 0) { return; }
+  if (part_stride == 0) { part_stride = static_cast<int64_t>(nq) * k; }
   // merged (score, id) go to scores_out / neighbors first; finish_kernel then converts in place
   const int n2      = next_pow2(parts * k) < 2 ? 2 : next_pow2(parts * k);
   const size_t smem = (sizeof(double) + sizeof(int64_t)) * static_cast<size_t>(n2);
   allow_smem(merge_kernel, smem);
-  merge_kernel<<<nq, 256, smem, s>>>(in_s, in_id, parts, nq, k, n2, scores_out, neighbors);
+  merge_kernel<<<nq, 256, smem, s>>>(in_s, in_id, parts, nq, k, n2, scores_out, neighbors, part_stride);
+  if (!finish) { return; }
   by_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
     finish_kernel<T><<<nq, 64, 0, s>>>(scores_out, nullptr, neighbors, 0, queries, qpitch, d, metric, k, neighbors, distances, scores_out);

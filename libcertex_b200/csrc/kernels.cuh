@@ -183,8 +183,15 @@ void launch_finish(const double* best_s, const int32_t* best_row, int64_t id_bas
                    cudaStream_t s);
 
 /// Merge of `parts` answer lists per query, [parts, nq, k] (score, id) with id -1 = missing, by (score, id);
-/// writes merged ids, fp64 scores and float distances.
+/// writes merged ids, fp64 scores and float distances. part_stride: elements between the lists of consecutive parts
+/// (0: nq * k, densely packed). With finish = false only the merged ids and fp64 scores are written (an intermediate
+/// round of a merge of more candidates than one block sorts).
 void launch_merge(const double* in_s, const int64_t* in_id, int parts, int nq, int k, const void* queries, size_t qpitch,
-                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s);
+                  int dtype, int d, int metric, int64_t* neighbors, float* distances, double* scores_out, cudaStream_t s,
+                  int64_t part_stride = 0, bool finish = true);
+
+/// *status = 1 if a candidate list of the call overflowed, + 2 if a pass gave up on a wait, + 4 if a query coordinate
+/// did not fit fp16 (count: the call's counters, see Index::search_begin).
+void launch_search_status(const unsigned int* count, const unsigned int* q_ovf, unsigned long long* status, cudaStream_t s);
 
 }  // namespace certex_b200

@@ -1,0 +1,252 @@
+// Row shards over several processes, one GPU each: the exchange step of the sharded search over NCCL.
+//
+// The reference keeps all shards in one process and moves the per-shard lists through host memory
+// (cpp/src/neighbors/certex/certex_shards.cu:85-167: one thread per shard, host std::sort of the lists). Here every
+// rank owns one shard and one GPU; a search call is, on one stream and without a host round trip in between,
+//   local exact top-k of all queries (Index::search_begin)            -> k (fp64 score, int64 global id) per query
+//   ncclAllGather of the lists (+ one status word per rank)           -> [ranks, nq, k] on every GPU
+//   merge by (score, id) (merge_shards)                               -> the answer, identical on every rank
+// and then one wait of the host, which reads every rank's status word: if a rank's candidate lists overflowed (rare)
+// it repairs its lists (Index::search_end) and all ranks run the exchange and the merge once more; if a rank failed,
+// every rank reports the failure instead of waiting for it. The optional first round of the reference (shards share
+// their thresholds, certex_shards.cu:136-141) is an ncclAllReduce(max) over the per-query threshold keys.
+//
+// NCCL is not linked: the library is found at run time (the copy that the process has already loaded, e.g. the one
+// PyTorch brings, else libnccl.so.2 on the loader's path), so libcertex_b200.so loads on machines without NCCL as long
+// as these entry points are not called. No kernel reads another GPU's memory; NCCL moves the lists.
+#include "../../include/certex_b200.h"
+
+#include "engine.hpp"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace certex_b200 {
+
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*)                                                            = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int)                                     = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t)                                                               = nullptr;
+  ncclResult_t (*CommCount)(const ncclComm_t, int*)                                                     = nullptr;
+  ncclResult_t (*CommUserRank)(const ncclComm_t, int*)                                                  = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t)       = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t)                                                           = nullptr;
+};
+
+const NcclApi& nccl()
+{
+  static NcclApi api = [] {
+    NcclApi a;
+    // the copy already in the process first (RTLD_NOLOAD finds it by its soname)
+    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!a.handle) { a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL); }
+    if (!a.handle) { a.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL); }
+    CERTEX_EXPECTS(a.handle != nullptr, std::string("certex: NCCL is not available (") + dlerror() + ")");
+    auto need = [&](const char* name) {
+      void* f = dlsym(a.handle, name);
+      CERTEX_EXPECTS(f != nullptr, std::string("certex: the NCCL library lacks ") + name);
+      return f;
+    };
+    a.GetUniqueId    = reinterpret_cast<decltype(a.GetUniqueId)>(need("ncclGetUniqueId"));
+    a.CommInitRank   = reinterpret_cast<decltype(a.CommInitRank)>(need("ncclCommInitRank"));
+    a.CommDestroy    = reinterpret_cast<decltype(a.CommDestroy)>(need("ncclCommDestroy"));
+    a.CommCount      = reinterpret_cast<decltype(a.CommCount)>(need("ncclCommCount"));
+    a.CommUserRank   = reinterpret_cast<decltype(a.CommUserRank)>(need("ncclCommUserRank"));
+    a.AllGather      = reinterpret_cast<decltype(a.AllGather)>(need("ncclAllGather"));
+    a.AllReduce      = reinterpret_cast<decltype(a.AllReduce)>(need("ncclAllReduce"));
+    a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(need("ncclGetErrorString"));
+    return a;
+  }();
+  return api;
+}
+
+#define CERTEX_NCCL(call)                                                                                        \
+  do {                                                                                                           \
+    ncclResult_t r_ = (call);                                                                                    \
+    if (r_ != ncclSuccess) {                                                                                     \
+      throw ::certex_b200::Error(std::string("certex: NCCL error ") + nccl().GetErrorString(r_) + " at " + __FILE__ + \
+                                 ":" + std::to_string(__LINE__));                                                \
+    }                                                                                                            \
+  } while (0)
+
+constexpr unsigned long long kStatusFailed = 8;  // the rank's local search threw: its lists are empty
+
+}  // namespace
+
+/// A communicator over the ranks of one sharded set, with the exchange buffers of its searches (kept between calls).
+struct Comm {
+  ncclComm_t comm = nullptr;
+  bool owned      = false;  // made by certexB200CommInitRank (destroyed with this object) or adopted from the caller
+  int n_ranks = 0, rank = 0, device = 0;
+  int64_t* send = nullptr;  // [2 nq k + 1]: fp64 scores as bits, global ids, the status word
+  int64_t* recv = nullptr;  // [n_ranks, 2 nq k + 1]
+  size_t send_words = 0;
+  unsigned long long* host_status = nullptr;  // page-locked, [n_ranks]
+  std::map<int, bool> all_screen;             // k -> every rank's search for k neighbours goes through the screen
+  int64_t all_screen_size = -1;               // ... decided for this index size
+  ~Comm()
+  {
+    cudaFree(send), cudaFree(recv);
+    if (host_status) { cudaFreeHost(host_status); }
+    if (owned && comm) { nccl().CommDestroy(comm); }
+  }
+  void reserve(size_t words)
+  {
+    if (words <= send_words) { return; }
+    cudaFree(send), cudaFree(recv);
+    send = recv = nullptr, send_words = 0;
+    CERTEX_CUDA(cudaMalloc(&send, words * 8));
+    CERTEX_CUDA(cudaMalloc(&recv, words * 8 * static_cast<size_t>(n_ranks)));
+    send_words = words;
+  }
+};
+
+namespace {
+
+void share_thresholds_hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
+{
+  // any k rows of one shard bound the k-th neighbour of the whole set: every rank screens with the tightest bound
+  auto* c = static_cast<Comm*>(ctx);
+  CERTEX_NCCL(nccl().AllReduce(keys, keys, static_cast<size_t>(n), ncclInt32, ncclMax, c->comm, stream));
+}
+
+}  // namespace
+
+void comm_unique_id(void* id128)
+{
+  static_assert(sizeof(ncclUniqueId) == 128, "the id buffer of the C ABI holds an ncclUniqueId");
+  ncclUniqueId id;
+  CERTEX_NCCL(nccl().GetUniqueId(&id));
+  std::memcpy(id128, &id, sizeof(id));
+}
+
+Comm* comm_create(const void* id128, int n_ranks, int rank, void* adopt)
+{
+  auto c = std::make_unique<Comm>();
+  CERTEX_CUDA(cudaGetDevice(&c->device));
+  if (adopt) {
+    c->comm = static_cast<ncclComm_t>(adopt);
+    CERTEX_NCCL(nccl().CommCount(c->comm, &c->n_ranks));
+    CERTEX_NCCL(nccl().CommUserRank(c->comm, &c->rank));
+  } else {
+    CERTEX_EXPECTS(id128 != nullptr && n_ranks >= 1 && rank >= 0 && rank < n_ranks, "certex: a rank in [0, n_ranks) and an id");
+    ncclUniqueId id;
+    std::memcpy(&id, id128, sizeof(id));
+    CERTEX_NCCL(nccl().CommInitRank(&c->comm, n_ranks, id, rank));
+    c->owned = true, c->n_ranks = n_ranks, c->rank = rank;
+  }
+  CERTEX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&c->host_status), sizeof(unsigned long long) * c->n_ranks, cudaHostAllocDefault));
+  return c.release();
+}
+
+void comm_destroy(Comm* c) { delete c; }
+
+int comm_ranks(const Comm* c) { return c->n_ranks; }
+
+void distributed_search(const Resources& res, Comm& c, const Index& index, const SearchParams& sp, const void* queries,
+                        int64_t nq, int k, int64_t* neighbors, float* distances, double* scores_out, int64_t id_base,
+                        bool share_thresholds)
+{
+  CERTEX_EXPECTS(res.device == c.device, "certex: the communicator was made on another device than these resources");
+  if (nq == 0) { return; }
+  const size_t cells = static_cast<size_t>(nq) * k, words = 2 * cells + 1;
+  c.reserve(words);
+  auto* send_scores = reinterpret_cast<double*>(c.send);
+  int64_t* send_ids = c.send + cells;
+  auto* send_status = reinterpret_cast<unsigned long long*>(c.send + 2 * cells);
+
+  if (share_thresholds && c.n_ranks > 1) {
+    // the exchange needs every rank to reach it, i.e. to screen: agreed once per k and index size
+    if (c.all_screen_size != index.size()) { c.all_screen.clear(), c.all_screen_size = index.size(); }
+    if (!c.all_screen.count(k)) {
+      int32_t mine = index.will_screen(k) ? 1 : 0, *d = reinterpret_cast<int32_t*>(c.send);
+      CERTEX_CUDA(cudaMemcpyAsync(d, &mine, 4, cudaMemcpyHostToDevice, res.stream));
+      CERTEX_NCCL(nccl().AllReduce(d, d, 1, ncclInt32, ncclMin, c.comm, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(&mine, d, 4, cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+      c.all_screen[k] = mine != 0;
+    }
+    share_thresholds = c.all_screen[k];
+  } else {
+    share_thresholds = false;
+  }
+
+  auto fail_lists = [&] {  // empty lists and the failure flag in this rank's contribution
+    cudaGetLastError();
+    CERTEX_CUDA(cudaMemsetAsync(c.send, 0xff, 2 * cells * 8, res.stream));  // ids -1 (scores: never read)
+    CERTEX_CUDA(cudaMemcpyAsync(send_status, &kStatusFailed, 8, cudaMemcpyHostToDevice, res.stream));
+  };
+  // ---- the local exact top-k, written straight into the send buffer (distances: scratch use of the caller's output)
+  Index::Pending* pending = nullptr;
+  std::exception_ptr failed;
+  try {
+    if (share_thresholds) { Index::threshold_hook = share_thresholds_hook, Index::threshold_hook_ctx = &c; }
+    pending = index.search_begin(res, sp, queries, nq, k, send_ids, distances, send_scores, Filter{}, id_base, send_status);
+    Index::threshold_hook = nullptr, Index::threshold_hook_ctx = nullptr;
+  } catch (...) {
+    // this rank cannot answer: it still takes part in the exchange, with empty lists and the failure in its status
+    // word, so that no rank is left waiting in the collective (a rank that failed inside the threshold exchange cannot
+    // be helped this way; NCCL's own timeout ends the others' wait)
+    Index::threshold_hook = nullptr, Index::threshold_hook_ctx = nullptr;
+    failed = std::current_exception();
+    fail_lists();
+  }
+
+  auto exchange = [&] {
+    CERTEX_NCCL(nccl().AllGather(c.send, c.recv, words, ncclInt64, c.comm, res.stream));
+    merge_shards(res, reinterpret_cast<const double*>(c.recv), c.recv + cells, c.n_ranks, static_cast<int>(nq), k, queries,
+                 index.dtype(), index.dim(), index.metric(), neighbors, distances, scores_out, static_cast<int64_t>(words));
+    CERTEX_CUDA(cudaMemcpy2DAsync(c.host_status, 8, c.recv + 2 * cells, words * 8, 8, static_cast<size_t>(c.n_ranks),
+                                  cudaMemcpyDeviceToHost, res.stream));
+  };
+  // round 1 assumes that no candidate list overflowed; the ranks' status words say whether that held everywhere
+  bool again = false;
+  int failed_rank = -1;
+  auto read_status = [&](bool first) {
+    res.sync();  // the one wait of a round: everything before it ran back to back on the device
+    for (int r = 0; r < c.n_ranks; ++r) {
+      if (first && (c.host_status[r] & 7ull) != 0) { again = true; }
+      if ((c.host_status[r] & kStatusFailed) != 0 && failed_rank < 0) { failed_rank = r; }
+    }
+  };
+  try {
+    exchange();
+    read_status(true);
+  } catch (...) {
+    if (pending) {
+      try {
+        index.search_end(pending);
+      } catch (...) {
+      }
+    }
+    throw;
+  }
+  if (pending) {
+    try {
+      index.search_end(pending);  // repairs this rank's lists when its own status word was set
+    } catch (...) {
+      // only a rank whose status word was set can fail here, so every rank is about to run the second round: this
+      // rank takes part in it with the failure in its status word
+      failed = std::current_exception();
+      fail_lists();
+    }
+  }
+  if (failed_rank < 0 && again) {
+    exchange();
+    read_status(false);
+  }
+  if (failed) { std::rethrow_exception(failed); }
+  CERTEX_EXPECTS(failed_rank < 0, "certex: the local search of rank " + std::to_string(failed_rank) + " failed; no answer for this call");
+}
+
+}  // namespace certex_b200

@@ -173,6 +173,52 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
     : "memory");
 }
 
+/// The same instructions with the accumulate flag fixed at compile time (no predicate register to set up): the
+/// issuing thread's instruction count per MMA is what bounds the rate of short-K units.
+template <bool ACC>
+__device__ __forceinline__ void mma_i8_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc)
+{
+  asm volatile(
+    "{\n\t"
+    ".reg .pred p;\n\t"
+    "setp.ne.b32 p, %4, 0;\n\t"
+    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+    "}\n"
+    :
+    : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+    : "memory");
+}
+
+template <bool ACC>
+__device__ __forceinline__ void mma_f16_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc)
+{
+  asm volatile(
+    "{\n\t"
+    ".reg .pred p;\n\t"
+    "setp.ne.b32 p, %4, 0;\n\t"
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+    "}\n"
+    :
+    : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+    : "memory");
+}
+
+/// A 64-bit descriptor from its two words (a register pair: no instruction when the halves sit in place).
+__device__ __forceinline__ uint64_t pack64(uint32_t lo, uint32_t hi)
+{
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+/// a - b, saturating at the int32 limits.
+__device__ __forceinline__ int sub_sat(int a, int b)
+{
+  int r;
+  asm("sub.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 /**
  * Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the 128-byte swizzle
  * (what a TMA box of 128 bytes x rows with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are 1024 bytes apart

@@ -203,7 +203,9 @@ __device__ __forceinline__ int32_t float_key(float f)
   return i ^ ((i >> 31) & 0x7fffffff);
 }
 
-template <int MODE, bool F16, bool WIDE>
+// KB: K blocks per code row of the resident-panel variants, fixed at compile time (1 or 2) so that the issuing thread's
+// loop over a unit's MMAs unrolls; 0 for WIDE, where the number of K blocks is a run-time value.
+template <int MODE, bool F16, bool WIDE, int KB>
 __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                 const __grid_constant__ CUtensorMap tm_x,
                                                                 const ScreenArgs p)
@@ -227,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle)
   const uint32_t base      = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base        = smem_raw + (base - smem_u32(smem_raw));
-  const int kb             = p.kb;
+  const int kb             = WIDE ? p.kb : KB;
   const int ns             = WIDE ? kWideStages : p.n_stages;
   const uint32_t panel_off = 0;
   const uint32_t stage_off = WIDE ? 0u : panel_off + static_cast<uint32_t>(p.panel_tiles) * kb * kQTileBytes;
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       // descriptors differ only in their 14-bit start-address field: (byte offset >> 4) is added to the low word
       const uint64_t a_desc0 = smem_desc_sw128(base + panel_off);
       const uint64_t b_desc0 = smem_desc_sw128(base + stage_off);
-      int gu = 0, ts = 0;
+      uint32_t gu = 0;
       bool ok = true;
       if (WIDE) {
         int ks = 0;
@@ -397,7 +399,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
               tc_fence_after();
               const uint64_t s_desc = b_desc0 + static_cast<uint64_t>(st) * (kWideStage >> 4);
               for (int j = 0; j < sg.n_qtiles; ++j) {
-                const int u    = gu + j;
+                const int u    = static_cast<int>(gu) + j;
                 const int slot = u & (kSlots - 1);
                 if (b == 0 && u >= kSlots) {  // the slot's previous unit must be in the epilogue's registers
                   ok = mbar_wait(smem_u32(&ctl->tmem_empty[slot]), ((u >> 1) - 1) & 1, abort_flag, p.err, 5);
@@ -422,40 +424,55 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           }
         }
       }
-      for (int s = 0; s < nseg && ok && !WIDE; ++s) {
-        const ScreenSeg sg = segs[s];
-        ok                 = mbar_wait(smem_u32(&ctl->panel_full), s & 1, abort_flag, p.err, 3);
-        for (int t = sg.t0; t < sg.t1 && ok; ++t, ++ts) {
-          const int st = ts % ns;
-          ok           = mbar_wait(smem_u32(&ctl->full[st]), (ts / ns) & 1, abort_flag, p.err, 4);
-          if (!ok) { break; }
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(st * kb) * (kBTileBytes >> 4);
-          for (int j = 0; j < sg.n_qtiles; ++j, ++gu) {
-            const int slot = gu & (kSlots - 1);
-            if (MODE != kModeRate && gu >= kSlots) {
-              ok = mbar_wait(smem_u32(&ctl->tmem_empty[slot]), ((gu >> 1) - 1) & 1, abort_flag, p.err, 5);
-              if (!ok) { break; }
-            }
-            tc_fence_after();
-            const uint32_t d_tmem = tmem + static_cast<uint32_t>(slot * kBaseTile);
-            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(j * kb) * (kQTileBytes >> 4);
-            for (int b = 0; b < kb; ++b) {
+      if (!WIDE) {
+        // The thread that issues the MMAs is alone in its warp: every instruction it executes costs its full latency,
+        // and a unit of a 128-byte row is only four MMA instructions long. So the loop is kept to the waits, the
+        // instructions themselves and one add per descriptor: descriptors differ only in the low word (start address
+        // >> 4), the accumulate flag is an immediate, ring positions and parities are carried instead of divided out.
+        constexpr int kKB          = KB > 0 ? KB : 1;
+        const uint32_t desc_hi     = static_cast<uint32_t>(a_desc0 >> 32);
+        const uint32_t a_lo0       = static_cast<uint32_t>(a_desc0), b_lo0 = static_cast<uint32_t>(b_desc0);
+        const uint32_t full_bar0   = smem_u32(&ctl->full[0]), empty_bar0 = smem_u32(&ctl->empty[0]);
+        const uint32_t tfull_bar0  = smem_u32(&ctl->tmem_full[0]), tempty_bar0 = smem_u32(&ctl->tmem_empty[0]);
+        int st = 0;
+        uint32_t st_par = 0;
+        for (int s = 0; s < nseg && ok; ++s) {
+          const ScreenSeg sg = segs[s];
+          ok                 = mbar_wait(smem_u32(&ctl->panel_full), s & 1, abort_flag, p.err, 3);
+          for (int t = sg.t0; t < sg.t1 && ok; ++t) {
+            ok = mbar_wait(full_bar0 + st * 8, st_par, abort_flag, p.err, 4);
+            if (!ok) { break; }
+            const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(st) * (kKB * kBTileBytes >> 4);
+            uint32_t a_lo       = a_lo0;
+            for (int j = 0; j < sg.n_qtiles; ++j, ++gu, a_lo += kKB * kQTileBytes >> 4) {
+              const uint32_t slot = gu & 1u;
+              // a fresh barrier passes a wait for parity 1: the first unit of a slot does not wait
+              if (MODE != kModeRate) {
+                ok = mbar_wait(tempty_bar0 + slot * 8, ((gu >> 1) & 1u) ^ 1u, abort_flag, p.err, 5);
+                if (!ok) { break; }
+              }
+              tc_fence_after();
+              const uint32_t d_tmem = tmem + slot * kBaseTile;
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const uint64_t ad = a_desc + static_cast<uint64_t>(b * (kQTileBytes >> 4) + k * 2);
-                const uint64_t bd = b_desc + static_cast<uint64_t>(b * (kBTileBytes >> 4) + k * 2);
-                if (F16) {
-                  mma_f16(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
-                } else {
-                  mma_i8(d_tmem, ad, bd, idesc, (b | k) != 0 ? 1u : 0u);
+              for (int b = 0; b < kKB; ++b) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint64_t ad = pack64(a_lo + b * (kQTileBytes >> 4) + k * 2, desc_hi);
+                  const uint64_t bd = pack64(b_lo + b * (kBTileBytes >> 4) + k * 2, desc_hi);
+                  if (b == 0 && k == 0) {
+                    if (F16) { mma_f16_c<false>(d_tmem, ad, bd, idesc); } else { mma_i8_c<false>(d_tmem, ad, bd, idesc); }
+                  } else {
+                    if (F16) { mma_f16_c<true>(d_tmem, ad, bd, idesc); } else { mma_i8_c<true>(d_tmem, ad, bd, idesc); }
+                  }
                 }
               }
+              tc_commit(tfull_bar0 + slot * 8);
             }
-            tc_commit(smem_u32(&ctl->tmem_full[slot]));
+            if (ok) { tc_commit(empty_bar0 + st * 8); }
+            if (++st == ns) { st = 0, st_par ^= 1u; }
           }
-          if (ok) { tc_commit(smem_u32(&ctl->empty[st])); }
+          if (ok) { tc_commit(smem_u32(&ctl->panel_empty)); }
         }
-        if (ok) { tc_commit(smem_u32(&ctl->panel_empty)); }
       }
       // every MMA issued above has completed before TMEM is released
       tc_commit(smem_u32(&ctl->drain));
@@ -518,19 +535,24 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       }
     };
 
+    // Everything between a unit's completion and the release of its slot sits on the path that bounds the pass (two
+    // slots: the MMAs of the next unit but one wait for it): the loads of the query's threshold and of the chain maxima
+    // of e are issued before the wait and their values are not touched until the slot is released.
+    const uint32_t taddr0     = tmem + lane_base + static_cast<uint32_t>(piece * kGroupRows);
+    const uint32_t tfull_bar0 = smem_u32(&ctl->tmem_full[0]), tempty_bar0 = smem_u32(&ctl->tmem_empty[0]);
     while (ok && cur.valid) {
-      const int slot = gu & (kSlots - 1);
-      const int q    = (cur.q_tile0 + cur.j) * kQueryTile + row;
-      int thr        = F16 ? __float_as_int(CUDART_INF_F) : 0x7fffffff;  // float bits when F16
-      int4 ce        = make_int4(0, 0, 0, 0);
+      const uint32_t slot = static_cast<uint32_t>(gu) & 1u;
+      const int q         = (cur.q_tile0 + cur.j) * kQueryTile + row;
+      int thr             = F16 ? __float_as_int(CUDART_INF_F) : 0x7fffffff;  // float bits when F16
+      int4 ce             = make_int4(0, 0, 0, 0);
       if (MODE == kModeScreen) {
         if (q < p.nq) { thr = __ldg(p.thr + q); }
         // the four chain maxima of e for this warp's piece (one address per warp)
         ce = __ldg(reinterpret_cast<const int4*>(p.cmax + static_cast<size_t>(cur.t) * (kBaseTile / kChainRows)) + piece);
       }
-      if (!mbar_wait(smem_u32(&ctl->tmem_full[slot]), (gu >> 1) & 1, abort_flag, p.err, 7)) { break; }
+      if (!mbar_wait(tfull_bar0 + slot * 8, (static_cast<uint32_t>(gu) >> 1) & 1u, abort_flag, p.err, 7)) { break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + lane_base + static_cast<uint32_t>(slot * kBaseTile + piece * kGroupRows);
+      const uint32_t taddr = taddr0 + slot * kBaseTile;
       int32_t a[32], b[32];
       tmem_ld32(taddr, a);
       tmem_ld32(taddr + 32, b);
@@ -539,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       // the piece is in registers: the slot goes back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(smem_u32(&ctl->tmem_empty[slot])); }
+      if (lane == 0) { mbar_arrive(tempty_bar0 + slot * 8); }
 
       if (MODE == kModeScreen) {
         bool h0, h1, h2, h3;
@@ -550,6 +572,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           h2 = max16f(b) + __int_as_float(ce.z) >= tf;
           h3 = max16f(b + 16) + __int_as_float(ce.w) >= tf;
         } else {
+          // thr and ce are first used here, long after their loads were issued: a use before the wait would stall the
+          // warp on the load latency in front of the slot's release
           h0 = max16(a) + ce.x >= thr;
           h1 = max16(a + 16) + ce.y >= thr;
           h2 = max16(b) + ce.z >= thr;
@@ -646,15 +670,19 @@ cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, c
 {
   const size_t smem = args.wide ? screen_smem_bytes_wide() : screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
   // opt-in to large dynamic shared memory (cheap; set on every launch so that every device of the process has it)
-  auto kernel = screen_i8_kernel<kModeRate, false, false>;
+  if (!args.wide && args.kb != 1 && args.kb != 2) { return cudaErrorInvalidValue; }
+  const bool kb2 = args.kb == 2;
+  auto kernel    = kb2 ? screen_i8_kernel<kModeRate, false, false, 2> : screen_i8_kernel<kModeRate, false, false, 1>;
   if (args.mode == kModeRate) {
     if (args.wide) { return cudaErrorInvalidValue; }
   } else if (args.mode == kModeScreen) {
-    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeScreen, true, true> : screen_i8_kernel<kModeScreen, false, true>)
-                       : (args.f16 ? screen_i8_kernel<kModeScreen, true, false> : screen_i8_kernel<kModeScreen, false, false>);
+    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeScreen, true, true, 0> : screen_i8_kernel<kModeScreen, false, true, 0>)
+             : args.f16 ? (kb2 ? screen_i8_kernel<kModeScreen, true, false, 2> : screen_i8_kernel<kModeScreen, true, false, 1>)
+                        : (kb2 ? screen_i8_kernel<kModeScreen, false, false, 2> : screen_i8_kernel<kModeScreen, false, false, 1>);
   } else {
-    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeGroupMax, true, true> : screen_i8_kernel<kModeGroupMax, false, true>)
-                       : (args.f16 ? screen_i8_kernel<kModeGroupMax, true, false> : screen_i8_kernel<kModeGroupMax, false, false>);
+    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeGroupMax, true, true, 0> : screen_i8_kernel<kModeGroupMax, false, true, 0>)
+             : args.f16 ? (kb2 ? screen_i8_kernel<kModeGroupMax, true, false, 2> : screen_i8_kernel<kModeGroupMax, true, false, 1>)
+                        : (kb2 ? screen_i8_kernel<kModeGroupMax, false, false, 2> : screen_i8_kernel<kModeGroupMax, false, false, 1>);
   }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) { return e; }
