@@ -105,7 +105,11 @@ CERTEX_B200_EXPORT void cuvsSetLastErrorText(const char* text);
 /** certex.h:30-49. Every setting returns the same exact neighbours. `width`, `variance`, `pca_sample`, `n_lists`,
  *  `local_projections` and `int8_rows` tune the reference's projected screening rows; this engine has no projection
  *  (8-bit vectors are screened by their exact integer Gram product) and accepts them without effect.
- *  `host_vectors` is accepted; vectors are kept in device memory. */
+ *  `host_vectors` (certex.hpp:56-61) keeps the vectors in page-locked host memory instead of device memory, which about
+ *  halves the device memory of an 8-bit index: the screen's code rows stay on the device and the exact stage reads the
+ *  candidates it scores from the host in place (for 8-bit indexes from the code rows, which are the vectors, so a
+ *  screened search does not touch host memory; searches that score every vector -- per-query bitmaps, unpartitioned
+ *  labels, tiny sets -- read them all over the host link and are slow). Results are the same either way. */
 struct cuvsCertexIndexParams {
   cuvsDistanceType metric;
   int32_t width;
@@ -263,18 +267,27 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexWillScreen(cuvsCertexIndex_t index
 
 /** Test hook: mode 0 automatic, 1 always the dense path, 2 screen with candidate lists of `cap` entries per query
  *  (small values exercise the overflow fallback), 3 searches by label score their label's rows densely instead of
- *  screening them. */
+ *  screening them, 4 a search call of more than `cap` queries fails the way an allocation failure would (on the host,
+ *  no memory is exhausted), which exercises the halving of the call, 5 the threshold stage of plain searches computes
+ *  exact group maxima (the variant that searches with a bitset filter or many removed vectors use) instead of the
+ *  chained bound. */
 CERTEX_B200_EXPORT cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap);
 
 /**
  * The tensor-core pass alone on caller buffers (device pointers), the seam of the reference's
  * detail/kernels.hpp:290-304 (`screen_int8`) and :125-135 (`anchor_groups`), for kernel-level tests and timing.
- * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 rows, code_len a multiple of 128 up to 4096,
+ * q_codes [nq_pad, code_len] and x_codes [n, code_len] are uint8 (is_signed = 0) or int8 (1) rows, or rows of float16
+ * coordinates (2: code_len bytes = 2 bytes per coordinate; init, thr and the values compared are then float32 bit
+ * patterns, the products accumulate in float32, group maxima come back as monotone int32 keys of floats and rows that
+ * must never pass have init = -inf), code_len a multiple of 128 up to 4096,
  * nq_pad = nq rounded up to 128 with zero rows; init [n rounded up to 64] in row order (the per-row term added to the
  * product: -floor(|x|^2 / 2) for L2, -2^30 for rows that must never pass).
  * mode 0 (screen): keep iff init[x] + <q, x> >= thr[q]; cnt [nq] must be zeroed by the caller; cand [nq, cap].
  * mode 1 (group maxima): gmax [nq, ld] receives the maximum over every 64 rows of x, 4 * ceil(n / 256) groups.
  * mode 2 (rate probe): the same loads and MMAs with no epilogue and no output.
+ * mode 3 (chained group bound): gmax [nq, ld] receives, per 64 rows, the maximum over their four chains of 16 rows of
+ *   (largest <q, x> of the chain + smallest init of the chain): a value some row of the group reaches, at most the
+ *   group maximum of mode 1; what the threshold stage of a plain search runs.
  * Returns after the pass has finished; a pass that gave up on a wait is an error.
  */
 CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_t nq,
@@ -282,6 +295,15 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const vo
                                                    const int32_t* init, int32_t mode, const int32_t* thr,
                                                    int32_t* gmax, int64_t ld, uint32_t* cnt, int32_t* cand,
                                                    uint32_t cap, float* elapsed_ms);
+
+/** Profiling aid of the tensor-core pass, available in a trace build of the library only (`make trace` in csrc builds
+ *  lib/libcertex_b200_trace.so; the regular library answers CUVS_ERROR): `trace` is a device buffer of units * 12 int64
+ *  that CTA 0 of every later pass fills with SM clock stamps of its first `units` accumulator units; NULL switches it
+ *  off. Per unit: 0 the MMA-issuing thread starts waiting for the unit's TMEM slot, 1 has it, 2 has issued and
+ *  committed the unit's MMAs, 3 the first warp of the epilogue group that reads the unit starts waiting for it, 4 sees
+ *  it complete, 5 has its columns in registers, 6 has released the slot, 7 is done with the unit, 8 / 9 = 4 / 5 for
+ *  the last warp of that group. Process-wide, not for concurrent use. No counterpart in the reference. */
+CERTEX_B200_EXPORT cuvsError_t certexB200ScreenTrace(void* trace, int32_t units);
 
 /** Test hook (host only, no GPU needed): the split of n_query_tiles x n_base_tiles accumulator units over `grid` CTAs
  *  that the tensor-core pass uses. out receives grid * 4 segments of 4 ints (first query tile, query tiles, first base
@@ -312,8 +334,11 @@ CERTEX_B200_EXPORT cuvsError_t certexB200PlanRouted(int32_t n_runs, const int32_
  * The temporaries live in one array of CERTEX_B200_STATIC_SCRATCH_BYTES that is part of the library image: every GPU on
  * which the library is used holds it from load to process exit. A call whose temporaries
  * (n_queries * n_rows * 8 bytes for the scores plus the selection lists) exceed it fails with CUVS_ERROR and a message
- * that names both sizes. The first call on a device looks up the array's address on that device (the device must be
- * current, as for every call); make that first call outside any stream capture. All calls share the array and it keeps
+ * that names both sizes; so does a call with more than 7264 dimensions or 262 140 queries (the limits of one launch of
+ * the scoring kernel), before anything is launched. The device that is current must be the one `res` was created on.
+ * The first call on a device looks up the array's address on that device, and the first use of each of its three
+ * kernels lets the CUDA runtime load that kernel, which may itself allocate or synchronise: make one warm-up call per
+ * device at start-up, outside any stream capture. All calls share the array and it keeps
  * the previous call's contents: every value a call reads it has written itself, so no clearing is needed, but two
  * calls that overlap on the GPU (different streams, or different host threads without ordering between their
  * streams) race on it. Work is enqueued on the stream of `res`; the call returns without synchronising.

@@ -8,8 +8,9 @@ All arithmetic runs in the CUDA library `lib/libcertex_b200.so` (C ABI: include/
 PyTorch fallback.
 """
 
+from ._lib import CertexError
 from .attention import KeyCache, topk
 from .index import Index, ShardedIndex, merge_shards, search, search_stats, verify
 
 __version__ = "0.2.0"
-__all__ = ["KeyCache", "topk", "Index", "ShardedIndex", "merge_shards", "search", "search_stats", "verify", "__version__"]
+__all__ = ["CertexError", "KeyCache", "topk", "Index", "ShardedIndex", "merge_shards", "search", "search_stats", "verify", "__version__"]

@@ -11,7 +11,8 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libcertex_b200.so")
+# CERTEX_B200_LIB names another build of the same library (the trace build of the tensor-core pass, for profiling)
+LIB_PATH = os.environ.get("CERTEX_B200_LIB") or os.path.join(_HERE, "lib", "libcertex_b200.so")
 
 CUVS_SUCCESS = 1
 L2Expanded, CosineExpanded, InnerProduct = 0, 2, 6
@@ -113,7 +114,7 @@ SYMBOLS = [
     "certexB200SetThresholdHook", "certexB200IndexWillScreen", "certexB200PlanRouted",
     "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
     "certexB200CommGetUniqueId", "certexB200CommInitRank", "certexB200CommAdopt", "certexB200CommDestroy",
-    "certexB200DistributedSearch",
+    "certexB200DistributedSearch", "certexB200ScreenTrace",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -184,6 +185,13 @@ def lib():
                 L.certexB200ShardedDestroy.argtypes = [vp]
                 L.certexB200ShardedGetSize.argtypes = [vp, P(i64)]
                 L.certexB200ShardedSearch.argtypes = [P(SearchParams), vp, mt, mt, mt]
+                L.certexB200CommGetUniqueId.argtypes = [vp]
+                L.certexB200CommInitRank.argtypes = [vp, ctypes.c_int32, ctypes.c_int32, P(vp)]
+                L.certexB200CommAdopt.argtypes = [vp, P(vp)]
+                L.certexB200CommDestroy.argtypes = [vp]
+                L.certexB200DistributedSearch.argtypes = [vp, vp, P(SearchParams), P(IndexHandle), mt, mt, mt, mt, i64,
+                                                          ctypes.c_int32]
+                L.certexB200ScreenTrace.argtypes = [vp, ctypes.c_int32]
                 L.certexB200SearchStatic.argtypes = [vp, ctypes.c_int, DLDataType, vp, i64, vp, i64, i64, ctypes.c_int32, vp, vp]
                 _lib = L
     return _lib

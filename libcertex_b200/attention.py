@@ -16,6 +16,31 @@ def _as_half_or_float(x):
     return h if bool(torch.isfinite(h).all()) else x.to(torch.float32)
 
 
+class GrowingMap:
+    """A one-dimensional device tensor that is appended to: the buffer doubles when it is full, so that appending a few
+    entries per decoding step does not copy the whole map every time."""
+
+    def __init__(self, dtype):
+        self.dtype, self.buf, self.n = dtype, None, 0
+
+    def append(self, values, reserve=0):
+        need = self.n + values.numel()
+        if self.buf is None or need > self.buf.numel():
+            grown = torch.empty((max(need, int(reserve), 2 * self.n),), dtype=self.dtype, device="cuda")
+            if self.n:
+                grown[: self.n] = self.buf[: self.n]
+            self.buf = grown
+        self.buf[self.n : need] = values
+        self.n = need
+
+    def __len__(self):
+        return self.n
+
+    @property
+    def values(self):
+        return self.buf[: self.n]
+
+
 class KeyCache:
     """n_kv_heads, head_dim: the shape of the keys; k: the largest k searches will ask for; capacity: expected keys
     per head (reserves memory once).
@@ -28,7 +53,7 @@ class KeyCache:
         _need(1 <= k <= 2048, f"k must be between 1 and 2048, not {k}")
         self.n_kv_heads, self.head_dim, self.k, self.capacity = int(n_kv_heads), int(head_dim), int(k), capacity
         self.index, self.dtype, self.size = None, None, 0
-        self._position = None  # id of the index -> position of the key inside its head
+        self._map = GrowingMap(torch.int64)  # id of the index -> position of the key inside its head
 
     def append(self, keys):
         """Append keys of shape (n_kv_heads, n, head_dim); positions continue from the keys appended before."""
@@ -47,9 +72,13 @@ class KeyCache:
         heads = torch.arange(self.n_kv_heads, dtype=torch.int32, device="cuda").repeat_interleave(n_new)
         self.index.add(K.to(self.dtype).reshape(self.n_kv_heads * n_new, self.head_dim).contiguous(), labels=heads)
         pos = torch.arange(self.size, self.size + n_new, dtype=torch.int64, device="cuda").repeat(self.n_kv_heads)
-        self._position = pos if self._position is None else torch.cat([self._position, pos])
+        self._map.append(pos, reserve=0 if self.capacity is None else int(self.capacity) * self.n_kv_heads)
         self.size += n_new
         return self
+
+    @property
+    def _position(self):
+        return self._map.values
 
     def topk(self, q, k=None, batch=2048):
         """q: (n_heads, m, head_dim) or (n_heads, head_dim), n_heads a multiple of n_kv_heads. Returns (scores, ids) of

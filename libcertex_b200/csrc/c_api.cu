@@ -548,7 +548,7 @@ cuvsError_t certexB200IndexWillScreen(cuvsCertexIndex_t index, int32_t k, int32_
 cuvsError_t certexB200IndexSetTestMode(cuvsCertexIndex_t index, int32_t mode, int32_t cap)
 {
   return translate([=] {
-    CERTEX_EXPECTS(mode >= 0 && mode <= 3 && (mode != 2 || cap >= 1), "certex: unknown test mode");
+    CERTEX_EXPECTS(mode >= 0 && mode <= 5 && (mode != 2 || cap >= 1) && (mode != 4 || cap >= 0), "certex: unknown test mode");
     as_holder(index).index->set_test_mode(mode, cap);
   });
 }
@@ -562,7 +562,18 @@ cuvsError_t certexB200ScreenRaw(cuvsResources_t res, const void* q_codes, int64_
     Resources& r = as_res(res);
     CERTEX_EXPECTS(code_len >= 128 && code_len <= 4096 && code_len % 128 == 0, "certex: code_len must be a multiple of 128 up to 4096");
     CERTEX_EXPECTS(nq >= 1 && n >= 1 && n < (int64_t(1) << 31) && nq < (int64_t(1) << 24), "certex: sizes out of range");
-    screen_raw(r, q_codes, nq, x_codes, n, code_len, is_signed != 0, init, mode, thr, gmax, ld, cnt, cand, cap, elapsed_ms);
+    CERTEX_EXPECTS(mode >= 0 && mode <= 3, "certex: the mode is 0 (screen), 1 (group maxima), 2 (rate probe) or 3 (chained bound)");
+    CERTEX_EXPECTS(is_signed >= 0 && is_signed <= 2, "certex: the code kind is 0 (uint8), 1 (int8) or 2 (float16)");
+    screen_raw(r, q_codes, nq, x_codes, n, code_len, is_signed, init, mode, thr, gmax, ld, cnt, cand, cap, elapsed_ms);
+  });
+}
+
+cuvsError_t certexB200ScreenTrace(void* trace, int32_t units)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(trace == nullptr || screen_trace_compiled(),
+                   "certex: this library was built without the trace stamps of the tensor-core pass (make trace)");
+    screen_set_trace(static_cast<long long*>(trace), units);
   });
 }
 

@@ -126,6 +126,24 @@ CUtensorMap make_tile_map(const void* base, uint64_t row_bytes, uint64_t column_
   return m;
 }
 
+/// 4-D map of the chained anchor pass: (bytes of a row, anchor of a chain [16], chain of a tile [16], tile). Anchor a
+/// is sorted row a * stride; chain i of tile t holds the anchors (i * n_tiles + t) * 16 .. + 15, so a chain is 16
+/// neighbours in the norm order (their e is almost one value) and the chains of a tile, and of every group of 64
+/// columns, are spread over the whole set. Box 128 bytes x 16 x 16 x 1 = the 256 rows of a tile in shared memory.
+CUtensorMap make_chain_map(const void* base, uint64_t row_bytes, uint64_t anchor_stride_bytes, uint64_t n_tiles)
+{
+  CUtensorMap m;
+  const cuuint64_t dims[4]    = {row_bytes, static_cast<cuuint64_t>(kChainRows), static_cast<cuuint64_t>(kBaseTile / kChainRows), n_tiles};
+  const cuuint64_t strides[3] = {anchor_stride_bytes, n_tiles * kChainRows * anchor_stride_bytes, kChainRows * anchor_stride_bytes};
+  const cuuint32_t box[4]     = {128, static_cast<cuuint32_t>(kChainRows), static_cast<cuuint32_t>(kBaseTile / kChainRows), 1};
+  const cuuint32_t estr[4]    = {1, 1, 1, 1};
+  const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CERTEX_EXPECTS(r == CUDA_SUCCESS, "certex: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return m;
+}
+
 /// Splits nqt query tiles x nt base tiles over `grid` CTAs: query tiles are grouped into panels of at most
 /// `panel_tiles`; the (panel, base tile) items are laid out panel-major and cut into `grid` ranges of equal unit count.
 std::vector<ScreenSeg> plan_segments(int nqt, int nt, int panel_tiles, int grid)
@@ -200,9 +218,11 @@ void* Resources::pinned_block() const
 
 // ============================================================================================ Index
 Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t dim)
-  : params_(params), dtype_(dtype), dim_(dim), device_(res.device)
+  : params_(params), dtype_(dtype), dim_(dim), device_(res.device), host_vectors_(params.host_vectors)
 {
   CERTEX_EXPECTS(dim >= 1, "certex: the dimension must be positive");
+  // every index can end on the dense path (filters, small sets, overflow), which keeps four queries in shared memory
+  CERTEX_EXPECTS(dim <= kDenseMaxDim, "certex: at most " + std::to_string(kDenseMaxDim) + " dimensions per vector");
   CERTEX_EXPECTS(dtype >= kF32 && dtype <= kU8, "certex: vectors must be float32, float16, int8, or uint8");
   CERTEX_EXPECTS(params.metric == kL2 || params.metric == kIP || params.metric == kCos,
                  "certex: the metric must be L2Expanded, InnerProduct, or CosineExpanded");
@@ -228,9 +248,37 @@ Index::Index(const Resources& res, const IndexParams& params, int dtype, int64_t
   }
 }
 
+namespace {
+/// The vectors of an index: device memory, or page-locked host memory mapped into the device's address space (with
+/// unified addressing the same pointer serves host and device).
+void* alloc_vectors(size_t bytes, bool on_host)
+{
+  void* p = nullptr;
+  if (on_host) {
+    const cudaError_t e = cudaHostAlloc(&p, std::max<size_t>(bytes, 1), cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();
+      throw OutOfMemory("certex: out of page-locked host memory (" + std::to_string(bytes) + " bytes of vectors)");
+    }
+    CERTEX_CUDA(e);
+  } else {
+    CERTEX_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 1)));
+  }
+  return p;
+}
+void free_vectors(void* p, bool on_host)
+{
+  if (on_host) {
+    cudaFreeHost(p);
+  } else {
+    cudaFree(p);
+  }
+}
+}  // namespace
+
 Index::~Index()
 {
-  cudaFree(vectors_);
+  free_vectors(vectors_, host_vectors_);
   cudaFree(removed_);
   cudaFree(labels_);
   cudaFree(part_ids_);
@@ -253,7 +301,7 @@ void Index::reserve(const Resources& res, int64_t n)
   void* co          = nullptr;
   int32_t *pe = nullptr, *iv = nullptr, *in = nullptr, *cm = nullptr;
   const int64_t pad_old = round_up(size_, kTile), pad_new = round_up(cap, kTile);
-  CERTEX_CUDA(cudaMalloc(&v, static_cast<size_t>(cap) * pitch_));
+  v = alloc_vectors(static_cast<size_t>(cap) * pitch_, host_vectors_);
   CERTEX_CUDA(cudaMalloc(&r, static_cast<size_t>(round_up(cap, 4))));
   CERTEX_CUDA(cudaMemsetAsync(r, 0, static_cast<size_t>(round_up(cap, 4)), res.stream));
   if (labels_) {
@@ -273,7 +321,7 @@ void Index::reserve(const Resources& res, int64_t n)
   }
   if (size_ > 0) {
     const auto d2d = cudaMemcpyDeviceToDevice;
-    CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, d2d, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, cudaMemcpyDefault, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), d2d, res.stream));
     if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, d2d, res.stream)); }
     if (screen_kind_) {
@@ -294,7 +342,8 @@ void Index::reserve(const Resources& res, int64_t n)
     codes_ = co, perm_ = pe, inv_ = iv, init_ = in, cmax_ = cm;
     capacity_ = cap;
   }
-  for (int i = 0; i < 8; ++i) {
+  free_vectors(old[0], host_vectors_);
+  for (int i = 1; i < 8; ++i) {
     if (i != 2 || l) { cudaFree(old[i]); }
   }
 }
@@ -307,7 +356,7 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
   reserve(res, size_ + n);
   uint8_t* dst          = static_cast<uint8_t*>(vectors_) + static_cast<size_t>(size_) * pitch_;
   const size_t row_bytes = static_cast<size_t>(dim_) * dtype_size(dtype_);
-  const auto kind        = on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+  const auto kind        = host_vectors_ ? cudaMemcpyDefault : on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
   if (row_bytes == pitch_) {
     CERTEX_CUDA(cudaMemcpyAsync(dst, rows, static_cast<size_t>(n) * pitch_, kind, res.stream));
   } else {
@@ -525,7 +574,7 @@ void Index::search_dense(const Resources& res, const void* q, size_t qpitch, con
   Scratch scratch(res.stream);
   const int64_t ld      = round_up(std::max<int64_t>(n, 1), 4);
   const int64_t budget  = int64_t(1) << 30;  // bytes of score matrix per step
-  const int step        = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(nqb, budget / (ld * 8))));
+  const int step        = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({nqb, budget / (ld * 8), kDenseMaxQueries})));
   double* scores        = scratch.get<double>(static_cast<size_t>(step) * ld);
   const int parts       = select_topk_parts(n, k);
   double* part_s        = scratch.get<double>(static_cast<size_t>(step) * parts * k);
@@ -605,8 +654,11 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   rf.thr   = thr;
   rf.shift = shift;
   rf.kind  = screen_kind_;
-  launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes, nq, q0, cand, cnt,
-                       cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf, res.stream);
+  // 8-bit vectors kept in host memory: the exact stage reads the candidates' code rows, which are the vectors
+  const bool from_codes = host_vectors_ && screen_kind_ == 1;
+  launch_verify_select(from_codes ? codes_ : vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes,
+                       nq, q0, cand, cnt, cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf,
+                       res.stream, from_codes ? inv_ : nullptr);
   CERTEX_CUDA(cudaGetLastError());
 }
 
@@ -626,23 +678,34 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   const int n_groups      = nt_anchor * (kBaseTile / kGroupRows);
   const int64_t ld_g      = round_up(n_groups, 8);
 
-  int32_t* anchor_init = scratch.get<int32_t>(static_cast<size_t>(nt_anchor) * kTile);
+  // The threshold stage at the screen's price (chains of 16 adjacent anchors, e per chain: kModeGroupBound) unless
+  // anchors are masked one by one: a bitset filter, or many removed rows (a chain with a masked anchor drops out whole).
+  const bool chained   = adm.bits == nullptr && n_removed_ * 64 <= n && test_mode_ != 5;
+  int32_t* anchor_init = scratch.get<int32_t>(chained ? static_cast<size_t>(nt_anchor) * (kTile / kChainRows)
+                                                      : static_cast<size_t>(nt_anchor) * kTile);
   int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
   int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
   ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs);
 
   const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
   CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_a.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
-  // e of the anchors; with a bitset filter the anchors it drops do not count
-  launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream, adm.bits, perm_,
-                     screen_kind_ == 2 ? static_cast<int32_t>(0xff800000u) : kNeverInit);
+  if (chained) {  // the smallest e of every chain of 16 adjacent anchors
+    // anchor a = sorted row a * stride; chain i of tile t = anchors (i * nt_anchor + t) * 16 .. + 15
+    launch_gather_chain_min(init_, anchor_stride, static_cast<int64_t>(nt_anchor) * kChainRows * anchor_stride,
+                            static_cast<int64_t>(kChainRows) * anchor_stride, nt_anchor, anchor_init, screen_kind_ == 2, res.stream);
+  } else {        // e of the anchors; with a bitset filter the anchors it drops do not count
+    launch_gather_init(init_, anchor_stride, nt_anchor, anchor_init, res.stream, adm.bits, perm_,
+                       screen_kind_ == 2 ? static_cast<int32_t>(0xff800000u) : kNeverInit);
+  }
   CERTEX_CUDA(cudaGetLastError());
 
   const size_t cp        = code_pitch_;
   const uint8_t* qb      = qbuf + static_cast<size_t>(q0) * cp;
   const CUtensorMap tm_q = make_code_map(qb, cp, static_cast<uint64_t>(round_up(nq, kQTile)), cp, kQueryTile);
-  const CUtensorMap tm_a = make_tile_map(codes_, cp, static_cast<uint64_t>(nt_anchor) * anchor_stride * cp,
-                                         static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor));
+  const CUtensorMap tm_a =
+    chained ? make_chain_map(codes_, cp, static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor))
+            : make_tile_map(codes_, cp, static_cast<uint64_t>(nt_anchor) * anchor_stride * cp,
+                            static_cast<uint64_t>(anchor_stride) * cp, static_cast<uint64_t>(nt_anchor));
   ScreenArgs a{};
   a.nq          = nq;
   a.kb          = kb_;
@@ -653,9 +716,10 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   a.q_signed    = dtype_ == kI8 ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.err         = err;
-  // 1 anchors: maximum of acc over every group of 64 anchors
-  a.mode    = kModeGroupMax;
+  // 1 anchors: a value that some anchor of every group of 64 reaches (the group's maximum, or the chained bound)
+  a.mode    = chained ? kModeGroupBound : kModeGroupMax;
   a.init    = anchor_init;
+  a.cmax    = anchor_init;
   a.gmax    = gmax;
   a.ld_gmax = ld_g;
   a.segs    = d_segs;
@@ -936,8 +1000,10 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     launch_expand_records(rec, rec_count, rec_cap, n_lrows_, lperm_, cnt, cand, cap, res.sm_count, res.stream);
     Admit plain{};
     plain.removed = removed_;
-    launch_verify_select(vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, q_rows, q_rows_pitch, ns, 0, cand,
-                         cnt, cap, k, plain, slot_s, slot_row, ovf_list, d_flag, d_stats, rec_count, rec_cap, Refine{}, res.stream);
+    const bool from_codes = host_vectors_ && screen_kind_ == 1;
+    launch_verify_select(from_codes ? codes_ : vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, q_rows,
+                         q_rows_pitch, ns, 0, cand, cnt, cap, k, plain, slot_s, slot_row, ovf_list, d_flag, d_stats, rec_count,
+                         rec_cap, Refine{}, res.stream, from_codes ? inv_ : nullptr);
     launch_scatter_best(slot_s, slot_row, d_slot_q, ns, k, best_s, best_row, res.stream);
     CERTEX_CUDA(cudaGetLastError());
     st->launches += f16 ? 10 : 8;
@@ -1443,7 +1509,7 @@ void Index::save(const Resources& res, std::ostream& os) const
   const size_t row_bytes = static_cast<size_t>(dim_) * dtype_size(dtype_);
   std::vector<char> host(static_cast<size_t>(size_) * std::max(row_bytes, sizeof(int32_t)));
   if (size_ > 0) {
-    CERTEX_CUDA(cudaMemcpy2DAsync(host.data(), row_bytes, vectors_, pitch_, row_bytes, static_cast<size_t>(size_), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpy2DAsync(host.data(), row_bytes, vectors_, pitch_, row_bytes, static_cast<size_t>(size_), cudaMemcpyDefault, res.stream));
     res.sync();
     os.write(host.data(), static_cast<std::streamsize>(static_cast<size_t>(size_) * row_bytes));
     CERTEX_CUDA(cudaMemcpyAsync(host.data(), removed_, static_cast<size_t>(size_), cudaMemcpyDeviceToHost, res.stream));
@@ -1706,9 +1772,10 @@ void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out
 }
 
 void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n, int64_t code_len,
-                bool is_signed, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
+                int code_kind, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
                 uint32_t* cnt, int32_t* cand, uint32_t cap, float* elapsed_ms)
 {
+  const bool is_signed = code_kind == 1, f16 = code_kind == 2;
   Scratch scratch(res.stream);
   const int kb            = static_cast<int>(code_len / 128);
   const ScreenShape shape = shape_for(kb);
@@ -1722,6 +1789,24 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   CERTEX_CUDA(cudaMemsetAsync(err, 0, sizeof(int), res.stream));
   const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kQTile)), code_len, kQueryTile);
   CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len, kBaseTile);
+  if (mode == kModeGroupBound) {
+    // chains of 16 consecutive rows, tiles of 256 consecutive rows (padded), through the 4-D map
+    uint8_t* x_pad = scratch.get<uint8_t>(static_cast<size_t>(nt) * kTile * code_len);
+    CERTEX_CUDA(cudaMemsetAsync(x_pad, 0, static_cast<size_t>(nt) * kTile * code_len, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(x_pad, x_codes, static_cast<size_t>(n) * code_len, cudaMemcpyDeviceToDevice, res.stream));
+    CUtensorMap m;
+    const cuuint64_t dims[4]    = {static_cast<cuuint64_t>(code_len), static_cast<cuuint64_t>(kChainRows),
+                                   static_cast<cuuint64_t>(kBaseTile / kChainRows), static_cast<cuuint64_t>(nt)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(code_len), static_cast<cuuint64_t>(kChainRows) * code_len,
+                                   static_cast<cuuint64_t>(kTile) * code_len};
+    const cuuint32_t box[4]     = {128, static_cast<cuuint32_t>(kChainRows), static_cast<cuuint32_t>(kBaseTile / kChainRows), 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    const CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x_pad, dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CERTEX_EXPECTS(r == CUDA_SUCCESS, "certex: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+    tm_x = m;
+  }
   if (mode == kModeGroupMax) {
     // group maxima over consecutive rows: the pass reads whole tiles through the 3-D map, so the rows are padded
     uint8_t* x_pad = scratch.get<uint8_t>(static_cast<size_t>(nt) * kTile * code_len);
@@ -1734,9 +1819,13 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   const int64_t n_pad = static_cast<int64_t>(nt) * kTile;
   int32_t* init_pad   = scratch.get<int32_t>(static_cast<size_t>(n_pad));
   int32_t* cmax       = scratch.get<int32_t>(static_cast<size_t>(n_pad / kChainRows));
-  launch_fill_i32(init_pad, n_pad, kNeverInit, res.stream);
+  launch_fill_i32(init_pad, n_pad, f16 ? static_cast<int32_t>(0xff800000u) : kNeverInit, res.stream);
   CERTEX_CUDA(cudaMemcpyAsync(init_pad, init, static_cast<size_t>(n_in) * 4, cudaMemcpyDeviceToDevice, res.stream));
-  launch_chain_max(init_pad, 0, n_pad / kChainRows, cmax, false, res.stream);
+  if (mode == kModeGroupBound) {  // the chained threshold pass takes the chains' minima
+    launch_gather_chain_min(init_pad, 1, kChainRows, kTile, nt, cmax, f16, res.stream);
+  } else {
+    launch_chain_max(init_pad, 0, n_pad / kChainRows, cmax, f16, res.stream);
+  }
   CERTEX_CUDA(cudaGetLastError());
   const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(nq) * 1024ull);
   uint64_t* rec   = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
@@ -1757,6 +1846,7 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   a.n_stages    = shape.n_stages;
   a.mode        = mode;
   a.wide        = kb > 2 ? 1 : 0;
+  a.f16         = f16 ? 1 : 0;
   a.q_signed    = is_signed ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.segs        = d_segs;

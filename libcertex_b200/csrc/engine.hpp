@@ -68,7 +68,10 @@ struct Resources {
 /// cuvs::neighbors::certex::index_params (cpp/include/cuvs/neighbors/certex.hpp:43-87). Every setting returns the same
 /// exact neighbours. width, variance, pca_sample, n_lists, local_projections and int8_rows steer the reference's
 /// projected screening rows; this engine screens 8-bit vectors by their exact integer Gram product and has no
-/// projection, so it accepts and ignores them.
+/// projection, so it accepts and ignores them. host_vectors (certex.hpp:56-61) keeps the vectors in page-locked host
+/// memory instead of device memory: the screen's code rows stay on the device, the exact stage reads the few candidate
+/// rows it needs from the host in place (8-bit indexes: from the code rows, which are the vectors, so a screened search
+/// does not touch host memory at all).
 struct IndexParams {
   int metric             = kL2;
   int width              = 0;
@@ -158,6 +161,7 @@ class Index {
   bool has_labels() const { return has_labels_; }
   int64_t n_partitioned() const { return n_part_; }
   bool int_screen() const { return screen_kind_ != 0 && !code_overflow_; }  // a tensor-core screen is available
+  bool host_vectors() const { return host_vectors_; }
   const IndexParams& params() const { return params_; }
   size_t pitch() const { return pitch_; }
   const void* vectors() const { return vectors_; }
@@ -169,7 +173,8 @@ class Index {
 
   /// Forces a path for tests: 0 = automatic, 1 = always the dense path, 2 = screen with this candidate capacity,
   /// 3 = searches by label score their label's rows densely (no routed screen), 4 = a search call of more than `cap`
-  /// queries fails as if the device were out of memory (exercises the halving, on the host, without exhausting a GPU).
+  /// queries fails as if the device were out of memory (exercises the halving, on the host, without exhausting a GPU),
+  /// 5 = the threshold stage of plain searches computes exact group maxima instead of the chained bound.
   void set_test_mode(int mode, int cap) { test_mode_ = mode, test_cap_ = cap; }
 
   static thread_local SearchStats* stats_sink;  // counters of the calling thread's searches, when set
@@ -225,6 +230,7 @@ class Index {
   int64_t capacity_   = 0;
   int64_t n_removed_  = 0;
   bool has_labels_    = false;
+  bool host_vectors_  = false;    // vectors_ is page-locked host memory that the GPU reads in place (index_params.host_vectors)
   void* vectors_      = nullptr;  // [capacity, pitch]
   uint8_t* removed_   = nullptr;  // [capacity rounded up to 4]
   int32_t* labels_    = nullptr;  // [capacity], -1 = none
@@ -292,7 +298,7 @@ int plan_routed_flat(int n_runs, const int32_t* n_query_tiles, const int32_t* n_
 
 /// The tensor-core pass alone on caller buffers (see certexB200ScreenRaw in the public header). Synchronises.
 void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const void* x_codes, int64_t n, int64_t code_len,
-                bool is_signed, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
+                int code_kind, const int32_t* init, int mode, const int32_t* thr, int32_t* gmax, int64_t ld,
                 uint32_t* cnt, int32_t* cand, uint32_t cap, float* elapsed_ms);
 
 }  // namespace certex_b200

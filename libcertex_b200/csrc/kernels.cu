@@ -311,6 +311,26 @@ __global__ void gather_init_kernel(const int32_t* init, int64_t stride, int64_t 
   }
 }
 
+// Smallest e of every chain of 16 columns in the tile order of the chained anchor pass:
+// out[t * 16 + i] = min over w < 16 of init[t * stride_t + i * stride_i + w * stride_w]  (int32 values, or floats by their bits).
+__global__ void gather_chain_min_kernel(const int32_t* init, int64_t stride_w, int64_t stride_i, int64_t stride_t,
+                                        int64_t n_tiles, int32_t* out, int is_float)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j >= n_tiles * (kBaseTile / kChainRows)) { return; }
+  const int64_t t = j / (kBaseTile / kChainRows), i = j % (kBaseTile / kChainRows);
+  const int32_t* src = init + t * stride_t + i * stride_i;
+  if (is_float) {
+    float m = __int_as_float(src[0]);
+    for (int w = 1; w < kChainRows; ++w) { m = fminf(m, __int_as_float(src[w * stride_w])); }
+    out[j] = __float_as_int(m);
+  } else {
+    int32_t m = src[0];
+    for (int w = 1; w < kChainRows; ++w) { m = min(m, src[w * stride_w]); }
+    out[j] = m;
+  }
+}
+
 __global__ void remove_kernel(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init,
                               const int32_t* inv, unsigned long long* n_new, int32_t never)
 {
@@ -854,7 +874,8 @@ __global__ void __launch_bounds__(1024) verify_select_kernel(const uint8_t* vect
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
                                      Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
                                      unsigned int* ovf_count, unsigned long long* stats,
-                                     const unsigned long long* rec_count, unsigned long long rec_cap, Refine rf)
+                                     const unsigned long long* rec_count, unsigned long long rec_cap, Refine rf,
+                                     const int32_t* where)
 {
   extern __shared__ double sh[];
   __shared__ double s_qq;
@@ -945,7 +966,14 @@ __global__ void __launch_bounds__(1024) verify_select_kernel(const uint8_t* vect
       }
 #pragma unroll
       for (int u = 0; u < kRowUnroll; ++u) { ok[u] = row[u] >= 0 && admitted(adm, q, row[u]); }
-      int_row_scores<T, METRIC>(vectors, pitch, row, d, reinterpret_cast<const uint4*>(qd), s_qq_int, sub, v);
+      if (where) {  // `vectors` is not in id order: row `where[id]` of it holds the vector with that id
+        int32_t at[kRowUnroll];
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) { at[u] = row[u] >= 0 ? __ldg(where + row[u]) : -1; }
+        int_row_scores<T, METRIC>(vectors, pitch, at, d, reinterpret_cast<const uint4*>(qd), s_qq_int, sub, v);
+      } else {
+        int_row_scores<T, METRIC>(vectors, pitch, row, d, reinterpret_cast<const uint4*>(qd), s_qq_int, sub, v);
+      }
 #pragma unroll
       for (int u = 0; u < kRowUnroll; ++u) {
         const int i = i0 + u * n_groups + group;
@@ -1477,6 +1505,15 @@ void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, in
   gather_init_kernel<<<static_cast<unsigned>(n_tiles), kBaseTile, 0, s>>>(init, stride, n_tiles, out, bits, perm, never);
 }
 
+void launch_gather_chain_min(const int32_t* init, int64_t stride_w, int64_t stride_i, int64_t stride_t, int64_t n_tiles,
+                             int32_t* out, bool is_float, cudaStream_t s)
+{
+  if (n_tiles <= 0) { return; }
+  const int64_t n = n_tiles * (kBaseTile / kChainRows);
+  gather_chain_min_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(init, stride_w, stride_i, stride_t, n_tiles, out,
+                                                                                 is_float ? 1 : 0);
+}
+
 void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_count, unsigned long long rec_cap,
                            int64_t n_rows, const int32_t* perm, uint32_t* cnt, int32_t* cand, uint32_t cap, int sm_count,
                            cudaStream_t s)
@@ -1588,7 +1625,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          Refine rf, cudaStream_t s)
+                          Refine rf, cudaStream_t s, const int32_t* where)
 {
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
@@ -1605,7 +1642,8 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
     auto go   = [&](auto kernel) {
       allow_smem(kernel, smem);
       kernel<<<nq, threads, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
-                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf);
+                                   n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf,
+                                   where);
     };
     if (metric == kL2) {
       go(verify_select_kernel<T, kL2>);

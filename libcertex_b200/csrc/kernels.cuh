@@ -30,6 +30,12 @@ void launch_row_init(const void* vectors, size_t pitch, int dtype, int d, int me
 void launch_gather_init(const int32_t* init, int64_t stride, int64_t n_tiles, int32_t* out, cudaStream_t s,
                         const uint32_t* bits = nullptr, const int32_t* perm = nullptr, int32_t never = 0);
 
+/// Smallest e of every chain of 16 columns, in the tile order of the chained anchor pass: out[t * 16 + i] = min over
+/// w < 16 of init[t * stride_t + i * stride_i + w * stride_w] (strides in elements). A chain that holds a removed row
+/// gets the never-value and so drops out of the thresholds.
+void launch_gather_chain_min(const int32_t* init, int64_t stride_w, int64_t stride_i, int64_t stride_t, int64_t n_tiles,
+                             int32_t* out, bool is_float, cudaStream_t s);
+
 /// e[j] = never (-2^30, or -inf as float bits) where removed[j] is set, j < n.
 void launch_mask_removed(int32_t* e, const uint8_t* removed, int64_t n, bool is_float, cudaStream_t s);
 
@@ -117,15 +123,22 @@ void launch_compose(int32_t* list, const unsigned int* n, int n_max, const int32
  * cand [nq, cap] rows, cnt [nq] how many (a query with cnt > cap is skipped and its index appended to ovf_list;
  * so is every query when *rec_count > rec_cap, i.e. when the screen's survivor records did not all fit).
  * best_s / best_row [nq, k] (row -1, score +inf where fewer than k admitted candidates exist).
+ * `where` (8-bit rows only, optional): `vectors` is not in id order, row where[id] of it holds the vector with that id
+ * (the norm-sorted code rows of an index whose vectors live in host memory).
  */
 void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, int metric, const void* queries,
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          Refine rf, cudaStream_t s);
+                          Refine rf, cudaStream_t s, const int32_t* where = nullptr);
+
+/// Limits of one launch_dense_scores call: four queries of d doubles sit in shared memory (32 d bytes of the 227 KB a
+/// block may have), and the queries of a call are the second grid dimension in fours.
+constexpr int kDenseMaxDim     = 7264;
+constexpr int kDenseMaxQueries = 4 * 65535;
 
 /// All-pairs exact fp64 scores of queries qsel[0:nqb] (or q0.. when qsel is null) against rows [0, n): out [nqb, ld].
-/// Rows that `adm` rejects score +inf.
+/// Rows that `adm` rejects score +inf. d <= kDenseMaxDim, nqb <= kDenseMaxQueries.
 void launch_dense_scores(const void* vectors, size_t pitch, int dtype, int d, int metric, int64_t n, const void* queries,
                          size_t qpitch, const int32_t* qsel, int q0, int nqb, Admit adm, double* out, int64_t ld,
                          cudaStream_t s);

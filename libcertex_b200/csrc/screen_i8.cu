@@ -68,6 +68,25 @@ constexpr int kWideStage  = 2 * kQTileBytes + kBTileBytes;  // WIDE: one K block
 constexpr int kWideStages = 3;
 constexpr int kERing      = 4;                 // WIDE: tiles whose e values may be in flight
 constexpr int kSharedSegs = 64;                // segments of a CTA (a CTA is never given more)
+#ifndef CERTEX_SPLIT_EPILOGUE
+#define CERTEX_SPLIT_EPILOGUE 1
+#endif
+constexpr bool kSplit     = CERTEX_SPLIT_EPILOGUE != 0;  // two groups of 8 epilogue warps, one per TMEM slot
+
+#ifndef CERTEX_SCREEN_TRACE
+#define CERTEX_SCREEN_TRACE 0
+#endif
+#if CERTEX_SCREEN_TRACE
+#define TRACE_AT(cond, unit, slot) \
+  do {                             \
+    if ((cond) && (unit) < static_cast<uint32_t>(p.trace_units)) { p.trace[static_cast<size_t>(unit) * 12 + (slot)] = clock64(); } \
+  } while (0)
+#else
+#define TRACE_AT(cond, unit, slot) \
+  do {                             \
+  } while (0)
+#endif
+
 
 struct SharedCtl {
   uint64_t full[kMaxStages];    // TMA landed a base tile (GROUPMAX: and its e values) in the stage
@@ -79,31 +98,12 @@ struct SharedCtl {
   uint64_t drain;
   uint64_t e_full[kERing];      // WIDE: the e values of a tile have landed
   uint64_t e_empty[kERing];     // WIDE: every epilogue warp is done with them
+
   uint32_t tmem_base;
   int abort_flag;
   int rec_n[kEpiWarps];         // fill counts of the warps' record staging buffers
   ScreenSeg segs[kSharedSegs];
 };
-
-// Position in the CTA's unit sequence: for every base tile of a segment, the query tiles of the segment's panel.
-struct Cursor {
-  int s, t, j, ts, nqt, t1, q_tile0, col0;
-  bool valid;
-};
-
-template <bool COL0>
-__device__ __forceinline__ void cursor_seg(Cursor& c, const ScreenSeg* segs, const int* seg_col0, int nseg)
-{
-  c.valid = c.s < nseg;
-  if (c.valid) {
-    const ScreenSeg sg = segs[c.s];
-    c.t                = sg.t0;
-    c.t1               = sg.t1;
-    c.nqt              = sg.n_qtiles;
-    c.q_tile0          = sg.q_tile0;
-    if (COL0) { c.col0 = seg_col0 ? seg_col0[c.s] : 0; }
-  }
-}
 
 __device__ __forceinline__ int max3(int a, int b, int c) { return __vimax3_s32(a, b, c); }
 __device__ __forceinline__ int addmax(int a, int b, int c) { return __viaddmax_s32(a, b, c); }  // max(a + b, c)
@@ -121,7 +121,7 @@ __device__ __forceinline__ int max16(const int32_t* v)
 }
 
 // Maximum of v[i] + e[i] over 32 columns, e in shared memory (two chains).
-__device__ __forceinline__ int max32_plus(const int32_t (&v)[32], const int32_t* e)
+__device__ __forceinline__ int max32_plus(const int32_t* v, const int32_t* e)
 {
   const int4* e4 = reinterpret_cast<const int4*>(e);
   int m = kNeverInit * 2 + 1, n = m;
@@ -150,7 +150,7 @@ __device__ __forceinline__ float max16f(const int32_t* v)
   return fmax3(m, n, fmaxf(__int_as_float(v[14]), __int_as_float(v[15])));
 }
 
-__device__ __forceinline__ float max32f_plus(const int32_t (&v)[32], const int32_t* e)
+__device__ __forceinline__ float max32f_plus(const int32_t* v, const int32_t* e)
 {
   const float4* e4 = reinterpret_cast<const float4*>(e);
   float m = -CUDART_INF_F, n = m;
@@ -240,7 +240,12 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   SharedCtl* ctl           = reinterpret_cast<SharedCtl*>(gen_base + ctl_off);
   const int32_t* init_smem = reinterpret_cast<const int32_t*>(gen_base + init_off);
   volatile int* abort_flag = &ctl->abort_flag;
-  constexpr bool kNeedE    = MODE == kModeGroupMax;   // only the group maxima need the exact e of every row
+#if CERTEX_SCREEN_TRACE
+  const bool tr_cta = p.trace != nullptr && blockIdx.x == 0 && !WIDE;
+#endif
+  constexpr bool kNeedE    = MODE == kModeGroupMax;   // only the exact group maxima need the e of every row
+  constexpr bool kGroups   = MODE == kModeGroupMax || MODE == kModeGroupBound;  // the passes of the threshold stage
+  constexpr bool kChainE   = MODE == kModeScreen || MODE == kModeGroupBound;    // e enters per chain of 16 columns (p.cmax)
   constexpr bool kStageE   = kNeedE && !WIDE;          // resident panel: e travels with the stage; WIDE: in its own ring
 
   const ScreenSeg* segs = ctl->segs;
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     }
     for (int i = 0; i < kSlots; ++i) {
       mbar_init(smem_u32(&ctl->tmem_full[i]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty[i]), kEpiWarps);
+      mbar_init(smem_u32(&ctl->tmem_empty[i]), kSplit ? kEpiWarps / 2 : kEpiWarps);
     }
     mbar_init(smem_u32(&ctl->panel_full), 1);
     mbar_init(smem_u32(&ctl->panel_empty), 1);
@@ -261,6 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       mbar_init(smem_u32(&ctl->e_full[i]), 1);
       mbar_init(smem_u32(&ctl->e_empty[i]), kEpiWarps);
     }
+
     ctl->abort_flag = 0;
     for (int i = 0; i < kEpiWarps; ++i) { ctl->rec_n[i] = 0; }
     fence_barrier_init();
@@ -283,8 +289,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       bool aborted = false;
       for (int s = 0; s < nseg && !aborted; ++s) {
         const ScreenSeg sg = segs[s];
-        const int c0       = (kNeedE && seg_col0) ? seg_col0[s] : 0;
-        const int stp      = (kNeedE && seg_step) ? seg_step[s] : 1;
+        const int c0       = (kGroups && seg_col0) ? seg_col0[s] : 0;
+        const int stp      = (kGroups && seg_step) ? seg_step[s] : 1;
         for (int t = sg.t0; t < sg.t1 && !aborted; ++t, ++ts) {
           const int ta = c0 + (t - c0) * stp;  // the tile that is read
           if (kNeedE) {
@@ -309,7 +315,9 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             for (int j = 0; j < sg.n_qtiles; ++j) {
               tma_load_2d(dst + j * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, fbar);
             }
-            if (MODE == kModeGroupMax && !p.plain_tiles) {
+            if (MODE == kModeGroupBound) {
+              tma_load_4d(dst + 2 * kQTileBytes, &tm_x, b * 128, 0, 0, ta, fbar);
+            } else if (MODE == kModeGroupMax && !p.plain_tiles) {
               tma_load_3d(dst + 2 * kQTileBytes, &tm_x, b * 128, 0, ta, fbar);
             } else {
               tma_load_2d(dst + 2 * kQTileBytes, &tm_x, b * 128, ta * kBaseTile, fbar);
@@ -343,8 +351,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
             tma_load_2d(base + panel_off + (j * kb + b) * kQTileBytes, &tm_q, b * 128, (sg.q_tile0 + j) * kQueryTile, pbar);
           }
         }
-        const int c0  = (kNeedE && seg_col0) ? seg_col0[s] : 0;
-        const int stp = (kNeedE && seg_step) ? seg_step[s] : 1;
+        const int c0  = (kGroups && seg_col0) ? seg_col0[s] : 0;
+        const int stp = (kGroups && seg_step) ? seg_step[s] : 1;
         for (int t = sg.t0; t < sg.t1; ++t, ++ts) {
           const int ta = c0 + (t - c0) * stp;  // the tile that is read
           const int st = ts % ns;
@@ -355,7 +363,11 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
           const uint32_t fbar = smem_u32(&ctl->full[st]);
           mbar_arrive_expect_tx(fbar, static_cast<uint32_t>(kb) * kBTileBytes + (kStageE ? kBaseTile * 4 : 0));
           for (int b = 0; b < kb; ++b) {
-            if (MODE == kModeGroupMax && !p.plain_tiles) {
+            if (MODE == kModeGroupBound) {
+              // anchors in chains: columns 16 i .. 16 i + 15 of tile t are 16 adjacent anchors, the chains of a tile are
+              // spread over the whole (norm-sorted) set; the map is 4-D (bytes, anchor of the chain, chain, tile)
+              tma_load_4d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, 0, ta, fbar);
+            } else if (MODE == kModeGroupMax && !p.plain_tiles) {
               // anchors: column c of tile t is anchor c * n_tiles + t, so every group of 64 columns samples the whole
               // (norm-sorted) set; the map is 3-D (bytes, column, tile)
               tma_load_3d(base + stage_off + (st * kb + b) * kBTileBytes, &tm_x, b * 128, 0, ta, fbar);
@@ -448,8 +460,10 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
               const uint32_t slot = gu & 1u;
               // a fresh barrier passes a wait for parity 1: the first unit of a slot does not wait
               if (MODE != kModeRate) {
+                TRACE_AT(tr_cta, gu, 0);
                 ok = mbar_wait(tempty_bar0 + slot * 8, ((gu >> 1) & 1u) ^ 1u, abort_flag, p.err, 5);
                 if (!ok) { break; }
+                TRACE_AT(tr_cta, gu, 1);
               }
               tc_fence_after();
               const uint32_t d_tmem = tmem + slot * kBaseTile;
@@ -467,6 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
                 }
               }
               tc_commit(tfull_bar0 + slot * 8);
+              TRACE_AT(tr_cta, gu, 2);
             }
             if (ok) { tc_commit(empty_bar0 + st * 8); }
             if (++st == ns) { st = 0, st_par ^= 1u; }
@@ -491,11 +506,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
     uint64_t* rec_buf        = reinterpret_cast<uint64_t*>(gen_base + rec_off) + ew * kRecBuf;
     volatile int* rec_n      = &ctl->rec_n[ew];  // staged records of this warp
 
-    Cursor cur;
-    cur.s = 0, cur.j = 0, cur.ts = 0, cur.col0 = 0;
-    cursor_seg<MODE == kModeGroupMax>(cur, segs, seg_col0, nseg);
-    int gu  = 0;
-    bool ok = true;
+    uint32_t gu = 0;  // units of this CTA so far: slot = gu & 1, the slot's use number = gu >> 1
+    bool ok     = true;
 
     // Staged records -> global memory: one atomic add reserves the range, the lanes copy.
     auto flush = [&](int n_rec) {
@@ -535,106 +547,201 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
       }
     };
 
-    // Everything between a unit's completion and the release of its slot sits on the path that bounds the pass (two
-    // slots: the MMAs of the next unit but one wait for it): the loads of the query's threshold and of the chain maxima
-    // of e are issued before the wait and their values are not touched until the slot is released.
-    const uint32_t taddr0     = tmem + lane_base + static_cast<uint32_t>(piece * kGroupRows);
+    // An epilogue warp is one serial stream of instructions per unit, and the pass is as fast as that stream (the MMAs
+    // of a unit of a 128-byte row take about 610 cycles; a hundred dependent instructions of a warp that shares its
+    // scheduler with four others take more). So the loops are plain nested loops over the segment's tiles and query
+    // tiles with pointers that are bumped, nothing is recomputed per unit that is known per tile or per segment, and
+    // warp-wide steps (the check of the record buffer) happen once per tile. Everything between a unit's completion and
+    // the release of its slot also sits on the other path that bounds the pass (two slots: the MMAs of the next unit but
+    // one wait for the release): the threshold and the chain maxima of e are loaded before the wait and not touched
+    // until the slot is released, and the release follows tcgen05.wait::ld directly (it is warp-wide: when lane 0 is
+    // past it, every lane's columns are in registers).
     const uint32_t tfull_bar0 = smem_u32(&ctl->tmem_full[0]), tempty_bar0 = smem_u32(&ctl->tmem_empty[0]);
-    while (ok && cur.valid) {
-      const uint32_t slot = static_cast<uint32_t>(gu) & 1u;
-      const int q         = (cur.q_tile0 + cur.j) * kQueryTile + row;
-      int thr             = F16 ? __float_as_int(CUDART_INF_F) : 0x7fffffff;  // float bits when F16
-      int4 ce             = make_int4(0, 0, 0, 0);
-      if (MODE == kModeScreen) {
-        if (q < p.nq) { thr = __ldg(p.thr + q); }
-        // the four chain maxima of e for this warp's piece (one address per warp)
-        ce = __ldg(reinterpret_cast<const int4*>(p.cmax + static_cast<size_t>(cur.t) * (kBaseTile / kChainRows)) + piece);
-      }
-      if (!mbar_wait(tfull_bar0 + slot * 8, (static_cast<uint32_t>(gu) >> 1) & 1u, abort_flag, p.err, 7)) { break; }
-      tc_fence_after();
-      const uint32_t taddr = taddr0 + slot * kBaseTile;
-      int32_t a[32], b[32];
-      tmem_ld32(taddr, a);
-      tmem_ld32(taddr + 32, b);
-      tmem_wait_ld(a);
-      reg_fence32(b);
-      // the piece is in registers: the slot goes back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(tempty_bar0 + slot * 8); }
-
-      if (MODE == kModeScreen) {
-        bool h0, h1, h2, h3;
-        if (F16) {
-          const float tf = __int_as_float(thr);
-          h0 = max16f(a) + __int_as_float(ce.x) >= tf;
-          h1 = max16f(a + 16) + __int_as_float(ce.y) >= tf;
-          h2 = max16f(b) + __int_as_float(ce.z) >= tf;
-          h3 = max16f(b + 16) + __int_as_float(ce.w) >= tf;
-        } else {
-          // thr and ce are first used here, long after their loads were issued: a use before the wait would stall the
-          // warp on the load latency in front of the slot's release
-          h0 = max16(a) + ce.x >= thr;
-          h1 = max16(a + 16) + ce.y >= thr;
-          h2 = max16(b) + ce.z >= thr;
-          h3 = max16(b + 16) + ce.w >= thr;
+    const int never_thr       = F16 ? __float_as_int(CUDART_INF_F) : 0x7fffffff;  // float bits when F16
+    constexpr int kERingOrNs  = WIDE ? kERing : 0;
+    int est = 0;            // GROUPMAX: ring position of the tile's e values and its parity
+    uint32_t est_par = 0;
+    const int e_ring = kERingOrNs ? kERingOrNs : ns;
+#if CERTEX_SCREEN_TRACE
+    const bool tr_w = tr_cta && lane == 0 && ew == 0, tr_x = tr_cta && lane == 0 && ew == kEpiWarps - 1;
+#endif
+    // With kSplit the 16 warps form two groups of 8, one per TMEM slot: group g reads the units of slot g (every other
+    // unit), each warp two 64-column pieces of it. A warp then has two unit times for the fixed latencies of a unit
+    // (noticing its completion, tcgen05.ld, the release) and its comparisons run while the other group waits; the price
+    // is a later release: the second piece can only be loaded into the registers the first has left.
+    const uint32_t grp = kSplit ? static_cast<uint32_t>(ew) >> 3 : 0u;
+    const int piece0   = kSplit ? ((ew >> 2) & 1) * 2 : piece;  // first (or only) 64-column piece of this warp
+    const uint32_t taddr_w = tmem + lane_base + static_cast<uint32_t>(piece0 * kGroupRows);
+    for (int s = 0; s < nseg && ok; ++s) {
+      const ScreenSeg sg = segs[s];
+      const int nqt      = sg.n_qtiles;
+      const int q_first  = sg.q_tile0 * kQueryTile + row;
+      const int col0     = (kGroups && seg_col0) ? seg_col0[s] : 0;
+      const int4* cm     = reinterpret_cast<const int4*>(p.cmax) + static_cast<size_t>(sg.t0) * (kBaseTile / kChainRows / 4) + piece0;
+      for (int t = sg.t0; t < sg.t1 && ok; ++t, cm += kBaseTile / kChainRows / 4) {
+        // the four chain maxima of e of each of this warp's pieces of the tile
+        int4 ce0 = make_int4(0, 0, 0, 0), ce1 = ce0;
+        if (kChainE) {
+          ce0 = __ldg(cm);
+          if (kSplit) { ce1 = __ldg(cm + 1); }
         }
-        if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
-          const int64_t row0 = static_cast<int64_t>(cur.t) * kBaseTile + piece * kGroupRows;
-          if (h0) { record(a, thr, ce.x, q, row0); }
-          if (h1) { record(a + 16, thr, ce.y, q, row0 + 16); }
-          if (h2) { record(b, thr, ce.z, q, row0 + 32); }
-          if (h3) { record(b + 16, thr, ce.w, q, row0 + 48); }
-          __syncwarp();
+        if (kNeedE) {
+          // the tile's e values landed with (or, WIDE, ahead of) its code rows. Every warp waits for them, also one
+          // that has no unit of its own in this tile: its release at the end of the tile must not run ahead of the
+          // refill of the ring slot, or it would be counted for the wrong round
+          ok = mbar_wait(WIDE ? smem_u32(&ctl->e_full[est]) : smem_u32(&ctl->full[est]), est_par, abort_flag, p.err, 6);
+          if (!ok) { break; }
+        }
+        const int32_t* e   = init_smem + est * kBaseTile + piece0 * kGroupRows;  // GROUPMAX: the tile's e values
+        const int64_t row0 = static_cast<int64_t>(t) * kBaseTile + piece0 * kGroupRows;
+        bool kept          = false;
+        int q              = q_first;
+        for (int j = 0; j < nqt; ++j, ++gu, q += kQueryTile) {
+          const uint32_t slot = gu & 1u;
+          if (kSplit && slot != grp) { continue; }
+          int thr = never_thr;
+          if (MODE == kModeScreen && q < p.nq) { thr = __ldg(p.thr + q); }
+          TRACE_AT(tr_w, gu, 3);
+          ok = mbar_wait(tfull_bar0 + slot * 8, (gu >> 1) & 1u, abort_flag, p.err, 7);
+          if (!ok) { break; }
+          TRACE_AT(tr_w, gu, 4);
+          TRACE_AT(tr_x, gu, 8);
+          tc_fence_after();
+          const uint32_t taddr = taddr_w + slot * kBaseTile;
+          int32_t a[32], b[32];
+          tmem_ld32(taddr, a);
+          tmem_ld32(taddr + 32, b);
+          tmem_wait_ld(a);
+          reg_fence32(b);
+          auto release = [&] {
+            TRACE_AT(tr_w, gu, 5);
+            TRACE_AT(tr_x, gu, 9);
+            // the unit is in registers (tcgen05.wait::ld is warp-wide): the slot goes back to the MMA warp
+            tc_fence_before();
+            if (lane == 0) { mbar_arrive(tempty_bar0 + slot * 8); }
+            TRACE_AT(tr_w, gu, 6);
+          };
+          // 32 columns (two chains) of a SCREEN piece: v = a or b, c0 / c1 their chain maxima of e
+          auto screen32 = [&](const int32_t* v, int c0, int c1, int64_t r0) {
+            bool h0, h1;
+            if (F16) {
+              const float tf = __int_as_float(thr);
+              h0 = max16f(v) + __int_as_float(c0) >= tf;
+              h1 = max16f(v + 16) + __int_as_float(c1) >= tf;
+            } else {
+              h0 = max16(v) + c0 >= thr;
+              h1 = max16(v + 16) + c1 >= thr;
+            }
+            if (h0 | h1) {  // rare: the lanes that kept something stage their records, nobody else waits
+              if (h0) { record(v, thr, c0, q, r0); }
+              if (h1) { record(v + 16, thr, c1, q, r0 + 16); }
+              kept = true;
+            }
+          };
+          // GROUPMAX, 32 columns: partial results of a piece (.x/.y from a, .z/.w from b; coarse groups use .x and .z)
+          auto gmax32 = [&](const int32_t* v, const int32_t* ev, int& m0, int& m1) {
+            if (p.fine_groups) {
+              m0 = F16 ? float_key(max16f_plus(v, ev)) : max16_plus(v, ev);
+              m1 = F16 ? float_key(max16f_plus(v + 16, ev + 16)) : max16_plus(v + 16, ev + 16);
+            } else {
+              m0 = F16 ? __float_as_int(max32f_plus(v, ev)) : max32_plus(v, ev);
+            }
+          };
+          // GROUPBOUND, 32 columns: max over the two chains of (largest product + the chain's smallest e)
+          auto bound32 = [&](const int32_t* v, int c0, int c1) {
+            if (F16) {
+              return __float_as_int(fmaxf(max16f(v) + __int_as_float(c0), max16f(v + 16) + __int_as_float(c1)));
+            }
+            return max(max16(v) + c0, max16(v + 16) + c1);
+          };
+          // One group value per 64-column piece. Rows of gmax are far apart, so every 4-byte store of a thread is a memory
+          // transaction of its own; with the two-group epilogue a thread holds two adjacent pieces of its row and
+          // writes both values with one 8-byte store.
+          int held = 0;  // kSplit: the value of the warp's first piece, until the second is known
+          auto put = [&](int pc, int m) {
+            int32_t* dst = p.gmax + static_cast<size_t>(q) * p.ld_gmax + (t - col0) * (kBaseTile / kGroupRows) + pc;
+            if (!kSplit) {
+              if (q < p.nq) { *dst = m; }
+            } else if (pc == piece0) {
+              held = m;
+            } else if (q < p.nq) {
+              *reinterpret_cast<int2*>(dst - 1) = make_int2(held, m);
+            }
+          };
+          auto bound_store = [&](int ma, int mb, int pc) {
+            put(pc, F16 ? float_key(fmaxf(__int_as_float(ma), __int_as_float(mb))) : max(ma, mb));
+          };
+          auto gmax_store = [&](const int4& m4, int pc) {
+            if (q >= p.nq) { return; }
+            if (p.fine_groups) {
+              // one maximum per chain of 16 rows: four times as many groups, for labels too small for 2k groups of 64
+              *reinterpret_cast<int4*>(p.gmax + static_cast<size_t>(q) * p.ld_gmax + (t - col0) * (kBaseTile / kChainRows) + pc * 4) = m4;
+            } else {
+              put(pc, F16 ? float_key(fmaxf(__int_as_float(m4.x), __int_as_float(m4.z))) : max(m4.x, m4.z));
+            }
+          };
+          if (!kSplit) {
+            release();
+            if (MODE == kModeScreen) {
+              screen32(a, ce0.x, ce0.y, row0);
+              screen32(b, ce0.z, ce0.w, row0 + 32);
+            } else if (MODE == kModeGroupBound) {
+              bound_store(bound32(a, ce0.x, ce0.y), bound32(b, ce0.z, ce0.w), piece0);
+            } else {
+              int4 m4 = make_int4(0, 0, 0, 0);
+              gmax32(a, e, m4.x, m4.y);
+              gmax32(b, e + 32, m4.z, m4.w);
+              gmax_store(m4, piece0);
+            }
+          } else {
+            // first piece; each half of the second piece is fetched as soon as its registers are free
+            int4 m4 = make_int4(0, 0, 0, 0);
+            int ma = 0, mb = 0;
+            if (MODE == kModeScreen) {
+              screen32(a, ce0.x, ce0.y, row0);
+            } else if (MODE == kModeGroupBound) {
+              ma = bound32(a, ce0.x, ce0.y);
+            } else {
+              gmax32(a, e, m4.x, m4.y);
+            }
+            tmem_ld32(taddr + 64, a);
+            if (MODE == kModeScreen) {
+              screen32(b, ce0.z, ce0.w, row0 + 32);
+            } else if (MODE == kModeGroupBound) {
+              mb = bound32(b, ce0.z, ce0.w);
+            } else {
+              gmax32(b, e + 32, m4.z, m4.w);
+            }
+            tmem_ld32(taddr + 96, b);
+            if (MODE == kModeGroupBound) { bound_store(ma, mb, piece0); }
+            if (MODE == kModeGroupMax) { gmax_store(m4, piece0); }
+            tmem_wait_ld(a);
+            reg_fence32(b);
+            release();
+            if (MODE == kModeScreen) {
+              screen32(a, ce1.x, ce1.y, row0 + 64);
+              screen32(b, ce1.z, ce1.w, row0 + 96);
+            } else if (MODE == kModeGroupBound) {
+              bound_store(bound32(a, ce1.x, ce1.y), bound32(b, ce1.z, ce1.w), piece0 + 1);
+            } else {
+              gmax32(a, e + 64, m4.x, m4.y);
+              gmax32(b, e + 96, m4.z, m4.w);
+              gmax_store(m4, piece0 + 1);
+            }
+          }
+          TRACE_AT(tr_w, gu, 7);
+        }
+        if (!ok) { break; }
+        // the tile is done: staged records go out once the buffer is half full (records beyond its end go straight to
+        // global memory meanwhile), and the tile's e values are released (GROUPMAX)
+        if (MODE == kModeScreen && __any_sync(0xffffffffu, kept)) {
           const int staged = min(*rec_n, kRecBuf);
           if (staged > kRecBuf / 2) { flush(staged); }
         }
-      } else {
-        // exact group maximum: e of the tile was staged with it
-        const int er = WIDE ? cur.ts % kERing : cur.ts % ns;
-        if (!mbar_wait(WIDE ? smem_u32(&ctl->e_full[er]) : smem_u32(&ctl->full[er]), (cur.ts / (WIDE ? kERing : ns)) & 1,
-                       abort_flag, p.err, 6)) {
-          break;
-        }
-        const int32_t* e = init_smem + er * kBaseTile + piece * kGroupRows;
-        if (p.fine_groups) {
-          // one maximum per chain of 16 rows: four times as many groups, for labels too small for 2k groups of 64
-          int4 m4;
-          if (F16) {
-            m4.x = float_key(max16f_plus(a, e));
-            m4.y = float_key(max16f_plus(a + 16, e + 16));
-            m4.z = float_key(max16f_plus(b, e + 32));
-            m4.w = float_key(max16f_plus(b + 16, e + 48));
-          } else {
-            m4.x = max16_plus(a, e);
-            m4.y = max16_plus(a + 16, e + 16);
-            m4.z = max16_plus(b, e + 32);
-            m4.w = max16_plus(b + 16, e + 48);
-          }
-          if (q < p.nq) {
-            *reinterpret_cast<int4*>(p.gmax + static_cast<size_t>(q) * p.ld_gmax +
-                                     (cur.t - cur.col0) * (kBaseTile / kChainRows) + piece * 4) = m4;
-          }
-        } else {
-          const int m = F16 ? float_key(fmaxf(max32f_plus(a, e), max32f_plus(b, e + 32)))
-                            : max(max32_plus(a, e), max32_plus(b, e + 32));
-          if (q < p.nq) {
-            p.gmax[static_cast<size_t>(q) * p.ld_gmax + (cur.t - cur.col0) * (kBaseTile / kGroupRows) + piece] = m;
-          }
-        }
-      }
-      // next unit; a finished tile's e values are released (GROUPMAX)
-      ++gu;
-      if (++cur.j == cur.nqt) {
-        cur.j = 0;
         if (kNeedE) {
           __syncwarp();
-          if (lane == 0) { mbar_arrive(WIDE ? smem_u32(&ctl->e_empty[cur.ts % kERing]) : smem_u32(&ctl->empty[cur.ts % ns])); }
-        }
-        ++cur.ts;
-        if (++cur.t == cur.t1) {
-          ++cur.s;
-          cursor_seg<MODE == kModeGroupMax>(cur, segs, seg_col0, nseg);
+          if (lane == 0) { mbar_arrive(WIDE ? smem_u32(&ctl->e_empty[est]) : smem_u32(&ctl->empty[est])); }
+          if (++est == e_ring) { est = 0, est_par ^= 1u; }
         }
       }
     }
@@ -666,8 +773,19 @@ size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages)
          static_cast<size_t>(n_stages) * kBaseTile * 4 + kEpiWarps * kRecBuf * 8 + sizeof(SharedCtl) + 64;
 }
 
-cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args, int grid, cudaStream_t stream)
+namespace {
+long long* g_trace = nullptr;
+int g_trace_units  = 0;
+}  // namespace
+
+void screen_set_trace(long long* trace, int units) { g_trace = trace, g_trace_units = trace ? units : 0; }
+bool screen_trace_compiled() { return CERTEX_SCREEN_TRACE != 0; }
+
+cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args_in, int grid, cudaStream_t stream)
 {
+  ScreenArgs args  = args_in;
+  args.trace       = g_trace;
+  args.trace_units = g_trace_units;
   const size_t smem = args.wide ? screen_smem_bytes_wide() : screen_smem_bytes(args.kb, args.panel_tiles, args.n_stages);
   // opt-in to large dynamic shared memory (cheap; set on every launch so that every device of the process has it)
   if (!args.wide && args.kb != 1 && args.kb != 2) { return cudaErrorInvalidValue; }
@@ -679,6 +797,10 @@ cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, c
     kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeScreen, true, true, 0> : screen_i8_kernel<kModeScreen, false, true, 0>)
              : args.f16 ? (kb2 ? screen_i8_kernel<kModeScreen, true, false, 2> : screen_i8_kernel<kModeScreen, true, false, 1>)
                         : (kb2 ? screen_i8_kernel<kModeScreen, false, false, 2> : screen_i8_kernel<kModeScreen, false, false, 1>);
+  } else if (args.mode == kModeGroupBound) {
+    kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeGroupBound, true, true, 0> : screen_i8_kernel<kModeGroupBound, false, true, 0>)
+             : args.f16 ? (kb2 ? screen_i8_kernel<kModeGroupBound, true, false, 2> : screen_i8_kernel<kModeGroupBound, true, false, 1>)
+                        : (kb2 ? screen_i8_kernel<kModeGroupBound, false, false, 2> : screen_i8_kernel<kModeGroupBound, false, false, 1>);
   } else {
     kernel = args.wide ? (args.f16 ? screen_i8_kernel<kModeGroupMax, true, true, 0> : screen_i8_kernel<kModeGroupMax, false, true, 0>)
              : args.f16 ? (kb2 ? screen_i8_kernel<kModeGroupMax, true, false, 2> : screen_i8_kernel<kModeGroupMax, true, false, 1>)

@@ -15,7 +15,12 @@ constexpr int kBaseTile  = 256;  // stored rows per accumulator unit (TMEM colum
 constexpr int kGroupRows = 64;   // rows per group maximum (one epilogue warp's piece of a unit)
 
 // kModeRate issues the loads and MMAs of every unit back to back with no epilogue (tensor-pipe rate probe).
-enum : int { kModeScreen = 0, kModeGroupMax = 1, kModeRate = 2 };
+// kModeGroupBound is the threshold stage at the screen's price: a tile's 16 chains are 16 adjacent anchors each (the
+// 4-D anchor map below), e is taken per chain (its minimum, in `cmax`), and gmax receives per group of 64 columns
+//   max over its four chains of (max of <q, x> over the chain + min of e over the chain),
+// a value some row of the group reaches (the row with the chain's largest product has at least the chain's smallest e),
+// so the k-th largest of them is still reached by k distinct rows. kModeGroupMax is the exact maximum of <q, x> + e.
+enum : int { kModeScreen = 0, kModeGroupMax = 1, kModeRate = 2, kModeGroupBound = 3 };
 
 /// Init value of a column that must never pass a threshold (removed rows, padding beyond the last row).
 constexpr int32_t kNeverInit = -(1 << 30);
@@ -40,7 +45,7 @@ __host__ __device__ inline uint64_t make_record(uint32_t q, uint32_t chunk, uint
 
 struct ScreenArgs {
   const int32_t* init;            // [n_tiles * 256] per-row term e[x] added to <q, x> (kNeverInit: removed / padding)
-  const int32_t* cmax;            // SCREEN: [n_tiles * 16] maximum of e over every chain of 16 rows
+  const int32_t* cmax;            // SCREEN: [n_tiles * 16] maximum of e over every chain of 16 rows; GROUPBOUND: minimum
   const int32_t* thr;             // SCREEN: [nq] keep iff <q, x> + e[x] >= thr[q]
   int32_t* gmax;                  // GROUPMAX: [nq, ld_gmax] maximum of <q, x> + e[x] over every group of 64 rows
   int64_t ld_gmax;
@@ -63,10 +68,19 @@ struct ScreenArgs {
   int plain_tiles;                // GROUPMAX: tile t is rows [256 t, 256 t + 256) of a 2-D map (else the 3-D anchor map)
   int fine_groups;                // GROUPMAX: one maximum per 16 rows (16 columns of gmax per tile) instead of per 64 (4)
   int* err;                       // set to a non-zero code when a bounded wait gave up
+  long long* trace;               // trace builds only (see screen_set_trace): [trace_units, 12] clock stamps of CTA 0
+  int trace_units;
 };
 
 size_t screen_smem_bytes(int kb, int panel_tiles, int n_stages);
 size_t screen_smem_bytes_wide();
+
+/// Profiling aid, effective only in a library built with -DCERTEX_SCREEN_TRACE=1 (make trace): CTA 0 of every later
+/// pass writes SM clock stamps of its first `units` accumulator units to the device buffer `trace` ([units, 12] int64;
+/// nullptr: off). The stamps cost time themselves (every instruction on the MMA-issuing thread's and the epilogue's
+/// path does): a trace shows where a unit's round trip goes, not how fast the untraced pass is. Process-wide.
+void screen_set_trace(long long* trace, int units);
+bool screen_trace_compiled();
 
 cudaError_t screen_i8_launch(const CUtensorMap& tm_q, const CUtensorMap& tm_x, const ScreenArgs& args, int grid, cudaStream_t stream);
 

@@ -8,6 +8,7 @@
 // output buffers already; this entry point adds no allocation of its own.
 #include "../../include/certex_b200.h"
 
+#include "engine.hpp"
 #include "kernels.cuh"
 
 #include <cuda_runtime.h>
@@ -62,6 +63,15 @@ extern "C" cuvsError_t certexB200SearchStatic(cuvsResources_t res, cuvsDistanceT
   if (n_rows < 1 || n_queries < 1 || dim < 1 || k < 1 || k > 2048 || k > n_rows) {
     return fail("certex: need n_rows >= k >= 1, k <= 2048, and at least one query");
   }
+  // what one launch of the scoring kernel takes; checked before anything is launched, so that a refused call leaves
+  // the outputs untouched
+  if (dim > kDenseMaxDim) {
+    return fail("certex: certexB200SearchStatic takes at most " + std::to_string(kDenseMaxDim) + " dimensions");
+  }
+  if (n_queries > kDenseMaxQueries || n_rows >= (int64_t(1) << 31)) {
+    return fail("certex: certexB200SearchStatic takes at most " + std::to_string(kDenseMaxQueries) +
+                " queries and fewer than 2^31 rows per call");
+  }
   const size_t row_bytes = static_cast<size_t>(dim) * dtype_size(dt);
   if (row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(vectors) % 16 != 0) {
     return fail("certex: certexB200SearchStatic needs 16-byte aligned vectors whose rows are a multiple of 16 bytes");
@@ -84,6 +94,12 @@ extern "C" cuvsError_t certexB200SearchStatic(cuvsResources_t res, cuvsDistanceT
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) { return fail(std::string("certex: cudaGetDevice: ") + cudaGetErrorString(e)); }
   if (device < 0 || device >= kMaxDevices) { return fail("certex: device ordinal out of range"); }
+  // the scratch address is the current device's, the stream is the resources': they must be the same device
+  const int res_device = reinterpret_cast<const Resources*>(res)->device;
+  if (res_device != device) {
+    return fail("certex: certexB200SearchStatic was called with device " + std::to_string(device) +
+                " current, but the resources were created on device " + std::to_string(res_device));
+  }
   unsigned char* scratch = nullptr;
   {
     // first call on this device: ask the runtime where this device keeps the array (the device must be current)
@@ -113,12 +129,20 @@ extern "C" cuvsError_t certexB200SearchStatic(cuvsResources_t res, cuvsDistanceT
   // Every element that a later kernel reads is written by an earlier kernel of this call (scores for all n_rows
   // columns, both lists in full), so nothing has to be cleared although the array keeps the previous call's contents.
   const Admit everything{};
+  cudaGetLastError();  // an error left by earlier work of the thread is not this call's
+  auto launched = [&](const char* what) {
+    const cudaError_t le = cudaGetLastError();
+    if (le == cudaSuccess) { return true; }
+    fail(std::string("certex: certexB200SearchStatic could not launch the ") + what + " kernel: " + cudaGetErrorString(le));
+    return false;
+  };
   launch_dense_scores(vectors, row_bytes, dt, static_cast<int>(dim), m, n_rows, queries, row_bytes, nullptr, 0,
                       static_cast<int>(n_queries), everything, scores, ld, stream);
+  if (!launched("scoring")) { return CUVS_ERROR; }  // nothing after a failed launch: later kernels would read stale scratch
   launch_select_topk(scores, ld, n_rows, k, nullptr, 0, static_cast<int>(n_queries), best_s, best_row, part_s, part_row, stream);
+  if (!launched("selection")) { return CUVS_ERROR; }
   launch_finish(best_s, best_row, 0, queries, row_bytes, dt, static_cast<int>(dim), m, static_cast<int>(n_queries), k, neighbors,
                 distances, nullptr, stream);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) { return fail(std::string("certex: kernel launch failed: ") + cudaGetErrorString(e)); }
+  if (!launched("output")) { return CUVS_ERROR; }
   return CUVS_SUCCESS;
 }

@@ -5,6 +5,11 @@ row shards, rank s owns the global ids [n s / S, n (s + 1) / S), every rank comp
 queries, and the per-rank lists are merged by (exact score, id). The reference moves the lists through host memory and
 sorts on the CPU; here every rank contributes k (fp64 score, int64 id) pairs per query to one all-gather and merges the
 gathered lists with a device kernel. No kernel reads another GPU's memory.
+
+Two ways of running the exchange: `backend="native"` (the default on GPUs) is one call into the library, which runs the
+local search, ncclAllGather and the merge back to back on the stream over a communicator of its own and looks at the
+device only once, at the end (certexB200DistributedSearch); `backend="torch"` runs the same three steps from Python
+with torch.distributed's all_gather_into_tensor.
 """
 
 import contextlib
@@ -71,8 +76,10 @@ class DistributedIndex:
     the 10 M x 128 benchmark with two shards), and the extra synchronisation point cost more than it saved there
     (8.3 ms instead of 7.5 ms per 10 000 queries)."""
 
-    def __init__(self, dim, metric="l2", anchor_stride=16, group=None, share_thresholds=False):
-        self.d, self.metric, self.group = dim, metric, group
+    def __init__(self, dim, metric="l2", anchor_stride=16, group=None, share_thresholds=False, backend="native"):
+        _need(backend in ("native", "torch"), "backend must be 'native' or 'torch'")
+        self.d, self.metric, self.group, self.backend = dim, metric, group, backend
+        self._comm = None  # the library's communicator over the ranks of `group` (native backend)
         self.local = Index(dim, metric=metric, anchor_stride=anchor_stride)
         self.first = 0
         self.share_thresholds = share_thresholds
@@ -104,10 +111,47 @@ class DistributedIndex:
         lo, hi = shard_bounds(x.shape[0], dist.get_world_size(self.group), dist.get_rank(self.group))
         return self.add_shard(x[lo:hi], lo)
 
+    def __del__(self):
+        if getattr(self, "_comm", None) is not None:
+            L.lib().certexB200CommDestroy(self._comm)
+            self._comm = None
+
+    def _communicator(self):
+        """The library's NCCL communicator over the ranks of the group: rank 0 makes the id, the process group carries
+        it to the others (once)."""
+        if self._comm is None:
+            world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+            ident = ctypes.create_string_buffer(128)
+            if rank == 0:
+                L.check(L.lib().certexB200CommGetUniqueId(ident))
+            box = [ident.raw]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0) if self.group else 0, group=self.group)
+            ident = ctypes.create_string_buffer(box[0], 128)
+            comm = ctypes.c_void_p()
+            L.check(L.lib().certexB200CommInitRank(ident, world, rank, ctypes.byref(comm)))
+            self._comm = comm
+        return self._comm
+
+    def _search_native(self, Q, k, batch, return_scores):
+        nq = Q.shape[0]
+        I = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+        D = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+        S = torch.empty((nq, k), dtype=torch.float64, device="cuda") if return_scores else None
+        sp = L.SearchParams(128, int(batch), 2)
+        L.check(L.lib().certexB200DistributedSearch(
+            L.resources(), self._communicator(), ctypes.byref(sp), self.local.core.handle, L.Tensor(Q).ref,
+            L.Tensor(I).ref, L.Tensor(D).ref, None if S is None else L.Tensor(S).ref, self.first,
+            1 if self.share_thresholds else 0))
+        if self.metric == "cosine":
+            D = 1 - D
+        return (D, I, S) if return_scores else (D, I)
+
     def search(self, q, k=10, batch=2048, return_scores=False):
         _need(self.local.core is not None, "add vectors first")
         _need(k <= int(self.local.core.info().size), "every shard needs at least k vectors")
         Q = q.cuda().contiguous()
+        if self.backend == "native":
+            return self._search_native(Q.to(self.local.dtype), k, batch, return_scores)
         if self._shared(k):
             with threshold_hook(lambda keys: dist.all_reduce(keys, op=dist.ReduceOp.MAX, group=self.group)):
                 _, I, S = self.local.search(Q, k=k, batch=batch, return_scores=True, id_base=self.first)

@@ -15,7 +15,7 @@ slot slots[row_to_batch[i]] (default the batch position). Positions beyond a seq
 
 import torch
 
-from .attention import _as_half_or_float
+from .attention import GrowingMap, _as_half_or_float
 from .index import Index, _need
 
 
@@ -37,7 +37,7 @@ class ExactTopK:
         self.num_kv_heads, self.head_dim, self.k_max = int(num_kv_heads), int(head_dim), int(k_max)
         self.capacity = capacity
         self.index, self.dtype = None, None
-        self._position = None   # id of the index -> position of the key inside its sequence
+        self._map = GrowingMap(torch.int32)  # id of the index -> position of the key inside its sequence
         self._number = {}       # slot -> its number (labels number * num_kv_heads + head)
         self._next = 0          # numbers are never reused: the labels of removed rows stay theirs
         self._length = {}       # slot -> keys appended
@@ -66,11 +66,11 @@ class ExactTopK:
         # head-major rows: the keys of one (slot, head) label are adjacent and in position order
         rows = K.to(self.dtype).transpose(0, 1).reshape(self.num_kv_heads * n_new, self.head_dim).contiguous()
         labels = (base + torch.arange(self.num_kv_heads, dtype=torch.int32, device="cuda")).repeat_interleave(n_new)
-        first = 0 if self._position is None else int(self._position.shape[0])
+        first = len(self._map)
         self.index.add(rows, labels=labels)
         at = self._length[slot]
         pos = torch.arange(at, at + n_new, dtype=torch.int32, device="cuda").repeat(self.num_kv_heads)
-        self._position = pos if self._position is None else torch.cat([self._position, pos])
+        self._map.append(pos, reserve=0 if self.capacity is None else int(self.capacity) * self.num_kv_heads)
         self._ids[slot].append((first, self.num_kv_heads * n_new))
         self._length[slot] = at + n_new
         return self
@@ -125,7 +125,7 @@ class ExactTopK:
                   "these queries do not fit float16 but the selector holds float16 keys: start it with float32 keys")
             Qs = Qs.to(self.dtype).reshape(rows.numel() * H, d).contiguous()
             _, I = self.index.search(Qs, k=k, labels=labels)
-            out[rows] = self._position[I.clamp_(min=0)].reshape(rows.numel(), H, k)
+            out[rows] = self._map.values[I.clamp_(min=0)].reshape(rows.numel(), H, k)
         return out[:, 0] if single else out
 
     def ragged_transform(self, q, offsets, k, row_to_batch=None, slots=None):

@@ -19,9 +19,12 @@ def main():
     ap.add_argument("--nq", type=int, default=2048)
     ap.add_argument("--n", type=int, default=1_000_000)
     ap.add_argument("--code-len", type=int, default=128)
-    ap.add_argument("--mode", default="screen", choices=["screen", "groupmax", "rate"])
+    ap.add_argument("--mode", default="screen", choices=["screen", "groupmax", "rate", "groupbound"])
     ap.add_argument("--survivors", type=float, default=0.0, help="average kept pairs per query (screen mode)")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--trace", type=int, default=0,
+                    help="print SM clock stamps of this many units of CTA 0 of the last run (needs the trace build: "
+                         "CERTEX_B200_LIB=<...>/lib/libcertex_b200_trace.so)")
     args = ap.parse_args()
 
     L, res = _lib.lib(), _lib.resources()
@@ -39,13 +42,13 @@ def main():
     x = x[order].contiguous()
     init[:n] = init[:n][order]
     ld = -(-(n_pad // 64) // 8) * 8
-    need_gmax = args.mode == "groupmax" or args.survivors > 0
+    need_gmax = args.mode in ("groupmax", "groupbound") or args.survivors > 0
     gmax = torch.zeros((nq if need_gmax else 1, ld), dtype=torch.int32, device="cuda")
     cap = 4096
     cnt = torch.zeros((nq,), dtype=torch.int32, device="cuda")
     cand = torch.zeros((nq, cap), dtype=torch.int32, device="cuda")
     thr = torch.full((nq,), 2**31 - 1, dtype=torch.int32, device="cuda")
-    mode = {"screen": 0, "groupmax": 1, "rate": 2}[args.mode]
+    mode = {"screen": 0, "groupmax": 1, "rate": 2, "groupbound": 3}[args.mode]
     ms = ctypes.c_float()
 
     def run(m, t):
@@ -68,17 +71,31 @@ def main():
         h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
     except Exception:
         h = None
+    trace = None
+    if args.trace > 0:
+        trace = torch.zeros((args.trace, 12), dtype=torch.int64, device="cuda")
+        _lib.check(L.certexB200ScreenTrace(trace.data_ptr(), args.trace))
     times = []
     for _ in range(args.iters):
         times.append(run(mode, thr))
         if h is not None:
             clocks.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+    if trace is not None:
+        _lib.check(L.certexB200ScreenTrace(None, 0))
     best = min(times)
     tops = 2.0 * nq * n * cl / (best / 1e3) / 1e12
     units = (nq_pad // 128) * (n_pad // 256)
     print(f"mode={args.mode} nq={nq} n={n} code_len={cl}: best {best:.3f} ms of {args.iters} "
           f"({tops:.1f} int8 TOP/s, {units} units, kept/query {float(cnt.float().mean()):.1f}, "
           f"SM MHz after each run min/max {min(clocks) if clocks else None}/{max(clocks) if clocks else None})")
+
+    if trace is not None:
+        t = trace.cpu().numpy()
+        t0 = int(t[t > 0].min())
+        names = "m_wait m_have m_commit e_wait e_full e_ld e_rel e_done eL_full eL_ld".split()
+        print("unit " + " ".join(f"{n:>8s}" for n in names))
+        for u in range(args.trace):
+            print(f"{u:4d} " + " ".join(f"{int(v) - t0 if v > 0 else -1:8d}" for v in t[u, :10]))
 
 
 if __name__ == "__main__":

@@ -278,3 +278,64 @@ def test_golden_fixtures_on_gpu():
         index.add(x)
         _, I, S = index.search(q, k=k, return_scores=True)
         assert np.array_equal(I, g[f"{name}/ids"]) and np.array_equal(S, g[f"{name}/scores"]), name
+
+
+@pytest.mark.parametrize("dtype,metric", [("uint8", "l2"), ("float32", "cosine")])
+def test_a_call_short_of_memory_is_answered_in_halves(dtype, metric):
+    """A call whose temporaries cannot be allocated is split in halves, recursively, like the reference's batches
+    (cpp/src/neighbors/certex/certex.cu:1477-1502). The shortage is simulated on the host (test mode 4: calls of more
+    than 40 queries fail as an allocation failure would), for plain, labeled and per-query-filtered searches."""
+    x = synthetic.correlated(20000, 64, seed=51, dtype=dtype, unequal_norms=metric != "l2")
+    q = synthetic.correlated(300, 64, seed=52, dtype=dtype)
+    rng = np.random.default_rng(53)
+    lab = rng.integers(0, 4, 20000).astype(np.int32)
+    ql = rng.integers(0, 4, 300).astype(np.int32)
+    index = certex.Index(64, metric=metric)
+    index.add(x, labels=lab)
+    index._test_mode(4, 40)
+    _, I, S = index.search(q, k=10, return_scores=True)
+    ids, scores = oracle.knn(x, q, 10, metric)
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    _, I, S = index.search(q, k=10, labels=ql, return_scores=True)
+    ids, scores = oracle.knn(x, q, 10, metric, row_labels=lab, query_labels=ql)
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    index._test_mode(4, 70)  # a bitmap is cut at whole words of query rows: pieces of 64 queries are the smallest
+    per_query = rng.random((300, 20000)) < 0.05
+    _, I, S = index.search(q, k=10, filter=per_query, return_scores=True)
+    ids, scores = oracle.knn(x, q, 10, metric, keep_pair=per_query.astype(np.uint8))
+    assert np.array_equal(I, ids) and np.array_equal(S, scores)
+    index._test_mode(4, 0)
+    with pytest.raises(certex.CertexError, match="out of device memory"):
+        index.search(q[:1], k=10)
+
+
+def test_merge_of_more_candidates_than_one_block_sorts():
+    """8 shards x k = 2048 = 16 384 candidates per query: merged in rounds, equal to the oracle's merge."""
+    rng = np.random.default_rng(7)
+    parts, nq, k = 8, 12, 2048
+    s = np.sort(rng.integers(0, 5000, (parts, nq, k)).astype(np.float64), axis=2)
+    i = rng.permutation(parts * nq * k).reshape(parts, nq, k).astype(np.int64)
+    i[3, :, 2000:] = -1
+    s[3, :, 2000:] = np.inf
+    q = torch.zeros((nq, 8), dtype=torch.float32, device="cuda")
+    D, I, S = certex.merge_shards(q, torch.from_numpy(s).cuda(), torch.from_numpy(i).cuda(), "l2", return_scores=True)
+    wi, ws = oracle.merge(i, s)
+    assert np.array_equal(I.cpu().numpy(), wi) and np.array_equal(S.cpu().numpy(), ws)
+
+
+@pytest.mark.parametrize("dtype,metric,dim", [("uint8", "l2", 128), ("float32", "l2", 96), ("float32", "cosine", 300),
+                                             ("int8", "ip", 64)])
+def test_chained_and_exact_threshold_stages_agree(dtype, metric, dim):
+    """Plain searches take their thresholds from the chained bound of the anchor pass (a value below each group's exact
+    maximum); with test mode 5 from the exact group maxima, as searches with a bitset filter do. Both are exact, and
+    the bound costs hardly any extra survivors."""
+    x, q = make(60000, dim, 200, dtype, metric != "l2", 0, seed=71)
+    index = certex.Index(dim, metric=metric)
+    index.add(x)
+    with certex.search_stats() as chained:
+        check(index, x, q, 10, metric)
+    index._test_mode(5)
+    with certex.search_stats() as exact:
+        check(index, x, q, 10, metric)
+    assert chained.dense_queries == 0 and exact.dense_queries == 0
+    assert exact.survivors <= chained.survivors <= 1.25 * exact.survivors + 200 * 16

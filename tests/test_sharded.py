@@ -95,21 +95,41 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
     script.write_text(
         "import os, sys, numpy as np, torch, torch.distributed as dist\n"
         f"sys.path.insert(0, {ROOT!r})\n"
+        "import libcertex_b200 as certex\n"
         "from libcertex_b200 import distributed, synthetic\n"
         "from oracle import oracle\n"
         "rank = int(os.environ['RANK']); torch.cuda.set_device(int(os.environ['LOCAL_RANK']))\n"
         "dist.init_process_group('nccl')\n"
         "x = synthetic.correlated(40000, 32, seed=3, dtype='uint8'); q = synthetic.correlated(100, 32, seed=4, dtype='uint8')\n"
-        "idx = distributed.DistributedIndex(32, share_thresholds=True).add(torch.from_numpy(x))\n"
-        "D, I, S = idx.search(torch.from_numpy(q), k=10, return_scores=True)\n"
         "ids, scores = oracle.knn(x, q, 10, 'l2')\n"
-        "assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores)\n"
+        "for backend in ('native', 'torch'):\n"
+        "    idx = distributed.DistributedIndex(32, share_thresholds=True, backend=backend).add(torch.from_numpy(x))\n"
+        "    D, I, S = idx.search(torch.from_numpy(q), k=10, return_scores=True)\n"
+        "    assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores), backend\n"
+        "    D2, I2 = idx.search(torch.from_numpy(q), k=10)\n"
+        "    assert torch.equal(I2, I) and torch.equal(D2, D)\n"
+        "    # candidate lists that overflow on purpose (capacity 16 for k = 10): the repair and the second exchange\n"
+        "    idx.local._test_mode(2, 16)\n"
+        "    D, I, S = idx.search(torch.from_numpy(q), k=10, return_scores=True)\n"
+        "    assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores), backend + ' overflow'\n"
         "xf = synthetic.correlated(40000, 96, seed=5, dtype='float32'); qf = synthetic.correlated(100, 96, seed=6, dtype='float32')\n"
-        "for share in (True, False):\n"
-        "    fidx = distributed.DistributedIndex(96, metric='cosine', share_thresholds=share).add(torch.from_numpy(xf))\n"
-        "    D, I, S = fidx.search(torch.from_numpy(qf), k=20, return_scores=True)\n"
-        "    ids, scores = oracle.knn(xf, qf, 20, 'cosine')\n"
-        "    assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores)\n"
+        "ids, scores = oracle.knn(xf, qf, 20, 'cosine')\n"
+        "for backend in ('native', 'torch'):\n"
+        "    for share in (True, False):\n"
+        "        fidx = distributed.DistributedIndex(96, metric='cosine', share_thresholds=share, backend=backend).add(torch.from_numpy(xf))\n"
+        "        D, I, S = fidx.search(torch.from_numpy(qf), k=20, return_scores=True)\n"
+        "        assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores), (backend, share)\n"
+        "# a rank whose local search fails (a host-side simulated allocation failure on rank 1, one query so that no\n"
+        "# halving helps): every rank gets an error for the call instead of waiting, and the next call works\n"
+        "idx = distributed.DistributedIndex(32).add(torch.from_numpy(x))\n"
+        "if rank == 1: idx.local._test_mode(4, 0)\n"
+        "try:\n"
+        "    idx.search(torch.from_numpy(q[:1]), k=10); raise SystemExit('no error on rank %d' % rank)\n"
+        "except certex.CertexError as e:\n"
+        "    assert ('rank 1 failed' in str(e)) if rank == 0 else ('out of device memory' in str(e)), str(e)\n"
+        "idx.local._test_mode(0, 0)\n"
+        "D, I = idx.search(torch.from_numpy(q), k=10)\n"
+        "assert np.array_equal(I.cpu().numpy(), oracle.knn(x, q, 10, 'l2')[0])\n"
         "dist.barrier(); dist.destroy_process_group(); print('rank', rank, 'ok')\n"
     )
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")

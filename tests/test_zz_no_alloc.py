@@ -5,8 +5,10 @@ whole GPU at start-up (a cudaMalloc inside the search would fail), or a loop who
 device-wide synchronisation an allocation can cause. For them the library keeps the temporaries of its dense search in
 a fixed array inside the library image. This test calls that entry point through the C ABI twice in a row (different
 queries, different sizes, so the second call runs over what the first left in the array) and requires the same ids and
-distances as the regular entry point, cuvsCertexSearch, on an index built from the same vectors. It also checks that a
-request larger than the fixed array is refused with a message. The file sorts last so that a run that stops at the
+distances as the regular entry point, cuvsCertexSearch, on an index built from the same vectors, and as the CPU oracle
+(ids equal; distances equal to the oracle's fp64 scores brought to the entry point's float32 conventions), so that a
+fault shared by both entry points would not pass. It also checks that a request larger than the fixed array, or one
+made with another device's resources, is refused with a message. The file sorts last so that a run that stops at the
 first failure has already run every other test."""
 
 import ctypes
@@ -16,8 +18,27 @@ import pytest
 import torch
 
 from libcertex_b200 import _lib
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
+METRIC_NAME = {_lib.L2Expanded: "l2", _lib.InnerProduct: "ip", _lib.CosineExpanded: "cosine"}
+
+
+def _oracle(x, q, k, metric):
+    """ids and float32 distances of the CPU oracle in the conventions of cuvsCertexSearch: squared distance for L2,
+    <q, x> for the inner product, 1 - cos for the cosine metric."""
+    xh, qh = x.cpu().numpy(), q.cpu().numpy()
+    ids, s = oracle.knn(xh, qh, k, METRIC_NAME[metric])
+    if metric == _lib.L2Expanded:
+        d = s
+    elif metric == _lib.CosineExpanded:
+        d = s / 2
+    else:
+        qq = np.zeros(len(qh))
+        for t in range(qh.shape[1]):  # the sequential fp64 sum the engine and the oracle use for |q|^2
+            qq = qq + qh[:, t].astype(np.float64) * qh[:, t].astype(np.float64)
+        d = (qq[:, None] - s) / 2
+    return ids, d.astype(np.float32)
 
 
 def _regular(x, q, k, metric):
@@ -57,10 +78,15 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
     xf = torch.randn((20000, 32), generator=g, device="cuda")
     xf[17] = xf[3]  # equal scores: both entry points must pick the smaller id
     xu = torch.randint(0, 256, (6000, 64), generator=g, device="cuda", dtype=torch.uint8)
+    xh = xf.half()
+    xi = (torch.randint(0, 256, (6000, 48), generator=g, device="cuda") - 128).to(torch.int8)
     calls = [
         (xf, torch.randn((90, 32), generator=g, device="cuda"), 10, _lib.L2Expanded),
         (xu, torch.randint(0, 256, (300, 64), generator=g, device="cuda", dtype=torch.uint8), 25, _lib.L2Expanded),
         (xf, torch.randn((40, 32), generator=g, device="cuda"), 7, _lib.InnerProduct),
+        (xh, torch.randn((50, 32), generator=g, device="cuda").half(), 12, _lib.CosineExpanded),
+        (xi, (torch.randint(0, 256, (120, 48), generator=g, device="cuda") - 128).to(torch.int8), 5, _lib.InnerProduct),
+        (xf, torch.randn((60, 32), generator=g, device="cuda"), 9, _lib.CosineExpanded),
     ]
     for x, q, k, metric in calls:  # back to back: no other GPU work of the library in between
         status, nb, ds = _static(x, q, k, metric)
@@ -69,6 +95,13 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
         want_nb, want_ds = _regular(x, q, k, metric)
         assert torch.equal(nb, want_nb)
         assert torch.equal(ds, want_ds)
+        ids, dist = _oracle(x, q, k, metric)
+        assert np.array_equal(nb.cpu().numpy(), ids)
+        if metric == _lib.InnerProduct and x.dtype.is_floating_point:
+            # <q, x> = (|q|^2 - score) / 2 cancels digits: the float32 value may differ in its last place
+            np.testing.assert_allclose(ds.cpu().numpy(), dist, rtol=1e-6, atol=1e-6)
+        else:
+            assert np.array_equal(ds.cpu().numpy(), dist)
 
 
 def test_requests_beyond_the_fixed_scratch_are_refused():
@@ -81,3 +114,23 @@ def test_requests_beyond_the_fixed_scratch_are_refused():
     odd = torch.zeros((100, 10), dtype=torch.float32, device="cuda")  # rows of 40 bytes: not a multiple of 16
     status, _, _ = _static(odd, odd[:4].contiguous(), 5, _lib.L2Expanded)
     assert status == 0 and "16" in _lib.lib().cuvsGetLastErrorText().decode()
+    wide = torch.zeros((64, 8000), dtype=torch.float32, device="cuda")  # more dimensions than a launch takes
+    nb = torch.full((4, 5), -7, dtype=torch.int64, device="cuda")
+    status = _lib.lib().certexB200SearchStatic(_lib.resources(), _lib.L2Expanded, _lib.DLDataType(_lib.kDLFloat, 32, 1),
+                                               wide.data_ptr(), 64, wide.data_ptr(), 4, 8000, 5, nb.data_ptr(),
+                                               torch.zeros((4, 5), device="cuda").data_ptr())
+    torch.cuda.synchronize()
+    assert status == 0 and "dimensions" in _lib.lib().cuvsGetLastErrorText().decode()
+    assert bool((nb == -7).all())  # a refused call launches nothing
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_resources_of_another_device_are_refused():
+    x = torch.zeros((100, 16), dtype=torch.float32, device="cuda:0")
+    res0 = _lib.resources()
+    with torch.cuda.device(1):
+        nb = torch.zeros((4, 5), dtype=torch.int64, device="cuda:1")
+        status = _lib.lib().certexB200SearchStatic(res0, _lib.L2Expanded, _lib.DLDataType(_lib.kDLFloat, 32, 1),
+                                                   x.data_ptr(), 100, x.data_ptr(), 4, 16, 5, nb.data_ptr(),
+                                                   torch.zeros((4, 5), device="cuda:1").data_ptr())
+    assert status == 0 and "device" in _lib.lib().cuvsGetLastErrorText().decode()
