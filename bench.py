@@ -107,6 +107,7 @@ def config_of(args):
         "workload": f"{args.n_base}x{DIM} uint8 Gaussian mixture (1000 centres in [20,235], sigma 18), "
                     f"{args.n_queries} queries, k={K}, L2, {args.gpus} row shard(s)",
         "batch": args.batch, "anchor_stride": args.anchor_stride, "searches_per_step": per_step,
+        "share_thresholds": bool(args.share_thresholds) and args.gpus > 1,
         "l2_policy": "inputs exceed L2: every step streams the whole shard (>= 160 MB) from HBM",
     }
 
@@ -207,6 +208,13 @@ def main():
     ap.add_argument("--searches-per-step", type=int, default=0,
                     help="searches of all queries per step (default: 1 on one GPU, 4 on several)")
     ap.add_argument("--parity-queries", type=int, default=16, help="queries checked against the CPU oracle at N > 1")
+    ap.add_argument("--share-thresholds", type=int, default=1,
+                    help="N > 1: the shards screen with the tightest threshold any of them found (one all-reduce per "
+                         "batch, the first round of the reference's sharded search); 0: every shard with its own")
+    ap.add_argument("--shard-parity", type=int, default=0,
+                    help="sets too large for one host copy (the 500 M-row configuration): every rank checks the local "
+                         "top-k of this many queries against the CPU oracle over its own shard, streamed in chunks; "
+                         "replaces the check over all rows")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -231,7 +239,8 @@ def main():
     xb = synthetic.mixture_u8(hi - lo, seed=0, row0=lo)
     xq = synthetic.mixture_u8(nq, seed=1)
     if world > 1:
-        index = distributed.DistributedIndex(DIM, anchor_stride=args.anchor_stride).add_shard(xb, lo)
+        index = distributed.DistributedIndex(DIM, anchor_stride=args.anchor_stride,
+                                             share_thresholds=bool(args.share_thresholds)).add_shard(xb, lo)
     else:
         index = certex.Index(DIM, anchor_stride=args.anchor_stride)
         index.add(xb)
@@ -295,6 +304,32 @@ def main():
     torch.cuda.synchronize()
     assert torch.equal(I_all, I), "two searches of the same queries returned different ids"
 
+    # ---- per-shard parity for sets that do not fit one host copy: every rank against the oracle over its own rows
+    shard_parity = None
+    if args.shard_parity > 0:
+        from oracle import oracle
+
+        pick_s = np.arange(0, nq, max(1, nq // args.shard_parity))[: args.shard_parity]
+        local_index = index.local if world > 1 else index
+        _, I_loc, S_loc = local_index.search(xq[torch.from_numpy(pick_s).cuda()].contiguous(), k=K, batch=args.batch,
+                                             return_scores=True, id_base=lo)
+        cores = max(1, (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)) // world)
+        q_host = xq.cpu().numpy()[pick_s]
+        chunk, parts_i, parts_s = 4 * synthetic.CHUNK, [], []
+        for off in range(0, hi - lo, chunk):
+            rows = synthetic.mixture_u8(min(chunk, hi - lo - off), seed=0, row0=lo + off).cpu().numpy()
+            ids_c, sc_c = oracle.knn(rows, q_host, K, "l2", id_base=lo + off, threads=cores)
+            parts_i.append(ids_c)
+            parts_s.append(sc_c)
+        want_i, want_s = oracle.merge(np.stack(parts_i), np.stack(parts_s))
+        mine_ok = bool(np.array_equal(I_loc.cpu().numpy(), want_i) and np.array_equal(S_loc.cpu().numpy(), want_s))
+        flag = torch.tensor([1 if mine_ok else 0], dtype=torch.int32, device="cuda")
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        shard_parity = {"queries": int(len(pick_s)), "ranks": world, "every_rank_equal": bool(flag.item()),
+                        "against": "CPU oracle over each rank's own shard (streamed in chunks of 4 Mi rows), local ids "
+                                   "and fp64 scores bit for bit"}
+
     if rank == 0:
         pk = peaks()
         shard_rows = hi - lo
@@ -331,9 +366,17 @@ def main():
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},
         }
-        xb_host = synthetic.mixture_u8(n_base, seed=0).cpu().numpy()
+        if shard_parity is not None:
+            line["parity"] = shard_parity
+            print(json.dumps(line))
+            ok = shard_parity["every_rank_equal"]
+            xb_host = None
+        else:
+            xb_host = synthetic.mixture_u8(n_base, seed=0).cpu().numpy()
         xq_host = xq.cpu().numpy()
-        if world == 1 and not args.no_cpu_baseline:
+        if xb_host is None:
+            pass
+        elif world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], (pick, ids, scores) = cpu_baseline(xb_host, xq_host)
         else:
             from oracle import oracle
@@ -341,12 +384,13 @@ def main():
             pick = np.arange(0, nq, max(1, nq // max(args.parity_queries, 1)))[: args.parity_queries]
             cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
             ids, scores = oracle.knn(xb_host, xq_host[pick], K, "l2", threads=cores)
-        ids_equal = bool(np.array_equal(I_all[pick].cpu().numpy(), ids))
-        scores_equal = bool(np.array_equal(S_all[pick].cpu().numpy(), scores))
-        line["parity"] = {"queries": int(len(pick)), "ids_equal": ids_equal, "scores_equal": scores_equal,
-                          "against": "CPU oracle (fp64 exhaustive over all rows), ids and fp64 scores bit for bit"}
-        print(json.dumps(line))
-        ok = ids_equal and scores_equal
+        if xb_host is not None:
+            ids_equal = bool(np.array_equal(I_all[pick].cpu().numpy(), ids))
+            scores_equal = bool(np.array_equal(S_all[pick].cpu().numpy(), scores))
+            line["parity"] = {"queries": int(len(pick)), "ids_equal": ids_equal, "scores_equal": scores_equal,
+                              "against": "CPU oracle (fp64 exhaustive over all rows), ids and fp64 scores bit for bit"}
+            print(json.dumps(line))
+            ok = ids_equal and scores_equal
     else:
         ok = True
     if world > 1:

@@ -27,6 +27,7 @@ namespace certex_b200 {
 thread_local SearchStats* Index::stats_sink = nullptr;
 thread_local Index::ThresholdHook Index::threshold_hook = nullptr;
 thread_local void* Index::threshold_hook_ctx = nullptr;
+thread_local Index::TopkHook Index::topk_hook = nullptr;
 
 namespace {
 
@@ -736,10 +737,23 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   mark();
   // 2 threshold: the k-th largest group maximum
   launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
-  if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, 0, res.stream); }
+  const bool wide_exchange = topk_hook != nullptr && k <= kTopkExchangeMaxK;
+  int32_t* topk            = nullptr;
+  if (wide_exchange) {  // the k largest group values of every query, for the exchange between row shards
+    topk = scratch.get<int32_t>(static_cast<size_t>(nq) * k);
+    launch_collect_topk(gmax, ld_g, n_groups, k, nq, thr, topk, res.stream);
+  }
+  if (screen_kind_ == 2) {
+    launch_finish_thr_f16(thr, shift + q0, nq, 0, res.stream);
+    if (wide_exchange) { launch_finish_thr_f16(topk, shift + q0, nq * k, 0, res.stream, k); }
+  }
   CERTEX_CUDA(cudaGetLastError());
   // thr now holds, per query, (a key of) a score k rows of this index certainly reach: other shards may tighten it
-  if (threshold_hook) { threshold_hook(threshold_hook_ctx, thr, nq, res.stream); }
+  if (wide_exchange) {
+    topk_hook(threshold_hook_ctx, topk, thr, nq, k, res.stream);
+  } else if (threshold_hook) {
+    threshold_hook(threshold_hook_ctx, thr, nq, res.stream);
+  }
   if (screen_kind_ == 2) { launch_finish_thr_f16(thr, shift + q0, nq, 1, res.stream); }
   CERTEX_CUDA(cudaGetLastError());
   // 3 screen over all rows, 4 exact scores of the candidates and the k best

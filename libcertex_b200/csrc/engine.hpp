@@ -188,6 +188,14 @@ class Index {
   using ThresholdHook = void (*)(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream);
   static thread_local ThresholdHook threshold_hook;
   static thread_local void* threshold_hook_ctx;
+  /// The wider exchange for small k (k <= kTopkExchangeMaxK), used instead of threshold_hook when set: the hook gets
+  /// the k largest keys of every query in this shard, topk [n, k], next to thr [n] (their k-th) and leaves in thr the
+  /// k-th largest key over the lists of all shards. Every key is reached by a row of its own shard, so that value is
+  /// reached by k rows of the whole set: the threshold a single index over all rows would find, where the maximum of
+  /// the shards' own thresholds is only as tight as the best shard's.
+  using TopkHook = void (*)(void* ctx, const int32_t* topk, int32_t* thr, int64_t n, int k, cudaStream_t stream);
+  static thread_local TopkHook topk_hook;
+  static constexpr int kTopkExchangeMaxK = 64;
   /// Whether an unfiltered search for k neighbours goes through the tensor-core screen (and calls the hook).
   bool will_screen(int k) const;
 

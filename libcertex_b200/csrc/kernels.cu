@@ -539,13 +539,13 @@ __global__ void encode_f16_queries_kernel(const uint8_t* queries, size_t qpitch,
 // k-th largest group maximum (see float_key in the screen kernel) -> the key of value - shift[q] / 2, a score that k
 // rows of this index certainly reach in exact arithmetic. Step 1: such a key -> float bits of the screen's
 // threshold, bound - shift[q] / 2. Both subtractions round down.
-__global__ void finish_thr_f16_kernel(int32_t* thr, const float* shift, int nq, int step)
+__global__ void finish_thr_f16_kernel(int32_t* thr, const float* shift, int nq, int step, int per)
 {
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
   if (q >= nq) { return; }
   const int32_t key = thr[q];
   const float v     = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
-  const float r     = __fadd_rd(v, -__fmul_ru(0.5f, shift[q]));
+  const float r     = __fadd_rd(v, -__fmul_ru(0.5f, shift[q / per]));
   const int32_t b   = __float_as_int(r);
   thr[q]            = step == 0 ? (b ^ ((b >> 31) & 0x7fffffff)) : b;
 }
@@ -580,6 +580,38 @@ __global__ void expand_records_kernel(const uint64_t* rec, const unsigned long l
       }
     }
   }
+}
+
+// Block per query: the k largest of gmax[q, 0:ng] given their k-th, thr[q]: the values above it, then copies of it.
+// (Which k of several equal values are meant does not matter to a threshold.)
+__global__ void collect_topk_kernel(const int32_t* gmax, int64_t ld, int ng, int k, const int32_t* thr, int32_t* topk)
+{
+  __shared__ int s_n;
+  const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
+  int32_t* out       = topk + static_cast<int64_t>(blockIdx.x) * k;
+  const int32_t t    = thr[blockIdx.x];
+  if (threadIdx.x == 0) { s_n = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng; i += blockDim.x) {
+    const int32_t v = row[i];
+    if (v > t) {
+      const int pos = atomicAdd(&s_n, 1);
+      if (pos < k) { out[pos] = v; }  // fewer than k values lie above the k-th largest
+    }
+  }
+  __syncthreads();
+  for (int i = min(s_n, k) + threadIdx.x; i < k; i += blockDim.x) { out[i] = t; }
+}
+
+// rows [q, 0 : n_parts * k] = the lists parts[p, q, 0:k] of every part side by side.
+__global__ void union_rows_kernel(const int32_t* parts, int n_parts, int nq, int k, int32_t* rows, int64_t ld)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int m     = n_parts * k;
+  if (i >= static_cast<int64_t>(nq) * m) { return; }
+  const int64_t q = i / m;
+  const int c     = static_cast<int>(i % m), part = c / k, j = c % k;
+  rows[q * ld + c] = parts[(static_cast<int64_t>(part) * nq + q) * k + j];
 }
 
 // Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk. The row is copied to
@@ -1561,10 +1593,26 @@ void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, in
   }
 }
 
-void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s)
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s, int per)
 {
   if (nq <= 0) { return; }
-  finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq, step);
+  finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq, step, per);
+}
+
+void launch_collect_topk(const int32_t* gmax, int64_t ld, int ng, int k, int nq, const int32_t* thr, int32_t* topk, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  collect_topk_kernel<<<nq, 256, 0, s>>>(gmax, ld, ng, k, thr, topk);
+}
+
+void launch_union_kth(const int32_t* parts, int n_parts, int nq, int k, int32_t* scratch, int32_t* thr, cudaStream_t s)
+{
+  if (nq <= 0) { return; }
+  const int m       = n_parts * k;
+  const int64_t ld  = (m + 7) / 8 * 8;
+  const int64_t tot = static_cast<int64_t>(nq) * m;
+  union_rows_kernel<<<static_cast<unsigned>((tot + 255) / 256), 256, 0, s>>>(parts, n_parts, nq, k, scratch, ld);
+  launch_kth_largest(scratch, ld, m, k, nq, thr, s);
 }
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s)

@@ -55,7 +55,7 @@ void launch_encode_f16_queries(const void* queries, size_t qpitch, int dtype, in
 
 /// thr [nq] of fp16 codes. step 0: float keys of the k-th largest group maxima -> keys of (value - shift / 2), scores
 /// that k rows certainly reach; step 1: such keys -> float bits of the screen's threshold (bound - shift / 2).
-void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s);
+void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, cudaStream_t s, int per = 1);
 
 void launch_fill_i32(int32_t* p, int64_t n, int32_t v, cudaStream_t s);
 
@@ -79,6 +79,14 @@ void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_co
 /// (at most ng); a negative length gives thr[q] = never.
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
                         const int32_t* ng_rows = nullptr, int32_t never = 0x7fffffff);
+
+/// topk [nq, k] = the k largest of gmax[q, 0:ng] (any order), given thr[q] = their k-th (launch_kth_largest).
+void launch_collect_topk(const int32_t* gmax, int64_t ld, int ng, int k, int nq, const int32_t* thr, int32_t* topk, cudaStream_t s);
+
+/// thr[q] = the k-th largest of the union of parts[p, q, 0:k], p < n_parts (lists of the k largest keys of every row
+/// shard: every key is reached by a row of its own, so the k-th largest of all of them is reached by k rows of the
+/// whole set). scratch: nq * round_up(n_parts * k, 8) ints.
+void launch_union_kth(const int32_t* parts, int n_parts, int nq, int k, int32_t* scratch, int32_t* thr, cudaStream_t s);
 
 /// order [n] = the partition entries by (label, norm): inside a label the rows sorted by their term e of the screen
 /// (stable: equal norms keep ascending ids). keys_in / keys_out: scratch of n; temp of label_norm_order_temp_bytes(n).

@@ -92,11 +92,14 @@ struct Comm {
   int64_t* recv = nullptr;  // [n_ranks, 2 nq k + 1]
   size_t send_words = 0;
   unsigned long long* host_status = nullptr;  // page-locked, [n_ranks]
+  int32_t* topk_recv = nullptr;               // [n_ranks, nq, k] keys of the threshold exchange, and the rows made of them
+  int32_t* topk_rows = nullptr;
+  size_t topk_ints   = 0;
   std::map<int, bool> all_screen;             // k -> every rank's search for k neighbours goes through the screen
   int64_t all_screen_size = -1;               // ... decided for this index size
   ~Comm()
   {
-    cudaFree(send), cudaFree(recv);
+    cudaFree(send), cudaFree(recv), cudaFree(topk_recv), cudaFree(topk_rows);
     if (host_status) { cudaFreeHost(host_status); }
     if (owned && comm) { nccl().CommDestroy(comm); }
   }
@@ -112,6 +115,24 @@ struct Comm {
 };
 
 namespace {
+
+void share_topk_hook(void* ctx, const int32_t* topk, int32_t* thr, int64_t n, int k, cudaStream_t stream)
+{
+  // every rank's k largest keys per query -> the k-th largest of all of them: k rows of the whole set reach it
+  auto* c           = static_cast<Comm*>(ctx);
+  const size_t mine = static_cast<size_t>(n) * k, rows = static_cast<size_t>(n) * ((static_cast<size_t>(c->n_ranks) * k + 7) / 8 * 8);
+  if (mine * c->n_ranks > c->topk_ints || rows > c->topk_ints) {
+    cudaFree(c->topk_recv), cudaFree(c->topk_rows);
+    c->topk_recv = c->topk_rows = nullptr, c->topk_ints = 0;
+    const size_t want = std::max(mine * c->n_ranks, rows);
+    CERTEX_CUDA(cudaMalloc(&c->topk_recv, want * 4));
+    CERTEX_CUDA(cudaMalloc(&c->topk_rows, want * 4));
+    c->topk_ints = want;
+  }
+  CERTEX_NCCL(nccl().AllGather(topk, c->topk_recv, mine, ncclInt32, c->comm, stream));
+  launch_union_kth(c->topk_recv, c->n_ranks, static_cast<int>(n), k, c->topk_rows, thr, stream);
+  CERTEX_CUDA(cudaGetLastError());
+}
 
 void share_thresholds_hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
 {
@@ -190,14 +211,16 @@ void distributed_search(const Resources& res, Comm& c, const Index& index, const
   Index::Pending* pending = nullptr;
   std::exception_ptr failed;
   try {
-    if (share_thresholds) { Index::threshold_hook = share_thresholds_hook, Index::threshold_hook_ctx = &c; }
+    if (share_thresholds) {
+      Index::threshold_hook = share_thresholds_hook, Index::topk_hook = share_topk_hook, Index::threshold_hook_ctx = &c;
+    }
     pending = index.search_begin(res, sp, queries, nq, k, send_ids, distances, send_scores, Filter{}, id_base, send_status);
-    Index::threshold_hook = nullptr, Index::threshold_hook_ctx = nullptr;
+    Index::threshold_hook = nullptr, Index::topk_hook = nullptr, Index::threshold_hook_ctx = nullptr;
   } catch (...) {
     // this rank cannot answer: it still takes part in the exchange, with empty lists and the failure in its status
     // word, so that no rank is left waiting in the collective (a rank that failed inside the threshold exchange cannot
     // be helped this way; NCCL's own timeout ends the others' wait)
-    Index::threshold_hook = nullptr, Index::threshold_hook_ctx = nullptr;
+    Index::threshold_hook = nullptr, Index::topk_hook = nullptr, Index::threshold_hook_ctx = nullptr;
     failed = std::current_exception();
     fail_lists();
   }

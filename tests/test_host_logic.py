@@ -109,3 +109,23 @@ def test_integer_cast_is_checked():
 
 def test_version():
     assert certex.__version__.count(".") == 2
+
+
+def test_both_bench_arms_name_the_same_configuration():
+    """The benchmark's own arm and its CPU reference arm must print one and the same `config` object."""
+    import argparse
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for gpus in (1, 2, 8):
+        args = argparse.Namespace(gpus=gpus, n_base=bench.N_BASE, n_queries=bench.N_QUERIES, batch=10240,
+                                  anchor_stride=16, searches_per_step=0, share_thresholds=1)
+        cfg = bench.config_of(args)
+        assert cfg == bench.config_of(args)
+        assert cfg["searches_per_step"] == (1 if gpus == 1 else 4)
+        assert cfg["share_thresholds"] == (gpus > 1)
+        assert f"{gpus} row shard(s)" in cfg["workload"] and "10000000x128 uint8" in cfg["workload"]

@@ -119,6 +119,21 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
         "        fidx = distributed.DistributedIndex(96, metric='cosine', share_thresholds=share, backend=backend).add(torch.from_numpy(xf))\n"
         "        D, I, S = fidx.search(torch.from_numpy(qf), k=20, return_scores=True)\n"
         "        assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores), (backend, share)\n"
+        "# the exchange of thresholds: for k <= 64 the shards pool their k largest group values, beyond that they take the\n"
+        "# maximum of their thresholds; either way exact, and fewer pairs survive the screens than without an exchange\n"
+        "xu = synthetic.mixture_u8(400000, seed=9).cpu().numpy(); qu = synthetic.mixture_u8(200, seed=10).cpu().numpy()\n"
+        "for k in (10, 100):\n"
+        "    ids, scores = oracle.knn(xu, qu, k, 'l2')\n"
+        "    kept = {}\n"
+        "    for share in (False, True):\n"
+        "        uidx = distributed.DistributedIndex(128, share_thresholds=share).add(torch.from_numpy(xu))\n"
+        "        with certex.search_stats() as st:\n"
+        "            D, I, S = uidx.search(torch.from_numpy(qu), k=k, return_scores=True)\n"
+        "        assert np.array_equal(I.cpu().numpy(), ids) and np.array_equal(S.cpu().numpy(), scores), (k, share)\n"
+        "        assert st.dense_queries == 0\n"
+        "        kept[share] = st.survivors\n"
+        "    assert kept[True] < kept[False], (k, kept)\n"
+        "    if k == 10: assert kept[True] < 0.8 * kept[False], kept\n"
         "# a rank whose local search fails (a host-side simulated allocation failure on rank 1, one query so that no\n"
         "# halving helps): every rank gets an error for the call instead of waiting, and the next call works\n"
         "idx = distributed.DistributedIndex(32).add(torch.from_numpy(x))\n"
