@@ -29,8 +29,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "exact 10-NN QPS, 10Mx128 u8"
-# DRAM bytes per (query panel x stored row) of a SCREEN launch: 14.89 GB measured by ncu over 12 panels x 10 M rows
-TRAFFIC_PER_PANEL_ROW = 14.89e9 / (12 * 10_000_000)
+# DRAM bytes per (query panel x stored row) of a SCREEN launch: 14.86 GB read + 0.013 GB written, measured by ncu over
+# 12 panels x 10 M rows
+TRAFFIC_PER_PANEL_ROW = 14.875e9 / (12 * 10_000_000)
 N_BASE, N_QUERIES, DIM, K = 10_000_000, 10_000, 128, 10
 
 

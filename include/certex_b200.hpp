@@ -365,4 +365,55 @@ void search(search_params const& params, sharded_index<T> const& idx, host_matri
   detail::check(certexB200ShardedSearch(&sp, idx.handle(), q.ptr(), nb.ptr(), ds.ptr()));
 }
 
+/// One process per GPU, one row shard per process: the ranks of a communicator answer a search together (local exact
+/// top-k, ncclAllGather of the lists, merge by (score, id); certexB200DistributedSearch). The reference's sharded search
+/// (certex_shards.hpp:39-60, 104-120) keeps its shards in one process; this is the same search for processes that each
+/// own a device. Movable, not copyable.
+class communicator {
+ public:
+  /// 128 bytes that one rank makes and the application sends to the others (an ncclUniqueId).
+  static std::vector<uint8_t> unique_id()
+  {
+    std::vector<uint8_t> id(128);
+    detail::check(certexB200CommGetUniqueId(id.data()));
+    return id;
+  }
+  /// Every rank, with its device current.
+  communicator(std::vector<uint8_t> const& id, int n_ranks, int rank)
+  {
+    if (id.size() != 128) { throw error("certex: a communicator id has 128 bytes"); }
+    detail::check(certexB200CommInitRank(id.data(), n_ranks, rank, &handle_));
+  }
+  /// Wraps an ncclComm_t that the application made and keeps.
+  explicit communicator(void* nccl_comm) { detail::check(certexB200CommAdopt(nccl_comm, &handle_)); }
+  ~communicator()
+  {
+    if (handle_) { certexB200CommDestroy(handle_); }
+  }
+  communicator(communicator&& o) noexcept : handle_(std::exchange(o.handle_, nullptr)) {}
+  communicator(const communicator&)            = delete;
+  communicator& operator=(const communicator&) = delete;
+  certexB200Comm_t handle() const { return handle_; }
+
+ private:
+  certexB200Comm_t handle_ = nullptr;
+};
+
+/// Every rank calls it with the same queries and k; `idx` holds the rank's rows, whose global ids start at first_id.
+/// The same merged answer arrives on every rank (device matrices, complete on return). share_thresholds: the ranks
+/// agree on thresholds between the anchor pass and the screen (the reference's first round, certex_shards.cu:136-141).
+template <typename T, typename U>
+void search(resources const& res, communicator const& comm, search_params const& params, index<T> const& idx,
+            int64_t first_id, device_matrix_view<U> queries, device_matrix_view<int64_t> neighbors,
+            device_matrix_view<float> distances, bool share_thresholds = true)
+{
+  static_assert(std::is_same_v<std::remove_cv_t<U>, T>, "the queries must have the element type of the index");
+  cuvsCertexSearchParams sp{params.anchors, params.batch_size, params.probe_lists};
+  detail::tensor q(queries.data, detail::dl_type<T>(), 2, queries.rows, queries.cols, false);
+  detail::tensor nb(neighbors.data, detail::dl_type<int64_t>(), 2, neighbors.rows, neighbors.cols, false);
+  detail::tensor ds(distances.data, detail::dl_type<float>(), 2, distances.rows, distances.cols, false);
+  detail::check(certexB200DistributedSearch(res.handle(), comm.handle(), &sp, idx.handle(), q.ptr(), nb.ptr(), ds.ptr(), nullptr,
+                                            first_id, share_thresholds ? 1 : 0));
+}
+
 }  // namespace certex_b200

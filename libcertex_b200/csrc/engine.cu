@@ -1305,8 +1305,12 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
     const int64_t nq_pad = round_up(nq, kQTile);
     uint8_t* qbuf        = scratch.get<uint8_t>(static_cast<size_t>(nq_pad) * code_pitch_);
     float* shift         = nullptr;
-    unsigned int* q_ovf  = scratch.get<unsigned int>(1);  // a query coordinate that does not fit fp16
-    CERTEX_CUDA(cudaMemsetAsync(q_ovf, 0, sizeof(unsigned int), res.stream));
+    // the call's counters in one block with the layout of HostCounters: one memset, one copy to the host
+    auto* counters         = scratch.get<HostCounters>(1);
+    unsigned int* d_count  = counters->count;  // [0] overflowed queries, [1] error code, [2] after the 2nd pass
+    auto* d_stats          = counters->stats;
+    unsigned int* q_ovf    = &counters->q_ovf;  // a query coordinate that does not fit fp16
+    CERTEX_CUDA(cudaMemsetAsync(counters, 0, sizeof(HostCounters), res.stream));
     if (screen_kind_ == 2) {
       shift = scratch.get<float>(static_cast<size_t>(nq));
       CERTEX_CUDA(cudaMemsetAsync(qbuf + static_cast<size_t>(nq) * code_pitch_, 0, static_cast<size_t>(nq_pad - nq) * code_pitch_, res.stream));
@@ -1320,10 +1324,6 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
     }
     int32_t* ovf_list      = scratch.get<int32_t>(static_cast<size_t>(nq));
     int32_t* thr2          = scratch.get<int32_t>(static_cast<size_t>(nq));  // tighter thresholds of the queries in ovf_list
-    unsigned int* d_count  = scratch.get<unsigned int>(4);  // [0] overflowed queries, [1] error code, [2] after the 2nd pass
-    auto* d_stats          = scratch.get<unsigned long long>(2);
-    CERTEX_CUDA(cudaMemsetAsync(d_count, 0, 4 * sizeof(unsigned int), res.stream));
-    CERTEX_CUDA(cudaMemsetAsync(d_stats, 0, 2 * sizeof(unsigned long long), res.stream));
     const int64_t batch = std::min<int64_t>(sp.batch_size, 32768);
     P.qbuf = qbuf, P.shift = shift, P.q_ovf = q_ovf, P.ovf_list = ovf_list, P.thr2 = thr2, P.d_count = d_count;
     P.d_stats = d_stats, P.batch = batch;
@@ -1336,9 +1336,7 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
     // The outputs are written now, as if no list had overflowed; the counters follow them to the host and search_end
     // looks at them once the caller has enqueued what it wanted behind the search.
     auto* host = static_cast<HostCounters*>(res.pinned_block());
-    CERTEX_CUDA(cudaMemcpyAsync(host->count, d_count, sizeof(host->count), cudaMemcpyDeviceToHost, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(host->stats, d_stats, sizeof(host->stats), cudaMemcpyDeviceToHost, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(&host->q_ovf, q_ovf, sizeof(host->q_ovf), cudaMemcpyDeviceToHost, res.stream));
+    CERTEX_CUDA(cudaMemcpyAsync(host, counters, sizeof(HostCounters), cudaMemcpyDeviceToHost, res.stream));
     if (status_out) {
       launch_search_status(d_count, q_ovf, status_out, res.stream);
       local.launches += 1;
