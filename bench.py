@@ -29,9 +29,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "exact 10-NN QPS, 10Mx128 u8"
-# DRAM bytes per (query panel x stored row) of a SCREEN launch: 14.86 GB read + 0.013 GB written, measured by ncu over
-# 12 panels x 10 M rows
-TRAFFIC_PER_PANEL_ROW = 14.875e9 / (12 * 10_000_000)
+# DRAM bytes per stored row of a SCREEN launch: 1.318 GB read + 0.018 GB written, measured by ncu over 10 M rows of 128
+# bytes and 10 000 queries (the launch passes every query panel over one chunk of rows while the chunk is in L2, so the
+# codes come from DRAM once)
+TRAFFIC_PER_ROW = 1.336e9 / 10_000_000
 N_BASE, N_QUERIES, DIM, K = 10_000_000, 10_000, 128, 10
 
 
@@ -338,8 +339,7 @@ def main():
         screen_s = st.screen_ms / 1000 / max(n_searches, 1)
         achieved = ops / screen_s / 1e12 if screen_s > 0 else None
         proxy = 2 * pk["bf16_burst"]
-        n_panels = -(-(-(-min(nq, args.batch) // 128)) // 7) * -(-nq // args.batch)  # query panels of 7 tiles, all batches
-        traffic = int(TRAFFIC_PER_PANEL_ROW * n_panels * shard_rows)
+        traffic = int(TRAFFIC_PER_ROW * shard_rows * -(-nq // args.batch))  # once per batch of queries
         line = {
             "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -360,9 +360,9 @@ def main():
                         "the int8 rate measured in this run directly before the timed region by the pass's own TMA + "
                         "tcgen05.mma stream without epilogue (M128 x N256 x K32, 2048 queries x 1 M rows, best of 5); "
                         f"peak_2x_bf16_burst = twice the {pk['source']} burst bf16 cuBLAS rate, for comparison only",
-                "traffic_note": "DRAM bytes of one SCREEN launch, scaled by query panels x rows from the ncu capture of "
-                                "the 10M x 128, 10000-query launch under profiles/ (codes are read once per query "
-                                "panel)",
+                "traffic_note": "DRAM bytes of one SCREEN launch, scaled by rows from the ncu capture of the 10M x 128, "
+                                "10000-query launch under profiles/ (codes are read from DRAM once per launch: all "
+                                "query panels pass over a chunk of rows while it is in L2)",
                 "screen_ms_per_search": st.screen_ms / n_searches, "anchor_ms_per_search": st.anchor_ms / n_searches,
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},

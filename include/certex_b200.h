@@ -311,6 +311,13 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ScreenTrace(void* trace, int32_t units)
 CERTEX_B200_EXPORT cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
                                                       int32_t grid, int32_t* out);
 
+/** Test hook (host only): the split that searches use, with the base tiles taken in chunks of chunk_tiles (0: one
+ *  chunk) so that a chunk's rows stay in L2 while every query panel passes over them. segs receives 4 ints per segment
+ *  (as above), *n_segs their number (at most cap_segs), seg_begin [grid + 1] the range of every CTA. */
+CERTEX_B200_EXPORT cuvsError_t certexB200PlanChunked(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
+                                                     int32_t grid, int32_t chunk_tiles, int32_t* segs, int32_t cap_segs,
+                                                     int32_t* n_segs, int32_t* seg_begin);
+
 /** Test hook (host only): the work split of a routed pass (searches by label). Run r pairs n_query_tiles[r] query
  *  tiles with its own n_base_tiles[r] base tiles; runs follow one another in both directions. segs receives 5 ints
  *  per segment (first query tile, query tiles <= panel_tiles, first base tile, end base tile, first base tile of the

@@ -114,7 +114,7 @@ SYMBOLS = [
     "certexB200SetThresholdHook", "certexB200IndexWillScreen", "certexB200PlanRouted",
     "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
     "certexB200CommGetUniqueId", "certexB200CommInitRank", "certexB200CommAdopt", "certexB200CommDestroy",
-    "certexB200DistributedSearch", "certexB200ScreenTrace",
+    "certexB200DistributedSearch", "certexB200ScreenTrace", "certexB200PlanChunked",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -178,6 +178,8 @@ def lib():
                     ctypes.c_uint32, P(ctypes.c_float),
                 ]
                 L.certexB200PlanSegments.argtypes = [ctypes.c_int32] * 4 + [P(ctypes.c_int32)]
+                L.certexB200PlanChunked.argtypes = [ctypes.c_int32] * 5 + [P(ctypes.c_int32), ctypes.c_int32,
+                                                                           P(ctypes.c_int32), P(ctypes.c_int32)]
                 L.certexB200PlanRouted.argtypes = [ctypes.c_int32, P(ctypes.c_int32), P(ctypes.c_int32), ctypes.c_int32,
                                                    ctypes.c_int32, ctypes.c_int32, P(ctypes.c_int32), ctypes.c_int32,
                                                    P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32)]

@@ -583,6 +583,14 @@ cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, 
   return translate([=] { plan_segments_flat(n_query_tiles, n_base_tiles, panel_tiles, grid, out); });
 }
 
+cuvsError_t certexB200PlanChunked(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles, int32_t grid,
+                                  int32_t chunk_tiles, int32_t* segs, int32_t cap_segs, int32_t* n_segs, int32_t* seg_begin)
+{
+  return translate([=] {
+    *n_segs = plan_chunked_flat(n_query_tiles, n_base_tiles, panel_tiles, grid, chunk_tiles, segs, cap_segs, seg_begin);
+  });
+}
+
 cuvsError_t certexB200PlanRouted(int32_t n_runs, const int32_t* n_query_tiles, const int32_t* n_base_tiles,
                                  int32_t panel_tiles, int32_t grid, int32_t max_segs, int32_t* segs, int32_t cap_segs,
                                  int32_t* n_segs, int32_t* seg_begin, int32_t* runs_done)

@@ -187,6 +187,43 @@ std::vector<ScreenSeg> plan_segments(int nqt, int nt, int panel_tiles, int grid)
   return segs;
 }
 
+/// The same split, but with the base tiles taken in chunks that stay in L2 while every query panel passes over them:
+/// all CTAs work on one chunk at a time (each on its share of the chunk's panel x tile items), then on the next. A
+/// stored row then comes from HBM once per pass instead of once per query panel; the price is a reload of the query
+/// panel per chunk and CTA. One list of segments with per-CTA ranges (ScreenArgs::seg_begin).
+struct ChunkedPlan {
+  std::vector<ScreenSeg> segs;
+  std::vector<int> begin;  // [grid + 1]
+};
+
+ChunkedPlan plan_chunked(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles)
+{
+  const int n_panels = nqt > 0 ? (nqt + panel_tiles - 1) / panel_tiles : 0;
+  if (n_panels <= 1 || chunk_tiles <= 0) { chunk_tiles = std::max(nt, 1); }  // one panel reads every tile once anyway
+  std::vector<std::vector<ScreenSeg>> per(static_cast<size_t>(grid));
+  for (int c0 = 0; c0 < nt; c0 += chunk_tiles) {
+    const int c1 = std::min(nt, c0 + chunk_tiles);
+    const std::vector<ScreenSeg> part = plan_segments(nqt, c1 - c0, panel_tiles, grid);
+    for (int b = 0; b < grid; ++b) {
+      for (int i = 0; i < kMaxSegs; ++i) {
+        const ScreenSeg& sg = part[static_cast<size_t>(b) * kMaxSegs + i];
+        if (sg.t1 > sg.t0) { per[static_cast<size_t>(b)].push_back(ScreenSeg{sg.q_tile0, sg.n_qtiles, sg.t0 + c0, sg.t1 + c0}); }
+      }
+    }
+  }
+  ChunkedPlan plan;
+  plan.begin.assign(1, 0);
+  for (int b = 0; b < grid; ++b) {
+    plan.segs.insert(plan.segs.end(), per[static_cast<size_t>(b)].begin(), per[static_cast<size_t>(b)].end());
+    plan.begin.push_back(static_cast<int>(plan.segs.size()));
+  }
+  if (plan.segs.empty()) { plan.segs.push_back(ScreenSeg{0, 0, 0, 0}); }  // something to allocate and copy
+  return plan;
+}
+
+/// Base tiles per chunk of plan_chunked: the chunk's code rows take about a quarter of the L2 (126 MB on B200).
+int chunk_tiles_for(size_t code_pitch) { return static_cast<int>(std::max<size_t>(64, (size_t(32) << 20) / (kTile * code_pitch))); }
+
 }  // namespace
 
 // ============================================================================================ Resources
@@ -611,9 +648,11 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
   uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
   auto* rec_count      = scratch.get<unsigned long long>(1);
-  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs);
-  const std::vector<ScreenSeg> seg_s = plan_segments(nqt, nt_all, shape.panel_tiles, grid);
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_s.data(), seg_s.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  const ChunkedPlan plan = plan_chunked(nqt, nt_all, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
+  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(plan.segs.size());
+  int* d_seg_begin     = scratch.get<int>(plan.begin.size());
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, plan.begin.data(), plan.begin.size() * sizeof(int), cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
   const size_t cp        = code_pitch_;
@@ -637,6 +676,7 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   a.rec_count   = rec_count;
   a.rec_cap     = rec_cap;
   a.segs        = d_segs;
+  a.seg_begin   = d_seg_begin;
   auto mark = [&] {
     if (events) {
       cudaEvent_t e;
@@ -686,10 +726,12 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
                                                       : static_cast<size_t>(nt_anchor) * kTile);
   int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
   int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
-  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(static_cast<size_t>(grid) * kMaxSegs);
-
-  const std::vector<ScreenSeg> seg_a = plan_segments(nqt, nt_anchor, shape.panel_tiles, grid);
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, seg_a.data(), seg_a.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  // an anchor tile is 256 rows spread over the whole set: chunks by bytes of anchor rows, as for the screen
+  const ChunkedPlan plan_a = plan_chunked(nqt, nt_anchor, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
+  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(plan_a.segs.size());
+  int* d_seg_begin     = scratch.get<int>(plan_a.begin.size());
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, plan_a.segs.data(), plan_a.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, plan_a.begin.data(), plan_a.begin.size() * sizeof(int), cudaMemcpyHostToDevice, res.stream));
   if (chained) {  // the smallest e of every chain of 16 adjacent anchors
     // anchor a = sorted row a * stride; chain i of tile t = anchors (i * nt_anchor + t) * 16 .. + 15
     launch_gather_chain_min(init_, anchor_stride, static_cast<int64_t>(nt_anchor) * kChainRows * anchor_stride,
@@ -724,6 +766,7 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   a.gmax    = gmax;
   a.ld_gmax = ld_g;
   a.segs    = d_segs;
+  a.seg_begin = d_seg_begin;
   auto mark = [&] {
     if (events) {
       cudaEvent_t e;
@@ -1776,6 +1819,17 @@ int plan_routed_flat(int n_runs, const int32_t* n_query_tiles, const int32_t* n_
   return static_cast<int>(done);
 }
 
+int plan_chunked_flat(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles, int32_t* segs_out, int cap_segs,
+                      int32_t* seg_begin)
+{
+  CERTEX_EXPECTS(nqt >= 1 && nt >= 1 && panel_tiles >= 1 && grid >= 1, "certex: sizes must be positive");
+  const ChunkedPlan plan = plan_chunked(nqt, nt, panel_tiles, grid, chunk_tiles);
+  CERTEX_EXPECTS(static_cast<int>(plan.segs.size()) <= cap_segs, "certex: more segments than the output holds");
+  std::memcpy(segs_out, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg));
+  for (int b = 0; b <= grid; ++b) { seg_begin[b] = plan.begin[static_cast<size_t>(b)]; }
+  return plan.begin.back();
+}
+
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out)
 {
   CERTEX_EXPECTS(nqt >= 1 && nt >= 1 && panel_tiles >= 1 && grid >= 1, "certex: sizes must be positive");
@@ -1794,10 +1848,12 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   const int grid          = res.sm_count;
   const int nqt           = static_cast<int>((nq + kQTile - 1) / kQTile);
   const int nt            = static_cast<int>((n + kTile - 1) / kTile);
-  const auto segs         = plan_segments(nqt, nt, shape.panel_tiles, grid);
-  ScreenSeg* d_segs       = scratch.get<ScreenSeg>(segs.size());
+  const ChunkedPlan plan  = plan_chunked(nqt, nt, shape.panel_tiles, grid, chunk_tiles_for(static_cast<size_t>(code_len)));
+  ScreenSeg* d_segs       = scratch.get<ScreenSeg>(plan.segs.size());
+  int* d_seg_begin        = scratch.get<int>(plan.begin.size());
   int* err                = scratch.get<int>(1);
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_segs, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, plan.begin.data(), plan.begin.size() * sizeof(int), cudaMemcpyHostToDevice, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(err, 0, sizeof(int), res.stream));
   const CUtensorMap tm_q = make_code_map(q_codes, code_len, static_cast<uint64_t>(round_up(nq, kQTile)), code_len, kQueryTile);
   CUtensorMap tm_x = make_code_map(x_codes, code_len, static_cast<uint64_t>(n), code_len, kBaseTile);
@@ -1862,6 +1918,7 @@ void screen_raw(const Resources& res, const void* q_codes, int64_t nq, const voi
   a.q_signed    = is_signed ? 1u : 0u;
   a.x_signed    = a.q_signed;
   a.segs        = d_segs;
+  a.seg_begin   = d_seg_begin;
   a.err         = err;
   cudaEvent_t e0, e1;
   CERTEX_CUDA(cudaEventCreate(&e0));

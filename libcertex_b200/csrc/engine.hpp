@@ -297,6 +297,12 @@ void distributed_search(const Resources& res, Comm& c, const Index& index, const
 /// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);
 
+/// The split the searches use: the same, with the base tiles taken in chunks of `chunk_tiles` (0: one chunk) that every
+/// query panel passes over while they are in L2. Segments of 4 ints each, CTA b owns [seg_begin[b], seg_begin[b + 1]);
+/// returns their number.
+int plan_chunked_flat(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles, int32_t* segs_out, int cap_segs,
+                      int32_t* seg_begin);
+
 /// Host-side work split of a routed pass (searches by label): run r pairs n_query_tiles[r] query tiles with its own
 /// n_base_tiles[r] base tiles (runs are laid out one after the other in both directions). Writes the segments (5 ints
 /// each: first query tile, query tiles, first base tile, end base tile, first base tile of the run), their number and

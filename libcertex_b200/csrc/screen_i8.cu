@@ -67,7 +67,6 @@ constexpr int kRecBuf     = 64;                // staged survivor records per ep
 constexpr int kWideStage  = 2 * kQTileBytes + kBTileBytes;  // WIDE: one K block of two query tiles and a base tile
 constexpr int kWideStages = 3;
 constexpr int kERing      = 4;                 // WIDE: tiles whose e values may be in flight
-constexpr int kSharedSegs = 64;                // segments of a CTA (a CTA is never given more)
 #ifndef CERTEX_SPLIT_EPILOGUE
 #define CERTEX_SPLIT_EPILOGUE 1
 #endif
@@ -102,7 +101,6 @@ struct SharedCtl {
   uint32_t tmem_base;
   int abort_flag;
   int rec_n[kEpiWarps];         // fill counts of the warps' record staging buffers
-  ScreenSeg segs[kSharedSegs];
 };
 
 __device__ __forceinline__ int max3(int a, int b, int c) { return __vimax3_s32(a, b, c); }
@@ -220,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   const int* seg_step    = p.seg_step ? p.seg_step + seg_first : nullptr;  // GROUPMAX over a strided sample of tiles
   int nseg               = 0;
   if (p.seg_begin) {
-    nseg = min(p.seg_begin[blockIdx.x + 1] - seg_first, kSharedSegs);
+    nseg = p.seg_begin[blockIdx.x + 1] - seg_first;
   } else {
     while (nseg < kMaxSegs && gsegs[nseg].t1 > gsegs[nseg].t0) { ++nseg; }
   }
@@ -248,8 +246,8 @@ __global__ void __launch_bounds__(kThreads, 1) screen_i8_kernel(const __grid_con
   constexpr bool kChainE   = MODE == kModeScreen || MODE == kModeGroupBound;    // e enters per chain of 16 columns (p.cmax)
   constexpr bool kStageE   = kNeedE && !WIDE;          // resident panel: e travels with the stage; WIDE: in its own ring
 
-  const ScreenSeg* segs = ctl->segs;
-  if (threadIdx.x < nseg) { ctl->segs[threadIdx.x] = gsegs[threadIdx.x]; }
+  // every role walks the CTA's segment list in global memory (a segment is hundreds of units long: the read is nothing)
+  const ScreenSeg* segs = gsegs;
   if (threadIdx.x == 0) {
     for (int i = 0; i < ns; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);

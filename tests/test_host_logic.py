@@ -129,3 +129,35 @@ def test_both_bench_arms_name_the_same_configuration():
         assert cfg["searches_per_step"] == (1 if gpus == 1 else 4)
         assert cfg["share_thresholds"] == (gpus > 1)
         assert f"{gpus} row shard(s)" in cfg["workload"] and "10000000x128 uint8" in cfg["workload"]
+
+
+@pytest.mark.parametrize("nqt,nt,panel,grid,chunk", [(79, 39063, 7, 148, 1024), (79, 4883, 7, 148, 1024), (16, 3907, 7, 148, 1024),
+                                                     (3, 47, 7, 148, 16), (1, 500, 7, 148, 64), (33, 1234, 2, 7, 100),
+                                                     (79, 2441, 7, 148, 0)])
+def test_chunked_plan_covers_every_unit_once_chunk_by_chunk(built_library, nqt, nt, panel, grid, chunk):
+    cap = 4 * grid * (nt // max(chunk, 1) + 2)
+    segs = (ctypes.c_int32 * (4 * cap))()
+    begin = (ctypes.c_int32 * (grid + 1))()
+    n = ctypes.c_int32()
+    assert built_library.certexB200PlanChunked(nqt, nt, panel, grid, chunk, segs, cap, ctypes.byref(n), begin) == 1
+    segs = np.frombuffer(segs, dtype=np.int32).reshape(-1, 4)[: n.value]
+    begin = np.frombuffer(begin, dtype=np.int32)
+    assert begin[0] == 0 and begin[-1] == n.value and (np.diff(begin) >= 0).all()
+    cover = np.zeros((nqt, nt), dtype=np.int32)
+    n_panels = -(-nqt // panel)
+    step = chunk if (chunk > 0 and n_panels > 1) else nt
+    for b in range(grid):
+        last_chunk = -1
+        for q0, nq_, t0, t1 in segs[begin[b] : begin[b + 1]]:
+            assert 1 <= nq_ <= panel and q0 >= 0 and q0 + nq_ <= nqt and 0 <= t0 < t1 <= nt
+            assert t0 // step == (t1 - 1) // step, "a segment stays inside one chunk"
+            assert t0 // step >= last_chunk, "a CTA takes the chunks in order"
+            last_chunk = t0 // step
+            cover[q0 : q0 + nq_, t0:t1] += 1
+    assert (cover == 1).all()
+    # inside every chunk the CTAs get about the same number of units
+    for c0 in range(0, nt, step):
+        c1 = min(nt, c0 + step)
+        units = [sum(nq_ * (min(t1, c1) - max(t0, c0)) for _, nq_, t0, t1 in segs[begin[b] : begin[b + 1]] if t0 < c1 and t1 > c0)
+                 for b in range(grid)]
+        assert max(units) - nqt * (c1 - c0) / grid <= panel
