@@ -364,6 +364,9 @@ def main():
                                 "10000-query launch under profiles/ (codes are read from DRAM once per launch: all "
                                 "query panels pass over a chunk of rows while it is in L2)",
                 "screen_ms_per_search": st.screen_ms / n_searches, "anchor_ms_per_search": st.anchor_ms / n_searches,
+                # device time from the first to the last operation of a search on rank 0 (before the exchange of the
+                # shards' lists at N > 1): ms_per_step / searches_per_step minus this is device time not spent in the search
+                "span_ms_per_search": st.span_ms / n_searches,
             },
             "stats": {"survivors_per_query": st.survivors / max(st.queries, 1), "dense_queries": st.dense_queries},
         }

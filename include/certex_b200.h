@@ -249,7 +249,8 @@ CERTEX_B200_EXPORT cuvsError_t certexB200IndexReserve(cuvsResources_t res, cuvsC
  *  time in microseconds of the screen passes and of the anchor (group-maximum) passes, measured with CUDA events on
  *  the launching stream; out[7] = number of screen passes; out[8] = queries whose candidate list overflowed and that
  *  were screened a second time with a tighter threshold; out[9] = query slots of searches by label that went through
- *  the routed screen (a label's queries fill whole tiles of 128 slots); out[10..15] = 0, reserved. */
+ *  the routed screen (a label's queries fill whole tiles of 128 slots); out[10] = device time in microseconds from
+ *  the first to the last operation the screened searches enqueued; out[11..15] = 0, reserved. */
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsBegin(void);
 CERTEX_B200_EXPORT cuvsError_t certexB200StatsEnd(uint64_t out[16]);
 

@@ -525,7 +525,8 @@ cuvsError_t certexB200StatsEnd(uint64_t out[16])
     out[7] = g_stats.screen_passes;
     out[8] = g_stats.rescreened;
     out[9] = g_stats.routed_queries;
-    for (int i = 10; i < 16; ++i) { out[i] = 0; }
+    out[10] = static_cast<uint64_t>(g_stats.span_ms * 1000.0);
+    for (int i = 11; i < 16; ++i) { out[i] = 0; }
   });
 }
 

@@ -1282,11 +1282,13 @@ struct Index::Pending {
   unsigned long long* d_stats = nullptr;
   std::vector<cudaEvent_t> events;
   cudaEvent_t ready = nullptr;
+  cudaEvent_t first = nullptr;  // with statistics on: before the first operation of a screened search (ready then keeps time)
   Pending(const Resources& r, std::shared_mutex& m) : res(&r), lock(m), scratch(r.stream) {}
   ~Pending()
   {
     for (cudaEvent_t e : events) { cudaEventDestroy(e); }
     if (ready) { cudaEventDestroy(ready); }
+    if (first) { cudaEventDestroy(first); }
     res->search_in_flight_ = false;
   }
 };
@@ -1353,6 +1355,10 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
     unsigned int* d_count  = counters->count;  // [0] overflowed queries, [1] error code, [2] after the 2nd pass
     auto* d_stats          = counters->stats;
     unsigned int* q_ovf    = &counters->q_ovf;  // a query coordinate that does not fit fp16
+    if (stats_sink) {
+      CERTEX_CUDA(cudaEventCreate(&P.first));
+      CERTEX_CUDA(cudaEventRecord(P.first, res.stream));
+    }
     CERTEX_CUDA(cudaMemsetAsync(counters, 0, sizeof(HostCounters), res.stream));
     if (screen_kind_ == 2) {
       shift = scratch.get<float>(static_cast<size_t>(nq));
@@ -1396,7 +1402,7 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
   CERTEX_CUDA(cudaGetLastError());
   local.launches += 1;  // finish
   if (P.screened) {
-    CERTEX_CUDA(cudaEventCreateWithFlags(&P.ready, cudaEventDisableTiming));
+    CERTEX_CUDA(cudaEventCreateWithFlags(&P.ready, P.first ? cudaEventDefault : cudaEventDisableTiming));
     CERTEX_CUDA(cudaEventRecord(P.ready, res.stream));
   }
   return pending.release();
@@ -1413,6 +1419,11 @@ bool Index::search_end(Pending* raw) const
   if (P.screened && P.nq > 0) {
     CERTEX_CUDA(cudaEventSynchronize(P.ready));  // the one host round trip of a search call
     const HostCounters h = *static_cast<const HostCounters*>(res.pinned_block());
+    if (P.first) {
+      float ms = 0;
+      cudaEventElapsedTime(&ms, P.first, P.ready);
+      local.span_ms += ms;
+    }
     auto add_times = [&](size_t per_pass) {
       for (size_t e = 0; e + per_pass - 1 < P.events.size(); e += per_pass) {
         float ms = 0;
@@ -1494,6 +1505,7 @@ bool Index::search_end(Pending* raw) const
     stats_sink->launches += local.launches;
     stats_sink->screen_ms += local.screen_ms;
     stats_sink->anchor_ms += local.anchor_ms;
+    stats_sink->span_ms += local.span_ms;
     stats_sink->screen_passes += local.screen_passes;
     stats_sink->queries += local.queries;
     stats_sink->survivors += local.survivors;

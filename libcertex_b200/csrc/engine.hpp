@@ -96,6 +96,7 @@ struct SearchStats {
   unsigned long long queries = 0, survivors = 0, verified = 0, dense_queries = 0;
   unsigned long long launches = 0;     // kernels of this library launched by the searches
   double screen_ms = 0, anchor_ms = 0; // device time of the SCREEN and GROUPMAX tensor-core passes (CUDA events)
+  double span_ms = 0;                  // device time from the first to the last operation a screened search enqueued
   unsigned long long screen_passes = 0;
   unsigned long long rescreened = 0;   // queries screened a second time with a tighter threshold
   unsigned long long routed_queries = 0;  // query slots of searches by label that went through the routed screen

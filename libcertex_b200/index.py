@@ -77,13 +77,15 @@ class search_stats:
     verified (exact scores computed), dense_queries (queries answered without the screen), rescreened (queries screened
     a second time with a tighter threshold), routed_queries (query slots of searches by label screened against their
     label's rows), launches (kernels of the library), and the device time of the tensor-core
-    passes: screen_ms, anchor_ms over screen_passes passes."""
+    passes: screen_ms, anchor_ms over screen_passes passes, and span_ms, the device time from the first to the last
+    operation the screened searches enqueued (what it exceeds the passes by is small kernels and gaps between kernels;
+    what a caller's own clock exceeds it by is time the device waited for the host)."""
 
     def __enter__(self):
         L.check(L.lib().certexB200StatsBegin())
         self.queries = self.survivors = self.verified = self.dense_queries = 0
         self.launches = self.screen_passes = self.rescreened = self.routed_queries = 0
-        self.screen_ms = self.anchor_ms = 0.0
+        self.screen_ms = self.anchor_ms = self.span_ms = 0.0
         return self
 
     def __exit__(self, *exc):
@@ -92,7 +94,7 @@ class search_stats:
         L.check(L.lib().certexB200StatsEnd(out))
         self.queries, self.survivors, self.verified, self.dense_queries, self.launches = (int(v) for v in out[:5])
         self.screen_ms, self.anchor_ms, self.screen_passes = out[5] / 1000.0, out[6] / 1000.0, int(out[7])
-        self.rescreened, self.routed_queries = int(out[8]), int(out[9])
+        self.rescreened, self.routed_queries, self.span_ms = int(out[8]), int(out[9]), out[10] / 1000.0
         return False
 
 
