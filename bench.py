@@ -110,6 +110,9 @@ def config_of(args):
                     f"{args.n_queries} queries, k={K}, L2, {args.gpus} row shard(s)",
         "batch": args.batch, "anchor_stride": args.anchor_stride, "searches_per_step": per_step,
         "share_thresholds": bool(args.share_thresholds) and args.gpus > 1,
+        # searches of a step that are between search_begin and search_end at once (the host prepares one while the
+        # device works on the other); every search is complete and checked like the others
+        "searches_in_flight": max(1, min(args.pipeline, 2)) if args.gpus > 1 else 1,
         "l2_policy": "inputs exceed L2: every step streams the whole shard (>= 160 MB) from HBM",
     }
 
@@ -209,6 +212,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--searches-per-step", type=int, default=0,
                     help="searches of all queries per step (default: 1 on one GPU, 4 on several)")
+    ap.add_argument("--pipeline", type=int, default=2,
+                    help="N > 1: searches of a step between search_begin and search_end at once (1 or 2)")
     ap.add_argument("--parity-queries", type=int, default=16, help="queries checked against the CPU oracle at N > 1")
     ap.add_argument("--share-thresholds", type=int, default=1,
                     help="N > 1: the shards screen with the tightest threshold any of them found (one all-reduce per "
@@ -247,6 +252,26 @@ def main():
         index = certex.Index(DIM, anchor_stride=args.anchor_stride)
         index.add(xb)
     search = lambda q, **kw: index.search(q, k=K, batch=args.batch, **kw)  # noqa: E731
+    depth = max(1, min(args.pipeline, 2)) if world > 1 else 1
+
+    def run_step(make_queries, done):
+        """One step: per_step searches. On several GPUs up to `depth` of them are between search_begin and search_end,
+        so that the host prepares a search while the device works on the one before; done(answer) takes every answer."""
+        if depth == 1:
+            for _ in range(per_step):
+                out = search(make_queries())
+                done(out)
+            return out
+        tickets = []
+        for _ in range(per_step):
+            tickets.append(index.search_begin(make_queries(), k=K, batch=args.batch))
+            if len(tickets) == depth:
+                out = index.search_end(tickets.pop(0))
+                done(out)
+        while tickets:
+            out = index.search_end(tickets.pop(0))
+            done(out)
+        return out
     del xb
     torch.cuda.synchronize()
     i8_peak = measure_i8_peak() if rank == 0 else None  # a few ms of the screen's own MMA stream, before the timed region
@@ -262,7 +287,7 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        for _ in range(steps * per_step):
+        for _ in range(steps):
             out = fn()
         e1.record()
         barrier()
@@ -272,12 +297,12 @@ def main():
         return float(ms.item()), out
 
     # ---- device-resident inputs
-    for _ in range(args.warmup * per_step):
-        search(xq)
+    for _ in range(args.warmup):
+        run_step(lambda: xq, lambda out: None)
     sampler = ClockSampler(local)
     sampler.start()
     with certex.search_stats() as st:
-        ms, (D, I) = timed(lambda: search(xq), args.steps)
+        ms, (D, I) = timed(lambda: run_step(lambda: xq, lambda out: None), args.steps)
     clocks = sampler.stop()
     n_searches = args.steps * per_step
     qps = nq * n_searches / (ms / 1000)
@@ -288,12 +313,12 @@ def main():
     hI = torch.empty((nq, K), dtype=torch.int64).pin_memory()
     hD = torch.empty((nq, K), dtype=torch.float32).pin_memory()
 
+    def copy_back(out):
+        hI.copy_(out[1], non_blocking=True)
+        hD.copy_(out[0], non_blocking=True)
+
     def e2e_step():
-        dq = hq.to("cuda", non_blocking=True)
-        d, i = search(dq)
-        hI.copy_(i, non_blocking=True)
-        hD.copy_(d, non_blocking=True)
-        return d, i
+        return run_step(lambda: hq.to("cuda", non_blocking=True), copy_back)
 
     for _ in range(2):
         e2e_step()

@@ -396,15 +396,32 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ShardedSearch(cuvsCertexSearchParams_t 
  * certexB200DistributedSearch: called by every rank with the same queries (device, [nq, dim]), k, parameters and
  * share_thresholds; `index` is the rank's shard and id_base the global id of its first row; neighbors / distances /
  * scores (scores may be NULL) are device [nq, k] and receive the same merged answer on every rank. Every shard must
- * hold at least k vectors. share_thresholds != 0 adds the reference's first round (certex_shards.cu:136-141) as one
- * ncclAllReduce(max) over the per-query threshold keys of every batch. The call waits for its stream once, at its end.
+ * hold at least k vectors. share_thresholds != 0 adds the reference's first round (certex_shards.cu:136-141), on the
+ * stream, once per batch of queries: for k <= 64 one ncclAllGather of every rank's k best threshold candidates per
+ * query, of which each rank takes the k-th best (what one index over all rows would screen with); for larger k one
+ * ncclAllReduce(max) over the ranks' own thresholds. The call waits for its stream once, at its end.
  * If the local search of a rank fails, every rank returns CUVS_ERROR for the call.
+ * certexB200DistributedSearchBegin / End are the same search in two calls, for callers that keep the device busy
+ * across searches: Begin enqueues the local search, the exchange and the merge on the resources' stream and returns
+ * without waiting; End waits for that search only (not for work enqueued behind it) and, if a candidate list had
+ * overflowed on some rank, runs the repair and a second exchange. The outputs are final when End has returned
+ * CUVS_SUCCESS. Up to two searches may be between their Begin and End per communicator; they End in the order they
+ * Began, every rank makes the same sequence of calls, and queries and outputs stay valid and untouched from Begin to
+ * End. A Begin that returned CUVS_ERROR left nothing to End (*pending is NULL).
  */
 typedef struct certexB200Comm* certexB200Comm_t;
 CERTEX_B200_EXPORT cuvsError_t certexB200CommGetUniqueId(void* id /* 128 bytes */);
 CERTEX_B200_EXPORT cuvsError_t certexB200CommInitRank(const void* id, int32_t n_ranks, int32_t rank, certexB200Comm_t* comm);
 CERTEX_B200_EXPORT cuvsError_t certexB200CommAdopt(void* nccl_comm /* ncclComm_t */, certexB200Comm_t* comm);
 CERTEX_B200_EXPORT cuvsError_t certexB200CommDestroy(certexB200Comm_t comm);
+typedef struct certexB200PendingSearch* certexB200PendingSearch_t;
+CERTEX_B200_EXPORT cuvsError_t certexB200DistributedSearchBegin(cuvsResources_t res, certexB200Comm_t comm,
+                                                                cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
+                                                                DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                                                DLManagedTensor* distances, DLManagedTensor* scores,
+                                                                int64_t id_base, int32_t share_thresholds,
+                                                                certexB200PendingSearch_t* pending);
+CERTEX_B200_EXPORT cuvsError_t certexB200DistributedSearchEnd(certexB200PendingSearch_t pending);
 CERTEX_B200_EXPORT cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t comm,
                                                            cuvsCertexSearchParams_t params, cuvsCertexIndex_t index,
                                                            DLManagedTensor* queries, DLManagedTensor* neighbors,

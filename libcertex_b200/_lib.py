@@ -115,6 +115,7 @@ SYMBOLS = [
     "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
     "certexB200CommGetUniqueId", "certexB200CommInitRank", "certexB200CommAdopt", "certexB200CommDestroy",
     "certexB200DistributedSearch", "certexB200ScreenTrace", "certexB200PlanChunked",
+    "certexB200DistributedSearchBegin", "certexB200DistributedSearchEnd",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -193,6 +194,9 @@ def lib():
                 L.certexB200CommDestroy.argtypes = [vp]
                 L.certexB200DistributedSearch.argtypes = [vp, vp, P(SearchParams), P(IndexHandle), mt, mt, mt, mt, i64,
                                                           ctypes.c_int32]
+                L.certexB200DistributedSearchBegin.argtypes = [vp, vp, P(SearchParams), P(IndexHandle), mt, mt, mt, mt, i64,
+                                                               ctypes.c_int32, P(vp)]
+                L.certexB200DistributedSearchEnd.argtypes = [vp]
                 L.certexB200ScreenTrace.argtypes = [vp, ctypes.c_int32]
                 L.certexB200SearchStatic.argtypes = [vp, ctypes.c_int, DLDataType, vp, i64, vp, i64, i64, ctypes.c_int32, vp, vp]
                 _lib = L

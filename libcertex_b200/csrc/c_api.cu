@@ -756,14 +756,16 @@ cuvsError_t certexB200CommDestroy(certexB200Comm_t comm)
   return translate([=] { comm_destroy(reinterpret_cast<Comm*>(comm)); });
 }
 
-cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t comm, cuvsCertexSearchParams_t params,
-                                        cuvsCertexIndex_t index, DLManagedTensor* queries, DLManagedTensor* neighbors,
-                                        DLManagedTensor* distances, DLManagedTensor* scores, int64_t id_base,
-                                        int32_t share_thresholds)
+cuvsError_t certexB200DistributedSearchBegin(cuvsResources_t res, certexB200Comm_t comm, cuvsCertexSearchParams_t params,
+                                             cuvsCertexIndex_t index, DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                             DLManagedTensor* distances, DLManagedTensor* scores, int64_t id_base,
+                                             int32_t share_thresholds, certexB200PendingSearch_t* pending)
 {
   return translate([=] {
     Resources& r = as_res(res);
     Holder& h    = as_holder(index);
+    CERTEX_EXPECTS(pending != nullptr, "certex: null pending search");
+    *pending = nullptr;
     CERTEX_EXPECTS(comm != nullptr, "certex: null communicator");
     CERTEX_EXPECTS(params != nullptr, "certex: null search parameters");
     CERTEX_EXPECTS(queries != nullptr && queries->dl_tensor.dtype.code == index->dtype.code &&
@@ -788,9 +790,30 @@ cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t co
     sp.anchors     = params->anchors;
     sp.batch_size  = params->batch_size;
     sp.probe_lists = params->probe_lists;
-    distributed_search(r, *reinterpret_cast<Comm*>(comm), *h.index, sp, q, nq, static_cast<int>(k), nb, ds, sc, id_base,
-                       share_thresholds != 0);
+    *pending = reinterpret_cast<certexB200PendingSearch_t>(distributed_search_begin(
+      r, *reinterpret_cast<Comm*>(comm), *h.index, sp, q, nq, static_cast<int>(k), nb, ds, sc, id_base, share_thresholds != 0));
   });
+}
+
+cuvsError_t certexB200DistributedSearchEnd(certexB200PendingSearch_t pending)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(pending != nullptr, "certex: null pending search");
+    distributed_search_end(reinterpret_cast<DistributedPending*>(pending));
+  });
+}
+
+cuvsError_t certexB200DistributedSearch(cuvsResources_t res, certexB200Comm_t comm, cuvsCertexSearchParams_t params,
+                                        cuvsCertexIndex_t index, DLManagedTensor* queries, DLManagedTensor* neighbors,
+                                        DLManagedTensor* distances, DLManagedTensor* scores, int64_t id_base,
+                                        int32_t share_thresholds)
+{
+  certexB200PendingSearch_t pending = nullptr;
+  if (certexB200DistributedSearchBegin(res, comm, params, index, queries, neighbors, distances, scores, id_base, share_thresholds,
+                                       &pending) != CUVS_SUCCESS) {
+    return CUVS_ERROR;
+  }
+  return certexB200DistributedSearchEnd(pending);
 }
 
 const char* certexB200Version(void) { return "0.2.0"; }

@@ -222,6 +222,15 @@ ChunkedPlan plan_chunked(int nqt, int nt, int panel_tiles, int grid, int chunk_t
 }
 
 /// Base tiles per chunk of plan_chunked: the chunk's code rows take about a quarter of the L2 (126 MB on B200).
+/// A plan in the call's scratch memory, copied on the call's stream (from pageable memory: the host waits for the stream).
+void upload_plan(Scratch& scratch, const ChunkedPlan& plan, ScreenSeg*& segs, int*& begin)
+{
+  segs  = scratch.get<ScreenSeg>(plan.segs.size());
+  begin = scratch.get<int>(plan.begin.size());
+  CERTEX_CUDA(cudaMemcpyAsync(segs, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, scratch.stream));
+  CERTEX_CUDA(cudaMemcpyAsync(begin, plan.begin.data(), plan.begin.size() * sizeof(int), cudaMemcpyHostToDevice, scratch.stream));
+}
+
 int chunk_tiles_for(size_t code_pitch) { return static_cast<int>(std::max<size_t>(64, (size_t(32) << 20) / (kTile * code_pitch))); }
 
 }  // namespace
@@ -248,10 +257,10 @@ Resources::~Resources()
 
 void Resources::sync() const { CERTEX_CUDA(cudaStreamSynchronize(stream)); }
 
-void* Resources::pinned_block() const
+void* Resources::pinned_block(int slot) const
 {
-  if (!pinned_) { CERTEX_CUDA(cudaHostAlloc(&pinned_, 256, cudaHostAllocDefault)); }
-  return pinned_;
+  if (!pinned_) { CERTEX_CUDA(cudaHostAlloc(&pinned_, 256 * kPinnedSlots, cudaHostAllocDefault)); }
+  return static_cast<unsigned char*>(pinned_) + 256 * (slot % kPinnedSlots);
 }
 
 // ============================================================================================ Index
@@ -327,6 +336,32 @@ Index::~Index()
   cudaFree(init_);
   cudaFree(cmax_);
   cudaFree(maxima_);
+  for (auto& kv : plans_) { cudaFree(kv.second.segs), cudaFree(kv.second.begin); }
+}
+
+Index::DevicePlan Index::device_plan(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles) const
+{
+  const std::array<int, 5> key{nqt, nt, panel_tiles, grid, chunk_tiles};
+  std::lock_guard<std::mutex> lock(plans_mutex_);
+  auto it = plans_.find(key);
+  if (it != plans_.end()) { return it->second; }
+  DevicePlan d;
+  if (plans_.size() >= kMaxPlans) { return d; }  // shapes keep changing (an index that grows between searches): not kept
+  const ChunkedPlan plan = plan_chunked(nqt, nt, panel_tiles, grid, chunk_tiles);
+  CERTEX_CUDA(cudaMalloc(&d.segs, std::max<size_t>(plan.segs.size(), 1) * sizeof(ScreenSeg)));
+  if (cudaMalloc(&d.begin, plan.begin.size() * sizeof(int)) != cudaSuccess) {
+    cudaFree(d.segs);
+    throw Error("certex: out of device memory for a work split");
+  }
+  // blocking copies: the plan is complete before any stream of any thread can be given it
+  cudaError_t e = cudaMemcpy(d.segs, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) { e = cudaMemcpy(d.begin, plan.begin.data(), plan.begin.size() * sizeof(int), cudaMemcpyHostToDevice); }
+  if (e != cudaSuccess) {
+    cudaFree(d.segs), cudaFree(d.begin);
+    CERTEX_CUDA(e);
+  }
+  plans_[key] = d;
+  return d;
 }
 
 void Index::reserve(const Resources& res, int64_t n)
@@ -373,7 +408,7 @@ void Index::reserve(const Resources& res, int64_t n)
   res.sync();
   void* old[8] = {vectors_, removed_, labels_, codes_, perm_, inv_, init_, cmax_};
   {
-    std::unique_lock<std::shared_mutex> lock(rw_);  // waits for running searches, which read the old arrays
+    std::unique_lock<ReaderGate> lock(rw_);  // waits for running searches, which read the old arrays
     vectors_ = v;
     removed_ = r;
     if (l) { labels_ = l; }
@@ -402,7 +437,7 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
     CERTEX_CUDA(cudaMemcpy2DAsync(dst, pitch_, rows, row_bytes, row_bytes, static_cast<size_t>(n), kind, res.stream));
   }
   if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
-  std::unique_lock<std::shared_mutex> lock(rw_, std::defer_lock);
+  std::unique_lock<ReaderGate> lock(rw_, std::defer_lock);
   if (screen_kind_) {
     // The batch goes into sorted rows [size, size + n), ordered by squared norm; rows beyond the published size are
     // invisible to running searches, which bound tiles and candidates by their own size. With the L2 metric small
@@ -479,7 +514,7 @@ void Index::remove(const Resources& res, const int64_t* ids_device, int64_t n_id
   unsigned long long n_new = 0;
   CERTEX_CUDA(cudaMemcpyAsync(&n_new, counter, sizeof(n_new), cudaMemcpyDeviceToHost, res.stream));
   res.sync();
-  std::unique_lock<std::shared_mutex> lock(rw_);
+  std::unique_lock<ReaderGate> lock(rw_);
   n_removed_ += static_cast<int64_t>(n_new);
 }
 
@@ -492,14 +527,14 @@ void Index::set_labels(const Resources& res, const int32_t* labels_device, int64
     CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(std::max<int64_t>(capacity_, 1)) * 4));
     CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(std::max<int64_t>(capacity_, 1)) * 4, res.stream));
     res.sync();
-    std::unique_lock<std::shared_mutex> lock(rw_);
+    std::unique_lock<ReaderGate> lock(rw_);
     labels_ = l;
   }
   if (n > 0) {
     CERTEX_CUDA(cudaMemcpyAsync(labels_ + first, labels_device, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, res.stream));
   }
   res.sync();
-  std::unique_lock<std::shared_mutex> lock(rw_);
+  std::unique_lock<ReaderGate> lock(rw_);
   has_labels_ = true;
   if (first < n_part_ && n > 0) { n_part_ = 0; }  // labels of partitioned rows changed: the partition is void
 }
@@ -591,7 +626,7 @@ void Index::partition_by_labels(const Resources& res)
   }
   void* old[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   {
-    std::unique_lock<std::shared_mutex> lock(rw_);
+    std::unique_lock<ReaderGate> lock(rw_);
     old[0] = part_ids_, old[1] = lcodes_, old[2] = linit_, old[3] = lcmax_, old[4] = lperm_, old[5] = linv_;
     part_ids_     = ids;
     n_part_       = n;
@@ -648,11 +683,10 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   int32_t* cand        = scratch.get<int32_t>(static_cast<size_t>(nq) * cap);
   uint64_t* rec        = scratch.get<uint64_t>(static_cast<size_t>(rec_cap));
   auto* rec_count      = scratch.get<unsigned long long>(1);
-  const ChunkedPlan plan = plan_chunked(nqt, nt_all, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
-  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(plan.segs.size());
-  int* d_seg_begin     = scratch.get<int>(plan.begin.size());
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, plan.segs.data(), plan.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
-  CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, plan.begin.data(), plan.begin.size() * sizeof(int), cudaMemcpyHostToDevice, res.stream));
+  const DevicePlan plan = device_plan(nqt, nt_all, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
+  auto* d_segs          = static_cast<ScreenSeg*>(plan.segs);
+  int* d_seg_begin      = plan.begin;
+  if (!d_segs) { upload_plan(scratch, plan_chunked(nqt, nt_all, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_)), d_segs, d_seg_begin); }
   CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * nq, res.stream));
   CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
   const size_t cp        = code_pitch_;
@@ -727,11 +761,10 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   int32_t* gmax        = scratch.get<int32_t>(static_cast<size_t>(nq) * ld_g);
   int32_t* thr         = scratch.get<int32_t>(static_cast<size_t>(nq));
   // an anchor tile is 256 rows spread over the whole set: chunks by bytes of anchor rows, as for the screen
-  const ChunkedPlan plan_a = plan_chunked(nqt, nt_anchor, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
-  ScreenSeg* d_segs    = scratch.get<ScreenSeg>(plan_a.segs.size());
-  int* d_seg_begin     = scratch.get<int>(plan_a.begin.size());
-  CERTEX_CUDA(cudaMemcpyAsync(d_segs, plan_a.segs.data(), plan_a.segs.size() * sizeof(ScreenSeg), cudaMemcpyHostToDevice, res.stream));
-  CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, plan_a.begin.data(), plan_a.begin.size() * sizeof(int), cudaMemcpyHostToDevice, res.stream));
+  const DevicePlan plan_a = device_plan(nqt, nt_anchor, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_));
+  auto* d_segs            = static_cast<ScreenSeg*>(plan_a.segs);
+  int* d_seg_begin        = plan_a.begin;
+  if (!d_segs) { upload_plan(scratch, plan_chunked(nqt, nt_anchor, shape.panel_tiles, grid, chunk_tiles_for(code_pitch_)), d_segs, d_seg_begin); }
   if (chained) {  // the smallest e of every chain of 16 adjacent anchors
     // anchor a = sorted row a * stride; chain i of tile t = anchors (i * nt_anchor + t) * 16 .. + 15
     launch_gather_chain_min(init_, anchor_stride, static_cast<int64_t>(nt_anchor) * kChainRows * anchor_stride,
@@ -779,13 +812,10 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
   CERTEX_CUDA(screen_i8_launch(tm_q, tm_a, a, grid, res.stream));
   mark();
   // 2 threshold: the k-th largest group maximum
-  launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream);
+  // (with an exchange between row shards also the k largest group values of every query, in the same launch)
   const bool wide_exchange = topk_hook != nullptr && k <= kTopkExchangeMaxK;
-  int32_t* topk            = nullptr;
-  if (wide_exchange) {  // the k largest group values of every query, for the exchange between row shards
-    topk = scratch.get<int32_t>(static_cast<size_t>(nq) * k);
-    launch_collect_topk(gmax, ld_g, n_groups, k, nq, thr, topk, res.stream);
-  }
+  int32_t* topk            = wide_exchange ? scratch.get<int32_t>(static_cast<size_t>(nq) * k) : nullptr;
+  launch_kth_largest(gmax, ld_g, n_groups, k, nq, thr, res.stream, nullptr, 0x7fffffff, topk);
   if (screen_kind_ == 2) {
     launch_finish_thr_f16(thr, shift + q0, nq, 0, res.stream);
     if (wide_exchange) { launch_finish_thr_f16(topk, shift + q0, nq * k, 0, res.stream, k); }
@@ -1244,7 +1274,7 @@ int Index::anchor_stride_for(int64_t n, int k) const
 
 bool Index::will_screen(int k) const
 {
-  std::shared_lock<std::shared_mutex> lock(rw_);
+  std::shared_lock<ReaderGate> lock(rw_);
   return screen_kind_ != 0 && !code_overflow_ && test_mode_ != 1 && k >= 1 && anchor_stride_for(size_, k) >= 1;
 }
 
@@ -1258,7 +1288,7 @@ struct HostCounters {
 /// A search between search_begin and search_end: the reader lock, the temporaries and what the repair needs.
 struct Index::Pending {
   const Resources* res;
-  std::shared_lock<std::shared_mutex> lock;
+  std::shared_lock<ReaderGate> lock;
   Scratch scratch;
   SearchStats local{};
   SearchParams sp;
@@ -1283,13 +1313,14 @@ struct Index::Pending {
   std::vector<cudaEvent_t> events;
   cudaEvent_t ready = nullptr;
   cudaEvent_t first = nullptr;  // with statistics on: before the first operation of a screened search (ready then keeps time)
-  Pending(const Resources& r, std::shared_mutex& m) : res(&r), lock(m), scratch(r.stream) {}
+  int slot = 0;  // of the resources' page-locked blocks
+  Pending(const Resources& r, ReaderGate& m) : res(&r), lock(m), scratch(r.stream) {}
   ~Pending()
   {
     for (cudaEvent_t e : events) { cudaEventDestroy(e); }
     if (ready) { cudaEventDestroy(ready); }
     if (first) { cudaEventDestroy(first); }
-    res->search_in_flight_ = false;
+    --res->searches_in_flight_;
   }
 };
 
@@ -1297,10 +1328,12 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
                                     int64_t* neighbors, float* distances, double* scores_out, const Filter& filter,
                                     int64_t id_base, unsigned long long* status_out) const
 {
-  CERTEX_EXPECTS(!res.search_in_flight_, "certex: a search is already in flight on these resources (search_end it first)");
+  CERTEX_EXPECTS(res.searches_in_flight_ < Resources::kMaxInFlight,
+                 "certex: too many searches in flight on these resources (search_end the oldest first)");
   auto pending = std::make_unique<Pending>(res, rw_);
-  res.search_in_flight_ = true;
+  ++res.searches_in_flight_;
   Pending& P            = *pending;
+  P.slot                = static_cast<int>(res.next_slot_++ % Resources::kPinnedSlots);
   const int64_t n       = size_;
   CERTEX_EXPECTS(k >= 1 && k <= 2048, "certex: k must be between 1 and 2048");
   CERTEX_EXPECTS(n >= k, "certex: k exceeds the number of vectors added to the index");
@@ -1384,7 +1417,7 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
     }
     // The outputs are written now, as if no list had overflowed; the counters follow them to the host and search_end
     // looks at them once the caller has enqueued what it wanted behind the search.
-    auto* host = static_cast<HostCounters*>(res.pinned_block());
+    auto* host = static_cast<HostCounters*>(res.pinned_block(P.slot));
     CERTEX_CUDA(cudaMemcpyAsync(host, counters, sizeof(HostCounters), cudaMemcpyDeviceToHost, res.stream));
     if (status_out) {
       launch_search_status(d_count, q_ovf, status_out, res.stream);
@@ -1408,7 +1441,7 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
   return pending.release();
 }
 
-bool Index::search_end(Pending* raw) const
+bool Index::search_end(Pending* raw, bool refinish) const
 {
   std::unique_ptr<Pending> pending(raw);
   CERTEX_EXPECTS(raw != nullptr, "certex: no search to finish");
@@ -1418,7 +1451,7 @@ bool Index::search_end(Pending* raw) const
   bool changed        = false;
   if (P.screened && P.nq > 0) {
     CERTEX_CUDA(cudaEventSynchronize(P.ready));  // the one host round trip of a search call
-    const HostCounters h = *static_cast<const HostCounters*>(res.pinned_block());
+    const HostCounters h = *static_cast<const HostCounters*>(res.pinned_block(P.slot));
     if (P.first) {
       float ms = 0;
       cudaEventElapsedTime(&ms, P.first, P.ready);
@@ -1501,6 +1534,12 @@ bool Index::search_end(Pending* raw) const
       local.launches += 1;
     }
   }
+  if (refinish && !changed && P.nq > 0) {
+    launch_finish(P.best_s, P.best_row, P.id_base, P.queries, P.row_bytes, dtype_, static_cast<int>(dim_), params_.metric,
+                  static_cast<int>(P.nq), P.k, P.neighbors, P.distances, P.scores_out, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+    local.launches += 1;
+  }
   if (stats_sink && P.nq > 0) {
     stats_sink->launches += local.launches;
     stats_sink->screen_ms += local.screen_ms;
@@ -1564,7 +1603,7 @@ T take(std::istream& is)
 
 void Index::save(const Resources& res, std::ostream& os) const
 {
-  std::shared_lock<std::shared_mutex> lock(rw_);
+  std::shared_lock<ReaderGate> lock(rw_);
   put(os, kFileMagic);
   put(os, kFileVersion);
   put<int32_t>(os, params_.metric);

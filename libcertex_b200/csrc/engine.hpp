@@ -11,6 +11,10 @@
 #include <iosfwd>
 #include <memory>
 #include <mutex>
+#include <array>
+#include <map>
+#include <condition_variable>
+#include <mutex>
 #include <shared_mutex>
 #include <stdexcept>
 #include <string>
@@ -55,14 +59,62 @@ struct Resources {
   Resources(const Resources&)            = delete;
   Resources& operator=(const Resources&) = delete;
   void sync() const;
-  /// A small block of page-locked host memory (256 bytes) that the counters of a search in flight are copied to; made
-  /// on first use. One search at a time may be in flight per Resources (search_begin .. search_end).
-  void* pinned_block() const;
+  /// Searches that may be in flight at once per Resources (search_begin .. search_end).
+  static constexpr int kMaxInFlight = 2;
+  /// Block `slot` of kPinnedSlots small blocks of page-locked host memory (256 bytes each) that the counters of the
+  /// searches in flight are copied to; made on first use.
+  static constexpr int kPinnedSlots = 4;
+  void* pinned_block(int slot) const;
 
  private:
   mutable void* pinned_ = nullptr;
   friend class Index;
-  mutable bool search_in_flight_ = false;
+  mutable int searches_in_flight_ = 0;
+  mutable unsigned next_slot_     = 0;
+};
+
+/// Readers-writer gate of an index. Unlike std::shared_mutex the shared side may be taken again by a thread that holds
+/// it already (two searches in flight from one thread): a waiting writer does not hold back new readers.
+class ReaderGate {
+ public:
+  void lock_shared()
+  {
+    std::unique_lock<std::mutex> l(m_);
+    cv_.wait(l, [&] { return !writer_; });
+    ++readers_;
+  }
+  void unlock_shared()
+  {
+    std::lock_guard<std::mutex> l(m_);
+    if (--readers_ == 0) { cv_.notify_all(); }
+  }
+  void lock()
+  {
+    std::unique_lock<std::mutex> l(m_);
+    cv_.wait(l, [&] { return !writer_ && readers_ == 0; });
+    writer_ = true;
+  }
+  bool try_lock()
+  {
+    std::lock_guard<std::mutex> l(m_);
+    if (writer_ || readers_ != 0) { return false; }
+    writer_ = true;
+    return true;
+  }
+  void unlock()
+  {
+    {
+      std::lock_guard<std::mutex> l(m_);
+      writer_ = false;
+    }
+    cv_.notify_all();
+  }
+
+ private:
+  std::mutex m_;
+  std::condition_variable cv_;
+  int readers_ = 0;
+  bool writer_ = false;
 };
 
 /// cuvs::neighbors::certex::index_params (cpp/include/cuvs/neighbors/certex.hpp:43-87). Every setting returns the same
@@ -144,14 +196,16 @@ class Index {
    * hold for this call. search_end waits for the stream, and only then, if a list did overflow, enqueues the repair
    * (second pass or dense scan of the queries concerned) and writes the outputs again; it returns true in that case:
    * whatever the caller derived from the outputs in between must be derived again. Every search_begin needs its
-   * search_end on the same thread (it holds the index's reader lock and the call's temporaries); one search may be in
-   * flight per Resources. search() is search_begin + search_end (plus the halving on allocation failure).
+   * search_end on the same thread (it holds the index's reader lock and the call's temporaries); two searches may be in
+   * flight per Resources, ended in the order they were begun. search() is search_begin + search_end (plus the halving on allocation failure).
    */
   struct Pending;
   Pending* search_begin(const Resources& res, const SearchParams& sp, const void* queries, int64_t nq, int k,
                         int64_t* neighbors, float* distances, double* scores_out, const Filter& filter, int64_t id_base,
                         unsigned long long* status_out) const;
-  bool search_end(Pending* pending) const;
+  /// refinish: write the outputs once more from the kept lists even when nothing was repaired (a caller whose output
+  /// buffers were reused in between, as the sharded search's send buffer is by a later search in flight).
+  bool search_end(Pending* pending, bool refinish = false) const;
 
   int64_t size() const { return size_; }
   int64_t dim() const { return dim_; }
@@ -271,7 +325,18 @@ class Index {
   static constexpr int64_t kFrozenRun = 65536;
   int test_mode_      = 0;
   int test_cap_       = 0;
-  mutable std::shared_mutex rw_;  // searches hold it shared per call; size/pointer publication holds it exclusive
+  mutable ReaderGate rw_;  // searches hold it shared per call; size/pointer publication holds it exclusive
+  /// Work splits of the tensor-core passes, kept in device memory per shape (query tiles, base tiles, panel, CTAs,
+  /// chunk): a search then enqueues no copy from pageable host memory, which would make the host wait for the stream in
+  /// the middle of the search.
+  struct DevicePlan {
+    void* segs = nullptr;  // ScreenSeg[]
+    int* begin = nullptr;  // [grid + 1]
+  };
+  DevicePlan device_plan(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles) const;  // empty: not kept, upload it
+  mutable std::mutex plans_mutex_;
+  mutable std::map<std::array<int, 5>, DevicePlan> plans_;
+  static constexpr size_t kMaxPlans = 64;
   std::mutex writer_;             // serialises extend / remove / set_labels
 };
 
@@ -294,6 +359,16 @@ int comm_ranks(const Comm* c);
 void distributed_search(const Resources& res, Comm& c, const Index& index, const SearchParams& sp, const void* queries,
                         int64_t nq, int k, int64_t* neighbors, float* distances, double* scores_out, int64_t id_base,
                         bool share_thresholds);
+/// The same in two calls: begin enqueues the local search, the exchange and the merge and returns without waiting; end
+/// waits for that search (not for what was enqueued behind it), and runs the second round if a list had overflowed on
+/// some rank. Up to Resources::kMaxInFlight searches may be between their two calls per communicator, so that the
+/// host's work for the next search overlaps the device's work for this one; they end in the order they began, and
+/// every rank makes the same sequence of calls. Queries and outputs stay valid and untouched until end.
+struct DistributedPending;
+DistributedPending* distributed_search_begin(const Resources& res, Comm& c, const Index& index, const SearchParams& sp,
+                                             const void* queries, int64_t nq, int k, int64_t* neighbors, float* distances,
+                                             double* scores_out, int64_t id_base, bool share_thresholds);
+void distributed_search_end(DistributedPending* pending);
 
 /// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);

@@ -582,27 +582,6 @@ __global__ void expand_records_kernel(const uint64_t* rec, const unsigned long l
   }
 }
 
-// Block per query: the k largest of gmax[q, 0:ng] given their k-th, thr[q]: the values above it, then copies of it.
-// (Which k of several equal values are meant does not matter to a threshold.)
-__global__ void collect_topk_kernel(const int32_t* gmax, int64_t ld, int ng, int k, const int32_t* thr, int32_t* topk)
-{
-  __shared__ int s_n;
-  const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
-  int32_t* out       = topk + static_cast<int64_t>(blockIdx.x) * k;
-  const int32_t t    = thr[blockIdx.x];
-  if (threadIdx.x == 0) { s_n = 0; }
-  __syncthreads();
-  for (int i = threadIdx.x; i < ng; i += blockDim.x) {
-    const int32_t v = row[i];
-    if (v > t) {
-      const int pos = atomicAdd(&s_n, 1);
-      if (pos < k) { out[pos] = v; }  // fewer than k values lie above the k-th largest
-    }
-  }
-  __syncthreads();
-  for (int i = min(s_n, k) + threadIdx.x; i < k; i += blockDim.x) { out[i] = t; }
-}
-
 // rows [q, 0 : n_parts * k] = the lists parts[p, q, 0:k] of every part side by side.
 __global__ void union_rows_kernel(const int32_t* parts, int n_parts, int nq, int k, int32_t* rows, int64_t ld)
 {
@@ -617,22 +596,48 @@ __global__ void union_rows_kernel(const int32_t* parts, int n_parts, int nq, int
 // Block per query: the k-th largest of ng int32 values by a most-significant-digit radix walk. The row is copied to
 // shared memory first when it fits (vals != global row).
 // With ng_rows the rows have their own lengths; a negative length marks a row without a query: thr = never.
+// Every thread of the block: out [k] = the k largest of row[0:ng] (any order) given their k-th, t: the values above it,
+// then copies of it. (Which k of several equal values are meant does not matter to a threshold.) *counter is shared.
+__device__ void emit_topk(const int32_t* row, int ng, int32_t t, int k, int32_t* out, uint32_t* counter)
+{
+  __syncthreads();
+  if (threadIdx.x == 0) { *counter = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng; i += blockDim.x) {
+    const int32_t v = row[i];
+    if (v > t) {
+      const uint32_t pos = atomicAdd(counter, 1u);
+      if (pos < static_cast<uint32_t>(k)) { out[pos] = v; }  // fewer than k values lie above the k-th largest
+    }
+  }
+  __syncthreads();
+  for (int i = static_cast<int>(min(*counter, static_cast<uint32_t>(k))) + threadIdx.x; i < k; i += blockDim.x) { out[i] = t; }
+}
+
+// With topk [nq, k] the k largest values of every row are written there as well (emit_topk).
 __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr, int in_smem,
-                                   const int32_t* ng_rows, int32_t never)
+                                   const int32_t* ng_rows, int32_t never, int32_t* topk)
 {
   extern __shared__ int32_t row_smem[];
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_remaining;
   const int32_t* row = gmax + static_cast<int64_t>(blockIdx.x) * ld;
+  int32_t* topk_row  = topk ? topk + static_cast<int64_t>(blockIdx.x) * k : nullptr;
   if (ng_rows) {
     ng = ng_rows[blockIdx.x];
     if (ng < 0) {
       if (threadIdx.x == 0) { thr[blockIdx.x] = never; }
+      if (topk_row) {
+        for (int i = threadIdx.x; i < k; i += blockDim.x) { topk_row[i] = never; }
+      }
       return;
     }
   }
   if (ng < k) {
     if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(0x80000000u); }
+    if (topk_row) {
+      for (int i = threadIdx.x; i < k; i += blockDim.x) { topk_row[i] = static_cast<int32_t>(0x80000000u); }
+    }
     return;
   }
   // The row goes to shared memory (when it fits) and its smallest and largest key are found on the way: the radix walk
@@ -716,7 +721,9 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
         if (greater < k && k <= at_least) { s_answer = u; }  // every thread that gets here holds the same value
       }
       __syncthreads();
-      if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>(s_answer ^ 0x80000000u); }
+      const int32_t t = static_cast<int32_t>(s_answer ^ 0x80000000u);
+      if (threadIdx.x == 0) { thr[blockIdx.x] = t; }
+      if (topk_row) { emit_topk(row, ng, t, k, topk_row, &s_count); }
       return;
     }
   }
@@ -775,7 +782,33 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
     remaining = s_remaining;
     mask |= 0xffu << shift;
   }
-  if (threadIdx.x == 0) { thr[blockIdx.x] = static_cast<int32_t>((prefix + base) ^ 0x80000000u); }
+  const int32_t t = static_cast<int32_t>((prefix + base) ^ 0x80000000u);
+  if (threadIdx.x == 0) { thr[blockIdx.x] = t; }
+  if (topk_row) { emit_topk(row, ng, t, k, topk_row, &s_count); }
+}
+
+// Warp per query: the k-th largest of the n_parts * k values parts[p, q, 0:k], p < n_parts, by counting ranks
+// (m = n_parts * k <= kUnionMax). Shared memory: m ints per warp.
+constexpr int kUnionMax = 512;
+__global__ void union_kth_kernel(const int32_t* parts, int n_parts, int nq, int k, int32_t* thr)
+{
+  extern __shared__ int32_t union_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q    = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (q >= nq) { return; }  // warps are independent: no block-wide barrier below
+  const int m = n_parts * k;
+  int32_t* v  = union_smem + warp * m;
+  for (int i = lane; i < m; i += 32) { v[i] = parts[(static_cast<int64_t>(i / k) * nq + q) * k + (i % k)]; }
+  __syncwarp();
+  for (int i = lane; i < m; i += 32) {
+    const int32_t x = v[i];
+    int rank        = 0;
+    for (int j = 0; j < m; ++j) {
+      const int32_t y = v[j];
+      rank += (y > x || (y == x && j < i)) ? 1 : 0;
+    }
+    if (rank == k - 1) { thr[q] = x; }  // ranks are a permutation of 0 .. m - 1: exactly one element
+  }
 }
 
 // Exact scores of 8-bit rows against an 8-bit query in integer arithmetic: <q, x> and |x|^2 by 4-way byte dot products
@@ -1494,6 +1527,43 @@ __global__ void merge_kernel(const double* in_s, const int64_t* in_id, int parts
   }
 }
 
+// The same merge with a warp per query, for parts * k <= kMergeSmallMax candidates: every candidate's place is the number
+// of candidates that come before it by (score, id); the first k are written. Shared memory: m doubles + m int64 per warp.
+constexpr int kMergeSmallMax = 256;
+__global__ void merge_small_kernel(const double* in_s, const int64_t* in_id, int parts, int nq, int k, double* out_s,
+                                   int64_t* out_id, int64_t part_stride)
+{
+  extern __shared__ double merge_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int q    = blockIdx.x * warps + warp;
+  if (q >= nq) { return; }  // warps are independent: no block-wide barrier below
+  const int m = parts * k;
+  double* s   = merge_smem + static_cast<size_t>(warp) * m;
+  int64_t* id = reinterpret_cast<int64_t*>(merge_smem + static_cast<size_t>(warps) * m) + static_cast<size_t>(warp) * m;
+  for (int i = lane; i < m; i += 32) {
+    const size_t o = static_cast<size_t>(i / k) * part_stride + static_cast<size_t>(q) * k + (i % k);
+    const int64_t ii = in_id[o];
+    s[i]  = ii >= 0 ? in_s[o] : CUDART_INF;
+    id[i] = ii >= 0 ? ii : 0x7fffffffffffffffll;
+  }
+  __syncwarp();
+  for (int i = lane; i < m; i += 32) {
+    const double x   = s[i];
+    const int64_t xi = id[i];
+    int place        = 0;
+    for (int j = 0; j < m; ++j) {
+      const double y   = s[j];
+      const int64_t yi = id[j];
+      place += (y < x || (y == x && (yi < xi || (yi == xi && j < i)))) ? 1 : 0;
+    }
+    if (place < k) {
+      const bool have                           = xi != 0x7fffffffffffffffll;
+      out_s[static_cast<size_t>(q) * k + place]  = have ? x : CUDART_INF;
+      out_id[static_cast<size_t>(q) * k + place] = have ? xi : -1;
+    }
+  }
+}
+
 template <typename F>
 void by_dtype(int dtype, F&& f)
 {
@@ -1599,16 +1669,15 @@ void launch_finish_thr_f16(int32_t* thr, const float* shift, int nq, int step, c
   finish_thr_f16_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, shift, nq, step, per);
 }
 
-void launch_collect_topk(const int32_t* gmax, int64_t ld, int ng, int k, int nq, const int32_t* thr, int32_t* topk, cudaStream_t s)
-{
-  if (nq <= 0) { return; }
-  collect_topk_kernel<<<nq, 256, 0, s>>>(gmax, ld, ng, k, thr, topk);
-}
-
 void launch_union_kth(const int32_t* parts, int n_parts, int nq, int k, int32_t* scratch, int32_t* thr, cudaStream_t s)
 {
   if (nq <= 0) { return; }
   const int m       = n_parts * k;
+  if (m <= kUnionMax) {  // a warp per query ranks the values by counting
+    const int warps = 4;
+    union_kth_kernel<<<(nq + warps - 1) / warps, warps * 32, static_cast<size_t>(warps) * m * 4, s>>>(parts, n_parts, nq, k, thr);
+    return;
+  }
   const int64_t ld  = (m + 7) / 8 * 8;
   const int64_t tot = static_cast<int64_t>(nq) * m;
   union_rows_kernel<<<static_cast<unsigned>((tot + 255) / 256), 256, 0, s>>>(parts, n_parts, nq, k, scratch, ld);
@@ -1650,13 +1719,13 @@ void launch_sort_batch(const int32_t* e, int64_t n, int32_t id0, int64_t row0, c
 }
 
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
-                        const int32_t* ng_rows, int32_t never)
+                        const int32_t* ng_rows, int32_t never, int32_t* topk)
 {
   if (nq <= 0) { return; }
   const size_t bytes = static_cast<size_t>(ng) * 4;
   const int in_smem  = bytes <= 160 * 1024;
   if (in_smem) { allow_smem(kth_largest_kernel, bytes); }
-  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never);
+  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never, topk);
 }
 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
@@ -1927,10 +1996,16 @@ void launch_merge(const double* in_s, const int64_t* in_id, int parts, int nq, i
   if (nq <= 0) { return; }
   if (part_stride == 0) { part_stride = static_cast<int64_t>(nq) * k; }
   // merged (score, id) go to scores_out / neighbors first; finish_kernel then converts in place
-  const int n2      = next_pow2(parts * k) < 2 ? 2 : next_pow2(parts * k);
-  const size_t smem = (sizeof(double) + sizeof(int64_t)) * static_cast<size_t>(n2);
-  allow_smem(merge_kernel, smem);
-  merge_kernel<<<nq, 256, smem, s>>>(in_s, in_id, parts, nq, k, n2, scores_out, neighbors, part_stride);
+  if (parts * k <= kMergeSmallMax) {
+    const int warps = 4;
+    merge_small_kernel<<<(nq + warps - 1) / warps, warps * 32, static_cast<size_t>(warps) * parts * k * 16, s>>>(
+      in_s, in_id, parts, nq, k, scores_out, neighbors, part_stride);
+  } else {
+    const int n2      = next_pow2(parts * k) < 2 ? 2 : next_pow2(parts * k);
+    const size_t smem = (sizeof(double) + sizeof(int64_t)) * static_cast<size_t>(n2);
+    allow_smem(merge_kernel, smem);
+    merge_kernel<<<nq, 256, smem, s>>>(in_s, in_id, parts, nq, k, n2, scores_out, neighbors, part_stride);
+  }
   if (!finish) { return; }
   by_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);

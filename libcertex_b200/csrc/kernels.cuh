@@ -76,12 +76,10 @@ void launch_expand_records(const uint64_t* rec, const unsigned long long* rec_co
                            cudaStream_t s);
 
 /// thr[q] = k-th largest of gmax[q, 0:ng]  (INT_MIN when ng < k). With ng_rows [nq] every row has its own length
-/// (at most ng); a negative length gives thr[q] = never.
+/// (at most ng); a negative length gives thr[q] = never. With topk [nq, k] the k largest values of every row are
+/// written there too (any order: the values above the k-th, then copies of it), in the same launch.
 void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, int32_t* thr, cudaStream_t s,
-                        const int32_t* ng_rows = nullptr, int32_t never = 0x7fffffff);
-
-/// topk [nq, k] = the k largest of gmax[q, 0:ng] (any order), given thr[q] = their k-th (launch_kth_largest).
-void launch_collect_topk(const int32_t* gmax, int64_t ld, int ng, int k, int nq, const int32_t* thr, int32_t* topk, cudaStream_t s);
+                        const int32_t* ng_rows = nullptr, int32_t never = 0x7fffffff, int32_t* topk = nullptr);
 
 /// thr[q] = the k-th largest of the union of parts[p, q, 0:k], p < n_parts (lists of the k largest keys of every row
 /// shard: every key is reached by a row of its own, so the k-th largest of all of them is reached by k rows of the

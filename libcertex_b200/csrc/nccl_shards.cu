@@ -91,7 +91,11 @@ struct Comm {
   int64_t* send = nullptr;  // [2 nq k + 1]: fp64 scores as bits, global ids, the status word
   int64_t* recv = nullptr;  // [n_ranks, 2 nq k + 1]
   size_t send_words = 0;
-  unsigned long long* host_status = nullptr;  // page-locked, [n_ranks]
+  unsigned long long* host_status = nullptr;  // page-locked, [kStatusSlots][n_ranks]: the status words of the searches in flight
+  static constexpr int kStatusSlots = 4;
+  unsigned long long begun = 0, ended = 0;    // sharded searches begun / ended on this communicator
+  unsigned long long send_owner = ~0ull;      // the search whose lists the send buffer holds (in stream order)
+  unsigned long long* status_of(unsigned long long seq) const { return host_status + (seq % kStatusSlots) * n_ranks; }
   int32_t* topk_recv = nullptr;               // [n_ranks, nq, k] keys of the threshold exchange, and the rows made of them
   int32_t* topk_rows = nullptr;
   size_t topk_ints   = 0;
@@ -166,7 +170,7 @@ Comm* comm_create(const void* id128, int n_ranks, int rank, void* adopt)
     CERTEX_NCCL(nccl().CommInitRank(&c->comm, n_ranks, id, rank));
     c->owned = true, c->n_ranks = n_ranks, c->rank = rank;
   }
-  CERTEX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&c->host_status), sizeof(unsigned long long) * c->n_ranks, cudaHostAllocDefault));
+  CERTEX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&c->host_status), sizeof(unsigned long long) * c->n_ranks * Comm::kStatusSlots, cudaHostAllocDefault));
   return c.release();
 }
 
@@ -174,13 +178,70 @@ void comm_destroy(Comm* c) { delete c; }
 
 int comm_ranks(const Comm* c) { return c->n_ranks; }
 
-void distributed_search(const Resources& res, Comm& c, const Index& index, const SearchParams& sp, const void* queries,
-                        int64_t nq, int k, int64_t* neighbors, float* distances, double* scores_out, int64_t id_base,
-                        bool share_thresholds)
+/// A sharded search between its two calls: the local search in flight and what the second call needs.
+struct DistributedPending {
+  const Resources* res = nullptr;
+  Comm* c              = nullptr;
+  const Index* index   = nullptr;
+  Index::Pending* pending = nullptr;
+  std::exception_ptr failed;
+  const void* queries = nullptr;
+  int64_t nq = 0, id_base = 0;
+  int k = 0;
+  int64_t* neighbors = nullptr;
+  float* distances   = nullptr;
+  double* scores_out = nullptr;
+  size_t cells = 0, words = 0;
+  unsigned long long seq = 0;   // number of the search on its communicator: they end in the order they began
+  cudaEvent_t done = nullptr;   // behind the first exchange
+  ~DistributedPending()
+  {
+    if (done) { cudaEventDestroy(done); }
+  }
+};
+
+namespace {
+
+// empty lists and the failure flag in this rank's contribution
+void fail_lists(const Resources& res, Comm& c, size_t cells)
+{
+  cudaGetLastError();
+  CERTEX_CUDA(cudaMemsetAsync(c.send, 0xff, 2 * cells * 8, res.stream));  // ids -1 (scores: never read)
+  CERTEX_CUDA(cudaMemcpyAsync(c.send + 2 * cells, &kStatusFailed, 8, cudaMemcpyHostToDevice, res.stream));
+}
+
+// all-gather of the ranks' lists and status words, merge into the caller's outputs, status words to the host
+void exchange(DistributedPending& d)
+{
+  Comm& c = *d.c;
+  const Resources& res = *d.res;
+  CERTEX_NCCL(nccl().AllGather(c.send, c.recv, d.words, ncclInt64, c.comm, res.stream));
+  merge_shards(res, reinterpret_cast<const double*>(c.recv), c.recv + d.cells, c.n_ranks, static_cast<int>(d.nq), d.k, d.queries,
+               d.index->dtype(), d.index->dim(), d.index->metric(), d.neighbors, d.distances, d.scores_out,
+               static_cast<int64_t>(d.words));
+  CERTEX_CUDA(cudaMemcpy2DAsync(c.status_of(d.seq), 8, c.recv + 2 * d.cells, d.words * 8, 8, static_cast<size_t>(c.n_ranks),
+                                cudaMemcpyDeviceToHost, res.stream));
+}
+
+}  // namespace
+
+DistributedPending* distributed_search_begin(const Resources& res, Comm& c, const Index& index, const SearchParams& sp,
+                                             const void* queries, int64_t nq, int k, int64_t* neighbors, float* distances,
+                                             double* scores_out, int64_t id_base, bool share_thresholds)
 {
   CERTEX_EXPECTS(res.device == c.device, "certex: the communicator was made on another device than these resources");
-  if (nq == 0) { return; }
+  CERTEX_EXPECTS(c.begun - c.ended < static_cast<unsigned long long>(Resources::kMaxInFlight),
+                 "certex: too many sharded searches in flight on this communicator (end the oldest first)");
+  auto d = std::make_unique<DistributedPending>();
+  d->res = &res, d->c = &c, d->index = &index, d->queries = queries, d->nq = nq, d->k = k, d->id_base = id_base;
+  d->neighbors = neighbors, d->distances = distances, d->scores_out = scores_out;
+  d->seq = c.begun;
+  if (nq == 0) {
+    ++c.begun;
+    return d.release();
+  }
   const size_t cells = static_cast<size_t>(nq) * k, words = 2 * cells + 1;
+  d->cells = cells, d->words = words;
   c.reserve(words);
   auto* send_scores = reinterpret_cast<double*>(c.send);
   int64_t* send_ids = c.send + cells;
@@ -190,10 +251,11 @@ void distributed_search(const Resources& res, Comm& c, const Index& index, const
     // the exchange needs every rank to reach it, i.e. to screen: agreed once per k and index size
     if (c.all_screen_size != index.size()) { c.all_screen.clear(), c.all_screen_size = index.size(); }
     if (!c.all_screen.count(k)) {
-      int32_t mine = index.will_screen(k) ? 1 : 0, *d = reinterpret_cast<int32_t*>(c.send);
-      CERTEX_CUDA(cudaMemcpyAsync(d, &mine, 4, cudaMemcpyHostToDevice, res.stream));
-      CERTEX_NCCL(nccl().AllReduce(d, d, 1, ncclInt32, ncclMin, c.comm, res.stream));
-      CERTEX_CUDA(cudaMemcpyAsync(&mine, d, 4, cudaMemcpyDeviceToHost, res.stream));
+      int32_t mine = index.will_screen(k) ? 1 : 0, *dev = reinterpret_cast<int32_t*>(c.send);
+      res.sync();  // a search in flight may still use the send buffer
+      CERTEX_CUDA(cudaMemcpyAsync(dev, &mine, 4, cudaMemcpyHostToDevice, res.stream));
+      CERTEX_NCCL(nccl().AllReduce(dev, dev, 1, ncclInt32, ncclMin, c.comm, res.stream));
+      CERTEX_CUDA(cudaMemcpyAsync(&mine, dev, 4, cudaMemcpyDeviceToHost, res.stream));
       res.sync();
       c.all_screen[k] = mine != 0;
     }
@@ -201,75 +263,108 @@ void distributed_search(const Resources& res, Comm& c, const Index& index, const
   } else {
     share_thresholds = false;
   }
+  ++c.begun;  // from here on the search takes part in the collectives: it must be ended
+  c.send_owner = d->seq;
 
-  auto fail_lists = [&] {  // empty lists and the failure flag in this rank's contribution
-    cudaGetLastError();
-    CERTEX_CUDA(cudaMemsetAsync(c.send, 0xff, 2 * cells * 8, res.stream));  // ids -1 (scores: never read)
-    CERTEX_CUDA(cudaMemcpyAsync(send_status, &kStatusFailed, 8, cudaMemcpyHostToDevice, res.stream));
-  };
   // ---- the local exact top-k, written straight into the send buffer (distances: scratch use of the caller's output)
-  Index::Pending* pending = nullptr;
-  std::exception_ptr failed;
   try {
     if (share_thresholds) {
       Index::threshold_hook = share_thresholds_hook, Index::topk_hook = share_topk_hook, Index::threshold_hook_ctx = &c;
     }
-    pending = index.search_begin(res, sp, queries, nq, k, send_ids, distances, send_scores, Filter{}, id_base, send_status);
+    d->pending = index.search_begin(res, sp, queries, nq, k, send_ids, distances, send_scores, Filter{}, id_base, send_status);
     Index::threshold_hook = nullptr, Index::topk_hook = nullptr, Index::threshold_hook_ctx = nullptr;
   } catch (...) {
     // this rank cannot answer: it still takes part in the exchange, with empty lists and the failure in its status
     // word, so that no rank is left waiting in the collective (a rank that failed inside the threshold exchange cannot
     // be helped this way; NCCL's own timeout ends the others' wait)
     Index::threshold_hook = nullptr, Index::topk_hook = nullptr, Index::threshold_hook_ctx = nullptr;
-    failed = std::current_exception();
-    fail_lists();
+    d->failed = std::current_exception();
+    fail_lists(res, c, cells);
   }
-
-  auto exchange = [&] {
-    CERTEX_NCCL(nccl().AllGather(c.send, c.recv, words, ncclInt64, c.comm, res.stream));
-    merge_shards(res, reinterpret_cast<const double*>(c.recv), c.recv + cells, c.n_ranks, static_cast<int>(nq), k, queries,
-                 index.dtype(), index.dim(), index.metric(), neighbors, distances, scores_out, static_cast<int64_t>(words));
-    CERTEX_CUDA(cudaMemcpy2DAsync(c.host_status, 8, c.recv + 2 * cells, words * 8, 8, static_cast<size_t>(c.n_ranks),
-                                  cudaMemcpyDeviceToHost, res.stream));
-  };
   // round 1 assumes that no candidate list overflowed; the ranks' status words say whether that held everywhere
+  try {
+    exchange(*d);
+    CERTEX_CUDA(cudaEventCreateWithFlags(&d->done, cudaEventDisableTiming));
+    CERTEX_CUDA(cudaEventRecord(d->done, res.stream));
+  } catch (...) {
+    if (d->pending) {
+      try {
+        index.search_end(d->pending);
+      } catch (...) {
+      }
+    }
+    ++c.ended;
+    throw;
+  }
+  return d.release();
+}
+
+void distributed_search_end(DistributedPending* raw)
+{
+  CERTEX_EXPECTS(raw != nullptr, "certex: no sharded search to end");
+  CERTEX_EXPECTS(raw->seq == raw->c->ended, "certex: sharded searches end in the order they began");  // raw stays valid
+  std::unique_ptr<DistributedPending> d(raw);
+  Comm& c              = *d->c;
+  const Resources& res = *d->res;
+  ++c.ended;
+  if (d->nq == 0) { return; }
+  // Whether the send buffer has been reused meanwhile (by a later search that was begun, or by the second round of an
+  // earlier one): a second round must then write this search's lists there again, also on a rank that has nothing to
+  // repair.
+  const bool overtaken = c.send_owner != d->seq;
   bool again = false;
   int failed_rank = -1;
   auto read_status = [&](bool first) {
-    res.sync();  // the one wait of a round: everything before it ran back to back on the device
+    const unsigned long long* st = c.status_of(d->seq);
     for (int r = 0; r < c.n_ranks; ++r) {
-      if (first && (c.host_status[r] & 7ull) != 0) { again = true; }
-      if ((c.host_status[r] & kStatusFailed) != 0 && failed_rank < 0) { failed_rank = r; }
+      if (first && (st[r] & 7ull) != 0) { again = true; }
+      if ((st[r] & kStatusFailed) != 0 && failed_rank < 0) { failed_rank = r; }
     }
   };
   try {
-    exchange();
+    CERTEX_CUDA(cudaEventSynchronize(d->done));  // the one wait of a round: everything before it ran back to back on the device
     read_status(true);
   } catch (...) {
-    if (pending) {
+    if (d->pending) {
       try {
-        index.search_end(pending);
+        d->index->search_end(d->pending);
       } catch (...) {
       }
     }
     throw;
   }
-  if (pending) {
+  std::exception_ptr failed = d->failed;
+  if (d->pending) {
     try {
-      index.search_end(pending);  // repairs this rank's lists when its own status word was set
+      // repairs this rank's lists when its own status word was set
+      d->index->search_end(d->pending, /*refinish=*/again && failed_rank < 0 && overtaken);
     } catch (...) {
       // only a rank whose status word was set can fail here, so every rank is about to run the second round: this
       // rank takes part in it with the failure in its status word
       failed = std::current_exception();
-      fail_lists();
+      fail_lists(res, c, d->cells);
     }
   }
   if (failed_rank < 0 && again) {
-    exchange();
+    c.send_owner = d->seq;
+    if (overtaken && !failed) {
+      // the status word in the send buffer is the later search's by now: this rank's lists are in order
+      CERTEX_CUDA(cudaMemsetAsync(c.send + 2 * d->cells, 0, 8, res.stream));
+    }
+    exchange(*d);
+    res.sync();
     read_status(false);
   }
   if (failed) { std::rethrow_exception(failed); }
   CERTEX_EXPECTS(failed_rank < 0, "certex: the local search of rank " + std::to_string(failed_rank) + " failed; no answer for this call");
+}
+
+void distributed_search(const Resources& res, Comm& c, const Index& index, const SearchParams& sp, const void* queries,
+                        int64_t nq, int k, int64_t* neighbors, float* distances, double* scores_out, int64_t id_base,
+                        bool share_thresholds)
+{
+  distributed_search_end(distributed_search_begin(res, c, index, sp, queries, nq, k, neighbors, distances, scores_out, id_base,
+                                                  share_thresholds));
 }
 
 }  // namespace certex_b200

@@ -66,15 +66,24 @@ def gather_lists(scores, ids, group=None):
     return both[:, 0].contiguous().view(torch.float64), both[:, 1].contiguous()
 
 
+class _Ticket:
+    """A sharded search between search_begin and search_end: the library's handle and the tensors it works on."""
+
+    def __init__(self, pending, tensors, return_scores):
+        self.pending, self.tensors, self.return_scores = pending, tensors, return_scores
+
+
 class DistributedIndex:
     """One shard per rank of the process group. add_shard() takes this rank's rows and the global id of its first
     row; search() returns the same (distances, ids) on every rank.
 
-    share_thresholds=True adds the reference's optional first round: the ranks take the maximum of their thresholds
-    before they screen. It is off by default: a shard's threshold is about its (anchor_stride * k)-th best row, the
-    maximum over S shards is hardly tighter than each of them (131 instead of 160 survivors per query and shard on
-    the 10 M x 128 benchmark with two shards), and the extra synchronisation point cost more than it saved there
-    (8.3 ms instead of 7.5 ms per 10 000 queries)."""
+    share_thresholds=True adds the reference's optional first round: between the anchor pass and the screen the ranks
+    agree on thresholds. With the native backend and k <= 64 every rank contributes its k best threshold candidates per
+    query and all take the k-th best of the union, which is what one index over all rows would screen with: the shards
+    together then keep about as many pairs as one index would (80 per query and shard instead of 162 on the 10 M x 128
+    benchmark with two shards, 41 with four). For larger k, and with backend="torch", the ranks take the maximum of
+    their own thresholds (one all-reduce), which is hardly tighter than each of them. It is off by default because it
+    ties the ranks together once more per batch of queries."""
 
     def __init__(self, dim, metric="l2", anchor_stride=16, group=None, share_thresholds=False, backend="native"):
         _need(backend in ("native", "torch"), "backend must be 'native' or 'torch'")
@@ -112,7 +121,7 @@ class DistributedIndex:
         return self.add_shard(x[lo:hi], lo)
 
     def __del__(self):
-        if getattr(self, "_comm", None) is not None:
+        if getattr(self, "_comm", None) is not None and L is not None:  # L is None while the interpreter shuts down
             L.lib().certexB200CommDestroy(self._comm)
             self._comm = None
 
@@ -133,18 +142,42 @@ class DistributedIndex:
         return self._comm
 
     def _search_native(self, Q, k, batch, return_scores):
+        return self.search_end(self._begin_native(Q, k, batch, return_scores))
+
+    def _begin_native(self, Q, k, batch, return_scores):
         nq = Q.shape[0]
         I = torch.empty((nq, k), dtype=torch.int64, device="cuda")
         D = torch.empty((nq, k), dtype=torch.float32, device="cuda")
         S = torch.empty((nq, k), dtype=torch.float64, device="cuda") if return_scores else None
         sp = L.SearchParams(128, int(batch), 2)
-        L.check(L.lib().certexB200DistributedSearch(
-            L.resources(), self._communicator(), ctypes.byref(sp), self.local.core.handle, L.Tensor(Q).ref,
-            L.Tensor(I).ref, L.Tensor(D).ref, None if S is None else L.Tensor(S).ref, self.first,
-            1 if self.share_thresholds else 0))
+        tensors = (L.Tensor(Q), L.Tensor(I), L.Tensor(D), None if S is None else L.Tensor(S))
+        pending = ctypes.c_void_p()
+        L.check(L.lib().certexB200DistributedSearchBegin(
+            L.resources(), self._communicator(), ctypes.byref(sp), self.local.core.handle, tensors[0].ref, tensors[1].ref,
+            tensors[2].ref, None if S is None else tensors[3].ref, self.first, 1 if self.share_thresholds else 0,
+            ctypes.byref(pending)))
+        return _Ticket(pending, (Q, I, D, S), return_scores)
+
+    def search_begin(self, q, k=10, batch=2048, return_scores=False):
+        """First half of search() (native backend): enqueues the local search, the exchange and the merge on the current
+        stream and returns a ticket without waiting for the device. Up to two searches may be between search_begin and
+        search_end; they end in the order they began, and every rank makes the same sequence of calls. A caller that
+        begins the next search before it ends this one keeps the device busy while the host prepares the next call."""
+        _need(self.backend == "native", "search_begin needs the native backend")
+        _need(self.local.core is not None, "add vectors first")
+        _need(k <= int(self.local.core.info().size), "every shard needs at least k vectors")
+        return self._begin_native(q.cuda().contiguous().to(self.local.dtype), k, batch, return_scores)
+
+    def search_end(self, ticket):
+        """Second half: waits for that search (not for work enqueued behind it), lets the library repair and exchange
+        again if a candidate list had overflowed on some rank, and returns what search() returns."""
+        _need(ticket.pending is not None, "this search was ended already")
+        pending, ticket.pending = ticket.pending, None
+        L.check(L.lib().certexB200DistributedSearchEnd(pending))
+        _, I, D, S = ticket.tensors
         if self.metric == "cosine":
             D = 1 - D
-        return (D, I, S) if return_scores else (D, I)
+        return (D, I, S) if ticket.return_scores else (D, I)
 
     def search(self, q, k=10, batch=2048, return_scores=False):
         _need(self.local.core is not None, "add vectors first")

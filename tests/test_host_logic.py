@@ -123,11 +123,12 @@ def test_both_bench_arms_name_the_same_configuration():
     spec.loader.exec_module(bench)
     for gpus in (1, 2, 8):
         args = argparse.Namespace(gpus=gpus, n_base=bench.N_BASE, n_queries=bench.N_QUERIES, batch=10240,
-                                  anchor_stride=16, searches_per_step=0, share_thresholds=1)
+                                  anchor_stride=16, searches_per_step=0, share_thresholds=1, pipeline=2)
         cfg = bench.config_of(args)
         assert cfg == bench.config_of(args)
         assert cfg["searches_per_step"] == (1 if gpus == 1 else 4)
         assert cfg["share_thresholds"] == (gpus > 1)
+        assert cfg["searches_in_flight"] == (1 if gpus == 1 else 2)
         assert f"{gpus} row shard(s)" in cfg["workload"] and "10000000x128 uint8" in cfg["workload"]
 
 

@@ -134,6 +134,26 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
         "        kept[share] = st.survivors\n"
         "    assert kept[True] < kept[False], (k, kept)\n"
         "    if k == 10: assert kept[True] < 0.8 * kept[False], kept\n"
+        "# two searches between search_begin and search_end (different queries and k), ended in order; then with candidate\n"
+        "# lists that overflow on the last rank only: the second round of the first search then runs behind the second\n"
+        "# search, which has reused the exchange buffers, and the other ranks write their lists there once more\n"
+        "pidx = distributed.DistributedIndex(32, share_thresholds=True).add(torch.from_numpy(x))\n"
+        "qa, qb = torch.from_numpy(q[:60]), torch.from_numpy(q[40:])\n"
+        "want_a, want_b = oracle.knn(x, q[:60], 10, 'l2'), oracle.knn(x, q[40:], 7, 'l2')\n"
+        "for overflow in (False, True):\n"
+        "    if overflow and rank == dist.get_world_size() - 1: pidx.local._test_mode(2, 16)\n"
+        "    ta = pidx.search_begin(qa, k=10, return_scores=True)\n"
+        "    tb = pidx.search_begin(qb, k=7, return_scores=True)\n"
+        "    try:\n"
+        "        pidx.search_begin(qa, k=10); raise SystemExit('a third search in flight was accepted')\n"
+        "    except certex.CertexError as e:\n"
+        "        assert 'in flight' in str(e), str(e)\n"
+        "    Da, Ia, Sa = pidx.search_end(ta)\n"
+        "    Db, Ib, Sb = pidx.search_end(tb)\n"
+        "    assert np.array_equal(Ia.cpu().numpy(), want_a[0]) and np.array_equal(Sa.cpu().numpy(), want_a[1]), overflow\n"
+        "    assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1]), overflow\n"
+        "    D1, I1 = pidx.search(qa, k=10)\n"
+        "    assert torch.equal(I1, Ia) and torch.equal(D1, Da)\n"
         "# a rank whose local search fails (a host-side simulated allocation failure on rank 1, one query so that no\n"
         "# halving helps): every rank gets an error for the call instead of waiting, and the next call works\n"
         "idx = distributed.DistributedIndex(32).add(torch.from_numpy(x))\n"
@@ -151,4 +171,45 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29577", str(script)],
                        capture_output=True, text=True, env=env, timeout=600)
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-8000:]
+
+
+def test_two_searches_in_flight_on_a_communicator_of_one_rank(tmp_path):
+    """The two-call form of the sharded search on one GPU: a process group and a communicator of a single rank. Two
+    searches are begun before the first is ended, once plainly and once with candidate lists that overflow, whose
+    repair and second exchange then run behind the second search."""
+    script = tmp_path / "one_rank.py"
+    script.write_text(
+        "import os, sys, numpy as np, torch, torch.distributed as dist\n"
+        f"sys.path.insert(0, {ROOT!r})\n"
+        "import libcertex_b200 as certex\n"
+        "from libcertex_b200 import distributed, synthetic\n"
+        "from oracle import oracle\n"
+        "rank = 0; torch.cuda.set_device(0)\n"
+        "dist.init_process_group('nccl', rank=0, world_size=1)\n"
+        "x = synthetic.correlated(40000, 32, seed=3, dtype='uint8'); q = synthetic.correlated(100, 32, seed=4, dtype='uint8')\n"
+        "# two searches between search_begin and search_end (different queries and k), ended in order; then with candidate\n"
+        "# lists that overflow on the last rank only: the second round of the first search then runs behind the second\n"
+        "# search, which has reused the exchange buffers, and the other ranks write their lists there once more\n"
+        "pidx = distributed.DistributedIndex(32, share_thresholds=True).add(torch.from_numpy(x))\n"
+        "qa, qb = torch.from_numpy(q[:60]), torch.from_numpy(q[40:])\n"
+        "want_a, want_b = oracle.knn(x, q[:60], 10, 'l2'), oracle.knn(x, q[40:], 7, 'l2')\n"
+        "for overflow in (False, True):\n"
+        "    if overflow and rank == dist.get_world_size() - 1: pidx.local._test_mode(2, 16)\n"
+        "    ta = pidx.search_begin(qa, k=10, return_scores=True)\n"
+        "    tb = pidx.search_begin(qb, k=7, return_scores=True)\n"
+        "    try:\n"
+        "        pidx.search_begin(qa, k=10); raise SystemExit('a third search in flight was accepted')\n"
+        "    except certex.CertexError as e:\n"
+        "        assert 'in flight' in str(e), str(e)\n"
+        "    Da, Ia, Sa = pidx.search_end(ta)\n"
+        "    Db, Ib, Sb = pidx.search_end(tb)\n"
+        "    assert np.array_equal(Ia.cpu().numpy(), want_a[0]) and np.array_equal(Sa.cpu().numpy(), want_a[1]), overflow\n"
+        "    assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1]), overflow\n"
+        "    D1, I1 = pidx.search(qa, k=10)\n"
+        "    assert torch.equal(I1, Ia) and torch.equal(D1, Da)\n"
+        "dist.destroy_process_group(); print('ok')\n"
+    )
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29579")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-8000:]
