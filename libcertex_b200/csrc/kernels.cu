@@ -680,7 +680,7 @@ __global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int 
   __shared__ uint32_t s_group[512], s_list[kCollect];
   __shared__ uint32_t s_bound, s_count, s_answer;
   const int n_threads = blockDim.x;
-  if (in_smem && n_threads == 512 && 2 * k <= 512) {
+  if (in_smem && (n_threads == 512 || n_threads == 128) && 2 * k <= n_threads) {
     int groups = 16;
     while (groups < 2 * k) { groups <<= 1; }
     const int per_group = n_threads / groups;  // 32, 16, ..., 1 threads
@@ -1725,7 +1725,9 @@ void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, 
   const size_t bytes = static_cast<size_t>(ng) * 4;
   const int in_smem  = bytes <= 160 * 1024;
   if (in_smem) { allow_smem(kth_largest_kernel, bytes); }
-  kth_largest_kernel<<<nq, 512, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never, topk);
+  // short rows: smaller blocks, more of them per SM (the kernel is a chain of block-wide barriers)
+  const int threads = (ng <= 4096 && 2 * k <= 128) ? 128 : 512;
+  kth_largest_kernel<<<nq, threads, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never, topk);
 }
 
 void launch_remove(const int64_t* ids, int64_t n_ids, int64_t size, uint8_t* removed, int32_t* init, const int32_t* inv,
