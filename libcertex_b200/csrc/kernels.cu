@@ -615,8 +615,8 @@ __device__ void emit_topk(const int32_t* row, int ng, int32_t t, int k, int32_t*
 }
 
 // With topk [nq, k] the k largest values of every row are written there as well (emit_topk).
-__global__ void kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr, int in_smem,
-                                   const int32_t* ng_rows, int32_t never, int32_t* topk)
+__global__ void __launch_bounds__(512, 4) kth_largest_kernel(const int32_t* gmax, int64_t ld, int ng, int k, int32_t* thr,
+                                                              int in_smem, const int32_t* ng_rows, int32_t never, int32_t* topk)
 {
   extern __shared__ int32_t row_smem[];
   __shared__ uint32_t hist[256];
