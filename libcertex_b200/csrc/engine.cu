@@ -336,6 +336,7 @@ Index::~Index()
   cudaFree(init_);
   cudaFree(cmax_);
   cudaFree(maxima_);
+  cudaFree(sqnorm_);
   for (auto& kv : plans_) { cudaFree(kv.second.segs), cudaFree(kv.second.begin); }
 }
 
@@ -373,6 +374,7 @@ void Index::reserve(const Resources& res, int64_t n)
   int32_t* l        = nullptr;
   void* co          = nullptr;
   int32_t *pe = nullptr, *iv = nullptr, *in = nullptr, *cm = nullptr;
+  double* sq  = nullptr;
   const int64_t pad_old = round_up(size_, kTile), pad_new = round_up(cap, kTile);
   v = alloc_vectors(static_cast<size_t>(cap) * pitch_, host_vectors_);
   CERTEX_CUDA(cudaMalloc(&r, static_cast<size_t>(round_up(cap, 4))));
@@ -381,6 +383,9 @@ void Index::reserve(const Resources& res, int64_t n)
     CERTEX_CUDA(cudaMalloc(&l, static_cast<size_t>(cap) * 4));
     CERTEX_CUDA(cudaMemsetAsync(l, 0xff, static_cast<size_t>(cap) * 4, res.stream));
   }
+  // the squared norms the cosine verification would otherwise sum again for every candidate
+  const bool keep_sqnorm = params_.metric == kCos && !host_vectors_ && (dtype_ == kF32 || dtype_ == kF16);
+  if (keep_sqnorm) { CERTEX_CUDA(cudaMalloc(&sq, static_cast<size_t>(cap) * 8)); }
   if (screen_kind_) {
     const int32_t never = screen_kind_ == 2 ? static_cast<int32_t>(0xff800000u) : kNeverInit;  // -inf or -2^30
     CERTEX_CUDA(cudaMalloc(&co, static_cast<size_t>(cap) * code_pitch_));
@@ -397,6 +402,7 @@ void Index::reserve(const Resources& res, int64_t n)
     CERTEX_CUDA(cudaMemcpyAsync(v, vectors_, static_cast<size_t>(size_) * pitch_, cudaMemcpyDefault, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(r, removed_, static_cast<size_t>(round_up(size_, 4)), d2d, res.stream));
     if (labels_) { CERTEX_CUDA(cudaMemcpyAsync(l, labels_, static_cast<size_t>(size_) * 4, d2d, res.stream)); }
+    if (sq && sqnorm_) { CERTEX_CUDA(cudaMemcpyAsync(sq, sqnorm_, static_cast<size_t>(size_) * 8, d2d, res.stream)); }
     if (screen_kind_) {
       CERTEX_CUDA(cudaMemcpyAsync(co, codes_, static_cast<size_t>(size_) * code_pitch_, d2d, res.stream));
       CERTEX_CUDA(cudaMemcpyAsync(pe, perm_, static_cast<size_t>(size_) * 4, d2d, res.stream));
@@ -407,14 +413,17 @@ void Index::reserve(const Resources& res, int64_t n)
   }
   res.sync();
   void* old[8] = {vectors_, removed_, labels_, codes_, perm_, inv_, init_, cmax_};
+  double* old_sq = sqnorm_;
   {
     std::unique_lock<ReaderGate> lock(rw_);  // waits for running searches, which read the old arrays
     vectors_ = v;
     removed_ = r;
     if (l) { labels_ = l; }
     codes_ = co, perm_ = pe, inv_ = iv, init_ = in, cmax_ = cm;
+    if (sq) { sqnorm_ = sq; }
     capacity_ = cap;
   }
+  if (sq) { cudaFree(old_sq); }
   free_vectors(old[0], host_vectors_);
   for (int i = 1; i < 8; ++i) {
     if (i != 2 || l) { cudaFree(old[i]); }
@@ -437,6 +446,10 @@ void Index::extend(const Resources& res, const void* rows, int64_t n, bool on_ho
     CERTEX_CUDA(cudaMemcpy2DAsync(dst, pitch_, rows, row_bytes, row_bytes, static_cast<size_t>(n), kind, res.stream));
   }
   if (labels_) { CERTEX_CUDA(cudaMemsetAsync(labels_ + size_, 0xff, static_cast<size_t>(n) * 4, res.stream)); }
+  if (sqnorm_) {
+    launch_row_sqnorms(dst, pitch_, dtype_, static_cast<int>(dim_), n, sqnorm_ + size_, res.stream);
+    CERTEX_CUDA(cudaGetLastError());
+  }
   std::unique_lock<ReaderGate> lock(rw_, std::defer_lock);
   if (screen_kind_) {
     // The batch goes into sorted rows [size, size + n), ordered by squared norm; rows beyond the published size are
@@ -733,7 +746,7 @@ void Index::screen_pass(const Resources& res, const uint8_t* qcodes, const int32
   const bool from_codes = host_vectors_ && screen_kind_ == 1;
   launch_verify_select(from_codes ? codes_ : vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, queries, row_bytes,
                        nq, q0, cand, cnt, cap, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf,
-                       res.stream, from_codes ? inv_ : nullptr);
+                       res.stream, from_codes ? inv_ : nullptr, sqnorm_);
   CERTEX_CUDA(cudaGetLastError());
 }
 
@@ -1090,7 +1103,7 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     const bool from_codes = host_vectors_ && screen_kind_ == 1;
     launch_verify_select(from_codes ? codes_ : vectors_, pitch_, dtype_, static_cast<int>(dim_), params_.metric, q_rows,
                          q_rows_pitch, ns, 0, cand, cnt, cap, k, plain, slot_s, slot_row, ovf_list, d_flag, d_stats, rec_count,
-                         rec_cap, Refine{}, res.stream, from_codes ? inv_ : nullptr);
+                         rec_cap, Refine{}, res.stream, from_codes ? inv_ : nullptr, sqnorm_);
     launch_scatter_best(slot_s, slot_row, d_slot_q, ns, k, best_s, best_row, res.stream);
     CERTEX_CUDA(cudaGetLastError());
     st->launches += f16 ? 10 : 8;

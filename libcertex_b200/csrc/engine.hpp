@@ -318,6 +318,7 @@ class Index {
   int32_t* perm_      = nullptr;  // [capacity] sorted row -> id
   int32_t* inv_       = nullptr;  // [capacity] id -> sorted row
   int32_t* init_      = nullptr;  // [capacity rounded up to 256] e of the sorted row (kNeverInit: removed / padding)
+  double* sqnorm_     = nullptr;  // [capacity] cosine metric, float rows on the device: |x|^2 by id, the verification's own fp64 sum
   int32_t* cmax_      = nullptr;  // [capacity rounded up to 256, / 16] maximum of e over each chain of 16 sorted rows
   // L2 only: the sorted runs [first row, rows) at the end of the index that a later append may still sort again with
   // its own rows; a run of kFrozenRun rows or more stays as it is

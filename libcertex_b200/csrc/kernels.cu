@@ -115,8 +115,9 @@ __device__ __forceinline__ bool admitted(const Admit& a, int64_t q, int64_t row)
   return true;
 }
 
-// Accumulators of NQ queries against one stored row, coordinates in order.
-template <int METRIC, int NQ>
+// Accumulators of NQ queries against one stored row, coordinates in order. STORED_XX (cosine): |x|^2 is not summed here,
+// the caller sets xx from the value kept with the row (the same sum, made once when the row was added).
+template <int METRIC, int NQ, bool STORED_XX = false>
 struct Acc {
   double s[NQ];  // L2: sum of squared differences; otherwise: inner product
   double xx;
@@ -139,7 +140,7 @@ struct Acc {
         s[b] = __dadd_rn(s[b], __dmul_rn(a, x));
       }
     }
-    if constexpr (METRIC == kCos) { xx = __dadd_rn(xx, __dmul_rn(x, x)); }
+    if constexpr (METRIC == kCos && !STORED_XX) { xx = __dadd_rn(xx, __dmul_rn(x, x)); }
   }
   __device__ __forceinline__ double result(int b, double qq) const
   {
@@ -924,6 +925,50 @@ __device__ void select_smallest_keys(const unsigned long long* key, int n2, int 
   __syncthreads();
 }
 
+// ------------------------------------------------------------------------------------------- stored |x|^2 (cosine)
+// Warp per 32 consecutive rows: out[r] = the sum over the coordinates, in order, of x_t^2 in fp64 with every product and
+// every sum rounded on its own: bit for bit the sum the cosine verification makes for a candidate row (Acc). The rows
+// come through a shared-memory tile as in verify_select_kernel, so that the loads cover whole lines.
+constexpr int kSqnormStride = 144;
+template <typename T>
+__global__ void __launch_bounds__(128) row_sqnorm_kernel(const uint8_t* vectors, size_t pitch, int d, int64_t n, double* out)
+{
+  __shared__ __align__(16) uint8_t tiles[4 * 32 * kSqnormStride];
+  constexpr int V    = Elems<T>::kPerVec;
+  const int lane     = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * 4 + warp) * 32;
+  if (row0 >= n) { return; }  // warps are independent: no block-wide barrier below
+  uint8_t* tile      = tiles + warp * 32 * kSqnormStride;
+  const int piece = lane & 7, row_in_load = lane >> 3;
+  const int n_pieces = static_cast<int>((static_cast<size_t>(d) * sizeof(T) + 15) / 16);  // rows are zero padded to the pitch
+  const int64_t mine = row0 + lane;
+  double xx          = 0;
+  for (int p0 = 0; p0 < n_pieces; p0 += 8) {
+    uint4 w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t r = row0 + 4 * j + row_in_load;
+      w[j] = (r < n && p0 + piece < n_pieces) ? __ldg(reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(r) * pitch) + p0 + piece)
+                                              : make_uint4(0, 0, 0, 0);
+    }
+    __syncwarp();  // every lane is done with the slab before
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { *reinterpret_cast<uint4*>(tile + (4 * j + row_in_load) * kSqnormStride + piece * 16) = w[j]; }
+    __syncwarp();
+    if (mine < n) {
+      const int np = min(8, n_pieces - p0);
+      for (int p = 0; p < np; ++p) {
+        const uint4 x4 = *reinterpret_cast<const uint4*>(tile + lane * kSqnormStride + p * 16);
+        double x[V];
+        Elems<T>::unpack(x4, x);
+        const int t0 = (p0 + p) * V;
+        for (int e = 0; e < V && t0 + e < d; ++e) { xx = __dadd_rn(xx, __dmul_rn(x[e], x[e])); }
+      }
+    }
+  }
+  if (mine < n) { out[mine] = xx; }
+}
+
 // ------------------------------------------------------------------------------------------- verify + select
 // Staging tiles of the float rows: per warp 32 rows of a 128-byte slab, 144 bytes apart (a lane's 16-byte reads of its
 // own row then fall on distinct banks within every quarter warp).
@@ -934,13 +979,17 @@ __device__ __forceinline__ uint8_t* stage_of(void* after_the_arrays)
 }
 // Dynamic shared memory: qd [d] doubles | sc [n2] doubles | id [n2] int32, n2 = next_pow2(cap); for 8-bit rows
 // the query's bytes (in the space of qd) | n2 64-bit keys.
-template <typename T, int METRIC>
-__global__ void __launch_bounds__(1024) verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
+// Blocks of 128 threads for 8-bit rows (64 registers: 8 blocks per SM), of 256 threads for float rows (80 registers,
+// which the fetch of the next slab during the walk of this one needs: 3 blocks per SM, as many as the shared memory allows).
+template <typename T>
+constexpr bool kByteRows = std::is_same<T, int8_t>::value || std::is_same<T, uint8_t>::value;
+template <typename T, int METRIC, bool STORED_XX = false>
+__global__ void __launch_bounds__(kByteRows<T> ? 1024 : 256, kByteRows<T> ? 1 : 3) verify_select_kernel(const uint8_t* vectors, size_t pitch, int d, const void* queries, size_t qpitch,
                                      int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int n2max, int k,
                                      Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list,
                                      unsigned int* ovf_count, unsigned long long* stats,
                                      const unsigned long long* rec_count, unsigned long long rec_cap, Refine rf,
-                                     const int32_t* where)
+                                     const int32_t* where, const double* sqnorm)
 {
   extern __shared__ double sh[];
   __shared__ double s_qq;
@@ -1093,26 +1142,35 @@ __global__ void __launch_bounds__(1024) verify_select_kernel(const uint8_t* vect
         row = mine[i];
         ok  = admitted(adm, q, row);
       }
-      Acc<METRIC, 1> acc;
+      Acc<METRIC, 1, STORED_XX> acc;
       acc.clear();
+      if constexpr (STORED_XX) {
+        if (ok) { acc.xx = __ldg(sqnorm + row); }
+      }
       if (g * 32 < static_cast<int>(c)) {  // the same for every lane of the warp
         int32_t from[8];  // the rows this lane fetches pieces of
 #pragma unroll
         for (int j = 0; j < 8; ++j) { from[j] = __shfl_sync(0xffffffffu, ok ? row : -1, 4 * j + row_in_load); }
-        for (int p0 = 0; p0 < n_pieces; p0 += 8) {
-          uint4 w[8];
+        // The loads of the next slab are issued as soon as this slab's registers have been parked in the tile, so that
+        // they are in flight while the lanes walk the tile (a warp alone then overlaps its memory latency with its sums).
+        uint4 w[8];
+        auto fetch = [&](int p0) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             w[j] = (from[j] >= 0 && p0 + piece < n_pieces)
                      ? __ldg(reinterpret_cast<const uint4*>(vectors + static_cast<size_t>(from[j]) * pitch) + p0 + piece)
                      : make_uint4(0, 0, 0, 0);
           }
+        };
+        fetch(0);
+        for (int p0 = 0; p0 < n_pieces; p0 += 8) {
           __syncwarp();  // every lane is done with the slab before
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             *reinterpret_cast<uint4*>(tile + (4 * j + row_in_load) * kStageStride + piece * 16) = w[j];
           }
           __syncwarp();
+          if (p0 + 8 < n_pieces) { fetch(p0 + 8); }
           if (ok) {
             const int np = min(8, n_pieces - p0);
             for (int p = 0; p < np; ++p) {
@@ -1744,7 +1802,7 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          Refine rf, cudaStream_t s, const int32_t* where)
+                          Refine rf, cudaStream_t s, const int32_t* where, const double* sqnorm)
 {
   if (nq <= 0) { return; }
   const int n2max   = next_pow2(static_cast<int>(cap));
@@ -1762,16 +1820,29 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
       allow_smem(kernel, smem);
       kernel<<<nq, threads, smem, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, queries, qpitch, q0, cand, cnt, cap,
                                    n2max, k, adm, best_s, best_row, ovf_list, ovf_count, stats, rec_count, rec_cap, rf,
-                                   where);
+                                   where, sqnorm);
     };
     if (metric == kL2) {
       go(verify_select_kernel<T, kL2>);
     } else if (metric == kIP) {
       go(verify_select_kernel<T, kIP>);
+    } else if (sqnorm != nullptr && !bytes) {
+      go(verify_select_kernel<T, kCos, true>);
     } else {
       go(verify_select_kernel<T, kCos>);
     }
   });
+}
+
+void launch_row_sqnorms(const void* vectors, size_t pitch, int dtype, int d, int64_t n, double* out, cudaStream_t s)
+{
+  if (n <= 0) { return; }
+  const auto grid = static_cast<unsigned>((n + 127) / 128);
+  if (dtype == kF16) {
+    row_sqnorm_kernel<__half><<<grid, 128, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, n, out);
+  } else {
+    row_sqnorm_kernel<float><<<grid, 128, 0, s>>>(static_cast<const uint8_t*>(vectors), pitch, d, n, out);
+  }
 }
 
 void launch_gather_rows(const void* in, size_t in_pitch, const int32_t* sel, int64_t n, int64_t n_pad, void* out,

@@ -136,7 +136,12 @@ void launch_verify_select(const void* vectors, size_t pitch, int dtype, int d, i
                           size_t qpitch, int nq, int q0, const int32_t* cand, const uint32_t* cnt, uint32_t cap, int k,
                           Admit adm, double* best_s, int32_t* best_row, int32_t* ovf_list, unsigned int* ovf_count,
                           unsigned long long* stats, const unsigned long long* rec_count, unsigned long long rec_cap,
-                          Refine rf, cudaStream_t s, const int32_t* where = nullptr);
+                          Refine rf, cudaStream_t s, const int32_t* where = nullptr, const double* sqnorm = nullptr);
+
+/// out[r] = |x_r|^2 of n float32 / float16 rows, summed over the coordinates in order in fp64 with every product and sum
+/// rounded on its own: the sum the cosine verification makes per candidate. With it (sqnorm of launch_verify_select,
+/// indexed by row id) the verification of the cosine metric leaves that sum out.
+void launch_row_sqnorms(const void* vectors, size_t pitch, int dtype, int d, int64_t n, double* out, cudaStream_t s);
 
 /// Limits of one launch_dense_scores call: four queries of d doubles sit in shared memory (32 d bytes of the 227 KB a
 /// block may have), and the queries of a call are the second grid dimension in fours.
