@@ -142,6 +142,17 @@ struct Acc {
     }
     if constexpr (METRIC == kCos && !STORED_XX) { xx = __dadd_rn(xx, __dmul_rn(x, x)); }
   }
+  // the same for one query whose coordinate the caller has loaded (a)
+  __device__ __forceinline__ void add1(double x, double a)
+  {
+    if constexpr (METRIC == kL2) {
+      const double diff = __dsub_rn(a, x);
+      s[0]              = __dadd_rn(s[0], __dmul_rn(diff, diff));
+    } else {
+      s[0] = __dadd_rn(s[0], __dmul_rn(a, x));
+    }
+    if constexpr (METRIC == kCos && !STORED_XX) { xx = __dadd_rn(xx, __dmul_rn(x, x)); }
+  }
   __device__ __forceinline__ double result(int b, double qq) const
   {
     if constexpr (METRIC == kL2) {
@@ -1179,8 +1190,14 @@ __global__ void __launch_bounds__(kByteRows<T> ? 1024 : 256, kByteRows<T> ? 1 : 
               Elems<T>::unpack_finite(x4, x);  // screened rows are finite
               const int t0 = (p0 + p) * V;
               if (t0 + V <= d) {
+                // the query's doubles two at a time (t0 is a multiple of V, qd is 16-byte aligned): half the
+                // shared-memory instructions of the walk
 #pragma unroll
-                for (int e = 0; e < V; ++e) { acc.add(x[e], qd, d, t0 + e); }
+                for (int e = 0; e < V; e += 2) {
+                  const double2 a = *reinterpret_cast<const double2*>(qd + t0 + e);
+                  acc.add1(x[e], a.x);
+                  acc.add1(x[e + 1], a.y);
+                }
               } else {
                 for (int e = 0; e < V && t0 + e < d; ++e) { acc.add(x[e], qd, d, t0 + e); }
               }
