@@ -306,7 +306,9 @@ def main():
     clocks = sampler.stop()
     n_searches = args.steps * per_step
     qps = nq * n_searches / (ms / 1000)
-    launches = st.launches + (n_searches if world > 1 else 0) * 2  # merge + finish kernels of the distributed search
+    # kernels of the library outside the local searches, per sharded search: merge + finish of the merged lists, and the
+    # k-th largest of the shards' threshold candidates when thresholds are exchanged (NCCL's own kernels are not counted)
+    launches = st.launches + (n_searches if world > 1 else 0) * (3 if args.share_thresholds else 2)
 
     # ---- end to end through the public API with host buffers: H2D of the queries, search, D2H of ids + distances
     hq = xq.cpu().pin_memory()

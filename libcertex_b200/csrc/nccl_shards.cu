@@ -281,7 +281,7 @@ DistributedPending* distributed_search_begin(const Resources& res, Comm& c, cons
     d->failed = std::current_exception();
     fail_lists(res, c, cells);
   }
-  // round 1 assumes that no candidate list overflowed; the ranks' status words say whether that held everywhere
+  // the first exchange assumes that no candidate list overflowed; the ranks' status words say whether that held everywhere
   try {
     exchange(*d);
     CERTEX_CUDA(cudaEventCreateWithFlags(&d->done, cudaEventDisableTiming));
