@@ -247,7 +247,8 @@ DistributedPending* distributed_search_begin(const Resources& res, Comm& c, cons
   int64_t* send_ids = c.send + cells;
   auto* send_status = reinterpret_cast<unsigned long long*>(c.send + 2 * cells);
 
-  if (share_thresholds && c.n_ranks > 1) {
+  if (share_thresholds) {
+    // (also on a communicator of one rank, where the exchange returns the rank's own threshold: one code path)
     // the exchange needs every rank to reach it, i.e. to screen: agreed once per k and index size
     if (c.all_screen_size != index.size()) { c.all_screen.clear(), c.all_screen_size = index.size(); }
     if (!c.all_screen.count(k)) {
