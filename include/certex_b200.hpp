@@ -416,4 +416,51 @@ void search(resources const& res, communicator const& comm, search_params const&
                                             first_id, share_thresholds ? 1 : 0));
 }
 
+/// A sharded search between search_begin and search_end. Movable, not copyable; it must be ended (search_end) before
+/// it is destroyed, in the order the searches were begun.
+class pending_search {
+ public:
+  pending_search() = default;
+  explicit pending_search(certexB200PendingSearch_t h) : handle_(h) {}
+  pending_search(pending_search&& o) noexcept : handle_(std::exchange(o.handle_, nullptr)) {}
+  pending_search& operator=(pending_search&& o) noexcept
+  {
+    handle_ = std::exchange(o.handle_, nullptr);
+    return *this;
+  }
+  pending_search(const pending_search&)            = delete;
+  pending_search& operator=(const pending_search&) = delete;
+  certexB200PendingSearch_t release() { return std::exchange(handle_, nullptr); }
+
+ private:
+  certexB200PendingSearch_t handle_ = nullptr;
+};
+
+/// The sharded search in two calls (certexB200DistributedSearchBegin / End): search_begin enqueues the local search, the
+/// exchange and the merge and returns without waiting; search_end waits for that search and leaves the outputs final.
+/// Up to two searches may be between the calls per communicator, so that the host prepares one while the device works
+/// on the other. Queries and outputs must stay valid and untouched from search_begin to search_end.
+template <typename T, typename U>
+pending_search search_begin(resources const& res, communicator const& comm, search_params const& params, index<T> const& idx,
+                            int64_t first_id, device_matrix_view<U> queries, device_matrix_view<int64_t> neighbors,
+                            device_matrix_view<float> distances, bool share_thresholds = true)
+{
+  static_assert(std::is_same_v<std::remove_cv_t<U>, T>, "the queries must have the element type of the index");
+  cuvsCertexSearchParams sp{params.anchors, params.batch_size, params.probe_lists};
+  detail::tensor q(queries.data, detail::dl_type<T>(), 2, queries.rows, queries.cols, false);
+  detail::tensor nb(neighbors.data, detail::dl_type<int64_t>(), 2, neighbors.rows, neighbors.cols, false);
+  detail::tensor ds(distances.data, detail::dl_type<float>(), 2, distances.rows, distances.cols, false);
+  certexB200PendingSearch_t h = nullptr;
+  detail::check(certexB200DistributedSearchBegin(res.handle(), comm.handle(), &sp, idx.handle(), q.ptr(), nb.ptr(), ds.ptr(),
+                                                 nullptr, first_id, share_thresholds ? 1 : 0, &h));
+  return pending_search(h);
+}
+
+inline void search_end(pending_search& pending)
+{
+  certexB200PendingSearch_t h = pending.release();
+  if (h == nullptr) { throw error("certex: this search was ended already"); }
+  detail::check(certexB200DistributedSearchEnd(h));
+}
+
 }  // namespace certex_b200

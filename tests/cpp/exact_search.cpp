@@ -69,6 +69,20 @@ bool same(const char* what, const std::vector<float>& x, const std::vector<float
 }
 }  // namespace
 
+// The entry points for one process per GPU need NCCL ranks to run (tests/test_sharded.py runs them from Python); here
+// they are instantiated so that the header's wrappers are compiled and linked: one search, and two searches in flight.
+void sharded_over_nccl(cx::resources const& res, cx::communicator const& comm, cx::search_params const& sp,
+                       cx::index<float> const& shard, int64_t first_id, cx::device_matrix_view<const float> queries,
+                       cx::device_matrix_view<int64_t> n0, cx::device_matrix_view<float> d0,
+                       cx::device_matrix_view<int64_t> n1, cx::device_matrix_view<float> d1)
+{
+  cx::search(res, comm, sp, shard, first_id, queries, n0, d0);
+  cx::pending_search a = cx::search_begin(res, comm, sp, shard, first_id, queries, n0, d0);
+  cx::pending_search b = cx::search_begin(res, comm, sp, shard, first_id, queries, n1, d1);
+  cx::search_end(a);
+  cx::search_end(b);
+}
+
 int main(int argc, char** argv)
 {
   std::mt19937 gen(7);
