@@ -1454,6 +1454,12 @@ Index::Pending* Index::search_begin(const Resources& res, const SearchParams& sp
   return pending.release();
 }
 
+void Index::search_retarget(Pending* pending, int64_t* neighbors, float* distances, double* scores_out)
+{
+  CERTEX_EXPECTS(pending != nullptr, "certex: no search to retarget");
+  pending->neighbors = neighbors, pending->distances = distances, pending->scores_out = scores_out;
+}
+
 bool Index::search_end(Pending* raw, bool refinish) const
 {
   std::unique_ptr<Pending> pending(raw);

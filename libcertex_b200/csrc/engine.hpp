@@ -206,6 +206,9 @@ class Index {
   /// refinish: write the outputs once more from the kept lists even when nothing was repaired (a caller whose output
   /// buffers were reused in between, as the sharded search's send buffer is by a later search in flight).
   bool search_end(Pending* pending, bool refinish = false) const;
+  /// Gives a search in flight other output matrices for what search_end still writes (a repair, refinish): for a
+  /// caller whose first outputs have been given away in between.
+  static void search_retarget(Pending* pending, int64_t* neighbors, float* distances, double* scores_out);
 
   int64_t size() const { return size_; }
   int64_t dim() const { return dim_; }

@@ -336,6 +336,11 @@ void distributed_search_end(DistributedPending* raw)
   }
   std::exception_ptr failed = d->failed;
   if (d->pending) {
+    if (overtaken) {
+      // the send buffer may even be another allocation by now (a later, larger search): what this search still writes
+      // goes to where the second exchange will read it
+      Index::search_retarget(d->pending, c.send + d->cells, d->distances, reinterpret_cast<double*>(c.send));
+    }
     try {
       // repairs this rank's lists when its own status word was set
       d->index->search_end(d->pending, /*refinish=*/again && failed_rank < 0 && overtaken);

@@ -154,6 +154,15 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
         "    assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1]), overflow\n"
         "    D1, I1 = pidx.search(qa, k=10)\n"
         "    assert torch.equal(I1, Ia) and torch.equal(D1, Da)\n"
+        "# (lists still overflow) a later, larger search makes the library replace its exchange buffers while the first\n"
+        "# search is still to be ended: its second round writes to the new ones\n"
+        "want_all = oracle.knn(x, q, 10, 'l2')\n"
+        "tb = pidx.search_begin(qb, k=7, return_scores=True)\n"
+        "tc = pidx.search_begin(torch.from_numpy(q), k=10, return_scores=True)\n"
+        "Db, Ib, Sb = pidx.search_end(tb)\n"
+        "Dc, Ic, Sc = pidx.search_end(tc)\n"
+        "assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1])\n"
+        "assert np.array_equal(Ic.cpu().numpy(), want_all[0]) and np.array_equal(Sc.cpu().numpy(), want_all[1])\n"
         "# a rank whose local search fails (a host-side simulated allocation failure on rank 1, one query so that no\n"
         "# halving helps): every rank gets an error for the call instead of waiting, and the next call works\n"
         "idx = distributed.DistributedIndex(32).add(torch.from_numpy(x))\n"
@@ -208,6 +217,15 @@ def test_two_searches_in_flight_on_a_communicator_of_one_rank(tmp_path):
         "    assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1]), overflow\n"
         "    D1, I1 = pidx.search(qa, k=10)\n"
         "    assert torch.equal(I1, Ia) and torch.equal(D1, Da)\n"
+        "# (lists still overflow) a later, larger search makes the library replace its exchange buffers while the first\n"
+        "# search is still to be ended: its second round writes to the new ones\n"
+        "want_all = oracle.knn(x, q, 10, 'l2')\n"
+        "tb = pidx.search_begin(qb, k=7, return_scores=True)\n"
+        "tc = pidx.search_begin(torch.from_numpy(q), k=10, return_scores=True)\n"
+        "Db, Ib, Sb = pidx.search_end(tb)\n"
+        "Dc, Ic, Sc = pidx.search_end(tc)\n"
+        "assert np.array_equal(Ib.cpu().numpy(), want_b[0]) and np.array_equal(Sb.cpu().numpy(), want_b[1])\n"
+        "assert np.array_equal(Ic.cpu().numpy(), want_all[0]) and np.array_equal(Sc.cpu().numpy(), want_all[1])\n"
         "dist.destroy_process_group(); print('ok')\n"
     )
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29579")
