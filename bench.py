@@ -94,6 +94,11 @@ class ClockSampler(threading.Thread):
                 pass
             time.sleep(0.05)
 
+    def reset(self):
+        """Forgets what was seen so far: called where the timed region begins (the thread is started earlier, during
+        the warm-up, because the first NVML queries of a process take long and hold up CUDA calls meanwhile)."""
+        self.samples, self.reasons = [], set()
+
     def stop(self):
         self._halt.set()
         if self.is_alive():
@@ -297,10 +302,14 @@ def main():
         return float(ms.item()), out
 
     # ---- device-resident inputs
-    for _ in range(args.warmup):
-        run_step(lambda: xq, lambda out: None)
     sampler = ClockSampler(local)
     sampler.start()
+    # the warm-up steps run exactly what the timed region runs (statistics on, the same events and barriers), so that
+    # whatever the process sets up on first use (event pools, NVML) is set up before the clock starts
+    with certex.search_stats():
+        for _ in range(args.warmup):
+            timed(lambda: run_step(lambda: xq, lambda out: None), 1)
+    sampler.reset()
     with certex.search_stats() as st:
         ms, (D, I) = timed(lambda: run_step(lambda: xq, lambda out: None), args.steps)
     clocks = sampler.stop()
