@@ -692,7 +692,7 @@ __global__ void __launch_bounds__(512, 4) kth_largest_kernel(const int32_t* gmax
   __shared__ uint32_t s_group[512], s_list[kCollect];
   __shared__ uint32_t s_bound, s_count, s_answer;
   const int n_threads = blockDim.x;
-  if (in_smem && (n_threads == 512 || n_threads == 128) && 2 * k <= n_threads) {
+  if (in_smem && (n_threads == 512 || n_threads == 256 || n_threads == 128) && 2 * k <= n_threads) {
     int groups = 16;
     while (groups < 2 * k) { groups <<= 1; }
     const int per_group = n_threads / groups;  // 32, 16, ..., 1 threads
@@ -1801,7 +1801,7 @@ void launch_kth_largest(const int32_t* gmax, int64_t ld, int ng, int k, int nq, 
   const int in_smem  = bytes <= 160 * 1024;
   if (in_smem) { allow_smem(kth_largest_kernel, bytes); }
   // short rows: smaller blocks, more of them per SM (the kernel is a chain of block-wide barriers)
-  const int threads = (ng <= 4096 && 2 * k <= 128) ? 128 : 512;
+  const int threads = ng > 4096 ? 512 : 2 * k <= 128 ? 128 : 2 * k <= 256 ? 256 : 512;
   kth_largest_kernel<<<nq, threads, in_smem ? bytes : 0, s>>>(gmax, ld, ng, k, thr, in_smem, ng_rows, never, topk);
 }
 
