@@ -312,6 +312,10 @@ CERTEX_B200_EXPORT cuvsError_t certexB200ScreenTrace(void* trace, int32_t units)
 CERTEX_B200_EXPORT cuvsError_t certexB200PlanSegments(int32_t n_query_tiles, int32_t n_base_tiles, int32_t panel_tiles,
                                                       int32_t grid, int32_t* out);
 
+/** Test hook (host only): how a search by labels groups its queries: order [n] = 0 .. n - 1 sorted by labels[i], equal
+ *  labels in ascending order. */
+CERTEX_B200_EXPORT cuvsError_t certexB200OrderByLabel(const int32_t* labels, int64_t n, int32_t* order);
+
 /** Test hook (host only): the split that searches use, with the base tiles taken in chunks of chunk_tiles (0: one
  *  chunk) so that a chunk's rows stay in L2 while every query panel passes over them. segs receives 4 ints per segment
  *  (as above), *n_segs their number (at most cap_segs), seg_begin [grid + 1] the range of every CTA. */

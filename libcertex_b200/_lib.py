@@ -115,7 +115,7 @@ SYMBOLS = [
     "certexB200ShardedBuild", "certexB200ShardedDestroy", "certexB200ShardedGetSize", "certexB200ShardedSearch",
     "certexB200CommGetUniqueId", "certexB200CommInitRank", "certexB200CommAdopt", "certexB200CommDestroy",
     "certexB200DistributedSearch", "certexB200ScreenTrace", "certexB200PlanChunked",
-    "certexB200DistributedSearchBegin", "certexB200DistributedSearchEnd",
+    "certexB200DistributedSearchBegin", "certexB200DistributedSearchEnd", "certexB200OrderByLabel",
 ]
 
 # void hook(void* ctx, int32_t* keys, int64_t n, cudaStream_t stream)
@@ -198,6 +198,7 @@ def lib():
                                                                ctypes.c_int32, P(vp)]
                 L.certexB200DistributedSearchEnd.argtypes = [vp]
                 L.certexB200ScreenTrace.argtypes = [vp, ctypes.c_int32]
+                L.certexB200OrderByLabel.argtypes = [P(ctypes.c_int32), i64, P(ctypes.c_int32)]
                 L.certexB200SearchStatic.argtypes = [vp, ctypes.c_int, DLDataType, vp, i64, vp, i64, i64, ctypes.c_int32, vp, vp]
                 _lib = L
     return _lib

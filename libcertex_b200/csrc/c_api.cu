@@ -592,6 +592,14 @@ cuvsError_t certexB200PlanChunked(int32_t n_query_tiles, int32_t n_base_tiles, i
   });
 }
 
+cuvsError_t certexB200OrderByLabel(const int32_t* labels, int64_t n, int32_t* order)
+{
+  return translate([=] {
+    CERTEX_EXPECTS(n >= 0 && (n == 0 || (labels != nullptr && order != nullptr)), "certex: null argument");
+    order_by_label_flat(labels, n, order);
+  });
+}
+
 cuvsError_t certexB200PlanRouted(int32_t n_runs, const int32_t* n_query_tiles, const int32_t* n_base_tiles,
                                  int32_t panel_tiles, int32_t grid, int32_t max_segs, int32_t* segs, int32_t cap_segs,
                                  int32_t* n_segs, int32_t* seg_begin, int32_t* runs_done)

@@ -847,6 +847,41 @@ void Index::search_screened(const Resources& res, const uint8_t* qbuf, const flo
               adm, events);
 }
 
+namespace {
+
+/// The queries' numbers ordered by label, queries of one label in ascending order (a stable sort by label). Labels of
+/// a call span a small range as a rule: one counting pass then; otherwise four radix passes over the label's bytes.
+std::vector<int32_t> order_by_label(const std::vector<int32_t>& lab)
+{
+  const size_t nq = lab.size();
+  std::vector<int32_t> order(nq);
+  if (nq == 0) { return order; }
+  int32_t lo = lab[0], hi = lab[0];
+  for (int32_t l : lab) { lo = std::min(lo, l), hi = std::max(hi, l); }
+  const uint64_t range = static_cast<uint64_t>(static_cast<int64_t>(hi) - static_cast<int64_t>(lo)) + 1;
+  if (range <= (uint64_t(1) << 20)) {
+    std::vector<uint32_t> at(static_cast<size_t>(range) + 1, 0u);
+    for (int32_t l : lab) { ++at[static_cast<size_t>(static_cast<int64_t>(l) - lo) + 1]; }
+    for (size_t i = 1; i <= range; ++i) { at[i] += at[i - 1]; }
+    for (size_t i = 0; i < nq; ++i) { order[at[static_cast<size_t>(static_cast<int64_t>(lab[i]) - lo)]++] = static_cast<int32_t>(i); }
+    return order;
+  }
+  std::vector<uint64_t> a(nq), b(nq);  // (label with the sign bit flipped, query number)
+  for (size_t i = 0; i < nq; ++i) { a[i] = (static_cast<uint64_t>(static_cast<uint32_t>(lab[i]) ^ 0x80000000u) << 32) | i; }
+  for (int pass = 0; pass < 4; ++pass) {
+    size_t at[257] = {0};
+    const int shift = 32 + 8 * pass;
+    for (uint64_t v : a) { ++at[((v >> shift) & 255u) + 1]; }
+    for (int i = 0; i < 256; ++i) { at[i + 1] += at[i]; }
+    for (uint64_t v : a) { b[at[(v >> shift) & 255u]++] = v; }
+    a.swap(b);
+  }
+  for (size_t i = 0; i < nq; ++i) { order[i] = static_cast<int32_t>(a[i] & 0xffffffffu); }
+  return order;
+}
+
+}  // namespace
+
 /// The queries of one label in a search by labels.
 struct LabelRun {
   int64_t part_off  = 0;  // the label's entries in the partition
@@ -1159,9 +1194,7 @@ unsigned long long Index::search_by_labels(const Resources& res, const void* q, 
   std::vector<int32_t> lab(static_cast<size_t>(nq));
   CERTEX_CUDA(cudaMemcpyAsync(lab.data(), adm.query_labels, lab.size() * 4, cudaMemcpyDeviceToHost, res.stream));
   res.sync();
-  std::vector<int32_t> order(static_cast<size_t>(nq));
-  for (int i = 0; i < nq; ++i) { order[static_cast<size_t>(i)] = i; }
-  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return lab[a] < lab[b]; });
+  const std::vector<int32_t> order = order_by_label(lab);  // the device waits for the host here: no comparison sort
 
   const int64_t n_tail = n - n_part_;
   const bool can_route = lcodes_ != nullptr && screen_kind_ != 0 && !code_overflow_ && n_tail == 0 && test_mode_ != 3;
@@ -1887,6 +1920,13 @@ int plan_routed_flat(int n_runs, const int32_t* n_query_tiles, const int32_t* n_
   *n_segs = static_cast<int32_t>(segs.size());
   for (int b = 0; b <= grid; ++b) { seg_begin[b] = begin[static_cast<size_t>(b)]; }
   return static_cast<int>(done);
+}
+
+void order_by_label_flat(const int32_t* labels, int64_t n, int32_t* order)
+{
+  const std::vector<int32_t> lab(labels, labels + n);
+  const std::vector<int32_t> got = order_by_label(lab);
+  std::memcpy(order, got.data(), got.size() * sizeof(int32_t));
 }
 
 int plan_chunked_flat(int nqt, int nt, int panel_tiles, int grid, int chunk_tiles, int32_t* segs_out, int cap_segs,

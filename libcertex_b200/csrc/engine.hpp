@@ -377,6 +377,10 @@ void distributed_search_end(DistributedPending* pending);
 /// Host-side work split of the tensor-core pass: grid * kMaxSegs segments of 4 ints each.
 void plan_segments_flat(int nqt, int nt, int panel_tiles, int grid, int32_t* out);
 
+/// order [n] = the numbers 0 .. n - 1 sorted by labels[i], equal labels in ascending order: how a search by labels
+/// groups its queries (test hook).
+void order_by_label_flat(const int32_t* labels, int64_t n, int32_t* order);
+
 /// The split the searches use: the same, with the base tiles taken in chunks of `chunk_tiles` (0: one chunk) that every
 /// query panel passes over while they are in L2. Segments of 4 ints each, CTA b owns [seg_begin[b], seg_begin[b + 1]);
 /// returns their number.

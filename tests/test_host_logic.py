@@ -162,3 +162,25 @@ def test_chunked_plan_covers_every_unit_once_chunk_by_chunk(built_library, nqt, 
         units = [sum(nq_ * (min(t1, c1) - max(t0, c0)) for _, nq_, t0, t1 in segs[begin[b] : begin[b + 1]] if t0 < c1 and t1 > c0)
                  for b in range(grid)]
         assert max(units) - nqt * (c1 - c0) / grid <= panel
+
+
+@pytest.mark.parametrize("kind", ["few labels", "wide range", "negative", "one label", "empty", "extremes"])
+def test_queries_are_grouped_by_label_like_a_stable_sort(built_library, kind):
+    rng = np.random.default_rng(7)
+    if kind == "few labels":
+        lab = rng.integers(0, 64, size=10000)
+    elif kind == "wide range":
+        lab = rng.integers(-2**31, 2**31, size=5000)          # more than 2^20 apart: the radix passes
+    elif kind == "negative":
+        lab = rng.integers(-5, 5, size=3000)
+    elif kind == "one label":
+        lab = np.full(100, 42)
+    elif kind == "empty":
+        lab = np.zeros(0)
+    else:
+        lab = rng.choice(np.array([-2**31, -1, 0, 1, 2**31 - 1]), size=2000)
+    lab = np.ascontiguousarray(lab, dtype=np.int32)
+    order = np.full(len(lab), -1, dtype=np.int32)
+    p = ctypes.POINTER(ctypes.c_int32)
+    assert built_library.certexB200OrderByLabel(lab.ctypes.data_as(p), len(lab), order.ctypes.data_as(p)) == 1
+    assert np.array_equal(order, np.argsort(lab, kind="stable").astype(np.int32))
