@@ -253,6 +253,39 @@ Resources::Resources()
 Resources::~Resources()
 {
   if (pinned_) { cudaFreeHost(pinned_); }
+  if (staging_) { cudaFreeHost(staging_); }
+  if (staging_done_) { cudaEventDestroy(staging_done_); }
+}
+
+size_t Resources::upload_bytes(const std::vector<std::pair<const void*, size_t>>& pieces)
+{
+  size_t total = 0;
+  for (const auto& p : pieces) { total = (total + 255) / 256 * 256 + p.second; }
+  return std::max<size_t>(total, 1);
+}
+
+void Resources::upload(const std::vector<std::pair<const void*, size_t>>& pieces, void* device, std::vector<size_t>& offsets) const
+{
+  const size_t total = upload_bytes(pieces);
+  if (staging_done_) { CERTEX_CUDA(cudaEventSynchronize(staging_done_)); }  // the last copy out of the buffer (long finished, as a rule)
+  if (total > staging_bytes_) {
+    if (staging_) { cudaFreeHost(staging_); }
+    staging_ = nullptr, staging_bytes_ = 0;
+    const size_t want = std::max<size_t>(total * 2, size_t(1) << 20);
+    CERTEX_CUDA(cudaHostAlloc(&staging_, want, cudaHostAllocDefault));
+    staging_bytes_ = want;
+  }
+  if (!staging_done_) { CERTEX_CUDA(cudaEventCreateWithFlags(&staging_done_, cudaEventDisableTiming)); }
+  offsets.clear();
+  size_t at = 0;
+  for (const auto& p : pieces) {
+    at = (at + 255) / 256 * 256;
+    offsets.push_back(at);
+    if (p.second) { std::memcpy(static_cast<unsigned char*>(staging_) + at, p.first, p.second); }
+    at += p.second;
+  }
+  CERTEX_CUDA(cudaMemcpyAsync(device, staging_, total, cudaMemcpyHostToDevice, stream));
+  CERTEX_CUDA(cudaEventRecord(staging_done_, stream));
 }
 
 void Resources::sync() const { CERTEX_CUDA(cudaStreamSynchronize(stream)); }
@@ -1031,15 +1064,25 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     const int n_groups   = static_cast<int>(max_tiles) * per_tile;
     const int64_t ld_g   = round_up(n_groups, 8);
     const unsigned long long rec_cap = std::max<unsigned long long>(1ull << 20, static_cast<unsigned long long>(ns) * cap);
-    int32_t* d_slot_q    = scratch.get<int32_t>(static_cast<size_t>(ns));
-    int32_t* d_slot_ng   = scratch.get<int32_t>(static_cast<size_t>(ns));
-    ScreenSeg* d_segs    = scratch.get<ScreenSeg>(segs.size());
-    int* d_col0          = scratch.get<int>(col0.size());
-    int* d_seg_begin     = scratch.get<int>(seg_begin.size());
-    ScreenSeg* d_segs_g  = scratch.get<ScreenSeg>(segs_g.size());  // the threshold pass: leading tiles of every label
-    int* d_col0_g        = scratch.get<int>(col0_g.size());
-    int* d_seg_begin_g   = scratch.get<int>(seg_begin_g.size());
-    int* d_step_g        = scratch.get<int>(step_g.size());
+    // the host's tables of the pass, sent in one copy (segs_g ...: the threshold pass over the leading tiles of every label)
+    const std::vector<std::pair<const void*, size_t>> tables = {
+      {slot_query.data(), slot_query.size() * 4},      {slot_ng.data(), slot_ng.size() * 4},
+      {segs.data(), segs.size() * sizeof(ScreenSeg)},  {col0.data(), col0.size() * sizeof(int)},
+      {seg_begin.data(), seg_begin.size() * sizeof(int)}, {segs_g.data(), segs_g.size() * sizeof(ScreenSeg)},
+      {col0_g.data(), col0_g.size() * sizeof(int)},    {seg_begin_g.data(), seg_begin_g.size() * sizeof(int)},
+      {step_g.data(), step_g.size() * sizeof(int)}};
+    uint8_t* d_tables = scratch.get<uint8_t>(Resources::upload_bytes(tables));
+    std::vector<size_t> at;
+    res.upload(tables, d_tables, at);
+    int32_t* d_slot_q    = reinterpret_cast<int32_t*>(d_tables + at[0]);
+    int32_t* d_slot_ng   = reinterpret_cast<int32_t*>(d_tables + at[1]);
+    ScreenSeg* d_segs    = reinterpret_cast<ScreenSeg*>(d_tables + at[2]);
+    int* d_col0          = reinterpret_cast<int*>(d_tables + at[3]);
+    int* d_seg_begin     = reinterpret_cast<int*>(d_tables + at[4]);
+    ScreenSeg* d_segs_g  = reinterpret_cast<ScreenSeg*>(d_tables + at[5]);
+    int* d_col0_g        = reinterpret_cast<int*>(d_tables + at[6]);
+    int* d_seg_begin_g   = reinterpret_cast<int*>(d_tables + at[7]);
+    int* d_step_g        = reinterpret_cast<int*>(d_tables + at[8]);
     uint8_t* q_rows      = scratch.get<uint8_t>(static_cast<size_t>(ns) * (f16 ? qpitch : cp));  // the queries in slot order
     uint8_t* q_codes     = f16 ? scratch.get<uint8_t>(static_cast<size_t>(ns) * cp) : q_rows;
     float* shift         = f16 ? scratch.get<float>(static_cast<size_t>(ns)) : nullptr;
@@ -1054,16 +1097,6 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     int32_t* ovf_list    = scratch.get<int32_t>(static_cast<size_t>(ns));
     unsigned int* d_flag = scratch.get<unsigned int>(4);  // [0] overflowed slots, [1] error code, [2] fp16 overflow
     auto* d_stats        = scratch.get<unsigned long long>(2);
-    const auto h2d       = cudaMemcpyHostToDevice;
-    CERTEX_CUDA(cudaMemcpyAsync(d_slot_q, slot_query.data(), slot_query.size() * 4, h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_slot_ng, slot_ng.data(), slot_ng.size() * 4, h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_segs, segs.data(), segs.size() * sizeof(ScreenSeg), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_col0, col0.data(), col0.size() * sizeof(int), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin, seg_begin.data(), seg_begin.size() * sizeof(int), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_segs_g, segs_g.data(), segs_g.size() * sizeof(ScreenSeg), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_col0_g, col0_g.data(), col0_g.size() * sizeof(int), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_seg_begin_g, seg_begin_g.data(), seg_begin_g.size() * sizeof(int), h2d, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(d_step_g, step_g.data(), step_g.size() * sizeof(int), h2d, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(cnt, 0, sizeof(uint32_t) * ns, res.stream));
     CERTEX_CUDA(cudaMemsetAsync(rec_count, 0, sizeof(unsigned long long), res.stream));
     CERTEX_CUDA(cudaMemsetAsync(d_flag, 0, 4 * sizeof(unsigned int), res.stream));
@@ -1144,11 +1177,15 @@ unsigned long long Index::search_routed(const Resources& res, const void* q, siz
     st->launches += f16 ? 10 : 8;
     unsigned int h_flag[4]        = {0, 0, 0, 0};
     unsigned long long h_stats[2] = {0, 0};
-    std::vector<int32_t> h_ovf(static_cast<size_t>(ns));
+    std::vector<int32_t> h_ovf;
     CERTEX_CUDA(cudaMemcpyAsync(h_flag, d_flag, sizeof(h_flag), cudaMemcpyDeviceToHost, res.stream));
     CERTEX_CUDA(cudaMemcpyAsync(h_stats, d_stats, sizeof(h_stats), cudaMemcpyDeviceToHost, res.stream));
-    CERTEX_CUDA(cudaMemcpyAsync(h_ovf.data(), ovf_list, h_ovf.size() * 4, cudaMemcpyDeviceToHost, res.stream));
     res.sync();
+    if (h_flag[0] > 0) {  // the list of the slots that overflowed: fetched only when there are any
+      h_ovf.resize(std::min<size_t>(h_flag[0], static_cast<size_t>(ns)));
+      CERTEX_CUDA(cudaMemcpyAsync(h_ovf.data(), ovf_list, h_ovf.size() * 4, cudaMemcpyDeviceToHost, res.stream));
+      res.sync();
+    }
     for (size_t e = 0; e + 3 < events.size(); e += 4) {
       float ms = 0;
       cudaEventElapsedTime(&ms, events[e], events[e + 1]);

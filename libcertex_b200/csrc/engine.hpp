@@ -65,9 +65,17 @@ struct Resources {
   /// searches in flight are copied to; made on first use.
   static constexpr int kPinnedSlots = 4;
   void* pinned_block(int slot) const;
+  /// Sends small host arrays to the device in one copy: `pieces` (pointer, bytes) are packed, 256-byte aligned, into
+  /// page-locked memory and copied to `device` (at least upload_bytes(pieces) bytes) on the stream; offsets[i] is where
+  /// piece i starts. A copy from pageable memory would make the host wait for the stream once per array.
+  static size_t upload_bytes(const std::vector<std::pair<const void*, size_t>>& pieces);
+  void upload(const std::vector<std::pair<const void*, size_t>>& pieces, void* device, std::vector<size_t>& offsets) const;
 
  private:
   mutable void* pinned_ = nullptr;
+  mutable void* staging_        = nullptr;  // page-locked, grows; reused once the copy out of it has finished
+  mutable size_t staging_bytes_ = 0;
+  mutable cudaEvent_t staging_done_ = nullptr;
   friend class Index;
   mutable int searches_in_flight_ = 0;
   mutable unsigned next_slot_     = 0;
